@@ -1,0 +1,167 @@
+// The fused kernels.  Where the reference's fuser rewrites two kernels' source into one
+// __global__ function with the dispatch chain at the top and each body under
+// `if (KernelID_ == k && threadIdx.x < B_k)` (horizontal-fuser/src/Matchers.cc:464-602 for
+// block-level fusion, :604-727 for thread-level fusion), this file instantiates one kernel per
+// pair of operator bodies from the registry:
+//
+//   fused_block_kernel<A, B>   every CTA runs one operator (zig-zag, proportional, SM-striped,
+//                              range split) or, with table.queue set, loops over tickets drawn
+//                              from an atomic counter (persistent work queue);
+//   fused_thread_kernel<A, B>  both operators inside every CTA, split by thread range, each
+//                              synchronising on its own named barrier; shared memory is the sum;
+//   single_kernel<A>           the unfused launch of the same body (baselines, bit-exact check);
+//   trace_kernel               the dispatch decode alone, recording what each CTA would run.
+//
+// __launch_bounds__ come from the pair: the larger block, and the LARGER of the two bodies'
+// minimum-CTAs-per-SM, so the lighter operator keeps its occupancy and the heavier body is
+// compiled into that register budget.
+#pragma once
+
+#include "dispatch.h"
+#include "tile.h"
+
+namespace bfuse {
+
+__device__ __forceinline__ unsigned char *align_smem_1k(unsigned char *p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  return p + ((1024u - (a & 1023u)) & 1023u);
+}
+
+template <class Op>
+__device__ __forceinline__ void run_tile(const typename Op::Params &p, const DispatchTable &t, int k, int vb, int vtid,
+                                         int bar_id, unsigned char *smem) {
+  TileCtx c;
+  c.vblock = vb;
+  c.tid = vtid;
+  c.nthreads = t.n_thr[k];
+  c.bar_id = bar_id;
+  c.bar_count = t.bar_count[k];
+  c.gx = t.grid_x[k];
+  c.gy = t.grid_y[k];
+  c.bx = t.blk_x[k];
+  c.by = t.blk_y[k];
+  c.smem = smem;
+  c.status = t.status;
+  Op::run(p, c);
+}
+
+constexpr int cmax(int a, int b) { return a > b ? a : b; }
+constexpr int cmin(int a, int b) { return a < b ? a : b; }
+
+template <class A, class B>
+__global__ void __launch_bounds__(cmax(A::kMaxThreads, B::kMaxThreads), cmax(A::kMinBlocks, B::kMinBlocks))
+    fused_block_kernel(const __grid_constant__ DispatchTable t, const __grid_constant__ typename A::Params pa,
+                       const __grid_constant__ typename B::Params pb) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char *smem = align_smem_1k(smem_raw);
+  const int tid = threadIdx.x;
+  if (!t.queue) {
+    int k, vb;
+    if (!decode_cta(t, blockIdx.x, k, vb)) return;
+    // guard of the reference: KernelID_ == k && threadIdx.x < B_k (Algorithms.cc:699-717)
+    if (k == 0) {
+      if (tid < t.n_thr[0]) run_tile<A>(pa, t, 0, vb, tid, 1, smem);
+    } else {
+      if (tid < t.n_thr[1]) run_tile<B>(pb, t, 1, vb, tid, 2, smem);
+    }
+    return;
+  }
+  // Persistent CTAs: draw tickets until the queue is empty.  The last CTA to drain resets the
+  // counters, so the next launch on the stream starts from zero without a memset.
+  __shared__ int ticket_s;
+  for (;;) {
+    if (tid == 0) ticket_s = (int)atomicAdd(t.queue_ctr, 1u);
+    __syncthreads();
+    const int ticket = ticket_s;
+    __syncthreads();
+    if (ticket >= t.total) break;
+    int k, vb;
+    if (!decode_cta(t, ticket, k, vb)) continue;
+    if (k == 0) {
+      if (tid < t.n_thr[0]) run_tile<A>(pa, t, 0, vb, tid, 1, smem);
+    } else {
+      if (tid < t.n_thr[1]) run_tile<B>(pb, t, 1, vb, tid, 2, smem);
+    }
+  }
+  if (tid == 0) {
+    __threadfence();
+    if (atomicAdd(t.queue_ctr + 1, 1u) == gridDim.x - 1) {
+      t.queue_ctr[0] = 0;
+      t.queue_ctr[1] = 0;
+      __threadfence();
+    }
+  }
+}
+
+template <class A, class B>
+__global__ void __launch_bounds__(A::kMaxThreads + B::kMaxThreads, 1)
+    fused_thread_kernel(const __grid_constant__ DispatchTable t, const __grid_constant__ typename A::Params pa,
+                        const __grid_constant__ typename B::Params pb) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char *smem = align_smem_1k(smem_raw);
+  const int tid = threadIdx.x, b = blockIdx.x;
+  // thread ranges of hfusePattern (Algorithms.cc:23-49): kernel k owns [thr_lo[k], thr_lo[k] + B_k)
+  if (tid < t.thr_lo[1]) {
+    if (tid < t.n_thr[0] && b < t.n_cta[0]) run_tile<A>(pa, t, 0, b, tid, 1, smem + t.smem_off[0]);
+  } else {
+    const int vt = tid - t.thr_lo[1];
+    if (vt < t.n_thr[1] && b < t.n_cta[1]) run_tile<B>(pb, t, 1, b, vt, 2, smem + t.smem_off[1]);
+  }
+}
+
+template <class A>
+__global__ void __launch_bounds__(A::kMaxThreads, A::kMinBlocks)
+    single_kernel(const __grid_constant__ DispatchTable t, const __grid_constant__ typename A::Params pa) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char *smem = align_smem_1k(smem_raw);
+  if ((int)threadIdx.x < t.n_thr[0]) run_tile<A>(pa, t, 0, blockIdx.x, threadIdx.x, 1, smem);
+}
+
+// ---- host-side typed launchers, stored type-erased in the pair table ---------------------------
+
+typedef cudaError_t (*PairLaunchFn)(const DispatchTable &, const void *pa, const void *pb, unsigned grid,
+                                    unsigned block, size_t smem, cudaStream_t);
+typedef cudaError_t (*SingleLaunchFn)(const DispatchTable &, const void *pa, unsigned grid, unsigned block,
+                                      size_t smem, cudaStream_t);
+typedef cudaError_t (*AttrFn)(cudaFuncAttributes *);
+
+template <class Kernel>
+cudaError_t ensure_smem(Kernel k, size_t smem) {
+  if (smem <= 48 * 1024) return cudaSuccess;
+  return cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+}
+
+template <class A, class B>
+cudaError_t launch_block_pair(const DispatchTable &t, const void *pa, const void *pb, unsigned grid, unsigned block,
+                              size_t smem, cudaStream_t s) {
+  cudaError_t e = ensure_smem(fused_block_kernel<A, B>, smem);
+  if (e != cudaSuccess) return e;
+  fused_block_kernel<A, B><<<grid, block, smem, s>>>(t, *static_cast<const typename A::Params *>(pa),
+                                                      *static_cast<const typename B::Params *>(pb));
+  return cudaGetLastError();
+}
+template <class A, class B>
+cudaError_t launch_thread_pair(const DispatchTable &t, const void *pa, const void *pb, unsigned grid, unsigned block,
+                               size_t smem, cudaStream_t s) {
+  cudaError_t e = ensure_smem(fused_thread_kernel<A, B>, smem);
+  if (e != cudaSuccess) return e;
+  fused_thread_kernel<A, B><<<grid, block, smem, s>>>(t, *static_cast<const typename A::Params *>(pa),
+                                                       *static_cast<const typename B::Params *>(pb));
+  return cudaGetLastError();
+}
+template <class A>
+cudaError_t launch_single(const DispatchTable &t, const void *pa, unsigned grid, unsigned block, size_t smem,
+                          cudaStream_t s) {
+  cudaError_t e = ensure_smem(single_kernel<A>, smem);
+  if (e != cudaSuccess) return e;
+  single_kernel<A><<<grid, block, smem, s>>>(t, *static_cast<const typename A::Params *>(pa));
+  return cudaGetLastError();
+}
+template <class A, class B>
+cudaError_t attr_block_pair(cudaFuncAttributes *a) { return cudaFuncGetAttributes(a, fused_block_kernel<A, B>); }
+template <class A, class B>
+cudaError_t attr_thread_pair(cudaFuncAttributes *a) { return cudaFuncGetAttributes(a, fused_thread_kernel<A, B>); }
+template <class A>
+cudaError_t attr_single(cudaFuncAttributes *a) { return cudaFuncGetAttributes(a, single_kernel<A>); }
+
+}  // namespace bfuse

@@ -1,0 +1,37 @@
+// One row of the fused-kernel registry: operator BFUSE_ROW fused with every operator.
+#include "op_list.h"
+
+#ifndef BFUSE_ROW
+#error "compile with -DBFUSE_ROW=<operator id>"
+#endif
+
+namespace bfuse {
+
+template <int I, int J>
+struct RowFiller {
+  static void fill(PairEntry *row) {
+    using A = typename OpAt<I>::type;
+    using B = typename OpAt<J>::type;
+    row[J].block = &launch_block_pair<A, B>;
+    row[J].thread = &launch_thread_pair<A, B>;
+    row[J].block_attr = &attr_block_pair<A, B>;
+    row[J].thread_attr = &attr_thread_pair<A, B>;
+    RowFiller<I, J + 1>::fill(row);
+  }
+};
+template <int I>
+struct RowFiller<I, kNumOps> {
+  static void fill(PairEntry *) {}
+};
+
+template <>
+void fill_pair_row<BFUSE_ROW>(PairEntry *row, SingleEntry *single) {
+  using A = typename OpAt<BFUSE_ROW>::type;
+  RowFiller<BFUSE_ROW, 0>::fill(row);
+  single->launch = &launch_single<A>;
+  single->attr = &attr_single<A>;
+  single->max_threads = A::kMaxThreads;
+  single->params_size = sizeof(typename A::Params);
+}
+
+}  // namespace bfuse

@@ -1,0 +1,944 @@
+// Implementation of the C ABI in include/bfuse_b200.h: the pair registry, the launch boundary
+// (replacing test-utils/test-suite-files/operation_cu.py of the reference) and the timing /
+// checking helpers of its harness (main_cc.py, utils_cc.py).  No CPU fallback exists: every
+// compute entry point launches a CUDA kernel or returns an error.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "../../include/bfuse_b200.h"
+#include "op_list.h"
+#include "scheduler.h"
+
+using namespace bfuse;
+
+namespace {
+
+constexpr size_t kMaxSmemPerCta = 227 * 1024;
+constexpr int kParamsBytes = 512;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct ArgInfo {
+  size_t bytes;
+  int is_output;
+  int optional;
+};
+
+struct KernelRec {
+  alignas(64) unsigned char params[kParamsBytes];
+  bfuse_kernel_desc desc;
+  std::string name;
+  KernelDims dims;
+  size_t smem;
+  int nargs;
+  ArgInfo arg[BFUSE_MAX_ARGS];
+};
+
+struct FusionRec {
+  int k1, k2;
+  FusedPlan plan;
+  std::string name;
+  size_t smem;
+  unsigned launch_grid;
+  unsigned *queue_ctr;  // device, 2 words (work queue only)
+  int regs;
+};
+
+struct GraphRec {
+  cudaGraphExec_t exec;
+  int launches;
+};
+
+}  // namespace
+
+struct bfuse_context {
+  int device;
+  int sm_count;
+  cudaStream_t s1, s2, own;
+  cudaEvent_t ev_fork, ev_j1, ev_j2;
+  int *d_status;
+  EncodeTiledFn encode;
+  PairEntry pairs[kNumOps][kNumOps];
+  SingleEntry singles[kNumOps];
+  std::vector<std::unique_ptr<KernelRec>> kernels;
+  std::vector<std::unique_ptr<FusionRec>> fusions;
+  std::vector<GraphRec> graphs;
+  std::string err;
+};
+
+namespace {
+
+int fail(bfuse_context *ctx, int code, const std::string &msg) {
+  if (ctx) ctx->err = msg;
+  return code;
+}
+int fail_cuda(bfuse_context *ctx, cudaError_t e, const char *what) {
+  return fail(ctx, BFUSE_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e));
+}
+#define CK(call)                                                   \
+  do {                                                             \
+    cudaError_t e_ = (call);                                       \
+    if (e_ != cudaSuccess) return fail_cuda(ctx, e_, #call);       \
+  } while (0)
+
+bool is_pow2(int x) { return x > 0 && (x & (x - 1)) == 0; }
+int ceil_div(int a, int b) { return (a + b - 1) / b; }
+bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int conv_out(int in, int k, int stride, int pad) { return (in + 2 * pad - k) / stride + 1; }
+
+// ---- default tilings (what the reference reads back from TVM, configure_kernels.py:73-99) --------
+
+int pick_row_threads(int cols, int vec_elems, int max_vec) {
+  // smallest power-of-two thread count per row (>= 32) that keeps <= 4 vectors per thread
+  for (int tpr = 32; tpr <= 256; tpr *= 2)
+    if (cols % (vec_elems * tpr) == 0 && cols / (vec_elems * tpr) <= std::min(4, max_vec)) return tpr;
+  for (int tpr = 256; tpr >= 1; tpr /= 2)
+    if (cols % (vec_elems * tpr) == 0 && cols / (vec_elems * tpr) <= max_vec) return tpr;
+  return 0;
+}
+
+int default_bn(int batch, int M, int N, int sm_count) {
+  // widest tile that still yields about half an SM-count of CTAs (the pair partner fills the rest)
+  const int bns[4] = {256, 128, 64, 32};
+  for (int bn : bns)
+    if ((long long)batch * ceil_div(M, kUmmaBM) * ceil_div(N, bn) >= sm_count / 2) return bn;
+  return 32;
+}
+
+int default_launch(const bfuse_context *ctx, bfuse_kernel_desc *d, std::string *err) {
+  const int *s = d->shape;
+  auto set = [&](int gx, int gy, int gz, int bx, int by, size_t smem, int nargs) {
+    d->GridDim = {gx, gy, gz};
+    d->BlockDim = {bx, by, 1};
+    d->smem_bytes = smem;
+    d->nargs = nargs;
+    d->HasBarriers = 1;
+  };
+  const int sm = ctx ? ctx->sm_count : 148;
+  switch (d->op) {
+    case BFUSE_OP_SOFTMAX_F32:
+    case BFUSE_OP_LAYERNORM_F32: {
+      const int tpr = pick_row_threads(s[1], 4, kRowMaxVec);
+      if (s[0] <= 0 || !tpr) { *err = "row operator: cols must be a multiple of 4 * (power-of-two threads per row)"; return BFUSE_ERR_SHAPE; }
+      const int rpc = std::max(1, 256 / tpr);
+      set(ceil_div(s[0], rpc), 1, 1, tpr, rpc, 256, d->op == BFUSE_OP_SOFTMAX_F32 ? 2 : 5);
+      return BFUSE_OK;
+    }
+    case BFUSE_OP_RMSNORM_BF16: {
+      const int tpr = pick_row_threads(s[1], 8, RmsNormBf16::kMaxVec);
+      if (s[0] <= 0 || !tpr) { *err = "rmsnorm: cols must be a multiple of 8 * (power-of-two threads per row)"; return BFUSE_ERR_SHAPE; }
+      const int rpc = std::max(1, 256 / tpr);
+      set(ceil_div(s[0], rpc), 1, 1, tpr, rpc, 256, 3);
+      return BFUSE_OK;
+    }
+    case BFUSE_OP_ROPE_BF16: {
+      if (s[0] <= 0 || s[1] <= 0 || s[2] <= 0 || s[2] % 16) { *err = "rope: dim must be a multiple of 16"; return BFUSE_ERR_SHAPE; }
+      const int chunks = s[2] / 16;
+      int groups = 1;
+      while (groups * 2 * chunks <= 64 && s[1] % (groups * 2) == 0) groups *= 2;
+      const int bx = chunks * groups, by = std::max(1, 256 / bx);
+      set(ceil_div(s[0], by), 1, 1, bx, by, 0, 3);
+      d->HasBarriers = 0;
+      return BFUSE_OK;
+    }
+    case BFUSE_OP_GEMM_F32_SIMT:
+      if (s[0] <= 0 || s[1] <= 0 || s[2] <= 0 || s[3] <= 0) { *err = "gemm: batch, M, N, K must be positive"; return BFUSE_ERR_SHAPE; }
+      set(ceil_div(s[2], kSimtTile), ceil_div(s[1], kSimtTile), s[0], 16, 16, kSimtSmemBytes, 4);
+      return BFUSE_OK;
+    case BFUSE_OP_CONV2D_F32_SIMT: {
+      if (s[0] <= 0 || s[1] <= 0 || s[4] <= 0 || s[7] <= 0) { *err = "conv2d: bad shape"; return BFUSE_ERR_SHAPE; }
+      const int oh = conv_out(s[2], s[5], s[7], s[8]), ow = conv_out(s[3], s[6], s[7], s[8]);
+      if (oh <= 0 || ow <= 0) { *err = "conv2d: empty output"; return BFUSE_ERR_SHAPE; }
+      set(ceil_div(s[0] * oh * ow, kSimtTile), ceil_div(s[4], kSimtTile), 1, 16, 16, kSimtSmemBytes, 3);
+      return BFUSE_OK;
+    }
+    case BFUSE_OP_GEMM_TF32:
+    case BFUSE_OP_GEMM_BF16: {
+      if (s[0] <= 0 || s[1] <= 0 || s[2] <= 0 || s[3] <= 0) { *err = "gemm: batch, M, N, K must be positive"; return BFUSE_ERR_SHAPE; }
+      const int bn = s[4] ? s[4] : default_bn(s[0], s[1], s[2], sm);
+      if (bn != 32 && bn != 64 && bn != 128 && bn != 256) { *err = "gemm: BN must be 32, 64, 128 or 256"; return BFUSE_ERR_SHAPE; }
+      d->shape[4] = bn;
+      const int bk = kUmmaRowBytes / (d->op == BFUSE_OP_GEMM_TF32 ? 4 : 2);
+      const int num_kb = ceil_div(s[3], bk);
+      // ring depth: enough to cover K, at most 8, and at most ~100 KB so two CTAs share an SM
+      // (one CTA for the 256-wide tile)
+      const int budget = bn == 256 ? 200 * 1024 : 100 * 1024;
+      int stages = std::min({num_kb, kUmmaMaxStages, (budget - kUmmaHeaderBytes) / umma_stage_bytes(bn)});
+      stages = std::max(stages, 1);
+      set(ceil_div(s[2], bn), ceil_div(s[1], kUmmaBM), s[0], kUmmaThreads, 1, umma_smem_bytes(bn, stages), 4);
+      return BFUSE_OK;
+    }
+    default:
+      *err = "operator not in the registry";
+      return BFUSE_ERR_INVALID;
+  }
+}
+
+// ---- argument lists ---------------------------------------------------------------------------
+
+int describe_args(const bfuse_kernel_desc &d, ArgInfo *a, std::string *err) {
+  const int *s = d.shape;
+  auto n = [](long long x) { return (size_t)std::max(0LL, x); };
+  switch (d.op) {
+    case BFUSE_OP_SOFTMAX_F32:
+      a[0] = {n(4LL * s[0] * s[1]), 0, 0};
+      a[1] = {n(4LL * s[0] * s[1]), 1, 0};
+      return 2;
+    case BFUSE_OP_LAYERNORM_F32:
+      a[0] = {n(4LL * s[0] * s[1]), 0, 0};
+      a[1] = {n(4LL * s[0] * s[1]), 0, 1};
+      a[2] = {n(4LL * s[1]), 0, 0};
+      a[3] = {n(4LL * s[1]), 0, 0};
+      a[4] = {n(4LL * s[0] * s[1]), 1, 0};
+      return 5;
+    case BFUSE_OP_RMSNORM_BF16:
+      a[0] = {n(2LL * s[0] * s[1]), 0, 0};
+      a[1] = {n(2LL * s[1]), 0, 0};
+      a[2] = {n(2LL * s[0] * s[1]), 1, 0};
+      return 3;
+    case BFUSE_OP_ROPE_BF16:
+      a[0] = {n(2LL * s[0] * s[1] * s[2]), 0, 0};
+      a[1] = {n(4LL * (s[2] / 2)), 0, 0};
+      a[2] = {n(2LL * s[0] * s[1] * s[2]), 1, 0};
+      return 3;
+    case BFUSE_OP_GEMM_F32_SIMT:
+    case BFUSE_OP_GEMM_TF32:
+    case BFUSE_OP_GEMM_BF16: {
+      const long long e = d.op == BFUSE_OP_GEMM_BF16 ? 2 : 4;
+      a[0] = {n(e * s[0] * s[1] * s[3]), 0, 0};
+      a[1] = {n(e * s[0] * s[2] * s[3]), 0, 0};
+      a[2] = {n(4LL * s[2]), 0, 1};
+      a[3] = {n(e * s[0] * s[1] * s[2]), 1, 0};
+      return 4;
+    }
+    case BFUSE_OP_CONV2D_F32_SIMT: {
+      const int oh = conv_out(s[2], s[5], s[7], s[8]), ow = conv_out(s[3], s[6], s[7], s[8]);
+      a[0] = {n(4LL * s[0] * s[1] * s[2] * s[3]), 0, 0};
+      a[1] = {n(4LL * s[4] * s[1] * s[5] * s[6]), 0, 0};
+      a[2] = {n(4LL * s[0] * s[4] * oh * ow), 1, 0};
+      return 3;
+    }
+    default:
+      *err = "operator not in the registry";
+      return -1;
+  }
+}
+
+// ---- typed parameter blocks ---------------------------------------------------------------------
+
+int encode_map(bfuse_context *ctx, CUtensorMap *map, int dtype_bytes, const void *base, int k, int rows, int batch,
+               int box_rows) {
+  const CUtensorMapDataType dt = dtype_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const cuuint64_t dims[3] = {(cuuint64_t)k, (cuuint64_t)rows, (cuuint64_t)batch};
+  const cuuint64_t strides[2] = {(cuuint64_t)k * dtype_bytes, (cuuint64_t)k * rows * dtype_bytes};
+  const cuuint32_t box[3] = {(cuuint32_t)(kUmmaRowBytes / dtype_bytes), (cuuint32_t)box_rows, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = ctx->encode(map, dt, 3, const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(ctx, BFUSE_ERR_CUDA, "cuTensorMapEncodeTiled failed (" + std::to_string((int)r) + ")");
+  return BFUSE_OK;
+}
+
+int build_params(bfuse_context *ctx, KernelRec &k) {
+  const bfuse_kernel_desc &d = k.desc;
+  const int *s = d.shape;
+  const KernelDims &kd = k.dims;
+  void *const *a = d.args;
+  auto shape_err = [&](const char *m) { return fail(ctx, BFUSE_ERR_SHAPE, k.name + ": " + m); };
+  if (kd.block() % 32) return shape_err("BlockDim.size() must be a multiple of 32 (named-barrier arrival counts)");
+  if (kd.block() > ctx->singles[d.op].max_threads) return shape_err("BlockDim exceeds the body's maximum");
+  for (int i = 0; i < k.nargs; ++i) {
+    if (!a[i] && !k.arg[i].optional) return fail(ctx, BFUSE_ERR_INVALID, k.name + ": missing argument buffer");
+    if (a[i] && !aligned16(a[i])) return fail(ctx, BFUSE_ERR_INVALID, k.name + ": argument buffers must be 16-byte aligned");
+  }
+  std::memset(k.params, 0, sizeof(k.params));
+  switch (d.op) {
+    case BFUSE_OP_SOFTMAX_F32:
+    case BFUSE_OP_LAYERNORM_F32:
+    case BFUSE_OP_RMSNORM_BF16: {
+      const int vec = d.op == BFUSE_OP_RMSNORM_BF16 ? 8 : 4;
+      const int maxv = d.op == BFUSE_OP_RMSNORM_BF16 ? RmsNormBf16::kMaxVec : kRowMaxVec;
+      const int tpr = kd.bx, rpc = kd.by;
+      if (s[0] <= 0 || s[1] <= 0) return shape_err("rows and cols must be positive");
+      if (!is_pow2(tpr) || kd.bz != 1) return shape_err("BlockDim must be (power-of-two threads per row, rows per CTA, 1)");
+      if (s[1] % (vec * tpr) || s[1] / (vec * tpr) > maxv) return shape_err("cols do not fit the per-thread vector budget");
+      if (kd.gy != 1 || kd.gz != 1 || (long long)kd.gx * rpc < s[0]) return shape_err("GridDim.X * rows per CTA must cover the rows");
+      if (tpr > 32 && k.smem < 256) return shape_err("rows wider than a warp need 256 bytes of shared memory");
+      if (d.op == BFUSE_OP_SOFTMAX_F32) {
+        SoftmaxF32::Params p{(const float *)a[0], (float *)a[1], s[0], s[1], d.fparam[0]};
+        std::memcpy(k.params, &p, sizeof(p));
+      } else if (d.op == BFUSE_OP_LAYERNORM_F32) {
+        LayerNormF32::Params p{(const float *)a[0], (const float *)a[1], (const float *)a[2], (const float *)a[3],
+                               (float *)a[4], s[0], s[1], d.fparam[0]};
+        std::memcpy(k.params, &p, sizeof(p));
+      } else {
+        RmsNormBf16::Params p{(const uint16_t *)a[0], (const uint16_t *)a[1], (uint16_t *)a[2], s[0], s[1], d.fparam[0]};
+        std::memcpy(k.params, &p, sizeof(p));
+      }
+      return BFUSE_OK;
+    }
+    case BFUSE_OP_ROPE_BF16: {
+      if (s[0] <= 0 || s[1] <= 0 || s[2] <= 0 || s[2] % 16) return shape_err("dim must be a positive multiple of 16");
+      const int chunks = s[2] / 16;
+      if (kd.bx % chunks || s[1] % (kd.bx / chunks) || kd.bz != 1) return shape_err("BlockDim.X must be chunks * (a divisor of heads)");
+      if (kd.gy != 1 || kd.gz != 1 || (long long)kd.gx * kd.by < s[0]) return shape_err("GridDim.X * positions per CTA must cover seq");
+      RopeBf16::Params p{(const uint16_t *)a[0], (const float *)a[1], (uint16_t *)a[2], s[0], s[1], s[2]};
+      std::memcpy(k.params, &p, sizeof(p));
+      return BFUSE_OK;
+    }
+    case BFUSE_OP_GEMM_F32_SIMT: {
+      if (s[0] <= 0 || s[1] <= 0 || s[2] <= 0 || s[3] <= 0) return shape_err("batch, M, N, K must be positive");
+      if (kd.bx != 16 || kd.by != 16 || kd.bz != 1) return shape_err("BlockDim must be (16, 16, 1)");
+      if (kd.gx != ceil_div(s[2], kSimtTile) || kd.gy != ceil_div(s[1], kSimtTile) || kd.gz != s[0])
+        return shape_err("GridDim must be (ceil(N/64), ceil(M/64), batch)");
+      if (k.smem < (size_t)kSimtSmemBytes) return shape_err("needs 8704 bytes of shared memory");
+      GemmSimtF32::Params p{(const float *)a[0], (const float *)a[1], (const float *)a[2], (float *)a[3],
+                            s[0], s[1], s[2], s[3], (int)(d.flags & BFUSE_FLAG_CAUSAL)};
+      std::memcpy(k.params, &p, sizeof(p));
+      return BFUSE_OK;
+    }
+    case BFUSE_OP_CONV2D_F32_SIMT: {
+      if (s[0] <= 0 || s[1] <= 0 || s[4] <= 0 || s[5] <= 0 || s[6] <= 0 || s[7] <= 0 || s[8] < 0) return shape_err("bad conv shape");
+      const int oh = conv_out(s[2], s[5], s[7], s[8]), ow = conv_out(s[3], s[6], s[7], s[8]);
+      if (oh <= 0 || ow <= 0) return shape_err("empty output");
+      if (kd.bx != 16 || kd.by != 16 || kd.bz != 1) return shape_err("BlockDim must be (16, 16, 1)");
+      if (kd.gx != ceil_div(s[0] * oh * ow, kSimtTile) || kd.gy != ceil_div(s[4], kSimtTile) || kd.gz != 1)
+        return shape_err("GridDim must be (ceil(n*oh*ow/64), ceil(co/64), 1)");
+      if (k.smem < (size_t)kSimtSmemBytes) return shape_err("needs 8704 bytes of shared memory");
+      ConvSimtF32::Params p{(const float *)a[0], (const float *)a[1], (float *)a[2], s[0], s[1], s[2], s[3],
+                            s[4], s[5], s[6], s[7], s[8], oh, ow};
+      std::memcpy(k.params, &p, sizeof(p));
+      return BFUSE_OK;
+    }
+    case BFUSE_OP_GEMM_TF32:
+    case BFUSE_OP_GEMM_BF16: {
+      const int eb = d.op == BFUSE_OP_GEMM_TF32 ? 4 : 2;
+      const int bn = s[4];
+      if (s[0] <= 0 || s[1] <= 0 || s[2] <= 0 || s[3] <= 0) return shape_err("batch, M, N, K must be positive");
+      if (bn != 32 && bn != 64 && bn != 128 && bn != 256) return shape_err("shape[4] (BN) must be 32, 64, 128 or 256");
+      if ((s[3] * eb) % 16) return shape_err("K rows must be a multiple of 16 bytes (TMA stride rule)");
+      if ((s[2] * eb) % 16) return shape_err("N must make output rows a multiple of 16 bytes");
+      if (kd.bx != kUmmaThreads || kd.by != 1 || kd.bz != 1) return shape_err("BlockDim must be (192, 1, 1)");
+      if (kd.gx != ceil_div(s[2], bn) || kd.gy != ceil_div(s[1], kUmmaBM) || kd.gz != s[0])
+        return shape_err("GridDim must be (ceil(N/BN), ceil(M/128), batch)");
+      if (k.smem < (size_t)umma_smem_bytes(bn, 1)) return shape_err("shared memory below one pipeline stage");
+      GemmUmmaParams p;
+      std::memset(&p, 0, sizeof(p));
+      int rc = encode_map(ctx, &p.map_a, eb, a[0], s[3], s[1], s[0], kUmmaBM);
+      if (rc) return rc;
+      rc = encode_map(ctx, &p.map_b, eb, a[1], s[3], s[2], s[0], bn);
+      if (rc) return rc;
+      p.bias = (const float *)a[2];
+      p.out = a[3];
+      p.batch = s[0], p.M = s[1], p.N = s[2], p.K = s[3];
+      p.causal = (int)(d.flags & BFUSE_FLAG_CAUSAL);
+      p.stages = std::min<int>(kUmmaMaxStages, (int)((k.smem - kUmmaHeaderBytes) / umma_stage_bytes(bn)));
+      p.bn = bn;
+      static_assert(sizeof(p) <= kParamsBytes, "parameter block too small");
+      std::memcpy(k.params, &p, sizeof(p));
+      return BFUSE_OK;
+    }
+    default:
+      return fail(ctx, BFUSE_ERR_INVALID, "operator not in the registry");
+  }
+}
+
+__global__ void trace_kernel(const __grid_constant__ DispatchTable t, int *kernel_of, int *vblock_of, int *sm_of) {
+  unsigned smid;
+  asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+  if (!t.queue) {
+    int k = -1, vb = -1;
+    decode_cta(t, blockIdx.x, k, vb);
+    if (threadIdx.x == 0) {
+      kernel_of[blockIdx.x] = k;
+      vblock_of[blockIdx.x] = vb;
+      sm_of[blockIdx.x] = (int)smid;
+    }
+    return;
+  }
+  __shared__ int ticket_s;
+  for (;;) {
+    if (threadIdx.x == 0) ticket_s = (int)atomicAdd(t.queue_ctr, 1u);
+    __syncthreads();
+    const int ticket = ticket_s;
+    __syncthreads();
+    if (ticket >= t.total) break;
+    int k = -1, vb = -1;
+    decode_cta(t, ticket, k, vb);
+    if (threadIdx.x == 0) {
+      kernel_of[ticket] = k;
+      vblock_of[ticket] = vb;
+      sm_of[ticket] = (int)smid;
+    }
+  }
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(t.queue_ctr + 1, 1u) == gridDim.x - 1) {
+      t.queue_ctr[0] = 0;
+      t.queue_ctr[1] = 0;
+    }
+  }
+}
+
+template <int I>
+void fill_rows(bfuse_context *ctx) {
+  fill_pair_row<I>(ctx->pairs[I], &ctx->singles[I]);
+  if constexpr (I + 1 < kNumOps) fill_rows<I + 1>(ctx);
+}
+
+KernelRec *get_kernel(bfuse_context *ctx, int h) {
+  return (ctx && h >= 0 && h < (int)ctx->kernels.size()) ? ctx->kernels[h].get() : nullptr;
+}
+FusionRec *get_fusion(const bfuse_context *ctx, int h) {
+  return (ctx && h >= 0 && h < (int)ctx->fusions.size()) ? ctx->fusions[h].get() : nullptr;
+}
+
+DispatchTable single_table(const bfuse_context *ctx, const KernelRec &k) {
+  DispatchTable t;
+  std::memset(&t, 0, sizeof(t));
+  t.n_cta[0] = k.dims.grid();
+  t.n_thr[0] = k.dims.block();
+  t.grid_x[0] = k.dims.gx, t.grid_y[0] = k.dims.gy;
+  t.blk_x[0] = k.dims.bx, t.blk_y[0] = k.dims.by;
+  t.bar_count[0] = round_up32(k.dims.block());
+  t.total = t.n_cta[0];
+  t.status = ctx->d_status;
+  return t;
+}
+
+int launch_one(bfuse_context *ctx, KernelRec &k, cudaStream_t s) {
+  const DispatchTable t = single_table(ctx, k);
+  const size_t smem = k.smem + 1024;
+  cudaError_t e = ctx->singles[k.desc.op].launch(t, k.params, (unsigned)k.dims.grid(), (unsigned)k.dims.block(), smem, s);
+  if (e != cudaSuccess) return fail_cuda(ctx, e, ("launch " + k.name).c_str());
+  return BFUSE_OK;
+}
+
+int launch_fused_rec(bfuse_context *ctx, FusionRec &f, cudaStream_t s) {
+  KernelRec &a = *ctx->kernels[f.k1], &b = *ctx->kernels[f.k2];
+  const PairEntry &pe = ctx->pairs[a.desc.op][b.desc.op];
+  PairLaunchFn fn = f.plan.table.kind == DISPATCH_THREADS ? pe.thread : pe.block;
+  cudaError_t e = fn(f.plan.table, a.params, b.params, f.launch_grid, (unsigned)f.plan.fused_block, f.smem, s);
+  if (e != cudaSuccess) return fail_cuda(ctx, e, ("launch " + f.name).c_str());
+  return BFUSE_OK;
+}
+
+int launch_parallel_rec(bfuse_context *ctx, FusionRec &f, cudaStream_t s) {
+  // fork the caller's stream into S1 / S2 and join back (run_parallel, operation_cu.py:203-229)
+  CK(cudaEventRecord(ctx->ev_fork, s));
+  CK(cudaStreamWaitEvent(ctx->s1, ctx->ev_fork, 0));
+  CK(cudaStreamWaitEvent(ctx->s2, ctx->ev_fork, 0));
+  int rc = launch_one(ctx, *ctx->kernels[f.k1], ctx->s1);
+  if (rc) return rc;
+  rc = launch_one(ctx, *ctx->kernels[f.k2], ctx->s2);
+  if (rc) return rc;
+  CK(cudaEventRecord(ctx->ev_j1, ctx->s1));
+  CK(cudaEventRecord(ctx->ev_j2, ctx->s2));
+  CK(cudaStreamWaitEvent(s, ctx->ev_j1, 0));
+  CK(cudaStreamWaitEvent(s, ctx->ev_j2, 0));
+  return BFUSE_OK;
+}
+
+int launch_mode(bfuse_context *ctx, FusionRec &f, int mode, cudaStream_t s) {
+  switch (mode) {
+    case 0: return launch_one(ctx, *ctx->kernels[f.k1], s);
+    case 1: return launch_one(ctx, *ctx->kernels[f.k2], s);
+    case 2: return launch_parallel_rec(ctx, f, s);
+    case 3: {
+      int rc = launch_one(ctx, *ctx->kernels[f.k1], s);
+      return rc ? rc : launch_one(ctx, *ctx->kernels[f.k2], s);
+    }
+    case 4: return launch_fused_rec(ctx, f, s);
+    default: return fail(ctx, BFUSE_ERR_INVALID, "mode must be 0..4");
+  }
+}
+
+}  // namespace
+
+// ================================================================================ C ABI
+
+extern "C" {
+
+int bfuse_create(int device, bfuse_context **out) {
+  if (!out) return BFUSE_ERR_INVALID;
+  *out = nullptr;
+  std::unique_ptr<bfuse_context> c(new bfuse_context());
+  bfuse_context *ctx = c.get();
+  static std::string create_err;
+  auto bail = [&](int code) {
+    create_err = ctx->err;
+    fprintf(stderr, "bfuse_create: %s\n", create_err.c_str());
+    return code;
+  };
+  ctx->device = device;
+  cudaDeviceProp prop;
+  if (cudaSetDevice(device) != cudaSuccess || cudaGetDeviceProperties(&prop, device) != cudaSuccess) {
+    ctx->err = "no usable CUDA device " + std::to_string(device);
+    return bail(BFUSE_ERR_DEVICE);
+  }
+  if (prop.major != 10) {
+    ctx->err = std::string("device is sm_") + std::to_string(prop.major * 10 + prop.minor) + ", this library is built for sm_100a only";
+    return bail(BFUSE_ERR_DEVICE);
+  }
+  ctx->sm_count = prop.multiProcessorCount;
+  void *fn = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn) {
+    ctx->err = "driver entry point cuTensorMapEncodeTiled not found";
+    return bail(BFUSE_ERR_DEVICE);
+  }
+  ctx->encode = reinterpret_cast<EncodeTiledFn>(fn);
+  fill_rows<0>(ctx);
+  if (cudaStreamCreateWithFlags(&ctx->s1, cudaStreamNonBlocking) != cudaSuccess ||
+      cudaStreamCreateWithFlags(&ctx->s2, cudaStreamNonBlocking) != cudaSuccess ||
+      cudaStreamCreateWithFlags(&ctx->own, cudaStreamNonBlocking) != cudaSuccess ||
+      cudaEventCreateWithFlags(&ctx->ev_fork, cudaEventDisableTiming) != cudaSuccess ||
+      cudaEventCreateWithFlags(&ctx->ev_j1, cudaEventDisableTiming) != cudaSuccess ||
+      cudaEventCreateWithFlags(&ctx->ev_j2, cudaEventDisableTiming) != cudaSuccess ||
+      cudaMalloc(&ctx->d_status, sizeof(int)) != cudaSuccess || cudaMemset(ctx->d_status, 0, sizeof(int)) != cudaSuccess) {
+    ctx->err = std::string("context set-up failed: ") + cudaGetErrorString(cudaGetLastError());
+    return bail(BFUSE_ERR_CUDA);
+  }
+  *out = c.release();
+  return BFUSE_OK;
+}
+
+int bfuse_destroy(bfuse_context *ctx) {
+  if (!ctx) return BFUSE_ERR_INVALID;
+  cudaSetDevice(ctx->device);
+  cudaDeviceSynchronize();
+  for (auto &g : ctx->graphs)
+    if (g.exec) cudaGraphExecDestroy(g.exec);
+  for (auto &f : ctx->fusions)
+    if (f->queue_ctr) cudaFree(f->queue_ctr);
+  cudaFree(ctx->d_status);
+  cudaEventDestroy(ctx->ev_fork);
+  cudaEventDestroy(ctx->ev_j1);
+  cudaEventDestroy(ctx->ev_j2);
+  cudaStreamDestroy(ctx->s1);
+  cudaStreamDestroy(ctx->s2);
+  cudaStreamDestroy(ctx->own);
+  delete ctx;
+  return BFUSE_OK;
+}
+
+const char *bfuse_last_error(const bfuse_context *ctx) { return ctx ? ctx->err.c_str() : "null context"; }
+int bfuse_device_sm_count(const bfuse_context *ctx) { return ctx ? ctx->sm_count : -1; }
+
+int bfuse_default_launch(const bfuse_context *ctx, bfuse_kernel_desc *desc) {
+  if (!desc) return BFUSE_ERR_INVALID;
+  std::string err;
+  const int rc = default_launch(ctx, desc, &err);
+  if (rc && ctx) const_cast<bfuse_context *>(ctx)->err = err;
+  return rc;
+}
+
+int bfuse_arg_info(const bfuse_context *ctx, const bfuse_kernel_desc *desc, int i, size_t *bytes, int *is_output) {
+  if (!desc) return BFUSE_ERR_INVALID;
+  ArgInfo a[BFUSE_MAX_ARGS];
+  std::string err;
+  const int n = describe_args(*desc, a, &err);
+  if (n < 0 || i < 0 || i >= n) {
+    if (ctx) const_cast<bfuse_context *>(ctx)->err = n < 0 ? err : "argument index out of range";
+    return BFUSE_ERR_INVALID;
+  }
+  if (bytes) *bytes = a[i].bytes;
+  if (is_output) *is_output = a[i].is_output;
+  return BFUSE_OK;
+}
+
+int bfuse_register_kernel(bfuse_context *ctx, const bfuse_kernel_desc *desc, int *kernel) {
+  if (!ctx || !desc || !kernel) return BFUSE_ERR_INVALID;
+  if (desc->op < 0 || desc->op >= kNumOps) return fail(ctx, BFUSE_ERR_INVALID, "operator not in the registry");
+  std::unique_ptr<KernelRec> k(new KernelRec());
+  k->desc = *desc;
+  k->name = desc->KernelName ? desc->KernelName : ("kernel" + std::to_string(ctx->kernels.size()));
+  k->desc.KernelName = nullptr;
+  k->dims = {desc->GridDim.X, desc->GridDim.Y, desc->GridDim.Z, desc->BlockDim.X, desc->BlockDim.Y, desc->BlockDim.Z};
+  if (k->dims.gx <= 0 || k->dims.gy <= 0 || k->dims.gz <= 0 || k->dims.bx <= 0 || k->dims.by <= 0 || k->dims.bz <= 0)
+    return fail(ctx, BFUSE_ERR_SHAPE, k->name + ": GridDim and BlockDim must be positive");
+  k->smem = desc->smem_bytes;
+  if (k->smem + 1024 > kMaxSmemPerCta) return fail(ctx, BFUSE_ERR_SMEM, k->name + ": shared memory over the 227 KB per-CTA budget");
+  std::string err;
+  k->nargs = describe_args(k->desc, k->arg, &err);
+  if (k->nargs < 0) return fail(ctx, BFUSE_ERR_INVALID, err);
+  if (desc->nargs != k->nargs) return fail(ctx, BFUSE_ERR_INVALID, k->name + ": wrong number of arguments for this operator");
+  cudaSetDevice(ctx->device);
+  const int rc = build_params(ctx, *k);
+  if (rc) return rc;
+  ctx->kernels.push_back(std::move(k));
+  *kernel = (int)ctx->kernels.size() - 1;
+  return BFUSE_OK;
+}
+
+int bfuse_set_kernel_args(bfuse_context *ctx, int kernel, void *const *args, int nargs) {
+  KernelRec *k = get_kernel(ctx, kernel);
+  if (!k || !args || nargs != k->nargs) return fail(ctx, BFUSE_ERR_INVALID, "bad kernel handle or argument count");
+  void *saved[BFUSE_MAX_ARGS];
+  std::memcpy(saved, k->desc.args, sizeof(saved));
+  for (int i = 0; i < nargs; ++i) k->desc.args[i] = args[i];
+  cudaSetDevice(ctx->device);
+  const int rc = build_params(ctx, *k);
+  if (rc) {
+    std::memcpy(k->desc.args, saved, sizeof(saved));
+    build_params(ctx, *k);
+  }
+  return rc;
+}
+
+int bfuse_register_fusion(bfuse_context *ctx, int kernel1, int kernel2, int pattern, int param_m, int param_n, int *fusion) {
+  KernelRec *a = get_kernel(ctx, kernel1), *b = get_kernel(ctx, kernel2);
+  if (!a || !b || !fusion) return fail(ctx, BFUSE_ERR_INVALID, "bad kernel handle");
+  std::unique_ptr<FusionRec> f(new FusionRec());
+  f->k1 = kernel1, f->k2 = kernel2;
+  const KernelDims kd[2] = {a->dims, b->dims};
+  if (pattern == PATTERN_SM_STRIPED && param_m == 0) param_m = ctx->sm_count;
+  if (pattern != PATTERN_SM_STRIPED && pattern != PATTERN_THREAD_SPLIT && pattern != PATTERN_RANGE_SPLIT) {
+    if (param_m == 0) param_m = 1;
+    if (param_n == 0) param_n = 1;
+  }
+  std::string err;
+  if (!plan_pair(kd, pattern, param_m, param_n, param_m, &f->plan, &err)) return fail(ctx, BFUSE_ERR_INVALID, err);
+  DispatchTable &t = f->plan.table;
+  t.status = ctx->d_status;
+  const bool thread_split = t.kind == DISPATCH_THREADS;
+  // fused kernel name as FusionContext::create builds it (src/Contexts.cc:67-84)
+  f->name = a->name + "_" + b->name + (thread_split ? "_fused_hfuse" : "_fused_bfuse");
+  // shared memory: union for block-level fusion, sum for thread-level fusion (Matchers.cc:512-519)
+  if (thread_split) {
+    t.smem_off[0] = 0;
+    t.smem_off[1] = (int)((a->smem + 1023) / 1024 * 1024);
+    f->smem = t.smem_off[1] + b->smem + 1024;
+  } else {
+    f->smem = std::max(a->smem, b->smem) + 1024;
+  }
+  if (f->smem > kMaxSmemPerCta) return fail(ctx, BFUSE_ERR_SMEM, f->name + ": fused shared memory over the 227 KB per-CTA budget");
+  f->launch_grid = (unsigned)f->plan.fused_grid;
+  cudaSetDevice(ctx->device);
+  const PairEntry &pe = ctx->pairs[a->desc.op][b->desc.op];
+  cudaFuncAttributes attr;
+  cudaError_t e = (thread_split ? pe.thread_attr : pe.block_attr)(&attr);
+  if (e != cudaSuccess) return fail_cuda(ctx, e, "cudaFuncGetAttributes");
+  f->regs = attr.numRegs;
+  if (t.queue) {
+    // persistent grid: as many CTAs as can be resident at once, never more than there are tickets
+    const int threads = f->plan.fused_block;
+    const int by_regs = std::max(1, 65536 / std::max(1, attr.numRegs * threads));
+    const int by_thr = std::max(1, 2048 / threads);
+    const int by_smem = std::max<int>(1, (int)((228 * 1024) / (f->smem + 1024)));
+    const int per_sm = std::min({by_regs, by_thr, by_smem, 32});
+    f->launch_grid = (unsigned)std::min(t.total, per_sm * ctx->sm_count);
+    CK(cudaMalloc(&f->queue_ctr, 2 * sizeof(unsigned)));
+    CK(cudaMemset(f->queue_ctr, 0, 2 * sizeof(unsigned)));
+    t.queue_ctr = f->queue_ctr;
+  }
+  ctx->fusions.push_back(std::move(f));
+  *fusion = (int)ctx->fusions.size() - 1;
+  return BFUSE_OK;
+}
+
+int bfuse_fusion_info(bfuse_context *ctx, int fusion, bfuse_kernel_desc *out) {
+  FusionRec *f = get_fusion(ctx, fusion);
+  if (!f || !out) return fail(ctx, BFUSE_ERR_INVALID, "bad fusion handle");
+  std::memset(out, 0, sizeof(*out));
+  out->KernelName = f->name.c_str();
+  out->HasBarriers = 1;
+  out->GridDim = {f->plan.fused_grid, 1, 1};
+  out->BlockDim = {f->plan.fused_block, 1, 1};
+  out->Reg = f->regs;
+  out->ExecTime = -1.f;
+  out->op = -1;
+  out->smem_bytes = f->smem;
+  out->shape[0] = (int)f->launch_grid;  // CTAs actually launched (differs from GridDim for the work queue)
+  return BFUSE_OK;
+}
+
+int bfuse_fusion_map_block(const bfuse_context *ctx, int fusion, int b, int *kernel, int *vblock) {
+  FusionRec *f = get_fusion(ctx, fusion);
+  if (!f || !kernel || !vblock || b < 0) return BFUSE_ERR_INVALID;
+  int k, vb;
+  if (b >= f->plan.table.total || !decode_cta(f->plan.table, b, k, vb)) return BFUSE_ERR_INVALID;
+  *kernel = k, *vblock = vb;
+  return BFUSE_OK;
+}
+
+int bfuse_fusion_map_thread(const bfuse_context *ctx, int fusion, int kernel, int b, int t, int *vblock, int *vthread, int *active) {
+  FusionRec *f = get_fusion(ctx, fusion);
+  if (!f || kernel < 0 || kernel > 1 || !active) return BFUSE_ERR_INVALID;
+  const DispatchTable &tb = f->plan.table;
+  if (tb.kind != DISPATCH_THREADS) return BFUSE_ERR_UNSUPPORTED;
+  const int vt = t - tb.thr_lo[kernel];
+  *active = vt >= 0 && vt < tb.n_thr[kernel] && b >= 0 && b < tb.n_cta[kernel];
+  if (vblock) *vblock = b;
+  if (vthread) *vthread = vt;
+  return BFUSE_OK;
+}
+
+int bfuse_launch_kernel(bfuse_context *ctx, int kernel, void *stream) {
+  KernelRec *k = get_kernel(ctx, kernel);
+  if (!k) return fail(ctx, BFUSE_ERR_INVALID, "bad kernel handle");
+  return launch_one(ctx, *k, (cudaStream_t)stream);
+}
+int bfuse_launch_sequential(bfuse_context *ctx, int fusion, void *stream) {
+  FusionRec *f = get_fusion(ctx, fusion);
+  if (!f) return fail(ctx, BFUSE_ERR_INVALID, "bad fusion handle");
+  return launch_mode(ctx, *f, 3, (cudaStream_t)stream);
+}
+int bfuse_launch_parallel(bfuse_context *ctx, int fusion, void *stream) {
+  FusionRec *f = get_fusion(ctx, fusion);
+  if (!f) return fail(ctx, BFUSE_ERR_INVALID, "bad fusion handle");
+  return launch_mode(ctx, *f, 2, (cudaStream_t)stream);
+}
+int bfuse_launch_fused(bfuse_context *ctx, int fusion, void *stream) {
+  FusionRec *f = get_fusion(ctx, fusion);
+  if (!f) return fail(ctx, BFUSE_ERR_INVALID, "bad fusion handle");
+  return launch_fused_rec(ctx, *f, (cudaStream_t)stream);
+}
+
+int bfuse_launch_list(bfuse_context *ctx, const int *fusions, int n, int mode, void *stream) {
+  if (!ctx || !fusions || n < 0) return BFUSE_ERR_INVALID;
+  for (int i = 0; i < n; ++i) {
+    FusionRec *f = get_fusion(ctx, fusions[i]);
+    if (!f) return fail(ctx, BFUSE_ERR_INVALID, "bad fusion handle in list");
+    const int rc = launch_mode(ctx, *f, mode, (cudaStream_t)stream);
+    if (rc) return rc;
+  }
+  return BFUSE_OK;
+}
+
+int bfuse_graph_create(bfuse_context *ctx, const int *fusions, int n, int mode, int *graph) {
+  if (!ctx || !fusions || n <= 0 || !graph) return BFUSE_ERR_INVALID;
+  cudaSetDevice(ctx->device);
+  // one plain pass first: it sets every kernel's shared-memory attribute outside the capture
+  int rc0 = bfuse_launch_list(ctx, fusions, n, mode, ctx->own);
+  if (rc0) return rc0;
+  CK(cudaStreamSynchronize(ctx->own));
+  cudaGraph_t g = nullptr;
+  CK(cudaStreamBeginCapture(ctx->own, cudaStreamCaptureModeThreadLocal));
+  int rc = bfuse_launch_list(ctx, fusions, n, mode, ctx->own);
+  cudaError_t e = cudaStreamEndCapture(ctx->own, &g);
+  if (rc) {
+    if (g) cudaGraphDestroy(g);
+    return rc;
+  }
+  if (e != cudaSuccess) return fail_cuda(ctx, e, "cudaStreamEndCapture");
+  GraphRec gr{nullptr, n * (mode == 2 || mode == 3 ? 2 : 1)};
+  e = cudaGraphInstantiate(&gr.exec, g, 0);
+  cudaGraphDestroy(g);
+  if (e != cudaSuccess) return fail_cuda(ctx, e, "cudaGraphInstantiate");
+  ctx->graphs.push_back(gr);
+  *graph = (int)ctx->graphs.size() - 1;
+  return BFUSE_OK;
+}
+
+int bfuse_graph_launch(bfuse_context *ctx, int graph, void *stream) {
+  if (!ctx || graph < 0 || graph >= (int)ctx->graphs.size()) return BFUSE_ERR_INVALID;
+  CK(cudaGraphLaunch(ctx->graphs[graph].exec, (cudaStream_t)stream));
+  return BFUSE_OK;
+}
+
+int bfuse_trace_fused(bfuse_context *ctx, int fusion, int *kernel_of, int *vblock_of, int *sm_of, int n) {
+  FusionRec *f = get_fusion(ctx, fusion);
+  if (!f || !kernel_of || !vblock_of || !sm_of) return fail(ctx, BFUSE_ERR_INVALID, "bad fusion handle");
+  const DispatchTable &t = f->plan.table;
+  if (t.kind == DISPATCH_THREADS) return fail(ctx, BFUSE_ERR_UNSUPPORTED, "thread-split fusions host both operators in every CTA");
+  if (n < t.total) return fail(ctx, BFUSE_ERR_INVALID, "trace arrays shorter than the fused grid");
+  cudaSetDevice(ctx->device);
+  int *d = nullptr;
+  CK(cudaMalloc(&d, 3 * sizeof(int) * t.total));
+  cudaError_t e = cudaMemset(d, 0xff, 3 * sizeof(int) * t.total);
+  if (e == cudaSuccess) {
+    trace_kernel<<<f->launch_grid, 32, 0, ctx->own>>>(t, d, d + t.total, d + 2 * t.total);
+    e = cudaGetLastError();
+  }
+  if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->own);
+  if (e == cudaSuccess) e = cudaMemcpy(kernel_of, d, sizeof(int) * t.total, cudaMemcpyDeviceToHost);
+  if (e == cudaSuccess) e = cudaMemcpy(vblock_of, d + t.total, sizeof(int) * t.total, cudaMemcpyDeviceToHost);
+  if (e == cudaSuccess) e = cudaMemcpy(sm_of, d + 2 * t.total, sizeof(int) * t.total, cudaMemcpyDeviceToHost);
+  cudaFree(d);
+  if (e != cudaSuccess) return fail_cuda(ctx, e, "trace");
+  return BFUSE_OK;
+}
+
+int bfuse_read_status(bfuse_context *ctx, int *status) {
+  if (!ctx || !status) return BFUSE_ERR_INVALID;
+  cudaSetDevice(ctx->device);
+  CK(cudaDeviceSynchronize());
+  CK(cudaMemcpy(status, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost));
+  if (*status) CK(cudaMemset(ctx->d_status, 0, sizeof(int)));
+  return BFUSE_OK;
+}
+
+// ---- host-buffer entry points (H2D, launch, sync, D2H) --------------------------------------------
+
+static int copy_in(bfuse_context *ctx, KernelRec &k, void *const *host, cudaStream_t s) {
+  for (int i = 0; i < k.nargs; ++i)
+    if (!k.arg[i].is_output && k.desc.args[i]) {
+      if (!host[i]) return fail(ctx, BFUSE_ERR_INVALID, k.name + ": missing host input buffer");
+      CK(cudaMemcpyAsync(k.desc.args[i], host[i], k.arg[i].bytes, cudaMemcpyHostToDevice, s));
+    }
+  return BFUSE_OK;
+}
+static int copy_out(bfuse_context *ctx, KernelRec &k, void *const *host, cudaStream_t s) {
+  for (int i = 0; i < k.nargs; ++i)
+    if (k.arg[i].is_output) {
+      if (!host[i]) return fail(ctx, BFUSE_ERR_INVALID, k.name + ": missing host output buffer");
+      CK(cudaMemcpyAsync(host[i], k.desc.args[i], k.arg[i].bytes, cudaMemcpyDeviceToHost, s));
+    }
+  return BFUSE_OK;
+}
+static int finish(bfuse_context *ctx, cudaStream_t s) {
+  CK(cudaStreamSynchronize(s));
+  int st = 0;
+  CK(cudaMemcpy(&st, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost));
+  if (st) {
+    cudaMemset(ctx->d_status, 0, sizeof(int));
+    char buf[64];
+    snprintf(buf, sizeof(buf), "device status 0x%x: a bounded wait gave up", st);
+    return fail(ctx, BFUSE_ERR_TIMEOUT, buf);
+  }
+  return BFUSE_OK;
+}
+
+int bfuse_run_kernel(bfuse_context *ctx, int kernel, void *const *host_args) {
+  KernelRec *k = get_kernel(ctx, kernel);
+  if (!k || !host_args) return fail(ctx, BFUSE_ERR_INVALID, "bad kernel handle");
+  cudaSetDevice(ctx->device);
+  int rc = copy_in(ctx, *k, host_args, ctx->own);
+  if (!rc) rc = launch_one(ctx, *k, ctx->own);
+  if (!rc) rc = copy_out(ctx, *k, host_args, ctx->own);
+  return rc ? rc : finish(ctx, ctx->own);
+}
+
+static int run_pair(bfuse_context *ctx, int fusion, void *const *h1, void *const *h2, int mode) {
+  FusionRec *f = get_fusion(ctx, fusion);
+  if (!f || !h1 || !h2) return fail(ctx, BFUSE_ERR_INVALID, "bad fusion handle");
+  cudaSetDevice(ctx->device);
+  KernelRec &a = *ctx->kernels[f->k1], &b = *ctx->kernels[f->k2];
+  int rc = copy_in(ctx, a, h1, ctx->own);
+  if (!rc) rc = copy_in(ctx, b, h2, ctx->own);
+  if (!rc) rc = launch_mode(ctx, *f, mode, ctx->own);
+  if (!rc) rc = copy_out(ctx, a, h1, ctx->own);
+  if (!rc) rc = copy_out(ctx, b, h2, ctx->own);
+  return rc ? rc : finish(ctx, ctx->own);
+}
+int bfuse_run_parallel(bfuse_context *ctx, int fusion, void *const *h1, void *const *h2) { return run_pair(ctx, fusion, h1, h2, 2); }
+int bfuse_run_fuse(bfuse_context *ctx, int fusion, void *const *h1, void *const *h2) { return run_pair(ctx, fusion, h1, h2, 4); }
+
+int bfuse_time(bfuse_context *ctx, int fusion, int mode, int warmup, int iters, float *mean_us, float *min_us) {
+  FusionRec *f = get_fusion(ctx, fusion);
+  if (!f || iters <= 0 || warmup < 0) return fail(ctx, BFUSE_ERR_INVALID, "bad fusion handle or iteration count");
+  cudaSetDevice(ctx->device);
+  cudaStream_t s = ctx->own;
+  for (int i = 0; i < warmup; ++i) {
+    const int rc = launch_mode(ctx, *f, mode, s);
+    if (rc) return rc;
+  }
+  std::vector<cudaEvent_t> ev(2 * iters + 2);
+  for (auto &e : ev) CK(cudaEventCreate(&e));
+  int rc = BFUSE_OK;
+  // individually bracketed launches -> min
+  for (int i = 0; i < iters && !rc; ++i) {
+    cudaEventRecord(ev[2 * i], s);
+    rc = launch_mode(ctx, *f, mode, s);
+    cudaEventRecord(ev[2 * i + 1], s);
+  }
+  // back-to-back launches under one bracket -> mean
+  cudaEventRecord(ev[2 * iters], s);
+  for (int i = 0; i < iters && !rc; ++i) rc = launch_mode(ctx, *f, mode, s);
+  cudaEventRecord(ev[2 * iters + 1], s);
+  cudaError_t e = cudaStreamSynchronize(s);
+  float mn = 1e30f, total = 0.f;
+  if (!rc && e == cudaSuccess) {
+    for (int i = 0; i < iters; ++i) {
+      float ms = 0.f;
+      cudaEventElapsedTime(&ms, ev[2 * i], ev[2 * i + 1]);
+      mn = std::min(mn, ms * 1000.f);
+    }
+    cudaEventElapsedTime(&total, ev[2 * iters], ev[2 * iters + 1]);
+  }
+  for (auto &x : ev) cudaEventDestroy(x);
+  if (rc) return rc;
+  if (e != cudaSuccess) return fail_cuda(ctx, e, "timing loop");
+  if (mean_us) *mean_us = total * 1000.f / iters;
+  if (min_us) *min_us = mn;
+  return BFUSE_OK;
+}
+
+long bfuse_check_matrix(const float *value, const float *answer, size_t n, float eps) {
+  long wrong = 0;
+  for (size_t i = 0; i < n; ++i) {
+    const float o = value[i], ans = answer[i];
+    if (!(std::fabs(o - ans) <= eps) && (ans == 0.f || !(std::fabs((o - ans) / ans) <= eps))) ++wrong;
+  }
+  return wrong;
+}
+
+// ---- scheduler without a device (the fuser itself runs on the CPU) ---------------------------------
+
+struct bfuse_plan {
+  FusedPlan plan;
+};
+
+int bfuse_plan_create(const bfuse_dim3 grid[2], const bfuse_dim3 block[2], int pattern, int param_m, int param_n,
+                      bfuse_plan **out) {
+  if (!grid || !block || !out) return BFUSE_ERR_INVALID;
+  const KernelDims kd[2] = {{grid[0].X, grid[0].Y, grid[0].Z, block[0].X, block[0].Y, block[0].Z},
+                            {grid[1].X, grid[1].Y, grid[1].Z, block[1].X, block[1].Y, block[1].Z}};
+  std::unique_ptr<bfuse_plan> p(new bfuse_plan());
+  std::string err;
+  if (!plan_pair(kd, pattern, param_m, param_n, param_m, &p->plan, &err)) return BFUSE_ERR_INVALID;
+  *out = p.release();
+  return BFUSE_OK;
+}
+void bfuse_plan_destroy(bfuse_plan *p) { delete p; }
+int bfuse_plan_fused_dims(const bfuse_plan *p, bfuse_dim3 *grid, bfuse_dim3 *block) {
+  if (!p || !grid || !block) return BFUSE_ERR_INVALID;
+  *grid = {p->plan.fused_grid, 1, 1};
+  *block = {p->plan.fused_block, 1, 1};
+  return BFUSE_OK;
+}
+int bfuse_plan_map_block(const bfuse_plan *p, int b, int *kernel, int *vblock) {
+  if (!p || !kernel || !vblock || b < 0 || b >= p->plan.table.total) return BFUSE_ERR_INVALID;
+  int k, vb;
+  if (!decode_cta(p->plan.table, b, k, vb)) return BFUSE_ERR_INVALID;
+  *kernel = k, *vblock = vb;
+  return BFUSE_OK;
+}
+int bfuse_plan_map_all(const bfuse_plan *p, int *kernel_of, int *vblock_of, int n) {
+  if (!p || !kernel_of || !vblock_of || n < p->plan.table.total) return BFUSE_ERR_INVALID;
+  if (p->plan.table.kind == DISPATCH_THREADS) return BFUSE_ERR_UNSUPPORTED;
+  for (int b = 0; b < p->plan.table.total; ++b)
+    if (!decode_cta(p->plan.table, b, kernel_of[b], vblock_of[b])) return BFUSE_ERR_INVALID;
+  return BFUSE_OK;
+}
+int bfuse_plan_map_thread(const bfuse_plan *p, int kernel, int b, int t, int *vblock, int *vthread, int *active) {
+  if (!p || kernel < 0 || kernel > 1 || !active) return BFUSE_ERR_INVALID;
+  const DispatchTable &tb = p->plan.table;
+  if (tb.kind != DISPATCH_THREADS) return BFUSE_ERR_UNSUPPORTED;
+  const int vt = t - tb.thr_lo[kernel];
+  *active = vt >= 0 && vt < tb.n_thr[kernel] && b >= 0 && b < tb.n_cta[kernel];
+  if (vblock) *vblock = b;
+  if (vthread) *vthread = vt;
+  return BFUSE_OK;
+}
+int bfuse_plan_barrier(const bfuse_plan *p, int kernel, int *bar_id, int *bar_count) {
+  if (!p || kernel < 0 || kernel > 1 || !bar_id || !bar_count) return BFUSE_ERR_INVALID;
+  *bar_id = kernel + 1;  // bar.sync <k+1>, <round32(B_k)> (Matchers.cc:301-311)
+  *bar_count = p->plan.table.bar_count[kernel];
+  return BFUSE_OK;
+}
+
+}  // extern "C"

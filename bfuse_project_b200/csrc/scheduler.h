@@ -1,0 +1,41 @@
+// Host scheduler: turns (two kernels' dims, a pattern, its parameters) into the DispatchTable the
+// fused kernel decodes.  Pure integer host code, usable without a GPU.
+#pragma once
+
+#include <string>
+
+#include "dispatch.h"
+
+namespace bfuse {
+
+struct KernelDims {
+  int gx, gy, gz;
+  int bx, by, bz;
+  int grid() const { return gx * gy * gz; }
+  int block() const { return bx * by * bz; }
+};
+
+enum Pattern : int {
+  PATTERN_ZIGZAG = 0,
+  PATTERN_PROPORTIONAL = 1,
+  PATTERN_SM_STRIPED = 2,
+  PATTERN_THREAD_SPLIT = 3,
+  PATTERN_RANGE_SPLIT = 4,
+  PATTERN_WORK_QUEUE = 5,
+};
+
+struct FusedPlan {
+  DispatchTable table;
+  int fused_grid;   // GridDim.X of the fused launch (Y = Z = 1)
+  int fused_block;  // BlockDim.X of the fused launch
+  int pattern;
+};
+
+inline int round_up32(int x) { return (x + 31) / 32 * 32; }
+
+// Returns false and sets err on invalid input.  For PATTERN_WORK_QUEUE the table describes the
+// ticket order (zig-zag param_m : param_n); the caller sizes the persistent grid.
+bool plan_pair(const KernelDims k[2], int pattern, int param_m, int param_n, int total_sm, FusedPlan *out,
+               std::string *err);
+
+}  // namespace bfuse
