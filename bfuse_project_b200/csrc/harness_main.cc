@@ -1,0 +1,285 @@
+// bfuse_harness -- seeded C++ benchmark / validation harness over the C ABI.
+//
+// Usage mirrors the reference's generated `benchmark [-v] [-n iters] T K1 K2`
+// (test-utils/test-suite-files/main_cc.py:22-36,139-299), with the pair chosen by name instead of
+// by two indices into generated shape tables:
+//
+//     bfuse_harness [-v] [-n iters] [-w warmup] [-p pattern] [-s seed] [-d device] T PAIR
+//
+//   T        0 kernel1 | 1 kernel2 | 2 parallel (two streams) | 3 hfuse (thread split)
+//            | 4 bfuse (block-level, pattern -p) | 5 sequential (kernel1 then kernel2)
+//   PAIR     cfg1 | cfg2 | cfg3 | cfg4a | cfg4b | cfg4c | cfg5
+//   pattern  zigzag (default) | range | striped | proportional | queue
+//   -v       validate like the reference: re-run the unfused kernels on the same inputs and compare
+//            (check_matrix rule, eps 1e-3) and additionally require bit-equality; exit code 1 on
+//            a mismatch (main_cc.py:288-292)
+//
+// Inputs are seeded (std::mt19937_64) instead of the reference's unseeded rand()
+// (utils_cc.py:28-31): activations ~N(0,1), weights ~N(0,0.02), gamma/beta ~U(0.5,1.5), conv
+// weights Kaiming-normal.  Prints one JSON line.
+#include <cuda_runtime.h>
+#include <getopt.h>
+
+#include <cmath>
+#include <cstdint>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <random>
+#include <string>
+#include <vector>
+
+#include "bfuse_b200.h"
+
+namespace {
+
+struct HostArg {
+  std::vector<unsigned char> data;
+  bool present = false;
+};
+
+struct KernelSetup {
+  bfuse_kernel_desc desc;
+  std::string name;
+  HostArg host[BFUSE_MAX_ARGS];
+  void *dev[BFUSE_MAX_ARGS] = {nullptr};
+  size_t bytes[BFUSE_MAX_ARGS] = {0};
+  int is_out[BFUSE_MAX_ARGS] = {0};
+  int handle = -1;
+  double flops = 0;
+};
+
+uint16_t to_bf16(float f) {
+  uint32_t u;
+  std::memcpy(&u, &f, 4);
+  u += 0x7fffu + ((u >> 16) & 1u);
+  return (uint16_t)(u >> 16);
+}
+
+enum Dist { NORMAL, UNIFORM_HALF_TO_ONE_AND_HALF, INV_FREQ };
+
+void fill(HostArg &a, size_t n, bool bf16, Dist dist, float scale, std::mt19937_64 &rng, float theta = 0.f) {
+  a.present = true;
+  a.data.resize(n * (bf16 ? 2 : 4));
+  std::normal_distribution<float> nd(0.f, 1.f);
+  std::uniform_real_distribution<float> ud(0.5f, 1.5f);
+  for (size_t i = 0; i < n; ++i) {
+    float v;
+    if (dist == NORMAL) v = scale * nd(rng);
+    else if (dist == UNIFORM_HALF_TO_ONE_AND_HALF) v = ud(rng);
+    else v = (float)std::pow((double)theta, -2.0 * (double)i / (2.0 * (double)n));
+    if (bf16) reinterpret_cast<uint16_t *>(a.data.data())[i] = to_bf16(v);
+    else reinterpret_cast<float *>(a.data.data())[i] = v;
+  }
+}
+
+void die(const char *msg, bfuse_context *ctx = nullptr) {
+  fprintf(stderr, "bfuse_harness: %s%s%s\n", msg, ctx ? ": " : "", ctx ? bfuse_last_error(ctx) : "");
+  exit(EXIT_FAILURE);
+}
+
+void base_desc(KernelSetup &k, const char *name, int op, std::initializer_list<int> shape) {
+  std::memset(&k.desc, 0, sizeof(k.desc));
+  k.name = name;
+  k.desc.op = op;
+  k.desc.ExecTime = -1.f;
+  int i = 0;
+  for (int v : shape) k.desc.shape[i++] = v;
+}
+
+void make_softmax(KernelSetup &k, int rows, int cols, float scale, std::mt19937_64 &rng) {
+  base_desc(k, "softmax", BFUSE_OP_SOFTMAX_F32, {rows, cols});
+  k.desc.fparam[0] = scale;
+  fill(k.host[0], (size_t)rows * cols, false, NORMAL, 1.f, rng);
+}
+void make_layernorm(KernelSetup &k, int rows, int cols, float eps, bool residual, std::mt19937_64 &rng) {
+  base_desc(k, residual ? "res_layernorm" : "layernorm", BFUSE_OP_LAYERNORM_F32, {rows, cols});
+  k.desc.fparam[0] = eps;
+  fill(k.host[0], (size_t)rows * cols, false, NORMAL, 1.f, rng);
+  if (residual) fill(k.host[1], (size_t)rows * cols, false, NORMAL, 1.f, rng);
+  fill(k.host[2], cols, false, UNIFORM_HALF_TO_ONE_AND_HALF, 1.f, rng);
+  fill(k.host[3], cols, false, UNIFORM_HALF_TO_ONE_AND_HALF, 1.f, rng);
+}
+void make_rmsnorm(KernelSetup &k, int rows, int cols, float eps, std::mt19937_64 &rng) {
+  base_desc(k, "rmsnorm", BFUSE_OP_RMSNORM_BF16, {rows, cols});
+  k.desc.fparam[0] = eps;
+  fill(k.host[0], (size_t)rows * cols, true, NORMAL, 1.f, rng);
+  fill(k.host[1], cols, true, UNIFORM_HALF_TO_ONE_AND_HALF, 1.f, rng);
+}
+void make_rope(KernelSetup &k, int seq, int heads, int dim, float theta, std::mt19937_64 &rng) {
+  base_desc(k, "rope_q", BFUSE_OP_ROPE_BF16, {seq, heads, dim});
+  fill(k.host[0], (size_t)seq * heads * dim, true, NORMAL, 1.f, rng);
+  fill(k.host[1], dim / 2, false, INV_FREQ, 1.f, rng, theta);
+}
+void make_gemm(KernelSetup &k, const char *name, int op, int batch, int M, int N, int K, bool bias, bool causal,
+               float w_std, std::mt19937_64 &rng) {
+  base_desc(k, name, op, {batch, M, N, K, 0});
+  const bool h = op == BFUSE_OP_GEMM_BF16;
+  k.desc.flags = causal ? BFUSE_FLAG_CAUSAL : 0;
+  fill(k.host[0], (size_t)batch * M * K, h, NORMAL, 1.f, rng);
+  fill(k.host[1], (size_t)batch * N * K, h, NORMAL, w_std, rng);
+  if (bias) fill(k.host[2], N, false, NORMAL, 0.1f, rng);
+  k.flops = 2.0 * batch * M * N * K;
+}
+void make_conv(KernelSetup &k, const char *name, int n, int ci, int hw, int co, int ksz, int stride, int pad,
+               std::mt19937_64 &rng) {
+  base_desc(k, name, BFUSE_OP_CONV2D_F32_SIMT, {n, ci, hw, hw, co, ksz, ksz, stride, pad});
+  fill(k.host[0], (size_t)n * ci * hw * hw, false, NORMAL, 1.f, rng);
+  fill(k.host[1], (size_t)co * ci * ksz * ksz, false, NORMAL, std::sqrt(2.f / (ci * ksz * ksz)), rng);
+  const int o = (hw + 2 * pad - ksz) / stride + 1;
+  k.flops = 2.0 * n * co * o * o * ci * ksz * ksz;
+}
+
+void build_pair(const std::string &pair, KernelSetup &a, KernelSetup &b, std::mt19937_64 &rng, int conv_batch) {
+  if (pair == "cfg1") {
+    make_softmax(a, 12 * 512, 512, 0.125f, rng);
+    make_layernorm(b, 512, 768, 1e-5f, false, rng);
+  } else if (pair == "cfg2") {
+    make_gemm(a, "q_proj", BFUSE_OP_GEMM_TF32, 1, 512, 768, 768, true, false, 0.02f, rng);
+    make_gemm(b, "k_proj", BFUSE_OP_GEMM_TF32, 1, 512, 768, 768, true, false, 0.02f, rng);
+  } else if (pair == "cfg3") {
+    make_gemm(a, "qkt", BFUSE_OP_GEMM_TF32, 12, 512, 512, 64, false, true, 1.f, rng);
+    make_layernorm(b, 512, 768, 1e-5f, true, rng);
+  } else if (pair == "cfg4a") {
+    make_gemm(a, "gate_proj", BFUSE_OP_GEMM_BF16, 1, 512, 14336, 4096, false, false, 0.02f, rng);
+    make_gemm(b, "up_proj", BFUSE_OP_GEMM_BF16, 1, 512, 14336, 4096, false, false, 0.02f, rng);
+  } else if (pair == "cfg4b") {
+    make_gemm(a, "k_proj", BFUSE_OP_GEMM_BF16, 1, 512, 1024, 4096, false, false, 0.02f, rng);
+    make_gemm(b, "v_proj", BFUSE_OP_GEMM_BF16, 1, 512, 1024, 4096, false, false, 0.02f, rng);
+  } else if (pair == "cfg4c") {
+    make_rmsnorm(a, 512, 4096, 1e-5f, rng);
+    make_rope(b, 512, 32, 128, 500000.f, rng);
+  } else if (pair == "cfg5") {
+    make_conv(a, "conv3x3_s2", conv_batch, 64, 56, 128, 3, 2, 1, rng);
+    make_conv(b, "conv1x1_s2", conv_batch, 64, 56, 128, 1, 2, 0, rng);
+  } else {
+    die("unknown PAIR (cfg1 cfg2 cfg3 cfg4a cfg4b cfg4c cfg5)");
+  }
+}
+
+void upload_and_register(bfuse_context *ctx, KernelSetup &k) {
+  if (bfuse_default_launch(ctx, &k.desc)) die("default launch", ctx);
+  for (int i = 0; i < k.desc.nargs; ++i) {
+    if (bfuse_arg_info(ctx, &k.desc, i, &k.bytes[i], &k.is_out[i])) die("arg info", ctx);
+    if (!k.is_out[i] && !k.host[i].present) continue;  // optional input left out
+    if (cudaMalloc(&k.dev[i], k.bytes[i]) != cudaSuccess) die("cudaMalloc failed");
+    if (k.is_out[i]) {
+      k.host[i].present = true;
+      k.host[i].data.assign(k.bytes[i], 0);
+      cudaMemset(k.dev[i], 0, k.bytes[i]);
+    } else {
+      if (k.host[i].data.size() != k.bytes[i]) die("host buffer size mismatch");
+      cudaMemcpy(k.dev[i], k.host[i].data.data(), k.bytes[i], cudaMemcpyHostToDevice);
+    }
+    k.desc.args[i] = k.dev[i];
+  }
+  k.desc.KernelName = k.name.c_str();
+  if (bfuse_register_kernel(ctx, &k.desc, &k.handle)) die("register kernel", ctx);
+}
+
+std::vector<std::vector<unsigned char>> download_outputs(KernelSetup &k) {
+  std::vector<std::vector<unsigned char>> out;
+  for (int i = 0; i < k.desc.nargs; ++i)
+    if (k.is_out[i]) {
+      std::vector<unsigned char> v(k.bytes[i]);
+      cudaMemcpy(v.data(), k.dev[i], k.bytes[i], cudaMemcpyDeviceToHost);
+      out.push_back(std::move(v));
+    }
+  return out;
+}
+void clear_outputs(KernelSetup &k) {
+  for (int i = 0; i < k.desc.nargs; ++i)
+    if (k.is_out[i]) cudaMemset(k.dev[i], 0, k.bytes[i]);
+}
+
+}  // namespace
+
+int main(int argc, char **argv) {
+  bool validate = false;
+  int iters = 30, warmup = 3, device = 0, conv_batch = 1;
+  uint64_t seed = 0;
+  std::string pattern = "zigzag";
+  int c;
+  while ((c = getopt(argc, argv, "vn:w:p:s:d:b:h")) != -1) {
+    switch (c) {
+      case 'v': validate = true; break;
+      case 'n': iters = atoi(optarg); break;
+      case 'w': warmup = atoi(optarg); break;
+      case 'p': pattern = optarg; break;
+      case 's': seed = strtoull(optarg, nullptr, 10); break;
+      case 'd': device = atoi(optarg); break;
+      case 'b': conv_batch = atoi(optarg); break;
+      default:
+        fprintf(stderr, "usage: %s [-v] [-n iters] [-w warmup] [-p pattern] [-s seed] [-d device] [-b conv batch] T PAIR\n", argv[0]);
+        return c == 'h' ? 0 : EXIT_FAILURE;
+    }
+  }
+  if (argc - optind != 2) die("expected: T PAIR");
+  const int T = atoi(argv[optind]);
+  const std::string pair = argv[optind + 1];
+  if (T < 0 || T > 5) die("T must be 0..5");
+
+  bfuse_context *ctx = nullptr;
+  if (bfuse_create(device, &ctx)) die("no usable sm_100 device");
+  std::mt19937_64 rng(seed);
+  KernelSetup a, b;
+  build_pair(pair, a, b, rng, conv_batch);
+  upload_and_register(ctx, a);
+  upload_and_register(ctx, b);
+
+  int pat = BFUSE_PATTERN_ZIGZAG, pm = 1, pn = 1;
+  if (T == 3) pat = BFUSE_PATTERN_THREAD_SPLIT, pm = pn = 0;
+  else if (pattern == "range") pat = BFUSE_PATTERN_RANGE_SPLIT, pm = pn = 0;
+  else if (pattern == "striped") pat = BFUSE_PATTERN_SM_STRIPED, pm = pn = 0;
+  else if (pattern == "proportional") pat = BFUSE_PATTERN_PROPORTIONAL;
+  else if (pattern == "queue") pat = BFUSE_PATTERN_WORK_QUEUE;
+  else if (pattern != "zigzag") die("unknown pattern");
+  int fusion = -1;
+  if (bfuse_register_fusion(ctx, a.handle, b.handle, pat, pm, pn, &fusion)) die("register fusion", ctx);
+  bfuse_kernel_desc info;
+  bfuse_fusion_info(ctx, fusion, &info);
+
+  const int mode = T == 3 ? 4 : (T == 5 ? 3 : T);
+  float mean_us = 0, min_us = 0;
+  if (bfuse_time(ctx, fusion, mode, warmup, iters, &mean_us, &min_us)) die("timing", ctx);
+  float seq_mean = 0, seq_min = 0;
+  if (bfuse_time(ctx, fusion, 3, warmup, iters, &seq_mean, &seq_min)) die("timing sequential", ctx);
+  int status = 0;
+  bfuse_read_status(ctx, &status);
+
+  long wrong = 0, bit_diff = 0;
+  if (validate) {
+    clear_outputs(a), clear_outputs(b);
+    if (mode == 4 ? bfuse_launch_fused(ctx, fusion, nullptr) : (mode == 2 ? bfuse_launch_parallel(ctx, fusion, nullptr) : bfuse_launch_sequential(ctx, fusion, nullptr)))
+      die("launch", ctx);
+    cudaDeviceSynchronize();
+    auto got_a = download_outputs(a), got_b = download_outputs(b);
+    clear_outputs(a), clear_outputs(b);
+    if (bfuse_launch_kernel(ctx, a.handle, nullptr) || bfuse_launch_kernel(ctx, b.handle, nullptr)) die("launch", ctx);
+    cudaDeviceSynchronize();
+    auto ans_a = download_outputs(a), ans_b = download_outputs(b);
+    auto cmp = [&](const KernelSetup &k, std::vector<std::vector<unsigned char>> &g, std::vector<std::vector<unsigned char>> &r) {
+      for (size_t i = 0; i < g.size(); ++i) {
+        if (std::memcmp(g[i].data(), r[i].data(), g[i].size())) ++bit_diff;
+        const bool f32 = k.desc.op != BFUSE_OP_RMSNORM_BF16 && k.desc.op != BFUSE_OP_ROPE_BF16 && k.desc.op != BFUSE_OP_GEMM_BF16;
+        if (f32) wrong += bfuse_check_matrix((const float *)g[i].data(), (const float *)r[i].data(), g[i].size() / 4, 1e-3f);
+      }
+    };
+    if (T != 1) cmp(a, got_a, ans_a);
+    if (T != 0) cmp(b, got_b, ans_b);
+  }
+
+  double bytes = 0;
+  for (auto *k : {&a, &b})
+    for (int i = 0; i < k->desc.nargs; ++i)
+      if (k->host[i].present) bytes += (double)k->bytes[i];
+  printf("{\"pair\": \"%s\", \"T\": %d, \"pattern\": \"%s\", \"kernel\": \"%s\", \"grid\": %d, \"block\": %d, \"smem\": %zu, "
+         "\"regs\": %d, \"iters\": %d, \"warmup\": %d, \"mean_us\": %.3f, \"min_us\": %.3f, \"sequential_mean_us\": %.3f, "
+         "\"speedup_vs_sequential\": %.4f, \"alg_bytes\": %.0f, \"alg_flops\": %.0f, \"status\": %d, \"validated\": %s, "
+         "\"wrong\": %ld, \"bit_mismatch\": %ld, \"seed\": %llu}\n",
+         pair.c_str(), T, T == 3 ? "thread_split" : pattern.c_str(), info.KernelName, info.GridDim.X, info.BlockDim.X,
+         info.smem_bytes, info.Reg, iters, warmup, mean_us, min_us, seq_mean, mean_us > 0 ? seq_mean / mean_us : 0.0,
+         bytes, a.flops + b.flops, status, validate ? "true" : "false", wrong, bit_diff, (unsigned long long)seed);
+  bfuse_destroy(ctx);
+  return (wrong || bit_diff || status) ? 1 : 0;
+}

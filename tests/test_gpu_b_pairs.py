@@ -1,0 +1,164 @@
+"""Parity of every fused pair on the GPU, through the C ABI: fused output == unfused output bit
+for bit (the reference's own check, main_cc.py:82-122, at eps = 0), and both against the CPU
+oracle within the tolerances in tests/pair_oracle.py."""
+import numpy as np
+import pytest
+
+import bfuse_project_b200 as bf
+from bfuse_project_b200 import workloads as wl
+from pair_oracle import check_against_oracle
+
+pytestmark = pytest.mark.gpu
+
+BLOCK_PATTERNS = [(bf.ZIGZAG, 1, 1), (bf.RANGE_SPLIT, 0, 0), (bf.SM_STRIPED, 0, 0), (bf.WORK_QUEUE, 1, 1),
+                  (bf.THREAD_SPLIT, 0, 0)]
+
+
+@pytest.fixture(scope="module")
+def rt():
+    r = bf.Runtime(0)
+    yield r
+    r.close()
+
+
+def run_and_check(rt, spec, patterns, check_oracle=True):
+    pair = wl.DevicePair(rt, spec)
+    pair.clear_outputs()
+    rt.launch_kernel(pair.kernels[0])
+    rt.launch_kernel(pair.kernels[1])
+    unfused = pair.read_outputs()
+    assert rt.read_status() == 0
+    if check_oracle:
+        check_against_oracle(spec.a, unfused[0], spec.name + "/" + spec.a.name)
+        check_against_oracle(spec.b, unfused[1], spec.name + "/" + spec.b.name)
+    for pat, m, n in patterns:
+        pair.clear_outputs()
+        rt.launch_fused(pair.fusion(pat, m, n))
+        fused = pair.read_outputs()
+        assert rt.read_status() == 0
+        for k in range(2):
+            for u, f in zip(unfused[k], fused[k]):
+                assert np.array_equal(u.view(np.uint8), f.view(np.uint8)), \
+                    "%s: fused (%s) differs from unfused for kernel %d" % (spec.name, bf.PATTERN_NAMES[pat], k)
+    # the parallel and sequential baselines run the same bodies
+    pair.clear_outputs()
+    rt.launch_parallel(pair.fusion(patterns[0][0], patterns[0][1], patterns[0][2]))
+    par = pair.read_outputs()
+    for k in range(2):
+        assert np.array_equal(par[k][0].view(np.uint8), unfused[k][0].view(np.uint8))
+    return pair
+
+
+@pytest.mark.parametrize("name", ["cfg1_softmax_layernorm", "cfg4c_rmsnorm_rope"])
+def test_memory_bound_pairs_small(rt, name):
+    run_and_check(rt, wl.make_pair(name, seed=3, scale=0.25), BLOCK_PATTERNS)
+
+
+@pytest.mark.parametrize("name", ["cfg1_softmax_layernorm", "cfg4c_rmsnorm_rope"])
+def test_memory_bound_pairs_full_size(rt, name):
+    run_and_check(rt, wl.make_pair(name, seed=4), [(bf.ZIGZAG, 1, 1), (bf.RANGE_SPLIT, 0, 0)])
+
+
+def test_softmax_rows_sum_to_one_full_size(rt):
+    # size-independent property at the full BASELINE size
+    pair = wl.DevicePair(rt, wl.make_pair("cfg1_softmax_layernorm", seed=5))
+    rt.launch_fused(pair.fusion(bf.ZIGZAG, 1, 1))
+    out = pair.read_outputs()
+    assert np.allclose(out[0][0].sum(1), 1.0, atol=1e-5)
+    y = out[1][0].astype(np.float64)
+    g, b = pair.spec.b.host[2].astype(np.float64), pair.spec.b.host[3].astype(np.float64)
+    z = (y - b) / g  # undo the affine part: rows must be standardised
+    assert np.allclose(z.mean(1), 0.0, atol=1e-4) and np.allclose(z.var(1), 1.0, atol=1e-3)
+
+
+def test_ragged_rows_and_custom_tilings(rt):
+    rng = np.random.default_rng(9)
+    a = wl.softmax("softmax", rng, 1001, 256, 0.5)       # 1001 rows: last CTA partly empty
+    a.block, a.grid = (64, 4, 1), (251, 1, 1)             # 64 threads per row, 4 rows per CTA
+    b = wl.layernorm("layernorm", rng, 77, 2048, 1e-5, residual=True)
+    b.block, b.grid = (128, 2, 1), (39, 1, 1)
+    run_and_check(rt, wl.PairSpec("ragged", a, b, "f32", "hbm"), BLOCK_PATTERNS)
+    c = wl.rmsnorm("rmsnorm", rng, 33, 1024, 1e-6)
+    d = wl.rope("rope", rng, 19, 8, 64, 10000.0)
+    run_and_check(rt, wl.PairSpec("ragged_bf16", c, d, "bf16", "hbm"), BLOCK_PATTERNS)
+
+
+def test_simt_gemm_and_conv_pairs(rt):
+    run_and_check(rt, wl.make_pair("cfg2_q_k_proj", seed=6, scale=0.25, tensor_cores=False), BLOCK_PATTERNS)
+    run_and_check(rt, wl.make_pair("cfg3_qkt_res_layernorm", seed=7, scale=0.25, tensor_cores=False),
+                  [(bf.ZIGZAG, 1, 1), (bf.THREAD_SPLIT, 0, 0), (bf.WORK_QUEUE, 2, 1)])
+    run_and_check(rt, wl.make_pair("cfg5_conv_branches", seed=8, conv_batch=2), BLOCK_PATTERNS)
+
+
+def test_simt_gemm_ragged_shapes(rt):
+    rng = np.random.default_rng(10)
+    a = wl.gemm("g1", rng, bf.OP_GEMM_F32_SIMT, 2, 70, 90, 36, bias=True, w_std=1.0)
+    b = wl.gemm("g2", rng, bf.OP_GEMM_F32_SIMT, 1, 130, 50, 20, causal=True, w_std=1.0)
+    run_and_check(rt, wl.PairSpec("ragged_gemm", a, b, "f32", "hbm"), BLOCK_PATTERNS)
+
+
+def test_host_buffer_entry_points(rt):
+    spec = wl.make_pair("cfg1_softmax_layernorm", seed=11, scale=0.25)
+    pair = wl.DevicePair(rt, spec)
+    h1 = [None if a is None else a.copy() for a in spec.a.host]
+    h2 = [None if a is None else a.copy() for a in spec.b.host]
+    rt.run_fuse(pair.fusion(bf.ZIGZAG, 1, 1), h1, h2)
+    check_against_oracle(spec.a, [h1[1]], "run_fuse softmax")
+    check_against_oracle(spec.b, [h2[4]], "run_fuse layernorm")
+    g1 = [None if a is None else a.copy() for a in spec.a.host]
+    rt.run_kernel(pair.kernels[0], g1)
+    assert np.array_equal(g1[1], h1[1])
+    p1 = [None if a is None else a.copy() for a in spec.a.host]
+    p2 = [None if a is None else a.copy() for a in spec.b.host]
+    rt.run_parallel(pair.fusion(bf.ZIGZAG, 1, 1), p1, p2)
+    assert np.array_equal(p1[1], h1[1]) and np.array_equal(p2[4], h2[4])
+    assert bf.check_matrix(h1[1], g1[1]) == 0
+
+
+def test_graph_replay_and_timing(rt):
+    specs = [wl.make_pair("cfg4c_rmsnorm_rope", seed=s, scale=0.25) for s in (1, 2, 3)]
+    pairs = [wl.DevicePair(rt, s) for s in specs]
+    fus = [p.fusion(bf.ZIGZAG, 1, 1) for p in pairs]
+    g = rt.graph_create(fus, bf.MODE_FUSED)
+    for p in pairs:
+        p.clear_outputs()
+    rt.graph_launch(g)
+    for p in pairs:
+        out = p.read_outputs()
+        check_against_oracle(p.spec.a, out[0], "graph rmsnorm")
+        check_against_oracle(p.spec.b, out[1], "graph rope")
+    mean, mn = rt.time(fus[0], bf.MODE_FUSED, warmup=3, iters=10)
+    assert 0 < mn <= mean * 4 and mean < 1e5
+
+
+def test_rejected_registrations(rt):
+    import torch
+    buf = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+    p = buf.data_ptr()
+    with pytest.raises(bf.BfuseError) as e:   # cols not divisible into 128-bit vectors
+        rt.describe("bad", bf.OP_SOFTMAX_F32, (4, 30), [p, p], (1.0,))
+    assert e.value.code == 2
+    d = rt.describe("s", bf.OP_SOFTMAX_F32, (64, 512), [p, p], (1.0,))
+    d.BlockDim = bf.Dim3(48, 1, 1)            # not a power of two / multiple of 32
+    with pytest.raises(bf.BfuseError):
+        rt.register_kernel(d)
+    d = rt.describe("s", bf.OP_SOFTMAX_F32, (64, 512), [p, p], (1.0,))
+    d.GridDim = bf.Dim3(2, 1, 1)              # grid does not cover the rows
+    with pytest.raises(bf.BfuseError):
+        rt.register_kernel(d)
+    d = rt.describe("s", bf.OP_SOFTMAX_F32, (64, 512), [p, 0], (1.0,))   # missing output buffer
+    with pytest.raises(bf.BfuseError):
+        rt.register_kernel(d)
+    d = rt.describe("s", bf.OP_SOFTMAX_F32, (64, 512), [p + 4, p], (1.0,))  # misaligned
+    with pytest.raises(bf.BfuseError):
+        rt.register_kernel(d)
+    with pytest.raises(bf.BfuseError):
+        rt.register_fusion(0, 10 ** 6, bf.ZIGZAG)
+    ok = rt.register_kernel(rt.describe("s", bf.OP_SOFTMAX_F32, (64, 512), [p, p], (1.0,)))
+    with pytest.raises(bf.BfuseError):
+        rt.register_fusion(ok, ok, 77)
+    d = rt.describe("g", bf.OP_GEMM_TF32, (1, 128, 128, 64, 0), [p, p, 0, p])
+    d.smem_bytes = 300 * 1024                  # over the per-CTA budget
+    with pytest.raises(bf.BfuseError) as e:
+        rt.register_kernel(d)
+    assert e.value.code == 3

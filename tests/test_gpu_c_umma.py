@@ -1,0 +1,93 @@
+"""Parity of the tcgen05 GEMM bodies (tf32 and bf16) and of the pairs built on them."""
+import numpy as np
+import pytest
+
+import bfuse_project_b200 as bf
+from bfuse_project_b200 import workloads as wl
+from pair_oracle import check_against_oracle
+from test_gpu_b_pairs import BLOCK_PATTERNS, run_and_check
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def rt():
+    r = bf.Runtime(0)
+    yield r
+    r.close()
+
+
+def test_single_tf32_tile(rt):
+    rng = np.random.default_rng(1)
+    a = wl.gemm("g1", rng, bf.OP_GEMM_TF32, 1, 128, 64, 32, w_std=1.0, bn=64)       # one tile, one K block
+    b = wl.gemm("g2", rng, bf.OP_GEMM_TF32, 1, 128, 128, 256, bias=True, w_std=1.0, bn=128)
+    run_and_check(rt, wl.PairSpec("tile", a, b, "tf32", "hbm"), [(bf.ZIGZAG, 1, 1)])
+
+
+def test_single_bf16_tile(rt):
+    rng = np.random.default_rng(2)
+    a = wl.gemm("g1", rng, bf.OP_GEMM_BF16, 1, 128, 32, 64, w_std=1.0, bn=32)
+    b = wl.gemm("g2", rng, bf.OP_GEMM_BF16, 1, 256, 256, 512, w_std=0.05, bn=256)
+    run_and_check(rt, wl.PairSpec("tile16", a, b, "bf16", "tensor"), [(bf.ZIGZAG, 1, 1)])
+
+
+def test_ragged_umma_shapes(rt):
+    rng = np.random.default_rng(3)
+    # M, N not multiples of the tile; K not a multiple of the K block; batch > 1; causal with M != N
+    a = wl.gemm("g1", rng, bf.OP_GEMM_TF32, 3, 200, 72, 40, bias=True, w_std=1.0, bn=32)
+    b = wl.gemm("g2", rng, bf.OP_GEMM_TF32, 2, 130, 260, 100, causal=True, w_std=1.0, bn=64)
+    run_and_check(rt, wl.PairSpec("ragged_tf32", a, b, "tf32", "hbm"), BLOCK_PATTERNS)
+    c = wl.gemm("g3", rng, bf.OP_GEMM_BF16, 2, 100, 136, 72, w_std=0.1, bn=64)
+    d = wl.gemm("g4", rng, bf.OP_GEMM_BF16, 1, 384, 96, 1000, w_std=0.05, bn=32)
+    run_and_check(rt, wl.PairSpec("ragged_bf16", c, d, "bf16", "tensor"), BLOCK_PATTERNS)
+
+
+def test_pipeline_depths(rt):
+    rng = np.random.default_rng(4)
+    for smem_stages in (1, 2, 3, 8):
+        a = wl.gemm("g1", rng, bf.OP_GEMM_TF32, 1, 128, 64, 512, w_std=1.0, bn=64)
+        a.smem = 1024 + smem_stages * (16384 + 64 * 128)
+        b = wl.gemm("g2", rng, bf.OP_GEMM_BF16, 1, 128, 128, 1024, w_std=0.05, bn=128)
+        b.smem = 1024 + smem_stages * (16384 + 128 * 128)
+        run_and_check(rt, wl.PairSpec("stages%d" % smem_stages, a, b, "tf32", "hbm"), [(bf.ZIGZAG, 1, 1), (bf.WORK_QUEUE, 1, 1)])
+
+
+@pytest.mark.parametrize("name", ["cfg2_q_k_proj", "cfg3_qkt_res_layernorm", "cfg4b_k_v_proj"])
+def test_tensor_core_pairs_small(rt, name):
+    run_and_check(rt, wl.make_pair(name, seed=5, scale=0.25), BLOCK_PATTERNS)
+
+
+@pytest.mark.parametrize("name", ["cfg2_q_k_proj", "cfg3_qkt_res_layernorm", "cfg4b_k_v_proj"])
+def test_tensor_core_pairs_full_size(rt, name):
+    run_and_check(rt, wl.make_pair(name, seed=6), [(bf.ZIGZAG, 1, 1), (bf.RANGE_SPLIT, 0, 0)])
+
+
+def test_tensor_core_matches_cuda_core_body(rt):
+    # the tcgen05 body against the CUDA-core body on the same inputs (both on the GPU)
+    tc = wl.make_pair("cfg2_q_k_proj", seed=7, scale=0.5)
+    cc = wl.make_pair("cfg2_q_k_proj", seed=7, scale=0.5, tensor_cores=False)
+    ptc, pcc = wl.DevicePair(rt, tc), wl.DevicePair(rt, cc)
+    rt.launch_fused(ptc.fusion(bf.ZIGZAG, 1, 1))
+    rt.launch_fused(pcc.fusion(bf.ZIGZAG, 1, 1))
+    a, b = ptc.read_outputs(), pcc.read_outputs()
+    for k in range(2):
+        rms = np.sqrt(np.mean(b[k][0].astype(np.float64) ** 2))
+        assert np.abs(a[k][0] - b[k][0]).max() <= 5e-3 * (np.abs(b[k][0]).max() + rms)
+
+
+def test_gate_up_row_sample_full_size(rt):
+    """Full-size gate || up (120 GFLOP, too large for the CPU oracle inside a test): a sample of
+    output rows spanning all four M tiles is checked against the oracle across all 14336 columns."""
+    import oracle
+    spec = wl.make_pair("cfg4a_gate_up_proj", seed=8)
+    pair = wl.DevicePair(rt, spec)
+    rt.launch_fused(pair.fusion(bf.ZIGZAG, 1, 1))
+    out = pair.read_outputs()
+    assert rt.read_status() == 0
+    rows = np.array([0, 1, 127, 128, 255, 300, 511])
+    for k, ks in enumerate((spec.a, spec.b)):
+        ref = oracle.gemm_nt_bf16(np.ascontiguousarray(ks.host[0][0][rows]), ks.host[1][0])
+        g = oracle.bf16_to_f32(out[k][0][0][rows].reshape(-1)).astype(np.float64)
+        r = oracle.bf16_to_f32(ref.reshape(-1)).astype(np.float64)
+        rms = np.sqrt(np.mean(r * r))
+        assert np.all(np.abs(g - r) <= 5e-3 * (np.abs(r) + rms))
