@@ -42,6 +42,7 @@ __device__ __forceinline__ void run_tile(const typename Op::Params &p, const Dis
   c.by = t.blk_y[k];
   c.smem = smem;
   c.status = t.status;
+  c.persistent = t.queue;
   Op::run(p, c);
 }
 

@@ -87,6 +87,10 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map
 }
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+// Lets co-resident CTAs allocate while this one still holds its columns.  A CTA that will allocate
+// again (a persistent CTA, once per tile) must NOT call this: allocating after it is illegal.
+__device__ __forceinline__ void tmem_relinquish() {
   asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
 }
 __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
@@ -226,7 +230,10 @@ struct GemmUmma {
       mbar_init(acc_bar, 1);
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 5) tmem_alloc(smem_u32(tmem_slot), BN);
+    if (warp == 5) {
+      tmem_alloc(smem_u32(tmem_slot), BN);
+      if (!c.persistent) tmem_relinquish();
+    }
     tc_fence_before();
     c.sync();
     tc_fence_after();
@@ -267,6 +274,11 @@ struct GemmUmma {
       }
       if (lane == 0) umma_commit(acc_bar);  // accumulator complete (also arrives if the loop bailed out)
       __syncwarp();
+      // The stage-release arrivals of the last ring pass are asynchronous and nobody consumes them;
+      // wait for them here so that none is still in flight when the barriers are invalidated and
+      // the shared memory is handed to the next tile or the next CTA.
+      for (int kb = max(0, num_kb - stages); kb < num_kb && ok; ++kb)
+        ok = mbar_wait(empty0 + 8 * (kb % stages), (kb / stages) & 1, c.status, UMMA_WAIT_EMPTY_TIMEOUT);
     } else {
       // epilogue: hardware warp w may only touch TMEM lanes [32 * (w % 4), +32)
       const int quad = (threadIdx.x >> 5) & 3;
