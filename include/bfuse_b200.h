@@ -160,6 +160,22 @@ int bfuse_time(bfuse_context *ctx, int fusion, int mode, int warmup, int iters, 
  * |a-b| > eps AND (b == 0 OR |(a-b)/b| > eps).  Returns the number of wrong elements. */
 long bfuse_check_matrix(const float *value, const float *answer, size_t n, float eps);
 
+/* No counterpart in the reference.  The softmax || LayerNorm pair through the persistent work queue
+ * for callers that cannot allocate device memory: processes whose memory is wholly owned by a pool
+ * or caching allocator, and latency-critical loops where cudaMalloc / cudaFree (which synchronise
+ * the device) are off limits.  Calls no cudaMalloc / cudaFree and keeps nothing on the heap; the
+ * queue's two counters live in a 256-byte static device array inside the library.  Buffers are the
+ * caller's device pointers (ln_res may be NULL).  At most BFUSE_NOALLOC_MAX_TICKETS fused CTAs;
+ * more is rejected with BFUSE_ERR_SHAPE.  The first call on a device performs a one-time address
+ * look-up and should happen outside stream capture; calls whose kernels overlap on one GPU race
+ * on the shared counters, so order them.  Output is bit-identical to bfuse_launch_fused on a
+ * BFUSE_PATTERN_WORK_QUEUE fusion of the same two kernels with default tilings. */
+#define BFUSE_NOALLOC_MAX_TICKETS (1 << 20)
+int bfuse_softmax_layernorm_queue_noalloc(const float *sm_x, float *sm_y, int sm_rows, int sm_cols, float sm_scale,
+                                          const float *ln_x, const float *ln_res, const float *ln_gamma,
+                                          const float *ln_beta, float *ln_y, int ln_rows, int ln_cols, float ln_eps,
+                                          void *stream);
+
 /* The scheduler alone, usable without a GPU: what `horizontal-fuser fusions.yaml kernels.yaml`
  * computes on the CPU (FusionContext::create, src/Contexts.cc:56-92) for one pair.  param_m /
  * param_n as for bfuse_register_fusion, except that SM_STRIPED needs an explicit SM count. */
