@@ -138,7 +138,12 @@ def other_pairs(rt, torch, bf, wl, pk, quick):
             for label, pattern, mode in (("fused_zigzag", bf.ZIGZAG, bf.MODE_FUSED), ("fused_range", bf.RANGE_SPLIT, bf.MODE_FUSED),
                                          ("fused_queue", bf.WORK_QUEUE, bf.MODE_FUSED), ("sequential", bf.ZIGZAG, bf.MODE_SEQUENTIAL),
                                          ("parallel", bf.ZIGZAG, bf.MODE_PARALLEL)):
-                fus = [p.fusion(pattern, 1 if pattern != bf.RANGE_SPLIT else 0, 1 if pattern != bf.RANGE_SPLIT else 0) for p in pairs]
+                try:
+                    fus = [p.fusion(pattern, 1 if pattern != bf.RANGE_SPLIT else 0, 1 if pattern != bf.RANGE_SPLIT else 0) for p in pairs]
+                except bf.BfuseError as e:
+                    if e.code != 7:
+                        raise
+                    continue   # pattern cannot host clustered (split-K) operators
                 g = rt.graph_create(fus, mode)
                 s = torch.cuda.current_stream().cuda_stream
                 for _ in range(3):
@@ -151,7 +156,7 @@ def other_pairs(rt, torch, bf, wl, pk, quick):
                 e1.record()
                 torch.cuda.synchronize()
                 res[label + "_us"] = e0.elapsed_time(e1) * 1e3 / (n_rep * reps)
-            best = min(res["fused_zigzag_us"], res["fused_range_us"], res["fused_queue_us"])
+            best = min(v for k, v in res.items() if k.startswith("fused_"))
             res["speedup_vs_sequential"] = res["sequential_us"] / best
             t_roof = max(spec.bytes / (pk["hbm_gbs"] * 1e3), spec.flops / (pk["bf16_tflops"] * (1e6 if spec.dtype == "bf16" else 0.5e6)))
             res["roofline_us"] = t_roof
@@ -200,11 +205,18 @@ def main():
     stream = torch.cuda.current_stream().cuda_stream
 
     def graph_for(pattern, mode, m=1, n=1):
-        return rt.graph_create([p.fusion(pattern, m, n) for p in pairs], mode)
+        try:
+            return rt.graph_create([p.fusion(pattern, m, n) for p in pairs], mode)
+        except bf.BfuseError as e:
+            if e.code != 7:
+                raise
+            return None   # pattern cannot host clustered (split-K) operators
 
     graphs = {"fused_zigzag": graph_for(bf.ZIGZAG, bf.MODE_FUSED), "fused_range": graph_for(bf.RANGE_SPLIT, bf.MODE_FUSED, 0, 0),
+              "fused_striped": graph_for(bf.SM_STRIPED, bf.MODE_FUSED, 0, 0),
               "fused_queue": graph_for(bf.WORK_QUEUE, bf.MODE_FUSED), "sequential": graph_for(bf.ZIGZAG, bf.MODE_SEQUENTIAL),
               "parallel": graph_for(bf.ZIGZAG, bf.MODE_PARALLEL)}
+    graphs = {k: g for k, g in graphs.items() if g is not None}
 
     def timed(graph, steps, warmup):
         for _ in range(warmup):
@@ -230,7 +242,7 @@ def main():
 
     # pick the fused pattern on a short trial, then time exactly K steps of it under the clock sampler
     trial = {k: timed(g, 3, 3) for k, g in graphs.items()}
-    best = min(("fused_zigzag", "fused_range", "fused_queue"), key=lambda k: trial[k])
+    best = min((k for k in trial if k.startswith("fused_")), key=lambda k: trial[k])
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -260,8 +272,9 @@ def main():
     for p in e2e_pairs:
         h = [[None if a is None else pinned_like(a) for a in ks.host] for ks in (p.spec.a, p.spec.b)]
         host.append([[None if t is None else t.numpy() for t in hk] for hk in h] + [h])
-    fus = [p.fusion({"fused_zigzag": bf.ZIGZAG, "fused_range": bf.RANGE_SPLIT, "fused_queue": bf.WORK_QUEUE}[best],
-                    0 if best == "fused_range" else 1, 0 if best == "fused_range" else 1) for p in e2e_pairs]
+    best_pat = {"fused_zigzag": bf.ZIGZAG, "fused_range": bf.RANGE_SPLIT, "fused_queue": bf.WORK_QUEUE, "fused_striped": bf.SM_STRIPED}[best]
+    best_mn = 1 if best_pat in (bf.ZIGZAG, bf.WORK_QUEUE) else 0
+    fus = [p.fusion(best_pat, best_mn, best_mn) for p in e2e_pairs]
     for i in range(min(3, len(fus))):
         rt.run_fuse(fus[i], host[i][0], host[i][1])
     e2e_steps = max(3, min(args.steps, 10))

@@ -80,10 +80,12 @@ def lib():
             "bfuse_launch_list": [vp, ip, C.c_int, C.c_int, vp],
             "bfuse_graph_create": [vp, ip, C.c_int, C.c_int, ip], "bfuse_graph_launch": [vp, C.c_int, vp],
             "bfuse_trace_fused": [vp, C.c_int, ip, ip, ip, C.c_int], "bfuse_read_status": [vp, ip],
+            "bfuse_debug_gemm_timeline": [vp, C.c_int, C.POINTER(C.c_longlong), C.c_int],
             "bfuse_run_kernel": [vp, C.c_int, pp], "bfuse_run_parallel": [vp, C.c_int, pp, pp],
             "bfuse_run_fuse": [vp, C.c_int, pp, pp],
             "bfuse_time": [vp, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_float)],
             "bfuse_plan_create": [C.POINTER(Dim3), C.POINTER(Dim3), C.c_int, C.c_int, C.c_int, pp],
+            "bfuse_plan_create_clustered": [C.POINTER(Dim3), C.POINTER(Dim3), C.c_int, C.c_int, C.c_int, C.c_int, pp],
             "bfuse_plan_fused_dims": [vp, C.POINTER(Dim3), C.POINTER(Dim3)],
             "bfuse_plan_map_block": [vp, C.c_int, ip, ip], "bfuse_plan_map_all": [vp, ip, ip, C.c_int],
             "bfuse_plan_map_thread": [vp, C.c_int, C.c_int, C.c_int, ip, ip, ip],
@@ -108,12 +110,12 @@ def lib():
 class Plan:
     """The block-dispatch plan of one pair, computed on the CPU (no GPU needed)."""
 
-    def __init__(self, kernels, pattern, param_m=1, param_n=1):
-        """kernels: two [gx, gy, gz, bx, by, bz] lists."""
+    def __init__(self, kernels, pattern, param_m=1, param_n=1, cluster=1):
+        """kernels: two [gx, gy, gz, bx, by, bz] lists; cluster: CTAs per dispatch unit."""
         g = (Dim3 * 2)(*[Dim3(*k[:3]) for k in kernels])
         b = (Dim3 * 2)(*[Dim3(*k[3:]) for k in kernels])
         self._h = C.c_void_p()
-        rc = lib().bfuse_plan_create(g, b, pattern, param_m, param_n, C.byref(self._h))
+        rc = lib().bfuse_plan_create_clustered(g, b, pattern, param_m, param_n, cluster, C.byref(self._h))
         if rc:
             raise BfuseError(rc, "plan rejected")
         fg, fb = Dim3(), Dim3()
@@ -277,6 +279,15 @@ class Runtime:
         self._ck(self._L.bfuse_trace_fused(self._ctx, fusion, ks.ctypes.data_as(ip), vbs.ctypes.data_as(ip),
                                            sms.ctypes.data_as(ip), n))
         return ks, vbs, sms
+
+    def gemm_timeline(self, kernel):
+        """Nanosecond offsets (from the first mark) of the first CTA's phases of a tcgen05 GEMM kernel."""
+        names = ["start", "setup_done", "first_load_issued", "last_load_issued", "first_stage_full", "last_mma_issued",
+                 "acc_ready", "partial_written", "cluster_sync1", "reduced", "cluster_sync2", "end"]
+        buf = (C.c_longlong * len(names))()
+        self._ck(self._L.bfuse_debug_gemm_timeline(self._ctx, kernel, buf, len(names)))
+        t0 = buf[0]
+        return {n: (buf[i] - t0 if buf[i] else None) for i, n in enumerate(names)}
 
     def read_status(self):
         s = C.c_int()

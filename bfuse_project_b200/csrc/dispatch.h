@@ -26,7 +26,8 @@ enum DispatchKind : int {
 struct DispatchTable {
   int kind;
   int queue;          // 1: persistent CTAs draw tickets from queue_ctr instead of using blockIdx.x
-  int total;          // fused CTAs (block-level kinds) or tickets (queue)
+  int total;          // dispatch units (block-level kinds) or tickets (queue); units = CTAs when cluster == 1
+  int cluster;        // CTAs per dispatch unit = hardware cluster width (1: the reference's CTA-level dispatch)
   int n_cta[2];       // G_k = GridDim.size() of operator k
   int n_thr[2];       // B_k = BlockDim.size() of operator k
   int grid_x[2], grid_y[2];
@@ -47,8 +48,9 @@ struct DispatchTable {
   int *status;             // device status word; non-zero = a bounded wait gave up
 };
 
-// CTA (or ticket) b -> operator k and its virtual block.  Returns false if b is unmapped.
-BFUSE_HD bool decode_cta(const DispatchTable &t, int b, int &k, int &vb) {
+// Dispatch unit (or ticket) b -> operator k and its virtual unit.  Returns false if b is unmapped.
+// With cluster == 1 a unit is a CTA and this is the reference's if / else-if chain.
+BFUSE_HD bool decode_unit(const DispatchTable &t, int b, int &k, int &vb) {
   if (t.kind == DISPATCH_ROTATE) {
     if (b < t.rot_end) {
       const int r = b % t.rot, q = b / t.rot;
@@ -87,6 +89,19 @@ BFUSE_HD bool decode_cta(const DispatchTable &t, int b, int &k, int &vb) {
     return true;
   }
   return false;
+}
+
+// Hardware CTA b -> operator k and its virtual block.  When operators are launched as thread-block
+// clusters (split-K GEMM tiles reduce over distributed shared memory) the patterns above schedule
+// whole clusters: unit u = b / cluster goes through decode_unit, and the CTA's virtual block is
+// vu * cluster + b % cluster, so the CTAs of one hardware cluster always belong to one operator
+// and to consecutive virtual blocks.  Returns false for an unmapped or padding CTA.
+BFUSE_HD bool decode_cta(const DispatchTable &t, int b, int &k, int &vb) {
+  if (t.cluster <= 1) return decode_unit(t, b, k, vb);
+  int vu;
+  if (!decode_unit(t, b / t.cluster, k, vu)) return false;
+  vb = vu * t.cluster + b % t.cluster;
+  return vb < t.n_cta[k];
 }
 
 }  // namespace bfuse

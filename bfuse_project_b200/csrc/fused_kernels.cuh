@@ -12,9 +12,8 @@
 //   single_kernel<A>           the unfused launch of the same body (baselines, bit-exact check);
 //   trace_kernel               the dispatch decode alone, recording what each CTA would run.
 //
-// __launch_bounds__ come from the pair: the larger block, and the LARGER of the two bodies'
-// minimum-CTAs-per-SM, so the lighter operator keeps its occupancy and the heavier body is
-// compiled into that register budget.
+// __launch_bounds__ come from the pair (pair_min_blocks): the larger block and a CTAs-per-SM target
+// that keeps the lighter operator's occupancy without starving the heavier body of registers.
 #pragma once
 
 #include "dispatch.h"
@@ -29,7 +28,7 @@ __device__ __forceinline__ unsigned char *align_smem_1k(unsigned char *p) {
 
 template <class Op>
 __device__ __forceinline__ void run_tile(const typename Op::Params &p, const DispatchTable &t, int k, int vb, int vtid,
-                                         int bar_id, unsigned char *smem) {
+                                         int bar_id, unsigned char *smem, int shares_cta = 0) {
   TileCtx c;
   c.vblock = vb;
   c.tid = vtid;
@@ -42,15 +41,23 @@ __device__ __forceinline__ void run_tile(const typename Op::Params &p, const Dis
   c.by = t.blk_y[k];
   c.smem = smem;
   c.status = t.status;
-  c.persistent = t.queue;
+  c.persistent = t.queue | shares_cta;
   Op::run(p, c);
 }
 
 constexpr int cmax(int a, int b) { return a > b ? a : b; }
 constexpr int cmin(int a, int b) { return a < b ? a : b; }
+// Minimum CTAs per SM the pair is compiled for.  Two memory-bound bodies: the larger of their two
+// wishes (occupancy is what hides HBM latency).  A memory-bound body next to a GEMM / conv body:
+// at most 4, so the heavier body is not squeezed below 64 registers per thread.
+template <class A, class B>
+constexpr int pair_min_blocks() {
+  return (A::kMemoryBound && B::kMemoryBound) ? cmax(A::kMinBlocks, B::kMinBlocks)
+                                              : cmin(4, cmax(A::kMinBlocks, B::kMinBlocks));
+}
 
 template <class A, class B>
-__global__ void __launch_bounds__(cmax(A::kMaxThreads, B::kMaxThreads), cmax(A::kMinBlocks, B::kMinBlocks))
+__global__ void __launch_bounds__(cmax(A::kMaxThreads, B::kMaxThreads), pair_min_blocks<A, B>())
     fused_block_kernel(const __grid_constant__ DispatchTable t, const __grid_constant__ typename A::Params pa,
                        const __grid_constant__ typename B::Params pb) {
   extern __shared__ unsigned char smem_raw[];
@@ -103,10 +110,10 @@ __global__ void __launch_bounds__(A::kMaxThreads + B::kMaxThreads, 1)
   const int tid = threadIdx.x, b = blockIdx.x;
   // thread ranges of hfusePattern (Algorithms.cc:23-49): kernel k owns [thr_lo[k], thr_lo[k] + B_k)
   if (tid < t.thr_lo[1]) {
-    if (tid < t.n_thr[0] && b < t.n_cta[0]) run_tile<A>(pa, t, 0, b, tid, 1, smem + t.smem_off[0]);
+    if (tid < t.n_thr[0] && b < t.n_cta[0]) run_tile<A>(pa, t, 0, b, tid, 1, smem + t.smem_off[0], 1);
   } else {
     const int vt = tid - t.thr_lo[1];
-    if (vt < t.n_thr[1] && b < t.n_cta[1]) run_tile<B>(pb, t, 1, b, vt, 2, smem + t.smem_off[1]);
+    if (vt < t.n_thr[1] && b < t.n_cta[1]) run_tile<B>(pb, t, 1, b, vt, 2, smem + t.smem_off[1], 1);
   }
 }
 
@@ -132,14 +139,32 @@ cudaError_t ensure_smem(Kernel k, size_t smem) {
   return cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
 }
 
+// Launch with `cluster` consecutive CTAs per thread-block cluster (1 = a plain launch).
+template <class Kernel, class... Args>
+cudaError_t launch_clustered(Kernel kern, unsigned grid, unsigned block, size_t smem, cudaStream_t s, int cluster,
+                             Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(block, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cluster > 1 ? cluster : 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = cluster > 1 ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, args...);
+}
+
 template <class A, class B>
 cudaError_t launch_block_pair(const DispatchTable &t, const void *pa, const void *pb, unsigned grid, unsigned block,
                               size_t smem, cudaStream_t s) {
   cudaError_t e = ensure_smem(fused_block_kernel<A, B>, smem);
   if (e != cudaSuccess) return e;
-  fused_block_kernel<A, B><<<grid, block, smem, s>>>(t, *static_cast<const typename A::Params *>(pa),
-                                                      *static_cast<const typename B::Params *>(pb));
-  return cudaGetLastError();
+  return launch_clustered(fused_block_kernel<A, B>, grid, block, smem, s, t.cluster, t,
+                          *static_cast<const typename A::Params *>(pa), *static_cast<const typename B::Params *>(pb));
 }
 template <class A, class B>
 cudaError_t launch_thread_pair(const DispatchTable &t, const void *pa, const void *pb, unsigned grid, unsigned block,
@@ -155,8 +180,8 @@ cudaError_t launch_single(const DispatchTable &t, const void *pa, unsigned grid,
                           cudaStream_t s) {
   cudaError_t e = ensure_smem(single_kernel<A>, smem);
   if (e != cudaSuccess) return e;
-  single_kernel<A><<<grid, block, smem, s>>>(t, *static_cast<const typename A::Params *>(pa));
-  return cudaGetLastError();
+  return launch_clustered(single_kernel<A>, grid, block, smem, s, t.cluster, t,
+                          *static_cast<const typename A::Params *>(pa));
 }
 template <class A, class B>
 cudaError_t attr_block_pair(cudaFuncAttributes *a) { return cudaFuncGetAttributes(a, fused_block_kernel<A, B>); }

@@ -224,6 +224,11 @@ int main(int argc, char **argv) {
   std::mt19937_64 rng(seed);
   KernelSetup a, b;
   build_pair(pair, a, b, rng, conv_batch);
+  if (T == 3 || pattern == "queue") {
+    // thread split and the work queue cannot host GEMMs whose k-slices form a cluster
+    for (KernelSetup *k : {&a, &b})
+      if (k->desc.op == BFUSE_OP_GEMM_TF32 || k->desc.op == BFUSE_OP_GEMM_BF16) k->desc.shape[5] = 1;
+  }
   upload_and_register(ctx, a);
   upload_and_register(ctx, b);
 

@@ -76,7 +76,7 @@ extern "C" int bfuse_softmax_layernorm_queue_noalloc(const float *sm_x, float *s
     return reject(BFUSE_ERR_INVALID, "buffers must be 16-byte aligned");
   if (sm_rows <= 0 || sm_cols <= 0 || ln_rows <= 0 || ln_cols <= 0) return reject(BFUSE_ERR_SHAPE, "rows and cols must be positive");
   const int tpr_a = row_threads(sm_cols), tpr_b = row_threads(ln_cols);
-  if (!tpr_a || !tpr_b) return reject(BFUSE_ERR_SHAPE, "cols must be a multiple of 4 * (power-of-two threads per row), at most 8192");
+  if (!tpr_a || !tpr_b) return reject(BFUSE_ERR_SHAPE, "cols must be a multiple of 4 * (power-of-two threads per row), at most 4096");
   const int rpc_a = 256 / tpr_a, rpc_b = 256 / tpr_b;
   const long long ctas_a = ((long long)sm_rows + rpc_a - 1) / rpc_a, ctas_b = ((long long)ln_rows + rpc_b - 1) / rpc_b;
   if (ctas_a + ctas_b > BFUSE_NOALLOC_MAX_TICKETS)

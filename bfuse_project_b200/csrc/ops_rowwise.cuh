@@ -15,7 +15,7 @@
 
 namespace bfuse {
 
-constexpr int kRowMaxVec = 8;  // 128-bit vectors a thread may hold per row
+constexpr int kRowMaxVec = 4;  // 128-bit vectors a thread may hold per row (rows up to 4096 fp32 / 8192 bf16)
 
 // ---------------------------------------------------------------------------------- softmax
 struct SoftmaxF32 {
@@ -26,7 +26,8 @@ struct SoftmaxF32 {
     float scale;
   };
   static constexpr int kMaxThreads = 256;
-  static constexpr int kMinBlocks = 4;
+  static constexpr int kMinBlocks = 6;   // 6 x 256 threads per SM: registers per thread <= 40
+  static constexpr bool kMemoryBound = true;
 
   __device__ __forceinline__ static void run(const Params &p, const TileCtx &c) {
     const int tpr = c.bx, lane = c.tid % tpr, row = c.vblock * c.by + c.tid / tpr;
@@ -81,7 +82,8 @@ struct LayerNormF32 {
     float eps;
   };
   static constexpr int kMaxThreads = 256;
-  static constexpr int kMinBlocks = 4;
+  static constexpr int kMinBlocks = 6;   // 6 x 256 threads per SM: registers per thread <= 40
+  static constexpr bool kMemoryBound = true;
 
   __device__ __forceinline__ static void run(const Params &p, const TileCtx &c) {
     const int tpr = c.bx, lane = c.tid % tpr, row = c.vblock * c.by + c.tid / tpr;
@@ -149,7 +151,8 @@ struct RmsNormBf16 {
     float eps;
   };
   static constexpr int kMaxThreads = 256;
-  static constexpr int kMinBlocks = 4;
+  static constexpr int kMinBlocks = 6;   // 6 x 256 threads per SM: registers per thread <= 40
+  static constexpr bool kMemoryBound = true;
   static constexpr int kMaxVec = 4;  // 8 bf16 per vector
 
   __device__ __forceinline__ static void run(const Params &p, const TileCtx &c) {
@@ -204,7 +207,8 @@ struct RopeBf16 {
     int seq, heads, dim;
   };
   static constexpr int kMaxThreads = 256;
-  static constexpr int kMinBlocks = 4;
+  static constexpr int kMinBlocks = 6;   // 6 x 256 threads per SM: registers per thread <= 40
+  static constexpr bool kMemoryBound = true;
 
   __device__ __forceinline__ static void run(const Params &p, const TileCtx &c) {
     const int half = p.dim >> 1, chunks = half >> 3;

@@ -62,6 +62,7 @@ struct GemmSimtF32 {
   };
   static constexpr int kMaxThreads = 256;
   static constexpr int kMinBlocks = 2;
+  static constexpr bool kMemoryBound = false;
 
   __device__ __forceinline__ static void run(const Params &p, const TileCtx &c) {
     const int n0 = c.block_x() * kSimtTile, m0 = c.block_y() * kSimtTile, bz = c.block_z();
@@ -108,6 +109,7 @@ struct ConvSimtF32 {
   };
   static constexpr int kMaxThreads = 256;
   static constexpr int kMinBlocks = 2;
+  static constexpr bool kMemoryBound = false;
 
   __device__ __forceinline__ static void run(const Params &p, const TileCtx &c) {
     const int px0 = c.block_x() * kSimtTile, co0 = c.block_y() * kSimtTile;

@@ -5,9 +5,16 @@
 // with tf32 or bf16 operands instead of CUDA-core fp32 FMAs.
 //
 // BlockDim = (192, 1, 1): warps 0-3 read the accumulator (one TMEM lane quadrant each), warp 4 is
-// the TMA producer, warp 5 allocates tensor memory and issues the MMAs.  A CTA owns one 128 x BN
-// output tile: GridDim = (ceil(N/BN), ceil(M/128), batch).  The ring depth comes from the
-// shared-memory size the caller registered for the operator.
+// the TMA producer, warp 5 allocates tensor memory and issues the MMAs.  One 128 x BN output tile
+// belongs to `split` CTAs that each multiply a slice of K: GridDim = (split * ceil(N/BN),
+// ceil(M/128), batch).  A tcgen05.mma of 128 x N x 32 bytes takes about the same time for N = 32
+// as for N = 256, so narrow problems are fast only with wide tiles whose K loop is spread over
+// several SMs.  With split > 1 the CTAs of a tile form a thread-block cluster and every CTA owns a
+// share of the tile's 128-byte column chunks: after one cluster barrier (all MMAs of the tile are
+// done, so every ring is free) each CTA pushes its fp32 partial sums of a chunk straight from
+// tensor memory into the owner's shared memory with st.async, the owner waits on an mbarrier that
+// counts the delivered bytes, sums the k-slices in order (deterministic) and stores the chunk.
+// The ring depth comes from the shared-memory size the caller registered.
 //
 // Every wait on an mbarrier is bounded: when it gives up it writes a code to the status word and
 // the body falls through to its normal exit (barrier, TMEM free) instead of spinning.
@@ -24,13 +31,14 @@ constexpr int kUmmaThreads = 192;
 constexpr int kUmmaBM = 128;
 constexpr int kUmmaRowBytes = 128;                      // one swizzle-128B row of K per stage
 constexpr int kUmmaABytes = kUmmaBM * kUmmaRowBytes;    // 16 KB of A per stage
-constexpr int kUmmaHeaderBytes = 1024;                  // barriers + tmem pointer, keeps tiles 1 KB aligned
+constexpr int kUmmaHeaderBytes = 2048;                  // barriers, tmem pointer, bias slice; keeps tiles 1 KB aligned
 constexpr int kUmmaMaxStages = 8;
 
 enum UmmaStatus : int {
   UMMA_WAIT_EMPTY_TIMEOUT = 0x101,
   UMMA_WAIT_FULL_TIMEOUT = 0x102,
   UMMA_WAIT_ACC_TIMEOUT = 0x103,
+  UMMA_WAIT_PEERS_TIMEOUT = 0x104,
 };
 
 __host__ __device__ constexpr int umma_stage_bytes(int bn) { return kUmmaABytes + bn * kUmmaRowBytes; }
@@ -118,6 +126,7 @@ __device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64
   }
 }
 // 32 lanes x 16 consecutive fp32 columns of the accumulator: thread i of the warp gets lane i.
+// Asynchronous: the registers are valid after tmem_ld_wait().
 __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
@@ -125,7 +134,31 @@ __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16])
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
         "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// address of `local` (a shared::cta address of this CTA) in the shared memory of cluster rank `rank`
+__device__ __forceinline__ uint32_t peer_smem(uint32_t local, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
+  return r;
+}
+// 16-byte store into a peer's shared memory that also credits 16 bytes to the peer's mbarrier
+__device__ __forceinline__ void st_async_u4(uint32_t peer_addr, uint32_t peer_bar, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%2, %3, %4, %5}, [%1];" ::"r"(peer_addr),
+               "r"(peer_bar), "r"(a), "r"(b), "r"(c), "r"(d)
+               : "memory");
+}
+__device__ __forceinline__ float4 ld_shared_f4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_shared_u4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
 // Shared-memory matrix descriptor of a K-major, 128B-swizzled operand tile whose rows are 128
@@ -140,87 +173,169 @@ __host__ __device__ constexpr uint32_t umma_idesc(int kind, int bn) {
 }
 
 struct GemmUmmaParams {
-  alignas(64) CUtensorMap map_a;  // {K, M, batch}, box {128 B of K, 128, 1}, 128B swizzle
-  alignas(64) CUtensorMap map_b;  // {K, N, batch}, box {128 B of K, BN, 1}, 128B swizzle
-  const float *bias;              // [N] or nullptr
-  void *out;                      // [batch, M, N] fp32 (tf32 kind) or bf16 (bf16 kind)
+  alignas(64) CUtensorMap map_a;    // {K, M, batch}, box {128 B of K, 128, 1}, 128B swizzle
+  alignas(64) CUtensorMap map_b;    // {K, N, batch}, box {128 B of K, BN, 1}, 128B swizzle
+  alignas(64) CUtensorMap map_out;  // {N, M, batch}, box {128 B of N, 32, 1}, 128B swizzle (stores)
+  const float *bias;                // [N] or nullptr
+  void *out;                        // [batch, M, N] fp32 (tf32 kind) or bf16 (bf16 kind)
   int batch, M, N, K;
   int causal;
   int stages;
-  int bn;  // output-tile width: 32, 64, 128 or 256 (also the TMEM columns allocated)
+  int bn;            // output-tile width: 32, 64, 128 or 256 (also the TMEM columns allocated)
+  int split;         // CTAs (k-slices) per output tile = cluster width; 1: no split
+  int kb_per_slice;  // K blocks (of 128 bytes per row) per k-slice
+  long long *timeline;  // diagnostic: when non-null, CTA 0 records globaltimer marks here (see UmmaMark)
 };
+
+// marks of the diagnostic timeline (nanoseconds on the global timer), written by virtual block 0
+enum UmmaMark : int {
+  MARK_START = 0, MARK_SETUP_DONE, MARK_FIRST_LOAD_ISSUED, MARK_LAST_LOAD_ISSUED, MARK_FIRST_FULL, MARK_LAST_MMA_ISSUED,
+  MARK_ACC_READY, MARK_PARTIAL_WRITTEN, MARK_CLUSTER_SYNC1, MARK_REDUCED, MARK_CLUSTER_SYNC2, MARK_END, MARK_COUNT
+};
+
+constexpr int kUmmaStagingBytes = 4 * 4096;  // one 32-row x 128-byte store buffer per epilogue warp
+// bytes of the ring that the epilogue needs: for split GEMMs the receive area -- per owned 128-byte
+// output chunk one fp32 partial (128 rows x chunk columns) from every k-slice -- plus the store buffers
+__host__ __device__ constexpr int umma_recv_bytes(int bn, int split, int elem) {
+  return split > 1 ? ((bn * elem / 128 + split - 1) / split) * split * (128 / elem) * kUmmaBM * 4 : 0;
+}
+__host__ __device__ constexpr int umma_epilogue_bytes(int bn, int split, int elem) {
+  return umma_recv_bytes(bn, split, elem) + kUmmaStagingBytes;
+}
+
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, uint32_t src, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(map), "r"(src),
+               "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+template <int PENDING>
+__device__ __forceinline__ void tma_store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(PENDING) : "memory");
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 template <int KIND>
 struct GemmUmma {
   using Params = GemmUmmaParams;
   static constexpr int kMaxThreads = kUmmaThreads;
   static constexpr int kMinBlocks = 1;
+  static constexpr bool kMemoryBound = false;
   static constexpr int kElem = KIND == 0 ? 4 : 2;
   static constexpr int kBK = kUmmaRowBytes / kElem;  // K elements per stage
+  static constexpr int kOutCols = 128 / kElem;       // output columns per 128-byte store chunk
+  static constexpr int kSub = kOutCols / 16;         // 16-column accumulator reads per chunk
 
-  // 16 consecutive outputs of one row, starting at column n0
-  __device__ __forceinline__ static void store_row(const Params &p, float *dst_f32, uint16_t *dst_bf16, const uint32_t (&v)[16], int n0) {
-    if (KIND == 0) {
-      if (n0 + 16 <= p.N) {
+  // The epilogue of one warp: 32 rows x 128-byte chunks go through a 128B-swizzled staging buffer
+  // and leave with one TMA store per chunk (full lines, clipped at the M / N edges by the hardware).
+  struct ChunkWriter {
+    const Params &p;
+    uint32_t buf0;   // staging buffers of this warp (nbuf x 4096 bytes)
+    int nbuf, lane, issued;
+    int m_base, bz;  // first output row of this warp's 32 rows, batch index
+    int n_tile0;     // first output column of the tile
+
+    __device__ __forceinline__ uint32_t begin_chunk() {
+      if (issued >= nbuf) {  // the buffer about to be overwritten must have been read by its store
+        if (lane == 0) {
+          if (nbuf == 2) tma_store_wait_read<1>();
+          else tma_store_wait_read<0>();
+        }
+        __syncwarp();
+      }
+      return buf0 + (uint32_t)(issued % nbuf) * 4096u;
+    }
+    // 16 finished fp32 values of this lane's row: columns [nb + sub*16, +16) of the chunk at column nb;
+    // bias_tile: this tile's slice of the bias vector in shared memory (zeros without a bias)
+    __device__ __forceinline__ void put16(uint32_t buf, int sub, int nb, float (&v)[16], const float *bias_tile) {
+      const int col0 = nb + sub * 16, m = m_base + lane;
+      const float4 *b4 = reinterpret_cast<const float4 *>(bias_tile + (col0 - n_tile0));
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float4 b = b4[j];
+        v[4 * j] += b.x, v[4 * j + 1] += b.y, v[4 * j + 2] += b.z, v[4 * j + 3] += b.w;
+      }
+      if (p.causal && col0 + 15 > m) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          if (col0 + j > m) v[j] = -FLT_MAX;
+      }
+      const uint32_t row = buf + (uint32_t)lane * 128u;
+      if (KIND == 0) {
 #pragma unroll
         for (int j = 0; j < 4; ++j)
-          *reinterpret_cast<uint4 *>(dst_f32 + 4 * j) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          st_shared_u4(row + (uint32_t)(((sub * 4 + j) ^ (lane & 7)) * 16), __float_as_uint(v[4 * j]), __float_as_uint(v[4 * j + 1]),
+                       __float_as_uint(v[4 * j + 2]), __float_as_uint(v[4 * j + 3]));
       } else {
-        for (int j = 0; j < 16; ++j)
-          if (n0 + j < p.N) dst_f32[j] = __uint_as_float(v[j]);
-      }
-    } else {
-      if (n0 + 16 <= p.N) {
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          uint4 o;
-          o.x = f2_to_bf16x2(__uint_as_float(v[8 * j]), __uint_as_float(v[8 * j + 1]));
-          o.y = f2_to_bf16x2(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
-          o.z = f2_to_bf16x2(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
-          o.w = f2_to_bf16x2(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
-          *reinterpret_cast<uint4 *>(dst_bf16 + 8 * j) = o;
-        }
-      } else {
-        for (int j = 0; j < 16; ++j)
-          if (n0 + j < p.N) {
-            const __nv_bfloat16 h = __float2bfloat16_rn(__uint_as_float(v[j]));
-            dst_bf16[j] = *reinterpret_cast<const uint16_t *>(&h);
-          }
+        for (int j = 0; j < 2; ++j)
+          st_shared_u4(row + (uint32_t)(((sub * 2 + j) ^ (lane & 7)) * 16), f2_to_bf16x2(v[8 * j], v[8 * j + 1]),
+                       f2_to_bf16x2(v[8 * j + 2], v[8 * j + 3]), f2_to_bf16x2(v[8 * j + 4], v[8 * j + 5]),
+                       f2_to_bf16x2(v[8 * j + 6], v[8 * j + 7]));
       }
     }
-  }
+    __device__ __forceinline__ void end_chunk(uint32_t buf, int nb) {
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0 && nb < p.N && m_base < p.M) tma_store_3d(&p.map_out, buf, nb, m_base, bz);
+      ++issued;
+    }
+    __device__ __forceinline__ void finish() {
+      if (lane == 0) tma_store_wait_read<0>();
+      __syncwarp();
+    }
+  };
 
   __device__ __forceinline__ static void run(const Params &p, const TileCtx &c) {
     const int warp = c.tid >> 5, lane = c.tid & 31;
+    const int quad = (threadIdx.x >> 5) & 3;  // hardware warp w may only touch TMEM lanes [32 * (w % 4), +32)
     const int BN = p.bn, kStageBytes = umma_stage_bytes(BN);
     const uint32_t idesc = umma_idesc(KIND, BN);
-    const int n0 = c.block_x() * BN, m0 = c.block_y() * kUmmaBM, bz = c.block_z();
-    float *out_f32 = reinterpret_cast<float *>(p.out) + (size_t)bz * p.M * p.N;
-    uint16_t *out_bf16 = reinterpret_cast<uint16_t *>(p.out) + (size_t)bz * p.M * p.N;
+    const int split = p.split, kslice = c.block_x() % split;
+    const int n0 = (c.block_x() / split) * BN, m0 = c.block_y() * kUmmaBM, bz = c.block_z();
+    const int stages = p.stages;
+    const int chunks = BN / kOutCols;
+
+    // operator window: [0,1024) barriers + tmem pointer, then `stages` x (A tile, B tile); once the
+    // MMAs are done the ring holds the partial tile (split GEMMs) and the store buffers
+    uint64_t *bars = reinterpret_cast<uint64_t *>(c.smem);
+    const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * kUmmaMaxStages, acc_bar = empty0 + 8 * kUmmaMaxStages;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(c.smem + 8 * (2 * kUmmaMaxStages + 2));
+    const uint32_t tiles = smem_u32(c.smem) + kUmmaHeaderBytes;
+    const uint32_t recv_bar = acc_bar + 8;                                  // counts partial sums delivered by peers
+    float *bias_tile = reinterpret_cast<float *>(c.smem + 1024);            // BN floats
+    const int max_owned = (chunks + split - 1) / split;                     // store chunks a k-slice finishes
+    constexpr uint32_t kChunkPartial = (uint32_t)kOutCols * kUmmaBM * 4;    // fp32 partial of one chunk from one k-slice
+    const uint32_t staging = tiles + (uint32_t)umma_recv_bytes(BN, split, kElem);
+    const int nbuf = (stages * kStageBytes - (int)(staging - tiles)) >= 2 * kUmmaStagingBytes ? 2 : 1;
+    ChunkWriter w{p, staging + (uint32_t)(quad * nbuf) * 4096u, nbuf, lane, 0, m0 + quad * 32, bz, n0};
+    long long *const tl = (p.timeline && c.vblock == 0) ? p.timeline : nullptr;
+    auto mark = [&](int what, bool who) {
+      if (tl && who) tl[what] = (long long)global_ns();
+    };
+    mark(MARK_START, c.tid == 0);
 
     if (p.causal && n0 > m0 + kUmmaBM - 1) {
-      // tile entirely above the diagonal: nothing to multiply, only the mask value to write
-      if (warp < 4) {
-        const int m = m0 + warp * 32 + lane;
-        if (m < p.M) {
-          uint32_t v[16];
+      // tile entirely above the diagonal (for every k-slice of it): only the mask value to write;
+      // k-slice 0 fills one buffer once and stores it to every chunk
+      if (warp < 4 && kslice == 0) {
+        const uint32_t buf = w.begin_chunk();
+        const uint32_t mask = KIND == 0 ? __float_as_uint(-FLT_MAX) : f2_to_bf16x2(-FLT_MAX, -FLT_MAX);
 #pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = __float_as_uint(-FLT_MAX);
-          for (int cc = 0; cc < BN / 16; ++cc)
-            if (n0 + cc * 16 < p.N)
-              store_row(p, out_f32 + (size_t)m * p.N + n0 + cc * 16, out_bf16 + (size_t)m * p.N + n0 + cc * 16, v, n0 + cc * 16);
-        }
+        for (int j = 0; j < 8; ++j) st_shared_u4(buf + (uint32_t)lane * 128u + j * 16, mask, mask, mask, mask);
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0 && w.m_base < p.M)
+          for (int ch = 0; ch < chunks; ++ch)
+            if (n0 + ch * kOutCols < p.N) tma_store_3d(&p.map_out, buf, n0 + ch * kOutCols, w.m_base, bz);
+        w.finish();
       }
       return;
     }
 
-    // operator window: [0,1024) barriers + tmem pointer, then `stages` x (A tile, B tile)
-    uint64_t *bars = reinterpret_cast<uint64_t *>(c.smem);
-    const int stages = p.stages;
-    const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * kUmmaMaxStages, acc_bar = empty0 + 8 * kUmmaMaxStages;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(c.smem + 8 * (2 * kUmmaMaxStages + 1));
-    const uint32_t tiles = smem_u32(c.smem) + kUmmaHeaderBytes;
-    const int num_kb = (p.K + kBK - 1) / kBK;
+    const int total_kb = (p.K + kBK - 1) / kBK;
+    const int kb0 = kslice * p.kb_per_slice;                 // first K block of this k-slice
+    const int num_kb = min(p.kb_per_slice, total_kb - kb0);  // K blocks this CTA multiplies (>= 1)
 
     if (c.tid == 0) {
       for (int s = 0; s < stages; ++s) {
@@ -228,19 +343,32 @@ struct GemmUmma {
         mbar_init(empty0 + 8 * s, 1);
       }
       mbar_init(acc_bar, 1);
+      mbar_init(recv_bar, 1);
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      if (split > 1) {
+        // bytes this CTA will receive: one partial per owned chunk from every k-slice (itself included)
+        int owned = 0;
+        for (int ch = kslice; ch < chunks; ch += split) ++owned;
+        mbar_expect_tx(recv_bar, (uint32_t)owned * (uint32_t)split * kChunkPartial);
+      }
     }
     if (warp == 5) {
       tmem_alloc(smem_u32(tmem_slot), BN);
       if (!c.persistent) tmem_relinquish();
+    } else if (warp < 4) {
+      // the epilogue warps are idle during the main loop: they fetch the tile's bias slice now
+      for (int i = c.tid; i < BN; i += 128) bias_tile[i] = (p.bias && n0 + i < p.N) ? __ldg(p.bias + n0 + i) : 0.f;
     }
     tc_fence_before();
     c.sync();
     tc_fence_after();
     const uint32_t tmem_acc = *reinterpret_cast<volatile uint32_t *>(tmem_slot);
+    const uint32_t tmem_row = tmem_acc + ((uint32_t)(quad * 32) << 16);
+    mark(MARK_SETUP_DONE, c.tid == 0);
 
     // Producer and MMA warps run their loops with all 32 lanes (so the warp reaches the closing
     // barrier converged); lane 0 alone issues the copies / MMAs.
+    bool acc_ok = true;
     if (warp == 4) {
       bool ok = true;
       for (int kb = 0; kb < num_kb && ok; ++kb) {
@@ -250,8 +378,10 @@ struct GemmUmma {
         if (ok && lane == 0) {
           mbar_expect_tx(full0 + 8 * s, kStageBytes);
           const uint32_t a_dst = tiles + s * kStageBytes;
-          tma_load_3d(a_dst, &p.map_a, full0 + 8 * s, kb * kBK, m0, bz);
-          tma_load_3d(a_dst + kUmmaABytes, &p.map_b, full0 + 8 * s, kb * kBK, n0, bz);
+          tma_load_3d(a_dst, &p.map_a, full0 + 8 * s, (kb0 + kb) * kBK, m0, bz);
+          tma_load_3d(a_dst + kUmmaABytes, &p.map_b, full0 + 8 * s, (kb0 + kb) * kBK, n0, bz);
+          if (kb == 0) mark(MARK_FIRST_LOAD_ISSUED, true);
+          if (kb == num_kb - 1) mark(MARK_LAST_LOAD_ISSUED, true);
         }
         __syncwarp();
       }
@@ -262,6 +392,7 @@ struct GemmUmma {
         const uint32_t ph = (kb / stages) & 1;
         ok = mbar_wait(full0 + 8 * s, ph, c.status, UMMA_WAIT_FULL_TIMEOUT);
         tc_fence_after();
+        if (kb == 0) mark(MARK_FIRST_FULL, lane == 0);
         if (ok && lane == 0) {
           const uint64_t a_desc = umma_smem_desc(tiles + s * kStageBytes);
           const uint64_t b_desc = umma_smem_desc(tiles + s * kStageBytes + kUmmaABytes);
@@ -273,6 +404,7 @@ struct GemmUmma {
         __syncwarp();
       }
       if (lane == 0) umma_commit(acc_bar);  // accumulator complete (also arrives if the loop bailed out)
+      mark(MARK_LAST_MMA_ISSUED, lane == 0);
       __syncwarp();
       // The stage-release arrivals of the last ring pass are asynchronous and nobody consumes them;
       // wait for them here so that none is still in flight when the barriers are invalidated and
@@ -280,30 +412,91 @@ struct GemmUmma {
       for (int kb = max(0, num_kb - stages); kb < num_kb && ok; ++kb)
         ok = mbar_wait(empty0 + 8 * (kb % stages), (kb / stages) & 1, c.status, UMMA_WAIT_EMPTY_TIMEOUT);
     } else {
-      // epilogue: hardware warp w may only touch TMEM lanes [32 * (w % 4), +32)
-      const int quad = (threadIdx.x >> 5) & 3;
-      const bool ok = mbar_wait(acc_bar, 0, c.status, UMMA_WAIT_ACC_TIMEOUT);
+      acc_ok = mbar_wait(acc_bar, 0, c.status, UMMA_WAIT_ACC_TIMEOUT);
       tc_fence_after();
-      const int m = m0 + quad * 32 + lane;
-      if (ok) {
+      mark(MARK_ACC_READY, c.tid == 0);
+      if (acc_ok && split == 1) {
 #pragma unroll 1
-        for (int cc = 0; cc < BN / 16; ++cc) {
-          uint32_t r[16];
-          tmem_ld_32x16(tmem_acc + ((uint32_t)(quad * 32) << 16) + cc * 16, r);
-          const int nb = n0 + cc * 16;
-          if (m < p.M && nb < p.N) {
-            if (p.bias) {
+        for (int ch = 0; ch < chunks; ++ch) {
+          const uint32_t buf = w.begin_chunk();
 #pragma unroll
-              for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) + __ldg(p.bias + min(nb + j, p.N - 1)));
-            }
-            if (p.causal && nb + 15 > m) {
+          for (int sub = 0; sub < kSub; sub += 2) {  // two accumulator reads in flight per wait
+            uint32_t r0[16], r1[16];
+            tmem_ld_32x16(tmem_row + (ch * kSub + sub) * 16, r0);
+            tmem_ld_32x16(tmem_row + (ch * kSub + sub + 1) * 16, r1);
+            tmem_ld_wait();
+            float v[16];
 #pragma unroll
-              for (int j = 0; j < 16; ++j)
-                if (nb + j > m) r[j] = __float_as_uint(-FLT_MAX);
+            for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r0[j]);
+            w.put16(buf, sub, n0 + ch * kOutCols, v, bias_tile);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r1[j]);
+            w.put16(buf, sub + 1, n0 + ch * kOutCols, v, bias_tile);
+          }
+          w.end_chunk(buf, n0 + ch * kOutCols);
+        }
+        w.finish();
+        mark(MARK_PARTIAL_WRITTEN, c.tid == 0);
+      }
+    }
+    if (split > 1) {
+      // (A) every k-slice of the tile has finished its MMAs, so every ring in the cluster is free
+      cluster_sync_all();
+      mark(MARK_CLUSTER_SYNC1, c.tid == 0);
+      if (warp < 4) {
+        const int row = quad * 32 + lane;
+        if (acc_ok) {
+          // push: chunk ch belongs to k-slice ch % split; its receive slot for this k-slice's partial
+          // is [ch / split][kslice], laid out [16-column group][quarter][row][4 floats]
+#pragma unroll 1
+          for (int cc = 0; cc < BN / 16; cc += 2) {
+            uint32_t r0[16], r1[16];
+            tmem_ld_32x16(tmem_row + cc * 16, r0);
+            tmem_ld_32x16(tmem_row + (cc + 1) * 16, r1);
+            tmem_ld_wait();
+            const int ch = cc / kSub, owner = ch % split;
+            const uint32_t slot = tiles + (uint32_t)((ch / split) * split + kslice) * kChunkPartial;
+            const uint32_t dst0 = peer_smem(slot + (uint32_t)((((cc % kSub) * 4) * kUmmaBM + row) * 16), (uint32_t)owner);
+            const uint32_t dst1 = dst0 + 4u * kUmmaBM * 16u;
+            const uint32_t bar = peer_smem(recv_bar, (uint32_t)owner);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              st_async_u4(dst0 + (uint32_t)(j * kUmmaBM * 16), bar, r0[4 * j], r0[4 * j + 1], r0[4 * j + 2], r0[4 * j + 3]);
+              st_async_u4(dst1 + (uint32_t)(j * kUmmaBM * 16), bar, r1[4 * j], r1[4 * j + 1], r1[4 * j + 2], r1[4 * j + 3]);
             }
-            store_row(p, out_f32 + (size_t)m * p.N + nb, out_bf16 + (size_t)m * p.N + nb, r, nb);
           }
         }
+        mark(MARK_PARTIAL_WRITTEN, c.tid == 0);
+        // (B) all partials of the chunks this CTA owns have landed
+        const bool got = mbar_wait(recv_bar, 0, c.status, UMMA_WAIT_PEERS_TIMEOUT);
+        mark(MARK_CLUSTER_SYNC2, c.tid == 0);
+        if (got) {
+#pragma unroll 1
+          for (int li = 0; li < max_owned; ++li) {
+            const int ch = li * split + kslice;
+            if (ch >= chunks) break;
+            const uint32_t buf = w.begin_chunk();
+#pragma unroll 1
+            for (int sub = 0; sub < kSub; ++sub) {
+              float acc[16];
+#pragma unroll
+              for (int j = 0; j < 16; ++j) acc[j] = 0.f;
+#pragma unroll 1
+              for (int peer = 0; peer < split; ++peer) {  // k-slice order: the sum is deterministic
+                const uint32_t src = tiles + (uint32_t)(li * split + peer) * kChunkPartial + (uint32_t)(((sub * 4) * kUmmaBM + row) * 16);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float4 v = ld_shared_f4(src + (uint32_t)(j * kUmmaBM * 16));
+                  acc[4 * j] += v.x, acc[4 * j + 1] += v.y, acc[4 * j + 2] += v.z, acc[4 * j + 3] += v.w;
+                }
+              }
+              w.put16(buf, sub, n0 + ch * kOutCols, acc, bias_tile);
+            }
+            w.end_chunk(buf, n0 + ch * kOutCols);
+          }
+          w.finish();
+        }
+        mark(MARK_REDUCED, c.tid == 0);
       }
     }
     tc_fence_before();
@@ -315,7 +508,9 @@ struct GemmUmma {
         mbar_inval(empty0 + 8 * s);
       }
       mbar_inval(acc_bar);
+      mbar_inval(recv_bar);
     }
+    mark(MARK_END, c.tid == 0);
   }
 };
 

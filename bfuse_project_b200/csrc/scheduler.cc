@@ -11,7 +11,7 @@ namespace {
 
 // Rotating region of `ratio[0] + ratio[1]` CTAs repeated `rounds` times, then what is left of
 // each operator as one contiguous tail (Algorithms.cc:570-587 and :661-685).
-void fill_rotate(DispatchTable &t, const int ratio[2], int rounds) {
+void fill_rotate(DispatchTable &t, const int units[2], const int ratio[2], int rounds) {
   t.kind = DISPATCH_ROTATE;
   t.rot = ratio[0] + ratio[1];
   t.ratio[0] = ratio[0];
@@ -21,7 +21,7 @@ void fill_rotate(DispatchTable &t, const int ratio[2], int rounds) {
   for (int k = 0; k < 2; ++k) {
     const int done = ratio[k] * rounds;
     t.tail_lo[k] = at;
-    t.tail_hi[k] = at + (t.n_cta[k] - done);
+    t.tail_hi[k] = at + (units[k] - done);
     t.tail_base[k] = done;
     at = t.tail_hi[k];
   }
@@ -30,7 +30,7 @@ void fill_rotate(DispatchTable &t, const int ratio[2], int rounds) {
 }  // namespace
 
 bool plan_pair(const KernelDims k[2], int pattern, int param_m, int param_n, int total_sm, FusedPlan *out,
-               std::string *err) {
+               std::string *err, int cluster) {
   auto fail = [&](const char *m) {
     if (err) *err = m;
     return false;
@@ -51,14 +51,19 @@ bool plan_pair(const KernelDims k[2], int pattern, int param_m, int param_n, int
     t.bar_count[i] = round_up32(k[i].block());
   }
   out->pattern = pattern;
-  const int g0 = t.n_cta[0], g1 = t.n_cta[1], gmin = std::min(g0, g1);
+  if (cluster < 1 || cluster > 8) return fail("cluster width must be 1..8");
+  t.cluster = cluster;
+  // the patterns schedule units of `cluster` CTAs; with cluster == 1 a unit is a CTA
+  const int units[2] = {(t.n_cta[0] + cluster - 1) / cluster, (t.n_cta[1] + cluster - 1) / cluster};
+  const int g0 = units[0], g1 = units[1], gmin = std::min(g0, g1);
   // block-level fusion: grid = sum, block = max (Algorithms.cc:719-736)
-  out->fused_grid = g0 + g1;
+  out->fused_grid = (g0 + g1) * cluster;
   out->fused_block = std::max(t.n_thr[0], t.n_thr[1]);
   t.total = g0 + g1;
 
   switch (pattern) {
     case PATTERN_WORK_QUEUE:
+      if (cluster != 1) return fail("the work queue cannot host operators launched as clusters");
       t.queue = 1;
       // fallthrough: tickets follow the zig-zag order
     case PATTERN_ZIGZAG: {
@@ -66,12 +71,12 @@ bool plan_pair(const KernelDims k[2], int pattern, int param_m, int param_n, int
       if (param_m < 1 || param_n < 1) return fail("zig-zag needs M >= 1 and N >= 1");
       int ratio[2], rounds = -1;
       for (int i = 0; i < 2; ++i) {
-        const int q = t.n_cta[i] / gmin;
+        const int q = units[i] / gmin;
         ratio[i] = q < param_m ? q * param_n : param_m * param_n;
-        const int r = t.n_cta[i] / ratio[i];
+        const int r = units[i] / ratio[i];
         rounds = rounds < 0 ? r : std::min(rounds, r);
       }
-      fill_rotate(t, ratio, rounds);
+      fill_rotate(t, units, ratio, rounds);
       break;
     }
     case PATTERN_PROPORTIONAL: {
@@ -80,16 +85,16 @@ bool plan_pair(const KernelDims k[2], int pattern, int param_m, int param_n, int
       const int unit = std::max(gmin / param_m, 1);
       int ratio[2], rounds = -1;
       for (int i = 0; i < 2; ++i) {
-        ratio[i] = t.n_cta[i] / unit;
-        const int r = t.n_cta[i] / ratio[i];
+        ratio[i] = units[i] / unit;
+        const int r = units[i] / ratio[i];
         rounds = rounds < 0 ? r : std::min(rounds, r);
       }
-      fill_rotate(t, ratio, rounds);
+      fill_rotate(t, units, ratio, rounds);
       break;
     }
     case PATTERN_RANGE_SPLIT: {
       const int ratio[2] = {1, 1};
-      fill_rotate(t, ratio, 0);  // no rotating region: operator 0 then operator 1
+      fill_rotate(t, units, ratio, 0);  // no rotating region: operator 0 then operator 1
       break;
     }
     case PATTERN_SM_STRIPED: {
@@ -99,17 +104,17 @@ bool plan_pair(const KernelDims k[2], int pattern, int param_m, int param_n, int
       t.kind = DISPATCH_STRIPE;
       t.sm = total_sm;
       t.small = g1 < g0 ? 1 : 0;  // stable: equal grids keep registration order
-      const int fs = t.n_cta[t.small] / total_sm * total_sm;
-      const int fl = t.n_cta[1 - t.small] / total_sm * total_sm;
+      const int fs = units[t.small] / total_sm * total_sm;
+      const int fl = units[1 - t.small] / total_sm * total_sm;
       t.ph0_end = 2 * fs;
       t.ph1_end = fs + fl;
       t.ph1_base = fs;
       int at = t.ph1_end;
       for (int i = 0; i < 2; ++i) {
-        const int rem = t.n_cta[i] % total_sm;
+        const int rem = units[i] % total_sm;
         t.tail_lo[i] = at;
         t.tail_hi[i] = at + rem;
-        t.tail_base[i] = t.n_cta[i] - rem;
+        t.tail_base[i] = units[i] - rem;
         at = t.tail_hi[i];
       }
       break;
@@ -120,6 +125,7 @@ bool plan_pair(const KernelDims k[2], int pattern, int param_m, int param_n, int
       t.kind = DISPATCH_THREADS;
       t.thr_lo[0] = 0;
       t.thr_lo[1] = round_up32(t.n_thr[0]);
+      if (cluster != 1) return fail("thread split cannot host operators launched as clusters");
       out->fused_grid = std::max(g0, g1);
       out->fused_block = round_up32(t.n_thr[0]) + round_up32(t.n_thr[1]);
       if (out->fused_block > 1024) return fail("thread split: the two blocks do not fit one CTA");

@@ -26,7 +26,7 @@ enum Pattern : int {
 
 struct FusedPlan {
   DispatchTable table;
-  int fused_grid;   // GridDim.X of the fused launch (Y = Z = 1)
+  int fused_grid;   // GridDim.X of the fused launch (Y = Z = 1), a multiple of table.cluster
   int fused_block;  // BlockDim.X of the fused launch
   int pattern;
 };
@@ -35,7 +35,8 @@ inline int round_up32(int x) { return (x + 31) / 32 * 32; }
 
 // Returns false and sets err on invalid input.  For PATTERN_WORK_QUEUE the table describes the
 // ticket order (zig-zag param_m : param_n); the caller sizes the persistent grid.
+// cluster > 1 schedules units of `cluster` consecutive CTAs (see decode_cta in dispatch.h).
 bool plan_pair(const KernelDims k[2], int pattern, int param_m, int param_n, int total_sm, FusedPlan *out,
-               std::string *err);
+               std::string *err, int cluster = 1);
 
 }  // namespace bfuse

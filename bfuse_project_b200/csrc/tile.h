@@ -24,7 +24,8 @@ struct TileCtx {
   int bx, by;     // BlockDim.X / .Y for the threadIdx decomposition
   unsigned char *smem;  // this operator's shared-memory window, 1024-byte aligned
   int *status;          // device status word (bounded waits report here)
-  int persistent;       // 1: this CTA runs more tiles after this one (work queue)
+  int persistent;       // 1: more tensor-memory allocations may follow in this CTA (work queue: the next
+                        // tile; thread split: the other operator), so the allocation permit must be kept
 
   __device__ __forceinline__ void sync() const {
     asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(bar_count) : "memory");

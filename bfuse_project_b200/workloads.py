@@ -92,8 +92,8 @@ def rope(name, rng, seq, heads, dim, theta):
     return KernelSpec(name, OP_ROPE_BF16, (seq, heads, dim), [q, rope_inv_freq(dim, theta), np.zeros_like(q)], [2])
 
 
-def gemm(name, rng, op, batch, M, N, K, bias=False, causal=False, w_std=0.02, a=None, bn=0):
-    """out[b, M, N] = A[b, M, K] . W[b, N, K]^T (+ bias)."""
+def gemm(name, rng, op, batch, M, N, K, bias=False, causal=False, w_std=0.02, a=None, bn=0, split=0):
+    """out[b, M, N] = A[b, M, K] . W[b, N, K]^T (+ bias).  bn / split = 0: chosen by the runtime."""
     A = rng.standard_normal((batch, M, K), dtype=np.float32) if a is None else a
     W = (w_std * rng.standard_normal((batch, N, K), dtype=np.float32)).astype(np.float32)
     bvec = rng.standard_normal(N, dtype=np.float32) * 0.1 if bias else None
@@ -103,7 +103,7 @@ def gemm(name, rng, op, batch, M, N, K, bias=False, causal=False, w_std=0.02, a=
         out = np.zeros((batch, M, N), np.uint16)
     else:
         out = np.zeros((batch, M, N), np.float32)
-    shape = (batch, M, N, K, bn) if op in (OP_GEMM_TF32, OP_GEMM_BF16) else (batch, M, N, K)
+    shape = (batch, M, N, K, bn, split) if op in (OP_GEMM_TF32, OP_GEMM_BF16) else (batch, M, N, K)
     return KernelSpec(name, op, shape, [A, W, bvec, out], [3], flags=FLAG_CAUSAL if causal else 0,
                       flops=2.0 * batch * M * N * K)
 
@@ -123,9 +123,10 @@ def pair_names():
             "cfg4b_k_v_proj", "cfg4c_rmsnorm_rope", "cfg5_conv_branches"]
 
 
-def make_pair(name, seed=0, scale=1.0, tensor_cores=True, conv_batch=1):
+def make_pair(name, seed=0, scale=1.0, tensor_cores=True, conv_batch=1, split=0):
     """Build one pair.  scale < 1 shrinks the row / token dimension for quick tests (512 tokens ->
-    512 * scale); tensor_cores=False swaps the tcgen05 GEMM bodies for the CUDA-core fp32 bodies."""
+    512 * scale); tensor_cores=False swaps the tcgen05 GEMM bodies for the CUDA-core fp32 bodies;
+    split = 1 keeps the tcgen05 GEMMs un-split (needed under thread split and the work queue)."""
     rng = np.random.default_rng(seed)
     T = max(64, int(round(512 * scale)) // 64 * 64)  # tokens
     tf32 = OP_GEMM_TF32 if tensor_cores else OP_GEMM_F32_SIMT
@@ -133,11 +134,11 @@ def make_pair(name, seed=0, scale=1.0, tensor_cores=True, conv_batch=1):
         return PairSpec(name, softmax("softmax", rng, 12 * T, 512, 0.125), layernorm("layernorm", rng, T, 768, 1e-5),
                         "f32", "hbm", "BERT-base attention softmax (scale 1/8) || LayerNorm")
     if name == "cfg2_q_k_proj":
-        return PairSpec(name, gemm("q_proj", rng, tf32, 1, T, 768, 768, bias=True),
-                        gemm("k_proj", rng, tf32, 1, T, 768, 768, bias=True), "tf32" if tensor_cores else "f32", "hbm",
+        return PairSpec(name, gemm("q_proj", rng, tf32, 1, T, 768, 768, bias=True, split=split),
+                        gemm("k_proj", rng, tf32, 1, T, 768, 768, bias=True, split=split), "tf32" if tensor_cores else "f32", "hbm",
                         "BERT-base Q projection || K projection")
     if name == "cfg3_qkt_res_layernorm":
-        q = gemm("qkt", rng, tf32, 12, T, T, 64, causal=True, w_std=1.0)
+        q = gemm("qkt", rng, tf32, 12, T, T, 64, causal=True, w_std=1.0, split=split)
         return PairSpec(name, q, layernorm("res_layernorm", rng, T, 768, 1e-5, residual=True),
                         "tf32" if tensor_cores else "f32", "hbm", "GPT-2 QK^T with causal mask || residual + LayerNorm")
     if name in ("cfg4a_gate_up_proj", "cfg4b_k_v_proj"):
@@ -146,8 +147,8 @@ def make_pair(name, seed=0, scale=1.0, tensor_cores=True, conv_batch=1):
         n_out = 14336 if name == "cfg4a_gate_up_proj" else 1024
         a = f32_to_bf16_bits(rng.standard_normal((1, T, 4096), dtype=np.float32))
         na, nb = ("gate_proj", "up_proj") if n_out == 14336 else ("k_proj", "v_proj")
-        return PairSpec(name, gemm(na, rng, OP_GEMM_BF16, 1, T, n_out, 4096, a=a),
-                        gemm(nb, rng, OP_GEMM_BF16, 1, T, n_out, 4096, a=a), "bf16", "tensor",
+        return PairSpec(name, gemm(na, rng, OP_GEMM_BF16, 1, T, n_out, 4096, a=a, split=split),
+                        gemm(nb, rng, OP_GEMM_BF16, 1, T, n_out, 4096, a=a, split=split), "bf16", "tensor",
                         "Llama-3-8B %s || %s (same activations)" % (na, nb))
     if name == "cfg4c_rmsnorm_rope":
         return PairSpec(name, rmsnorm("rmsnorm", rng, T, 4096, 1e-5), rope("rope_q", rng, T, 32, 128, 500000.0),

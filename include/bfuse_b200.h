@@ -43,8 +43,9 @@ enum {
   BFUSE_OP_ROPE_BF16 = 3,     /* args: q, inv_freq, y            shape: seq, heads, dim                     */
   BFUSE_OP_GEMM_F32_SIMT = 4, /* args: A, W, bias|NULL, out      shape: batch, M, N, K                      */
   BFUSE_OP_CONV2D_F32_SIMT = 5, /* args: x, w, y   shape: n, ci, h, w, co, kh, kw, stride, pad             */
-  BFUSE_OP_GEMM_TF32 = 6,     /* as GEMM_F32_SIMT, tcgen05 kind::tf32; shape[4] = BN tile (0: auto)         */
-  BFUSE_OP_GEMM_BF16 = 7,     /* bf16 A, W, out; fp32 accumulate; tcgen05 kind::f16; shape[4] = BN          */
+  BFUSE_OP_GEMM_TF32 = 6,     /* as GEMM_F32_SIMT, tcgen05 kind::tf32; shape[4] = BN tile, shape[5] = k-slices */
+                              /* per tile (a thread-block cluster reduces them); 0 = chosen by the runtime  */
+  BFUSE_OP_GEMM_BF16 = 7,     /* bf16 A, W, out; fp32 accumulate; tcgen05 kind::f16; shape[4], shape[5] same */
   BFUSE_OP_CONV2D_TF32 = 8,   /* as CONV2D_F32_SIMT on tcgen05 kind::tf32 (implicit GEMM)                   */
   BFUSE_OP_COUNT = 9
 };
@@ -141,6 +142,11 @@ int bfuse_graph_launch(bfuse_context *ctx, int graph, void *stream);
  * (the %smid printf of legacy/tests/thread_pooling_test/temp2.cu:7-9, as data).  Arrays hold
  * fused-grid entries; for WORK_QUEUE they are indexed by ticket.  Synchronises. */
 int bfuse_trace_fused(bfuse_context *ctx, int fusion, int *kernel_of, int *vblock_of, int *sm_of, int n);
+/* Diagnostic, no reference counterpart: run a registered tcgen05 GEMM kernel once (unfused) with its
+ * first CTA recording global-timer marks in nanoseconds: start, set-up done, first / last TMA load
+ * issued, first stage full, last MMA issued, accumulator ready, partial tile written, cluster
+ * barrier 1, reduction done, cluster barrier 2, end (12 values; unused marks stay 0). Synchronises. */
+int bfuse_debug_gemm_timeline(bfuse_context *ctx, int kernel, long long *marks, int n);
 /* Read and clear the device status word (0 = no bounded wait gave up). Synchronises. */
 int bfuse_read_status(bfuse_context *ctx, int *status);
 
@@ -151,9 +157,12 @@ int bfuse_run_kernel(bfuse_context *ctx, int kernel, void *const *host_args);   
 int bfuse_run_parallel(bfuse_context *ctx, int fusion, void *const *host_args1, void *const *host_args2); /* run_parallel */
 int bfuse_run_fuse(bfuse_context *ctx, int fusion, void *const *host_args1, void *const *host_args2);     /* run_fuse     */
 
-/* Timing protocol of scripts/profile_test_suite.py:10-11 + analyze_test_suite.py:103-123: `warmup`
- * untimed launches, then `iters` launches timed with CUDA events on the context's stream; mode is
- * the harness' T: 0 kernel1, 1 kernel2, 2 parallel, 3 sequential, 4 fused.  Mean and min in us. */
+/* Timing in the spirit of scripts/profile_test_suite.py:10-11 + analyze_test_suite.py:103-123
+ * (warm-ups, then the mean over 30 launches): `warmup` untimed launches, then a CUDA graph of `iters`
+ * launches is replayed (first until the clocks have ramped, then in 8 timed batches) under CUDA
+ * events on the context's stream; host launch cost is therefore not part of the figure and the
+ * buffers are L2-warm.  mode is the harness' T: 0 kernel1, 1 kernel2, 2 parallel, 3 sequential,
+ * 4 fused.  Mean over all batches and the best batch, in microseconds per launch. */
 int bfuse_time(bfuse_context *ctx, int fusion, int mode, int warmup, int iters, float *mean_us, float *min_us);
 
 /* check_matrix (test-utils/test-suite-files/utils_cc.py:52-86): element i is wrong iff
@@ -182,6 +191,12 @@ int bfuse_softmax_layernorm_queue_noalloc(const float *sm_x, float *sm_y, int sm
 typedef struct bfuse_plan bfuse_plan;
 int bfuse_plan_create(const bfuse_dim3 grid[2], const bfuse_dim3 block[2], int pattern, int param_m, int param_n,
                       bfuse_plan **out);
+/* The same with dispatch units of `cluster` consecutive CTAs: what bfuse_register_fusion uses when
+ * an operator is launched as thread-block clusters (split-K GEMM).  No reference counterpart; with
+ * cluster = 1 it is bfuse_plan_create.  bfuse_plan_map_all marks padding CTAs of a partly filled
+ * cluster with -1. */
+int bfuse_plan_create_clustered(const bfuse_dim3 grid[2], const bfuse_dim3 block[2], int pattern, int param_m,
+                                int param_n, int cluster, bfuse_plan **out);
 void bfuse_plan_destroy(bfuse_plan *plan);
 int bfuse_plan_fused_dims(const bfuse_plan *plan, bfuse_dim3 *grid, bfuse_dim3 *block);
 int bfuse_plan_map_block(const bfuse_plan *plan, int b, int *kernel, int *vblock);

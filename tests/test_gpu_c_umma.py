@@ -19,42 +19,81 @@ def rt():
 
 def test_single_tf32_tile(rt):
     rng = np.random.default_rng(1)
-    a = wl.gemm("g1", rng, bf.OP_GEMM_TF32, 1, 128, 64, 32, w_std=1.0, bn=64)       # one tile, one K block
-    b = wl.gemm("g2", rng, bf.OP_GEMM_TF32, 1, 128, 128, 256, bias=True, w_std=1.0, bn=128)
+    a = wl.gemm("g1", rng, bf.OP_GEMM_TF32, 1, 128, 64, 32, w_std=1.0, bn=64, split=1)       # one tile, one K block
+    b = wl.gemm("g2", rng, bf.OP_GEMM_TF32, 1, 128, 128, 256, bias=True, w_std=1.0, bn=128, split=1)
     run_and_check(rt, wl.PairSpec("tile", a, b, "tf32", "hbm"), [(bf.ZIGZAG, 1, 1)])
 
 
 def test_single_bf16_tile(rt):
     rng = np.random.default_rng(2)
-    a = wl.gemm("g1", rng, bf.OP_GEMM_BF16, 1, 128, 32, 64, w_std=1.0, bn=32)
-    b = wl.gemm("g2", rng, bf.OP_GEMM_BF16, 1, 256, 256, 512, w_std=0.05, bn=256)
+    a = wl.gemm("g1", rng, bf.OP_GEMM_BF16, 1, 128, 32, 64, w_std=1.0, bn=64, split=1)
+    b = wl.gemm("g2", rng, bf.OP_GEMM_BF16, 1, 256, 256, 512, w_std=0.05, bn=256, split=1)
     run_and_check(rt, wl.PairSpec("tile16", a, b, "bf16", "tensor"), [(bf.ZIGZAG, 1, 1)])
 
 
 def test_ragged_umma_shapes(rt):
     rng = np.random.default_rng(3)
     # M, N not multiples of the tile; K not a multiple of the K block; batch > 1; causal with M != N
-    a = wl.gemm("g1", rng, bf.OP_GEMM_TF32, 3, 200, 72, 40, bias=True, w_std=1.0, bn=32)
-    b = wl.gemm("g2", rng, bf.OP_GEMM_TF32, 2, 130, 260, 100, causal=True, w_std=1.0, bn=64)
+    a = wl.gemm("g1", rng, bf.OP_GEMM_TF32, 3, 200, 72, 40, bias=True, w_std=1.0, bn=32, split=1)
+    b = wl.gemm("g2", rng, bf.OP_GEMM_TF32, 2, 130, 260, 100, causal=True, w_std=1.0, bn=64, split=1)
     run_and_check(rt, wl.PairSpec("ragged_tf32", a, b, "tf32", "hbm"), BLOCK_PATTERNS)
-    c = wl.gemm("g3", rng, bf.OP_GEMM_BF16, 2, 100, 136, 72, w_std=0.1, bn=64)
-    d = wl.gemm("g4", rng, bf.OP_GEMM_BF16, 1, 384, 96, 1000, w_std=0.05, bn=32)
+    c = wl.gemm("g3", rng, bf.OP_GEMM_BF16, 2, 100, 136, 72, w_std=0.1, bn=64, split=1)
+    d = wl.gemm("g4", rng, bf.OP_GEMM_BF16, 1, 384, 96, 1000, w_std=0.05, bn=64, split=1)
     run_and_check(rt, wl.PairSpec("ragged_bf16", c, d, "bf16", "tensor"), BLOCK_PATTERNS)
+
+
+@pytest.mark.parametrize("kind", ["tf32", "bf16"])
+def test_split_k_cluster_reduction(rt, kind):
+    """k-slices of a tile reduced over distributed shared memory: every split width, ragged M / N,
+    uneven k-slices, bias and causal mask; unsplit and split results agree within the oracle tolerance
+    and fused == unfused bit for bit."""
+    rng = np.random.default_rng(40)
+    op = bf.OP_GEMM_TF32 if kind == "tf32" else bf.OP_GEMM_BF16
+    bk = 32 if kind == "tf32" else 64
+    std = 1.0 if kind == "tf32" else 0.05
+    cases = {"tf32": ((2, 256, 256, 512, 4), (3, 128, 200, 264, 7), (4, 256, 128, 768, 24), (6, 128, 512, 768, 24),
+                      (8, 256, 256, 520, 24), (8, 64, 130, 72, 19), (5, 32, 128, 32, 5)),
+             "bf16": ((2, 256, 256, 512, 4), (3, 128, 200, 264, 7), (4, 256, 128, 768, 24), (5, 128, 512, 768, 24),
+                      (4, 64, 130, 72, 19), (5, 64, 128, 64, 5))}[kind]
+    for split, bn, M, N, kblocks in cases:
+        K = kblocks * bk - (8 if kind == "tf32" and split == 3 else 0)
+        a = wl.gemm("g1", rng, op, 1, M, N, K, bias=(kind == "tf32"), w_std=std, bn=bn, split=split)
+        b = wl.gemm("g2", rng, op, 2 if split == 2 else 1, M, N, K, causal=(kind == "tf32" and split in (3, 4)),
+                    w_std=std, bn=bn, split=split)
+        run_and_check(rt, wl.PairSpec("split%d" % split, a, b, kind, "hbm"),
+                      [(bf.ZIGZAG, 1, 1), (bf.RANGE_SPLIT, 0, 0), (bf.SM_STRIPED, 0, 0), (bf.PROPORTIONAL, 1, 0)])
+
+
+def test_split_gemm_with_unsplit_partner_and_unsupported_patterns(rt):
+    rng = np.random.default_rng(41)
+    a = wl.gemm("g1", rng, bf.OP_GEMM_TF32, 1, 256, 256, 256, w_std=1.0, bn=256, split=4)
+    b = wl.layernorm("ln", rng, 100, 768, 1e-5, residual=True)   # 25 CTAs: clusters of 4 get padding CTAs
+    pair = run_and_check(rt, wl.PairSpec("split_ln", a, b, "tf32", "hbm"), [(bf.ZIGZAG, 1, 1), (bf.RANGE_SPLIT, 0, 0)])
+    for pat in (bf.THREAD_SPLIT, bf.WORK_QUEUE):
+        with pytest.raises(bf.BfuseError) as e:
+            pair.fusion(pat, 1, 1)
+        assert e.value.code == 7
+    c = wl.gemm("g3", rng, bf.OP_GEMM_TF32, 1, 256, 256, 256, w_std=1.0, bn=256, split=2)
+    mixed = wl.DevicePair(rt, wl.PairSpec("mixed", a, c, "tf32", "hbm"))
+    with pytest.raises(bf.BfuseError) as e:   # different cluster widths cannot share a launch
+        mixed.fusion(bf.ZIGZAG, 1, 1)
+    assert e.value.code == 7
 
 
 def test_pipeline_depths(rt):
     rng = np.random.default_rng(4)
     for smem_stages in (1, 2, 3, 6):
-        a = wl.gemm("g1", rng, bf.OP_GEMM_TF32, 1, 128, 64, 512, w_std=1.0, bn=64)
-        a.smem = 1024 + smem_stages * (16384 + 64 * 128)
-        b = wl.gemm("g2", rng, bf.OP_GEMM_BF16, 1, 128, 128, 1024, w_std=0.05, bn=128)
-        b.smem = 1024 + smem_stages * (16384 + 128 * 128)
+        a = wl.gemm("g1", rng, bf.OP_GEMM_TF32, 1, 128, 64, 512, w_std=1.0, bn=64, split=1)
+        a.smem = 2048 + smem_stages * (16384 + 64 * 128)
+        b = wl.gemm("g2", rng, bf.OP_GEMM_BF16, 1, 128, 128, 1024, w_std=0.05, bn=128, split=1)
+        b.smem = 2048 + smem_stages * (16384 + 128 * 128)
         run_and_check(rt, wl.PairSpec("stages%d" % smem_stages, a, b, "tf32", "hbm"), [(bf.ZIGZAG, 1, 1), (bf.WORK_QUEUE, 1, 1)])
 
 
 @pytest.mark.parametrize("name", ["cfg2_q_k_proj", "cfg3_qkt_res_layernorm", "cfg4b_k_v_proj"])
 def test_tensor_core_pairs_small(rt, name):
     run_and_check(rt, wl.make_pair(name, seed=5, scale=0.25), BLOCK_PATTERNS)
+    run_and_check(rt, wl.make_pair(name, seed=5, scale=0.25, split=1), BLOCK_PATTERNS)
 
 
 @pytest.mark.parametrize("name", ["cfg2_q_k_proj", "cfg3_qkt_res_layernorm", "cfg4b_k_v_proj"])

@@ -98,6 +98,40 @@ def test_runtime_scheduler_equals_oracle_on_random_pairs(pattern, name, kw, args
         assert p.map_block(o.fused_grid) is None
 
 
+@pytest.mark.parametrize("cluster", [2, 4, 6, 8])
+@pytest.mark.parametrize("pattern,args", [(bf.ZIGZAG, (1, 1)), (bf.ZIGZAG, (3, 2)), (bf.PROPORTIONAL, (2, 0)),
+                                          (bf.SM_STRIPED, (5, 0)), (bf.RANGE_SPLIT, (0, 0))])
+def test_cluster_granular_dispatch(pattern, args, cluster):
+    """With dispatch units of `cluster` CTAs the patterns schedule whole hardware clusters: all CTAs of
+    a cluster run one operator on consecutive virtual blocks, every real block runs exactly once,
+    and the unit-level order is exactly the oracle's order for the unit counts."""
+    rng = np.random.default_rng(5)
+    for _ in range(25):
+        ks = [[int(rng.integers(1, 50)), int(rng.integers(1, 6)), 1, 192, 1, 1],
+              [int(rng.integers(1, 90)), 1, int(rng.integers(1, 3)), 256, 1, 1]]
+        p = bf.Plan(ks, pattern, *args, cluster=cluster)
+        kern, vb = p.map_all()
+        g = [k[0] * k[1] * k[2] for k in ks]
+        units = [-(-x // cluster) for x in g]
+        assert p.fused_grid[0] == sum(units) * cluster
+        for i in range(2):
+            assert np.array_equal(np.sort(vb[kern == i]), np.arange(g[i]))
+        name = {bf.ZIGZAG: "zigzag", bf.PROPORTIONAL: "proportional", bf.SM_STRIPED: "sm_striped", bf.RANGE_SPLIT: "range_split"}[pattern]
+        kw = {bf.ZIGZAG: dict(M=args[0], N=args[1]), bf.PROPORTIONAL: dict(min_option=args[0]),
+              bf.SM_STRIPED: dict(total_sm=args[0]), bf.RANGE_SPLIT: {}}[pattern]
+        o = oracle.plan(name, [[units[0], 1, 1, 192, 1, 1], [units[1], 1, 1, 256, 1, 1]], **kw)
+        ok, ovu = oracle.block_table(o)
+        for u in range(sum(units)):
+            ck, cvb = kern[u * cluster:(u + 1) * cluster], vb[u * cluster:(u + 1) * cluster]
+            real = ck >= 0
+            assert real[0] and np.all(ck[real] == ok[u])
+            assert np.array_equal(cvb[real], ovu[u] * cluster + np.arange(cluster)[real])
+    with pytest.raises(bf.BfuseError):
+        bf.Plan(ks, bf.THREAD_SPLIT, cluster=2)
+    with pytest.raises(bf.BfuseError):
+        bf.Plan(ks, bf.WORK_QUEUE, 1, 1, cluster=2)
+
+
 def test_baseline_config1_dims():
     # softmax [6144, 512] (8 rows per CTA) x LayerNorm [512, 768] (4 rows per CTA)
     ks = [[768, 1, 1, 32, 8, 1], [128, 1, 1, 64, 4, 1]]
