@@ -123,7 +123,7 @@ void make_gemm(KernelSetup &k, const char *name, int op, int batch, int M, int N
 }
 void make_conv(KernelSetup &k, const char *name, int n, int ci, int hw, int co, int ksz, int stride, int pad,
                std::mt19937_64 &rng) {
-  base_desc(k, name, BFUSE_OP_CONV2D_F32_SIMT, {n, ci, hw, hw, co, ksz, ksz, stride, pad});
+  base_desc(k, name, BFUSE_OP_CONV2D_TF32, {n, ci, hw, hw, co, ksz, ksz, stride, pad});
   fill(k.host[0], (size_t)n * ci * hw * hw, false, NORMAL, 1.f, rng);
   fill(k.host[1], (size_t)co * ci * ksz * ksz, false, NORMAL, std::sqrt(2.f / (ci * ksz * ksz)), rng);
   const int o = (hw + 2 * pad - ksz) / stride + 1;

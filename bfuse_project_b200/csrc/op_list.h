@@ -9,11 +9,12 @@
 #include "fused_kernels.cuh"
 #include "ops_rowwise.cuh"
 #include "ops_simt.cuh"
+#include "ops_conv_umma.cuh"
 #include "ops_umma.cuh"
 
 namespace bfuse {
 
-constexpr int kNumOps = 8;
+constexpr int kNumOps = 9;
 
 template <int I> struct OpAt;
 template <> struct OpAt<0> { using type = SoftmaxF32; };
@@ -24,6 +25,7 @@ template <> struct OpAt<4> { using type = GemmSimtF32; };
 template <> struct OpAt<5> { using type = ConvSimtF32; };
 template <> struct OpAt<6> { using type = GemmUmma<0>; };
 template <> struct OpAt<7> { using type = GemmUmma<1>; };
+template <> struct OpAt<8> { using type = ConvUmmaTf32; };
 
 struct PairEntry {
   PairLaunchFn block, thread;

@@ -1,0 +1,193 @@
+// NCHW convolution as an implicit GEMM on the tensor cores (tcgen05, kind::tf32), the operator of
+// the reference's conv2d kernels (tests/benchmark/cuda/conv2d*.cu; files/resnet-18.txt:31,36).
+//
+//   y[n, co, pixel] = sum_k  w[co, k] * im2col(x)[n, pixel, k],   k = (ci, kh, kw) as in w[co][ci][kh][kw]
+//
+// A tile is 128 output channels x 128 output pixels of one image.  The weight operand is K-major in
+// global memory and arrives by TMA (128B swizzle).  The im2col operand does not exist in memory:
+// the four epilogue warps, idle during the main loop, gather it (one output pixel per thread, 32
+// values of k per stage) straight into the swizzled K-major layout the MMA expects, then publish the
+// stage with fence.proxy.async + an mbarrier arrive.  Per-k input offsets and tap coordinates are
+// tabulated once per CTA in shared memory, so the gather does no divisions.
+//
+// BlockDim = (192, 1, 1); GridDim = (ceil(oh*ow / 128), ceil(co / 128), n).
+#pragma once
+
+#include "ops_umma.cuh"
+
+namespace bfuse {
+
+constexpr int kConvBN = 128;                 // output pixels per tile
+constexpr int kConvMaxK = 1344;              // ci * kh * kw the offset table can hold
+constexpr int kConvTableBytes = 8 * 1024;    // int offset[K] + uint8 dy[K] + uint8 dx[K]
+constexpr int kConvHeaderBytes = kUmmaHeaderBytes + kConvTableBytes;
+constexpr int kConvStageBytes = kUmmaABytes + kConvBN * kUmmaRowBytes;  // 32 KB
+__host__ __device__ constexpr int conv_umma_smem_bytes(int stages) { return kConvHeaderBytes + stages * kConvStageBytes; }
+
+struct ConvUmmaParams {
+  alignas(64) CUtensorMap map_w;    // {K, co, 1}, box {32 fp32, 128, 1}, 128B swizzle
+  alignas(64) CUtensorMap map_out;  // {oh*ow, co, n}, box {32 fp32, 32, 1}, 128B swizzle (stores)
+  const float *x;
+  int n, ci, h, wd, co, kh, kw, stride, pad, oh, ow;
+  int K;
+  int stages;
+};
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+struct ConvUmmaTf32 {
+  using Params = ConvUmmaParams;
+  static constexpr int kMaxThreads = kUmmaThreads;
+  static constexpr int kMinBlocks = 1;
+  static constexpr bool kMemoryBound = false;
+  static constexpr int kBK = 32;  // K elements (fp32) per stage row of 128 bytes
+
+  __device__ __forceinline__ static void run(const Params &p, const TileCtx &c) {
+    const int warp = c.tid >> 5, lane = c.tid & 31;
+    const int quad = (threadIdx.x >> 5) & 3;
+    const int px0 = c.block_x() * kConvBN, co0 = c.block_y() * kUmmaBM, img = c.block_z();
+    const int stages = p.stages, ohw = p.oh * p.ow, K = p.K;
+    const int num_kb = (K + kBK - 1) / kBK;
+    const uint32_t idesc = umma_idesc(0, kConvBN);
+
+    uint64_t *bars = reinterpret_cast<uint64_t *>(c.smem);
+    const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * kUmmaMaxStages, acc_bar = empty0 + 8 * kUmmaMaxStages;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(c.smem + 8 * (2 * kUmmaMaxStages + 2));
+    int *tab_off = reinterpret_cast<int *>(c.smem + kUmmaHeaderBytes);
+    unsigned char *tab_dy = c.smem + kUmmaHeaderBytes + 4 * kConvMaxK;
+    unsigned char *tab_dx = tab_dy + kConvMaxK;
+    const uint32_t tiles = smem_u32(c.smem) + kConvHeaderBytes;
+    const int nbuf = stages * kConvStageBytes >= 2 * kUmmaStagingBytes ? 2 : 1;
+    ChunkWriter<0> w{&p.map_out, p.co, ohw, 0, tiles + (uint32_t)(quad * nbuf) * 4096u, nbuf, lane, 0, co0 + quad * 32, img, px0};
+
+    if (c.tid == 0) {
+      for (int s = 0; s < stages; ++s) {
+        mbar_init(full0 + 8 * s, 1 + 4);  // the weight copy's arrive.expect_tx + one arrive per gather warp
+        mbar_init(empty0 + 8 * s, 1);
+      }
+      mbar_init(acc_bar, 1);
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 5) {
+      tmem_alloc(smem_u32(tmem_slot), kConvBN);
+      if (!c.persistent) tmem_relinquish();
+    } else if (warp < 4) {
+      // k -> (input offset relative to the pixel's top-left tap, tap row, tap column)
+      const int khw = p.kh * p.kw;
+      for (int k = c.tid; k < K; k += 128) {
+        const int ch = k / khw, r = k % khw, dy = r / p.kw, dx = r % p.kw;
+        tab_off[k] = (ch * p.h + dy) * p.wd + dx;
+        tab_dy[k] = (unsigned char)dy;
+        tab_dx[k] = (unsigned char)dx;
+      }
+    }
+    tc_fence_before();
+    c.sync();
+    tc_fence_after();
+    const uint32_t tmem_acc = *reinterpret_cast<volatile uint32_t *>(tmem_slot);
+    const uint32_t tmem_row = tmem_acc + ((uint32_t)(quad * 32) << 16);
+
+    if (warp == 4) {
+      bool ok = true;
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        const int s = kb % stages;
+        ok = mbar_wait(empty0 + 8 * s, ((kb / stages) & 1) ^ 1, c.status, UMMA_WAIT_EMPTY_TIMEOUT);
+        if (ok && lane == 0) {
+          mbar_expect_tx(full0 + 8 * s, kUmmaABytes);
+          tma_load_3d(tiles + s * kConvStageBytes, &p.map_w, full0 + 8 * s, kb * kBK, co0, 0);
+        }
+        __syncwarp();
+      }
+    } else if (warp == 5) {
+      bool ok = true;
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        const int s = kb % stages;
+        ok = mbar_wait(full0 + 8 * s, (kb / stages) & 1, c.status, UMMA_WAIT_FULL_TIMEOUT);
+        tc_fence_after();
+        if (ok && lane == 0) {
+          const uint64_t a_desc = umma_smem_desc(tiles + s * kConvStageBytes);
+          const uint64_t b_desc = umma_smem_desc(tiles + s * kConvStageBytes + kUmmaABytes);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) umma_ss<0>(tmem_acc, a_desc + 2 * j, b_desc + 2 * j, idesc, (kb | j) != 0);
+          umma_commit(empty0 + 8 * s);
+        }
+        __syncwarp();
+      }
+      if (lane == 0) umma_commit(acc_bar);
+      __syncwarp();
+      for (int kb = max(0, num_kb - stages); kb < num_kb && ok; ++kb)
+        ok = mbar_wait(empty0 + 8 * (kb % stages), (kb / stages) & 1, c.status, UMMA_WAIT_EMPTY_TIMEOUT);
+    } else {
+      // gather warps: thread r fills row r (one output pixel) of every stage's im2col tile
+      const int r = quad * 32 + lane, pix = px0 + r;
+      const bool live = pix < ohw;
+      const int oy = pix / p.ow, ox = pix % p.ow;
+      const int iy0 = oy * p.stride - p.pad, ix0 = ox * p.stride - p.pad;
+      const float *xb = p.x + (size_t)img * p.ci * p.h * p.wd + (ptrdiff_t)iy0 * p.wd + ix0;
+      bool ok = true;
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        const int s = kb % stages;
+        ok = mbar_wait(empty0 + 8 * s, ((kb / stages) & 1) ^ 1, c.status, UMMA_WAIT_EMPTY_TIMEOUT);
+        if (!ok) break;
+        const uint32_t brow = tiles + s * kConvStageBytes + kUmmaABytes + (uint32_t)r * 128u;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {  // 16 values in flight per half
+          float v[16];
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            const int k = kb * kBK + half * 16 + e;
+            float val = 0.f;
+            if (live && k < K) {
+              const int iy = iy0 + tab_dy[k], ix = ix0 + tab_dx[k];
+              if (iy >= 0 && iy < p.h && ix >= 0 && ix < p.wd) val = __ldg(xb + tab_off[k]);
+            }
+            v[e] = val;
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            st_shared_u4(brow + (uint32_t)(((half * 4 + j) ^ (r & 7)) * 16), __float_as_uint(v[4 * j]), __float_as_uint(v[4 * j + 1]),
+                         __float_as_uint(v[4 * j + 2]), __float_as_uint(v[4 * j + 3]));
+        }
+        fence_async_smem();  // this thread's generic-proxy writes -> visible to the tensor core's reads
+        __syncwarp();
+        if (lane == 0) mbar_arrive(full0 + 8 * s);
+      }
+      // epilogue: accumulator rows are output channels, columns are this tile's pixels
+      const bool acc_ok = mbar_wait(acc_bar, 0, c.status, UMMA_WAIT_ACC_TIMEOUT);
+      tc_fence_after();
+      if (acc_ok) {
+#pragma unroll 1
+        for (int ch = 0; ch < kConvBN / 32; ++ch) {
+          const uint32_t buf = w.begin_chunk();
+          uint32_t r0[16], r1[16];
+          tmem_ld_32x16(tmem_row + ch * 32, r0);
+          tmem_ld_32x16(tmem_row + ch * 32 + 16, r1);
+          tmem_ld_wait();
+          float v[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r0[j]);
+          w.put16(buf, 0, px0 + ch * 32, v, nullptr);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r1[j]);
+          w.put16(buf, 1, px0 + ch * 32, v, nullptr);
+          w.end_chunk(buf, px0 + ch * 32);
+        }
+        w.finish();
+      }
+    }
+    tc_fence_before();
+    c.sync();
+    if (warp == 5) tmem_dealloc(tmem_acc, kConvBN);
+    if (c.tid == 0) {
+      for (int s = 0; s < stages; ++s) {
+        mbar_inval(full0 + 8 * s);
+        mbar_inval(empty0 + 8 * s);
+      }
+      mbar_inval(acc_bar);
+    }
+  }
+};
+
+}  // namespace bfuse

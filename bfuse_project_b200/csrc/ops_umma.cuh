@@ -207,13 +207,85 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, uint32_t sr
   asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(map), "r"(src),
                "r"(c0), "r"(c1), "r"(c2)
                : "memory");
-  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int PENDING>
 __device__ __forceinline__ void tma_store_wait_read() {
   asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(PENDING) : "memory");
 }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// The epilogue of one warp: 32 rows x 128-byte chunks go through a 128B-swizzled staging buffer
+// and leave with one TMA store per chunk (full lines, clipped at the M / N edges by the hardware).
+// The epilogue of one warp: 32 rows x 128-byte chunks go through a 128B-swizzled staging buffer and
+// leave with one TMA store per chunk (full lines, clipped at the tensor's edges by the hardware).
+template <int KIND>
+struct ChunkWriter {
+  const CUtensorMap *map_out;
+  int M, N, causal;  // output rows / columns (clipping, mask) of the tensor the map describes
+  uint32_t buf0;   // staging buffers of this warp (nbuf x 4096 bytes)
+  int nbuf, lane, issued;
+  int m_base, bz;  // first output row of this warp's 32 rows, batch index
+  int n_tile0;     // first output column of the tile
+
+  __device__ __forceinline__ uint32_t begin_chunk() {
+    if (issued >= nbuf) {  // the buffer about to be overwritten must have been read by its store
+      if (lane == 0) {
+        if (nbuf == 2) tma_store_wait_read<1>();
+        else tma_store_wait_read<0>();
+      }
+      __syncwarp();
+    }
+    return buf0 + (uint32_t)(issued % nbuf) * 4096u;
+  }
+  // 16 finished fp32 values of this lane's row: columns [nb + sub*16, +16) of the chunk at column nb;
+  // bias_tile: this tile's slice of the bias vector in shared memory (zeros without a bias)
+  __device__ __forceinline__ void put16(uint32_t buf, int sub, int nb, float (&v)[16], const float *bias_tile) {
+    const int col0 = nb + sub * 16, m = m_base + lane;
+    if (bias_tile) {
+      const float4 *b4 = reinterpret_cast<const float4 *>(bias_tile + (col0 - n_tile0));
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float4 b = b4[j];
+        v[4 * j] += b.x, v[4 * j + 1] += b.y, v[4 * j + 2] += b.z, v[4 * j + 3] += b.w;
+      }
+    }
+    if (causal && col0 + 15 > m) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        if (col0 + j > m) v[j] = -FLT_MAX;
+    }
+    const uint32_t row = buf + (uint32_t)lane * 128u;
+    if (KIND == 0) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        st_shared_u4(row + (uint32_t)(((sub * 4 + j) ^ (lane & 7)) * 16), __float_as_uint(v[4 * j]), __float_as_uint(v[4 * j + 1]),
+                     __float_as_uint(v[4 * j + 2]), __float_as_uint(v[4 * j + 3]));
+    } else {
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+        st_shared_u4(row + (uint32_t)(((sub * 2 + j) ^ (lane & 7)) * 16), f2_to_bf16x2(v[8 * j], v[8 * j + 1]),
+                     f2_to_bf16x2(v[8 * j + 2], v[8 * j + 3]), f2_to_bf16x2(v[8 * j + 4], v[8 * j + 5]),
+                     f2_to_bf16x2(v[8 * j + 6], v[8 * j + 7]));
+    }
+  }
+  __device__ __forceinline__ void end_chunk(uint32_t buf, int nb) {
+    fence_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      if (nb < N && m_base < M) tma_store_3d(map_out, buf, nb, m_base, bz);
+      // one group per chunk, even an empty one for a chunk that lies outside the tensor: begin_chunk
+      // counts groups to know when a staging buffer may be overwritten
+      tma_store_commit();
+    }
+    ++issued;
+  }
+  __device__ __forceinline__ void finish() {
+    if (lane == 0) tma_store_wait_read<0>();
+    __syncwarp();
+  }
+};
+
 
 template <int KIND>
 struct GemmUmma {
@@ -225,66 +297,6 @@ struct GemmUmma {
   static constexpr int kBK = kUmmaRowBytes / kElem;  // K elements per stage
   static constexpr int kOutCols = 128 / kElem;       // output columns per 128-byte store chunk
   static constexpr int kSub = kOutCols / 16;         // 16-column accumulator reads per chunk
-
-  // The epilogue of one warp: 32 rows x 128-byte chunks go through a 128B-swizzled staging buffer
-  // and leave with one TMA store per chunk (full lines, clipped at the M / N edges by the hardware).
-  struct ChunkWriter {
-    const Params &p;
-    uint32_t buf0;   // staging buffers of this warp (nbuf x 4096 bytes)
-    int nbuf, lane, issued;
-    int m_base, bz;  // first output row of this warp's 32 rows, batch index
-    int n_tile0;     // first output column of the tile
-
-    __device__ __forceinline__ uint32_t begin_chunk() {
-      if (issued >= nbuf) {  // the buffer about to be overwritten must have been read by its store
-        if (lane == 0) {
-          if (nbuf == 2) tma_store_wait_read<1>();
-          else tma_store_wait_read<0>();
-        }
-        __syncwarp();
-      }
-      return buf0 + (uint32_t)(issued % nbuf) * 4096u;
-    }
-    // 16 finished fp32 values of this lane's row: columns [nb + sub*16, +16) of the chunk at column nb;
-    // bias_tile: this tile's slice of the bias vector in shared memory (zeros without a bias)
-    __device__ __forceinline__ void put16(uint32_t buf, int sub, int nb, float (&v)[16], const float *bias_tile) {
-      const int col0 = nb + sub * 16, m = m_base + lane;
-      const float4 *b4 = reinterpret_cast<const float4 *>(bias_tile + (col0 - n_tile0));
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float4 b = b4[j];
-        v[4 * j] += b.x, v[4 * j + 1] += b.y, v[4 * j + 2] += b.z, v[4 * j + 3] += b.w;
-      }
-      if (p.causal && col0 + 15 > m) {
-#pragma unroll
-        for (int j = 0; j < 16; ++j)
-          if (col0 + j > m) v[j] = -FLT_MAX;
-      }
-      const uint32_t row = buf + (uint32_t)lane * 128u;
-      if (KIND == 0) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          st_shared_u4(row + (uint32_t)(((sub * 4 + j) ^ (lane & 7)) * 16), __float_as_uint(v[4 * j]), __float_as_uint(v[4 * j + 1]),
-                       __float_as_uint(v[4 * j + 2]), __float_as_uint(v[4 * j + 3]));
-      } else {
-#pragma unroll
-        for (int j = 0; j < 2; ++j)
-          st_shared_u4(row + (uint32_t)(((sub * 2 + j) ^ (lane & 7)) * 16), f2_to_bf16x2(v[8 * j], v[8 * j + 1]),
-                       f2_to_bf16x2(v[8 * j + 2], v[8 * j + 3]), f2_to_bf16x2(v[8 * j + 4], v[8 * j + 5]),
-                       f2_to_bf16x2(v[8 * j + 6], v[8 * j + 7]));
-      }
-    }
-    __device__ __forceinline__ void end_chunk(uint32_t buf, int nb) {
-      fence_async_smem();
-      __syncwarp();
-      if (lane == 0 && nb < p.N && m_base < p.M) tma_store_3d(&p.map_out, buf, nb, m_base, bz);
-      ++issued;
-    }
-    __device__ __forceinline__ void finish() {
-      if (lane == 0) tma_store_wait_read<0>();
-      __syncwarp();
-    }
-  };
 
   __device__ __forceinline__ static void run(const Params &p, const TileCtx &c) {
     const int warp = c.tid >> 5, lane = c.tid & 31;
@@ -308,7 +320,7 @@ struct GemmUmma {
     constexpr uint32_t kChunkPartial = (uint32_t)kOutCols * kUmmaBM * 4;    // fp32 partial of one chunk from one k-slice
     const uint32_t staging = tiles + (uint32_t)umma_recv_bytes(BN, split, kElem);
     const int nbuf = (stages * kStageBytes - (int)(staging - tiles)) >= 2 * kUmmaStagingBytes ? 2 : 1;
-    ChunkWriter w{p, staging + (uint32_t)(quad * nbuf) * 4096u, nbuf, lane, 0, m0 + quad * 32, bz, n0};
+    ChunkWriter<KIND> w{&p.map_out, p.M, p.N, p.causal, staging + (uint32_t)(quad * nbuf) * 4096u, nbuf, lane, 0, m0 + quad * 32, bz, n0};
     long long *const tl = (p.timeline && c.vblock == 0) ? p.timeline : nullptr;
     auto mark = [&](int what, bool who) {
       if (tl && who) tl[what] = (long long)global_ns();
@@ -325,9 +337,11 @@ struct GemmUmma {
         for (int j = 0; j < 8; ++j) st_shared_u4(buf + (uint32_t)lane * 128u + j * 16, mask, mask, mask, mask);
         fence_async_smem();
         __syncwarp();
-        if (lane == 0 && w.m_base < p.M)
+        if (lane == 0 && w.m_base < p.M) {
           for (int ch = 0; ch < chunks; ++ch)
             if (n0 + ch * kOutCols < p.N) tma_store_3d(&p.map_out, buf, n0 + ch * kOutCols, w.m_base, bz);
+          tma_store_commit();
+        }
         w.finish();
       }
       return;

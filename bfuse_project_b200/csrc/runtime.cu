@@ -180,6 +180,14 @@ int default_launch(const bfuse_context *ctx, bfuse_kernel_desc *d, std::string *
       set(ceil_div(s[0] * oh * ow, kSimtTile), ceil_div(s[4], kSimtTile), 1, 16, 16, kSimtSmemBytes, 3);
       return BFUSE_OK;
     }
+    case BFUSE_OP_CONV2D_TF32: {
+      if (s[0] <= 0 || s[1] <= 0 || s[4] <= 0 || s[5] <= 0 || s[6] <= 0 || s[7] <= 0) { *err = "conv2d: bad shape"; return BFUSE_ERR_SHAPE; }
+      const int oh = conv_out(s[2], s[5], s[7], s[8]), ow = conv_out(s[3], s[6], s[7], s[8]);
+      if (oh <= 0 || ow <= 0) { *err = "conv2d: empty output"; return BFUSE_ERR_SHAPE; }
+      const int num_kb = ceil_div(s[1] * s[5] * s[6], ConvUmmaTf32::kBK);
+      set(ceil_div(oh * ow, kConvBN), ceil_div(s[4], kUmmaBM), s[0], kUmmaThreads, 1, conv_umma_smem_bytes(std::min(num_kb, 3)), 3);
+      return BFUSE_OK;
+    }
     case BFUSE_OP_GEMM_TF32:
     case BFUSE_OP_GEMM_BF16: {
       if (s[0] <= 0 || s[1] <= 0 || s[2] <= 0 || s[3] <= 0) { *err = "gemm: batch, M, N, K must be positive"; return BFUSE_ERR_SHAPE; }
@@ -249,7 +257,8 @@ int describe_args(const bfuse_kernel_desc &d, ArgInfo *a, std::string *err) {
       a[3] = {n(e * s[0] * s[1] * s[2]), 1, 0};
       return 4;
     }
-    case BFUSE_OP_CONV2D_F32_SIMT: {
+    case BFUSE_OP_CONV2D_F32_SIMT:
+    case BFUSE_OP_CONV2D_TF32: {
       const int oh = conv_out(s[2], s[5], s[7], s[8]), ow = conv_out(s[3], s[6], s[7], s[8]);
       a[0] = {n(4LL * s[0] * s[1] * s[2] * s[3]), 0, 0};
       a[1] = {n(4LL * s[4] * s[1] * s[5] * s[6]), 0, 0};
@@ -348,6 +357,32 @@ int build_params(bfuse_context *ctx, KernelRec &k) {
       if (k.smem < (size_t)kSimtSmemBytes) return shape_err("needs 8704 bytes of shared memory");
       ConvSimtF32::Params p{(const float *)a[0], (const float *)a[1], (float *)a[2], s[0], s[1], s[2], s[3],
                             s[4], s[5], s[6], s[7], s[8], oh, ow};
+      std::memcpy(k.params, &p, sizeof(p));
+      return BFUSE_OK;
+    }
+    case BFUSE_OP_CONV2D_TF32: {
+      if (s[0] <= 0 || s[1] <= 0 || s[4] <= 0 || s[5] <= 0 || s[6] <= 0 || s[7] <= 0 || s[8] < 0) return shape_err("bad conv shape");
+      const int oh = conv_out(s[2], s[5], s[7], s[8]), ow = conv_out(s[3], s[6], s[7], s[8]);
+      if (oh <= 0 || ow <= 0) return shape_err("empty output");
+      const int K = s[1] * s[5] * s[6];
+      if (K > kConvMaxK || K % 4) return shape_err("ci*kh*kw must be a multiple of 4 and at most 1344 (offset table, TMA stride rule)");
+      if ((oh * ow) % 4) return shape_err("oh*ow must be a multiple of 4 (output rows of 16-byte multiples)");
+      if (s[5] > 255 || s[6] > 255) return shape_err("kernel window too large");
+      if (kd.bx != kUmmaThreads || kd.by != 1 || kd.bz != 1) return shape_err("BlockDim must be (192, 1, 1)");
+      if (kd.gx != ceil_div(oh * ow, kConvBN) || kd.gy != ceil_div(s[4], kUmmaBM) || kd.gz != s[0])
+        return shape_err("GridDim must be (ceil(oh*ow/128), ceil(co/128), n)");
+      if (k.smem < (size_t)conv_umma_smem_bytes(1)) return shape_err("shared memory below one pipeline stage");
+      ConvUmmaParams p;
+      std::memset(&p, 0, sizeof(p));
+      int rc = encode_map(ctx, &p.map_w, 4, a[1], K, s[4], 1, kUmmaBM);
+      if (rc) return rc;
+      rc = encode_map(ctx, &p.map_out, 4, a[2], oh * ow, s[4], s[0], 32);
+      if (rc) return rc;
+      p.x = (const float *)a[0];
+      p.n = s[0], p.ci = s[1], p.h = s[2], p.wd = s[3], p.co = s[4], p.kh = s[5], p.kw = s[6], p.stride = s[7], p.pad = s[8];
+      p.oh = oh, p.ow = ow, p.K = K;
+      p.stages = std::min<int>(kUmmaMaxStages, (int)((k.smem - kConvHeaderBytes) / kConvStageBytes));
+      static_assert(sizeof(p) <= kParamsBytes, "parameter block too small");
       std::memcpy(k.params, &p, sizeof(p));
       return BFUSE_OK;
     }

@@ -14,7 +14,7 @@ from typing import List, Optional
 
 import numpy as np
 
-from . import (FLAG_CAUSAL, OP_CONV2D_F32_SIMT, OP_GEMM_BF16, OP_GEMM_F32_SIMT, OP_GEMM_TF32, OP_LAYERNORM_F32,
+from . import (FLAG_CAUSAL, OP_CONV2D_F32_SIMT, OP_CONV2D_TF32, OP_GEMM_BF16, OP_GEMM_F32_SIMT, OP_GEMM_TF32, OP_LAYERNORM_F32,
                OP_RMSNORM_BF16, OP_ROPE_BF16, OP_SOFTMAX_F32)
 
 
@@ -155,9 +155,10 @@ def make_pair(name, seed=0, scale=1.0, tensor_cores=True, conv_batch=1, split=0)
                         "bf16", "hbm", "Llama-3-8B RMSNorm || RoPE on Q")
     if name == "cfg5_conv_branches":
         x = rng.standard_normal((conv_batch, 64, 56, 56), dtype=np.float32)
-        return PairSpec(name, conv2d("conv3x3_s2", rng, OP_CONV2D_F32_SIMT, conv_batch, 64, 56, 56, 128, 3, 2, 1, x=x),
-                        conv2d("conv1x1_s2", rng, OP_CONV2D_F32_SIMT, conv_batch, 64, 56, 56, 128, 1, 2, 0, x=x),
-                        "f32", "hbm", "ResNet-18 3x3 s2 conv || 1x1 s2 downsample (same input)")
+        op = OP_CONV2D_TF32 if tensor_cores else OP_CONV2D_F32_SIMT
+        return PairSpec(name, conv2d("conv3x3_s2", rng, op, conv_batch, 64, 56, 56, 128, 3, 2, 1, x=x),
+                        conv2d("conv1x1_s2", rng, op, conv_batch, 64, 56, 56, 128, 1, 2, 0, x=x),
+                        "tf32" if tensor_cores else "f32", "hbm", "ResNet-18 3x3 s2 conv || 1x1 s2 downsample (same input)")
     raise KeyError(name)
 
 

@@ -96,7 +96,7 @@ def test_simt_gemm_and_conv_pairs(rt):
     run_and_check(rt, wl.make_pair("cfg2_q_k_proj", seed=6, scale=0.25, tensor_cores=False), BLOCK_PATTERNS)
     run_and_check(rt, wl.make_pair("cfg3_qkt_res_layernorm", seed=7, scale=0.25, tensor_cores=False),
                   [(bf.ZIGZAG, 1, 1), (bf.THREAD_SPLIT, 0, 0), (bf.WORK_QUEUE, 2, 1)])
-    run_and_check(rt, wl.make_pair("cfg5_conv_branches", seed=8, conv_batch=2), BLOCK_PATTERNS)
+    run_and_check(rt, wl.make_pair("cfg5_conv_branches", seed=8, conv_batch=2, tensor_cores=False), BLOCK_PATTERNS)
 
 
 def test_simt_gemm_ragged_shapes(rt):

@@ -130,3 +130,34 @@ def test_gate_up_row_sample_full_size(rt):
         r = oracle.bf16_to_f32(ref.reshape(-1)).astype(np.float64)
         rms = np.sqrt(np.mean(r * r))
         assert np.all(np.abs(g - r) <= 5e-3 * (np.abs(r) + rms))
+
+
+def test_conv_tensor_core_pairs(rt):
+    """Implicit-GEMM conv on tcgen05: the ResNet-18 branch pair (N = 1 and 3), both against the
+    oracle and fused == unfused under every pattern."""
+    run_and_check(rt, wl.make_pair("cfg5_conv_branches", seed=9, conv_batch=1), BLOCK_PATTERNS)
+    run_and_check(rt, wl.make_pair("cfg5_conv_branches", seed=10, conv_batch=3), [(bf.ZIGZAG, 1, 1), (bf.WORK_QUEUE, 1, 1)])
+
+
+def test_conv_tensor_core_ragged_shapes(rt):
+    rng = np.random.default_rng(11)
+    # co not a multiple of 128, pixels not a multiple of 128, K = ci*kh*kw not a multiple of the K block
+    a = wl.conv2d("c1", rng, bf.OP_CONV2D_TF32, 2, 12, 20, 20, 200, 3, 1, 1)     # K = 108, 400 pixels, stride 1
+    b = wl.conv2d("c2", rng, bf.OP_CONV2D_TF32, 1, 36, 30, 18, 40, 1, 2, 0)      # 1x1, K = 36, 15 x 9 = 135 ... must be %4
+    b = wl.conv2d("c2", rng, bf.OP_CONV2D_TF32, 1, 36, 31, 16, 40, 1, 2, 0)      # 16 x 8 = 128 pixels exactly
+    run_and_check(rt, wl.PairSpec("ragged_conv", a, b, "tf32", "hbm"), BLOCK_PATTERNS)
+    c = wl.conv2d("c3", rng, bf.OP_CONV2D_TF32, 1, 8, 17, 17, 130, 5, 3, 2)      # 5x5 stride 3 pad 2: 6 x 6 = 36 pixels, K = 200
+    d = wl.gemm("g", rng, bf.OP_GEMM_TF32, 1, 100, 64, 64, w_std=1.0, bn=64, split=1)
+    run_and_check(rt, wl.PairSpec("conv_gemm", c, d, "tf32", "hbm"), BLOCK_PATTERNS)
+
+
+def test_conv_tensor_core_matches_cuda_core_body(rt):
+    tc = wl.make_pair("cfg5_conv_branches", seed=12, conv_batch=2)
+    cc = wl.make_pair("cfg5_conv_branches", seed=12, conv_batch=2, tensor_cores=False)
+    ptc, pcc = wl.DevicePair(rt, tc), wl.DevicePair(rt, cc)
+    rt.launch_fused(ptc.fusion(bf.ZIGZAG, 1, 1))
+    rt.launch_fused(pcc.fusion(bf.ZIGZAG, 1, 1))
+    a, b = ptc.read_outputs(), pcc.read_outputs()
+    for k in range(2):
+        rms = np.sqrt(np.mean(b[k][0].astype(np.float64) ** 2))
+        assert np.abs(a[k][0] - b[k][0]).max() <= 5e-3 * (np.abs(b[k][0]).max() + rms)
