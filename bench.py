@@ -8,9 +8,14 @@ Workload (config.workload): the BERT-base Q-projection || K-projection pair -- t
 [512x768]x[768x768]+bias GEMMs, fp32 in, tf32 tensor cores, fp32 accumulate -- on seeded synthetic
 inputs.  One "step" is one pass over R independent instances of the pair (distinct buffers, like
 the layers of a model) replayed from a CUDA graph; R is chosen so the instances together are
-larger than twice the 126 MB L2, so every launch reads its operands from HBM.  Multi-GPU: replicas
-only (each fused pair runs on one GPU, there is no exchange step); every rank runs the same step on
-its own GPU and the reported time is the max over ranks.
+larger than twice the 126 MB L2, so every launch reads its operands from HBM.  Multi-GPU: each fused
+pair runs on one GPU and there is no exchange step, so the headline pair runs as replicas (every
+rank the same step on its own GPU, max over ranks reported); the partitioned workloads ride along
+in the same line: `pairs` (the other BASELINE pairs, pair i measured on rank i mod N) and
+`conv_n256_sharded` (the ResNet branch pair at batch 256, images split evenly across the ranks, no
+collective, time = max over ranks).  `reference_fuser_output` times the reference fuser's own
+generated kernels (baseline/_ref/*.cubin, batch-1024 fp32 shapes) beside this runtime's pair at
+the same shapes.
 
 One JSON line on stdout (rank 0).  `value` = microseconds per fused pair, inputs resident in HBM;
 `e2e` = the same metric through bfuse_run_fuse with pinned HOST buffers (H2D of every input,
@@ -122,50 +127,112 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
-def other_pairs(rt, torch, bf, wl, pk, quick):
-    """Short measurements of the remaining configs: fused / sequential / parallel microseconds."""
-    out = {}
-    for name in wl.pair_names():
-        if name == WORKLOAD:
-            continue
+def replay_us(rt, torch, graph, launches, reps=5, warm=3):
+    """Microseconds per launch of a CUDA-graph replay, CUDA events on torch's current stream."""
+    s = torch.cuda.current_stream().cuda_stream
+    for _ in range(warm):
+        rt.graph_launch(graph, s)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        rt.graph_launch(graph, s)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / (reps * launches)
+
+
+MODES = (("fused_zigzag", "ZIGZAG", 4), ("fused_range", "RANGE_SPLIT", 4), ("fused_striped", "SM_STRIPED", 4),
+         ("fused_queue", "WORK_QUEUE", 4), ("sequential", "ZIGZAG", 3), ("parallel", "ZIGZAG", 2))
+
+
+def measure_pair(rt, torch, bf, wl, pk, name, device, conv_batch=1, max_reps=24):
+    """Fused (every pattern that can host the pair) / sequential / two-stream microseconds of one
+    BASELINE pair, replayed over enough instances to exceed twice the L2."""
+    spec = wl.make_pair(name, seed=0, conv_batch=conv_batch)
+    reps = max(2, min(max_reps, int(2.2 * L2_BYTES / spec.bytes) + 1))
+    pairs = [wl.DevicePair(rt, spec if s == 0 else wl.make_pair(name, seed=s, conv_batch=conv_batch), device) for s in range(reps)]
+    res = {"instances": reps, "alg_bytes": spec.bytes, "alg_flops": spec.flops, "dtype": spec.dtype,
+           "launch": [list(spec.a.launch[0]) + list(spec.a.launch[1]), list(spec.b.launch[0]) + list(spec.b.launch[1])]}
+    for label, pattern, mode in MODES:
+        pat = getattr(bf, pattern)
+        mn = 1 if pat in (bf.ZIGZAG, bf.WORK_QUEUE) else 0
         try:
-            spec = wl.make_pair(name, seed=0, conv_batch=1)
-            reps = max(2, min(24, int(2.2 * L2_BYTES / spec.bytes) + 1))
-            if quick:
-                reps = min(reps, 4)
-            pairs = [wl.DevicePair(rt, wl.make_pair(name, seed=s, conv_batch=1) if s else spec) for s in range(reps)]
-            res = {"instances": reps, "alg_bytes": spec.bytes, "alg_flops": spec.flops, "dtype": spec.dtype}
-            for label, pattern, mode in (("fused_zigzag", bf.ZIGZAG, bf.MODE_FUSED), ("fused_range", bf.RANGE_SPLIT, bf.MODE_FUSED),
-                                         ("fused_queue", bf.WORK_QUEUE, bf.MODE_FUSED), ("sequential", bf.ZIGZAG, bf.MODE_SEQUENTIAL),
-                                         ("parallel", bf.ZIGZAG, bf.MODE_PARALLEL)):
-                try:
-                    fus = [p.fusion(pattern, 1 if pattern != bf.RANGE_SPLIT else 0, 1 if pattern != bf.RANGE_SPLIT else 0) for p in pairs]
-                except bf.BfuseError as e:
-                    if e.code != 7:
-                        raise
-                    continue   # pattern cannot host clustered (split-K) operators
-                g = rt.graph_create(fus, mode)
-                s = torch.cuda.current_stream().cuda_stream
-                for _ in range(3):
-                    rt.graph_launch(g, s)
+            fus = [p.fusion(pat, mn, mn) for p in pairs]
+        except bf.BfuseError as e:
+            if e.code != 7:
+                raise
+            continue   # the pattern cannot host clustered (split-K) operators
+        res[label + "_us"] = replay_us(rt, torch, rt.graph_create(fus, mode), reps)
+    best = min(v for k, v in res.items() if k.startswith("fused_"))
+    res["best_fused_us"] = best
+    res["speedup_vs_sequential"] = res["sequential_us"] / best
+    res["speedup_vs_parallel_streams"] = res["parallel_us"] / best
+    tensor_peak = pk["bf16_tflops"] * (1e6 if spec.dtype == "bf16" else 0.5e6)   # flop per us; tf32 = half of bf16
+    res["roofline_us"] = max(spec.bytes / (pk["hbm_gbs"] * 1e3), spec.flops / tensor_peak)
+    res["roofline_frac"] = res["roofline_us"] / best
+    del pairs
+    torch.cuda.empty_cache()
+    return res
+
+
+def reference_fuser_output(rt, torch, bf, wl, pk):
+    """The reference fuser's generated bfuse / hfuse kernels compiled for sm_100a, at their own
+    batch-1024 fp32 shapes, beside this runtime's fused pair on the same shapes (fp32 in, tf32 MMA)."""
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    import numpy as np
+    import ref_fuser
+    out = {}
+    stream = torch.cuda.current_stream().cuda_stream
+    for name in ref_fuser.available():
+        try:
+            cfg = ref_fuser.PAIRS[name]
+            sh1, sh2 = ref_fuser.shapes(name)
+            bufs = [torch.randn(*s, device="cuda") * (0.02 if i % 3 == 1 else 1.0) for i, s in enumerate(sh1 + sh2)]
+            ptrs = [b.data_ptr() for b in bufs]
+            res = {"shape": {k: v for k, v in cfg.items() if k != "grids"}}
+            for flavour in ("bfuse", "hfuse"):
+                k = ref_fuser.RefKernel(name, flavour)
+                for _ in range(2):
+                    k.launch(ptrs, stream)
+                torch.cuda.synchronize()
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                n_rep = 5
+                n = 5
                 e0.record()
-                for _ in range(n_rep):
-                    rt.graph_launch(g, s)
+                for _ in range(n):
+                    k.launch(ptrs, stream)
                 e1.record()
                 torch.cuda.synchronize()
-                res[label + "_us"] = e0.elapsed_time(e1) * 1e3 / (n_rep * reps)
-            best = min(v for k, v in res.items() if k.startswith("fused_"))
-            res["speedup_vs_sequential"] = res["sequential_us"] / best
-            t_roof = max(spec.bytes / (pk["hbm_gbs"] * 1e3), spec.flops / (pk["bf16_tflops"] * (1e6 if spec.dtype == "bf16" else 0.5e6)))
-            res["roofline_us"] = t_roof
-            res["roofline_frac"] = t_roof / best
+                res["reference_%s_us" % flavour] = e0.elapsed_time(e1) * 1e3 / n
+            ref_out = [bufs[2].clone(), bufs[5].clone()]
+            # this runtime on the same buffers and shapes
+            if cfg["kind"] == "conv":
+                shapes = [(cfg["n"], cfg["ci"], cfg["h"], cfg["w"], cfg["co"], kk, kk, cfg["stride"], pp) for kk, pp in zip(cfg["k"], cfg["pad"])]
+                descs = [rt.describe("conv%d" % i, bf.OP_CONV2D_TF32, shapes[i], [ptrs[3 * i], ptrs[3 * i + 1], ptrs[3 * i + 2]]) for i in range(2)]
+            else:
+                b = cfg.get("b", 1)
+                descs = [rt.describe("gemm%d" % i, bf.OP_GEMM_TF32, (b, cfg["M"], cfg["N"], cfg["K"], 0, 0),
+                                     [ptrs[3 * i], ptrs[3 * i + 1], None, ptrs[3 * i + 2]]) for i in range(2)]
+            for i in (2, 5):
+                bufs[i].zero_()
+            f = rt.register_fusion(rt.register_kernel(descs[0]), rt.register_kernel(descs[1]), bf.ZIGZAG, 1, 1)
+            rt.launch_fused(f, stream)
+            torch.cuda.synchronize()
+            # same operator, tf32 operands: agree with the reference's fp32 FMA output within 5e-3
+            for got, ref in ((bufs[2], ref_out[0]), (bufs[5], ref_out[1])):
+                rms = float(ref.float().pow(2).mean().sqrt())
+                err = float((got - ref).abs().max())
+                res.setdefault("max_abs_diff_over_rms", []).append(err / max(rms, 1e-30))
+            g = rt.graph_create([f], bf.MODE_FUSED)
+            res["ours_fused_us"] = replay_us(rt, torch, g, 1, reps=5, warm=2)
+            res["speedup_vs_reference_bfuse"] = res["reference_bfuse_us"] / res["ours_fused_us"]
+            res["speedup_vs_reference_hfuse"] = res["reference_hfuse_us"] / res["ours_fused_us"]
             out[name] = res
-            del pairs
+            del bufs, ref_out
             torch.cuda.empty_cache()
-        except Exception as e:  # a pair that cannot run is reported, not hidden
-            out[name] = {"error": str(e)}
+        except Exception as e:
+            out[name] = {"error": str(e)[:300]}
+    if not out:
+        out["unavailable"] = "baseline/_ref/*.cubin not built (needs a reference checkout at build time)"
     return out
 
 
@@ -240,7 +307,12 @@ def main():
             ms = float(t.item())
         return ms
 
-    # pick the fused pattern on a short trial, then time exactly K steps of it under the clock sampler
+    # spin ~100 ms first so the clocks have left their idle state, pick the fused pattern on a short
+    # trial, then time exactly K steps of it under the clock sampler
+    t_spin = time.perf_counter()
+    while time.perf_counter() - t_spin < 0.1:
+        rt.graph_launch(graphs["sequential"], stream)
+        torch.cuda.synchronize()
     trial = {k: timed(g, 3, 3) for k, g in graphs.items()}
     best = min((k for k in trial if k.startswith("fused_")), key=lambda k: trial[k])
     sampler = ClockSampler(local)
@@ -293,6 +365,35 @@ def main():
     h2d = sum(a.nbytes for ks in (spec0.a, spec0.b) for i, a in enumerate(ks.host) if a is not None and i not in ks.outputs)
     d2h = sum(ks.host[i].nbytes for ks in (spec0.a, spec0.b) for i in ks.outputs)
 
+    # ---- partitioned side workloads (no collective on the data path) --------------------------------
+    side_pairs, conv256 = {}, None
+    if not args.quick:
+        names = [n for n in wl.pair_names() if n != WORKLOAD]
+        for i, name in enumerate(names):               # pair sweep: pair i on rank i mod N
+            if i % world == rank:
+                try:
+                    side_pairs[name] = measure_pair(rt, torch, bf, wl, pk, name, local)
+                    side_pairs[name]["rank"] = rank
+                except Exception as e:                  # a pair that cannot run is reported, not hidden
+                    side_pairs[name] = {"error": str(e)[:300], "rank": rank}
+        # ResNet branch pair at batch 256, images split across the ranks
+        per_rank = 256 // world
+        try:
+            r = measure_pair(rt, torch, bf, wl, pk, "cfg5_conv_branches", local, conv_batch=per_rank, max_reps=2)
+            t = torch.tensor([r["best_fused_us"], r["sequential_us"]], device="cuda")
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            conv256 = {"images_total": 256, "images_per_rank": per_rank, "fused_us": float(t[0]), "sequential_us": float(t[1]),
+                       "speedup_vs_sequential": float(t[1] / t[0]), "alg_bytes_total": r["alg_bytes"] * world,
+                       "roofline_us": r["alg_bytes"] / (pk["hbm_gbs"] * 1e3), "images_per_s": 256 / (float(t[0]) * 1e-6)}
+            conv256["roofline_frac"] = conv256["roofline_us"] / conv256["fused_us"]
+        except Exception as e:
+            conv256 = {"error": str(e)[:300]}
+        if world > 1:
+            gathered = [None] * world
+            dist.all_gather_object(gathered, side_pairs)
+            side_pairs = {k: v for d in gathered for k, v in d.items()}
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -326,7 +427,9 @@ def main():
         "clocks": clocks,
     }
     if not args.quick:
-        line["pairs"] = other_pairs(rt, torch, bf, wl, pk, False)
+        line["pairs"] = side_pairs
+        line["conv_n256_sharded"] = conv256
+        line["reference_fuser_output"] = reference_fuser_output(rt, torch, bf, wl, pk)
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
