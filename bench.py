@@ -368,16 +368,17 @@ def main():
     # ---- partitioned side workloads (no collective on the data path) --------------------------------
     side_pairs, conv256 = {}, None
     if not args.quick:
+        from bfuse_project_b200 import partition
         names = [n for n in wl.pair_names() if n != WORKLOAD]
-        for i, name in enumerate(names):               # pair sweep: pair i on rank i mod N
-            if i % world == rank:
+        for name in partition.assign_pairs(names, world, rank):   # pair sweep: pair i on rank i mod N
+            if True:
                 try:
                     side_pairs[name] = measure_pair(rt, torch, bf, wl, pk, name, local)
                     side_pairs[name]["rank"] = rank
                 except Exception as e:                  # a pair that cannot run is reported, not hidden
                     side_pairs[name] = {"error": str(e)[:300], "rank": rank}
         # ResNet branch pair at batch 256, images split across the ranks
-        per_rank = 256 // world
+        per_rank = partition.shard_batch(256, world, rank)[1]
         try:
             r = measure_pair(rt, torch, bf, wl, pk, "cfg5_conv_branches", local, conv_batch=per_rank, max_reps=2)
             t = torch.tensor([r["best_fused_us"], r["sequential_us"]], device="cuda")
@@ -392,7 +393,7 @@ def main():
         if world > 1:
             gathered = [None] * world
             dist.all_gather_object(gathered, side_pairs)
-            side_pairs = {k: v for d in gathered for k, v in d.items()}
+            side_pairs = partition.merge_results(gathered)
 
     if rank != 0:
         if world > 1:
