@@ -84,6 +84,7 @@ class ClockSampler:
 def cpu_pair_time(spec, budget_s=8.0):
     """Time the oracle's plain loops (OpenMP) on one instance of the pair; microseconds per pair."""
     import oracle
+    oracle.set_num_threads(len(os.sched_getaffinity(0)))   # all host cores, whatever OMP_NUM_THREADS a launcher exported
     oracle_outputs = _load_pair_oracle().oracle_outputs
     oracle_outputs(spec.a), oracle_outputs(spec.b)  # warm-up
     best, n, t_end = None, 0, time.perf_counter() + budget_s

@@ -6,9 +6,11 @@
 // A tile is 128 output channels x 128 output pixels of one image.  The weight operand is K-major in
 // global memory and arrives by TMA (128B swizzle).  The im2col operand does not exist in memory:
 // the four epilogue warps, idle during the main loop, gather it (one output pixel per thread, 32
-// values of k per stage) straight into the swizzled K-major layout the MMA expects, then publish the
-// stage with fence.proxy.async + an mbarrier arrive.  Per-k input offsets and tap coordinates are
-// tabulated once per CTA in shared memory, so the gather does no divisions.
+// values of k per stage) with 4-byte cp.async copies straight into the swizzled K-major layout the
+// MMA expects (out-of-image taps are zero-filled by the copy itself), and each thread's
+// cp.async.mbarrier.arrive makes the stage's "full" barrier fire when its copies have landed, so
+// the gather runs several stages ahead of the tensor core.  Per-k input offsets and tap coordinates
+// are tabulated once per CTA in shared memory, so the gather does no divisions.
 //
 // BlockDim = (192, 1, 1); GridDim = (ceil(oh*ow / 128), ceil(co / 128), n).
 #pragma once
@@ -18,8 +20,8 @@
 namespace bfuse {
 
 constexpr int kConvBN = 128;                 // output pixels per tile
-constexpr int kConvMaxK = 1344;              // ci * kh * kw the offset table can hold
-constexpr int kConvTableBytes = 8 * 1024;    // int offset[K] + uint8 dy[K] + uint8 dx[K]
+constexpr int kConvMaxK = 1024;              // ci * kh * kw the offset table can hold
+constexpr int kConvTableBytes = 8 * 1024;    // int2 {input offset, tap index dy*kw+dx} per k (tap 31 = padding of K)
 constexpr int kConvHeaderBytes = kUmmaHeaderBytes + kConvTableBytes;
 constexpr int kConvStageBytes = kUmmaABytes + kConvBN * kUmmaRowBytes;  // 32 KB
 __host__ __device__ constexpr int conv_umma_smem_bytes(int stages) { return kConvHeaderBytes + stages * kConvStageBytes; }
@@ -31,10 +33,18 @@ struct ConvUmmaParams {
   int n, ci, h, wd, co, kh, kw, stride, pad, oh, ow;
   int K;
   int stages;
+  long long *timeline;  // diagnostic: when non-null, CTA 0 records globaltimer marks (UmmaMark indices)
 };
 
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+// 4-byte asynchronous copy global -> shared; src_bytes = 0 writes zeros instead
+__device__ __forceinline__ void cp_async_4(uint32_t dst, const float *src, uint32_t src_bytes) {
+  // no "memory" clobber on purpose: nothing reads the destination through C++ pointers, and the
+  // clobber would serialise the table look-ups of neighbouring elements behind every copy
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(src_bytes));
+}
+// arrive on `bar` once all cp.async copies issued so far by this thread have completed
+__device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
 
 struct ConvUmmaTf32 {
@@ -55,16 +65,19 @@ struct ConvUmmaTf32 {
     uint64_t *bars = reinterpret_cast<uint64_t *>(c.smem);
     const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * kUmmaMaxStages, acc_bar = empty0 + 8 * kUmmaMaxStages;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(c.smem + 8 * (2 * kUmmaMaxStages + 2));
-    int *tab_off = reinterpret_cast<int *>(c.smem + kUmmaHeaderBytes);
-    unsigned char *tab_dy = c.smem + kUmmaHeaderBytes + 4 * kConvMaxK;
-    unsigned char *tab_dx = tab_dy + kConvMaxK;
+    int2 *tab = reinterpret_cast<int2 *>(c.smem + kUmmaHeaderBytes);
     const uint32_t tiles = smem_u32(c.smem) + kConvHeaderBytes;
     const int nbuf = stages * kConvStageBytes >= 2 * kUmmaStagingBytes ? 2 : 1;
     ChunkWriter<0> w{&p.map_out, p.co, ohw, 0, tiles + (uint32_t)(quad * nbuf) * 4096u, nbuf, lane, 0, co0 + quad * 32, img, px0};
 
+    long long *const tl = (p.timeline && c.vblock == 0) ? p.timeline : nullptr;
+    auto mark = [&](int what, bool who) {
+      if (tl && who) tl[what] = (long long)global_ns();
+    };
+    mark(MARK_START, c.tid == 0);
     if (c.tid == 0) {
       for (int s = 0; s < stages; ++s) {
-        mbar_init(full0 + 8 * s, 1 + 4);  // the weight copy's arrive.expect_tx + one arrive per gather warp
+        mbar_init(full0 + 8 * s, 1 + 128);  // the weight copy's arrive.expect_tx + one arrive per gather thread
         mbar_init(empty0 + 8 * s, 1);
       }
       mbar_init(acc_bar, 1);
@@ -76,11 +89,9 @@ struct ConvUmmaTf32 {
     } else if (warp < 4) {
       // k -> (input offset relative to the pixel's top-left tap, tap row, tap column)
       const int khw = p.kh * p.kw;
-      for (int k = c.tid; k < K; k += 128) {
+      for (int k = c.tid; k < num_kb * kBK; k += 128) {
         const int ch = k / khw, r = k % khw, dy = r / p.kw, dx = r % p.kw;
-        tab_off[k] = (ch * p.h + dy) * p.wd + dx;
-        tab_dy[k] = (unsigned char)dy;
-        tab_dx[k] = (unsigned char)dx;
+        tab[k] = k < K ? make_int2((ch * p.h + dy) * p.wd + dx, r) : make_int2(0, 31);
       }
     }
     tc_fence_before();
@@ -88,6 +99,7 @@ struct ConvUmmaTf32 {
     tc_fence_after();
     const uint32_t tmem_acc = *reinterpret_cast<volatile uint32_t *>(tmem_slot);
     const uint32_t tmem_row = tmem_acc + ((uint32_t)(quad * 32) << 16);
+    mark(MARK_SETUP_DONE, c.tid == 0);
 
     if (warp == 4) {
       bool ok = true;
@@ -105,7 +117,9 @@ struct ConvUmmaTf32 {
       for (int kb = 0; kb < num_kb && ok; ++kb) {
         const int s = kb % stages;
         ok = mbar_wait(full0 + 8 * s, (kb / stages) & 1, c.status, UMMA_WAIT_FULL_TIMEOUT);
+        fence_async_smem();  // the gathered operand was written through the generic proxy
         tc_fence_after();
+        if (kb == 0) mark(MARK_FIRST_FULL, lane == 0);
         if (ok && lane == 0) {
           const uint64_t a_desc = umma_smem_desc(tiles + s * kConvStageBytes);
           const uint64_t b_desc = umma_smem_desc(tiles + s * kConvStageBytes + kUmmaABytes);
@@ -116,6 +130,7 @@ struct ConvUmmaTf32 {
         __syncwarp();
       }
       if (lane == 0) umma_commit(acc_bar);
+      mark(MARK_LAST_MMA_ISSUED, lane == 0);
       __syncwarp();
       for (int kb = max(0, num_kb - stages); kb < num_kb && ok; ++kb)
         ok = mbar_wait(empty0 + 8 * (kb % stages), (kb / stages) & 1, c.status, UMMA_WAIT_EMPTY_TIMEOUT);
@@ -126,6 +141,12 @@ struct ConvUmmaTf32 {
       const int oy = pix / p.ow, ox = pix % p.ow;
       const int iy0 = oy * p.stride - p.pad, ix0 = ox * p.stride - p.pad;
       const float *xb = p.x + (size_t)img * p.ci * p.h * p.wd + (ptrdiff_t)iy0 * p.wd + ix0;
+      // which taps of the window fall inside the image for this pixel (bit dy*kw+dx; none for a dead row)
+      uint32_t tapmask = 0;
+      if (live)
+        for (int dy = 0; dy < p.kh; ++dy)
+          for (int dx = 0; dx < p.kw; ++dx)
+            if (iy0 + dy >= 0 && iy0 + dy < p.h && ix0 + dx >= 0 && ix0 + dx < p.wd) tapmask |= 1u << (dy * p.kw + dx);
       bool ok = true;
       for (int kb = 0; kb < num_kb && ok; ++kb) {
         const int s = kb % stages;
@@ -133,30 +154,29 @@ struct ConvUmmaTf32 {
         if (!ok) break;
         const uint32_t brow = tiles + s * kConvStageBytes + kUmmaABytes + (uint32_t)r * 128u;
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {  // 16 values in flight per half
-          float v[16];
+        for (int e0 = 0; e0 < kBK; e0 += 8) {
+          // look the 8 taps up first (the shared-memory reads overlap), then issue the 8 copies
+          const float *src[8];
+          uint32_t bytes[8];
 #pragma unroll
-          for (int e = 0; e < 16; ++e) {
-            const int k = kb * kBK + half * 16 + e;
-            float val = 0.f;
-            if (live && k < K) {
-              const int iy = iy0 + tab_dy[k], ix = ix0 + tab_dx[k];
-              if (iy >= 0 && iy < p.h && ix >= 0 && ix < p.wd) val = __ldg(xb + tab_off[k]);
-            }
-            v[e] = val;
+          for (int i = 0; i < 8; ++i) {
+            const int2 t = tab[kb * kBK + e0 + i];
+            const bool in = (tapmask >> t.y) & 1u;
+            src[i] = in ? xb + t.x : p.x;
+            bytes[i] = in ? 4u : 0u;
           }
 #pragma unroll
-          for (int j = 0; j < 4; ++j)
-            st_shared_u4(brow + (uint32_t)(((half * 4 + j) ^ (r & 7)) * 16), __float_as_uint(v[4 * j]), __float_as_uint(v[4 * j + 1]),
-                         __float_as_uint(v[4 * j + 2]), __float_as_uint(v[4 * j + 3]));
+          for (int i = 0; i < 8; ++i)
+            cp_async_4(brow + (uint32_t)(((((e0 + i) >> 2) ^ (r & 7)) << 4) + (((e0 + i) & 3) << 2)), src[i], bytes[i]);
         }
-        fence_async_smem();  // this thread's generic-proxy writes -> visible to the tensor core's reads
-        __syncwarp();
-        if (lane == 0) mbar_arrive(full0 + 8 * s);
+        cp_async_arrive(full0 + 8 * s);
+        if (kb == 0) mark(MARK_FIRST_LOAD_ISSUED, c.tid == 0);
+        if (kb == num_kb - 1) mark(MARK_LAST_LOAD_ISSUED, c.tid == 0);
       }
       // epilogue: accumulator rows are output channels, columns are this tile's pixels
       const bool acc_ok = mbar_wait(acc_bar, 0, c.status, UMMA_WAIT_ACC_TIMEOUT);
       tc_fence_after();
+      mark(MARK_ACC_READY, c.tid == 0);
       if (acc_ok) {
 #pragma unroll 1
         for (int ch = 0; ch < kConvBN / 32; ++ch) {
@@ -187,6 +207,7 @@ struct ConvUmmaTf32 {
       }
       mbar_inval(acc_bar);
     }
+    mark(MARK_END, c.tid == 0);
   }
 };
 

@@ -26,7 +26,7 @@ struct SoftmaxF32 {
     float scale;
   };
   static constexpr int kMaxThreads = 256;
-  static constexpr int kMinBlocks = 6;   // 6 x 256 threads per SM: registers per thread <= 40
+  static constexpr int kMinBlocks = 6;   // 6 x 256 threads per SM: registers per thread <= 40 (32 made the fused kernels spill and ran slower)
   static constexpr bool kMemoryBound = true;
 
   __device__ __forceinline__ static void run(const Params &p, const TileCtx &c) {
@@ -82,7 +82,7 @@ struct LayerNormF32 {
     float eps;
   };
   static constexpr int kMaxThreads = 256;
-  static constexpr int kMinBlocks = 6;   // 6 x 256 threads per SM: registers per thread <= 40
+  static constexpr int kMinBlocks = 6;   // 6 x 256 threads per SM: registers per thread <= 40 (32 made the fused kernels spill and ran slower)
   static constexpr bool kMemoryBound = true;
 
   __device__ __forceinline__ static void run(const Params &p, const TileCtx &c) {
@@ -151,7 +151,7 @@ struct RmsNormBf16 {
     float eps;
   };
   static constexpr int kMaxThreads = 256;
-  static constexpr int kMinBlocks = 6;   // 6 x 256 threads per SM: registers per thread <= 40
+  static constexpr int kMinBlocks = 6;   // 6 x 256 threads per SM: registers per thread <= 40 (32 made the fused kernels spill and ran slower)
   static constexpr bool kMemoryBound = true;
   static constexpr int kMaxVec = 4;  // 8 bf16 per vector
 
@@ -207,7 +207,7 @@ struct RopeBf16 {
     int seq, heads, dim;
   };
   static constexpr int kMaxThreads = 256;
-  static constexpr int kMinBlocks = 6;   // 6 x 256 threads per SM: registers per thread <= 40
+  static constexpr int kMinBlocks = 6;   // 6 x 256 threads per SM: registers per thread <= 40 (32 made the fused kernels spill and ran slower)
   static constexpr bool kMemoryBound = true;
 
   __device__ __forceinline__ static void run(const Params &p, const TileCtx &c) {

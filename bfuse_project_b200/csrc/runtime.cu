@@ -365,9 +365,9 @@ int build_params(bfuse_context *ctx, KernelRec &k) {
       const int oh = conv_out(s[2], s[5], s[7], s[8]), ow = conv_out(s[3], s[6], s[7], s[8]);
       if (oh <= 0 || ow <= 0) return shape_err("empty output");
       const int K = s[1] * s[5] * s[6];
-      if (K > kConvMaxK || K % 4) return shape_err("ci*kh*kw must be a multiple of 4 and at most 1344 (offset table, TMA stride rule)");
+      if (K > kConvMaxK || K % 4) return shape_err("ci*kh*kw must be a multiple of 4 and at most 1024 (offset table, TMA stride rule)");
       if ((oh * ow) % 4) return shape_err("oh*ow must be a multiple of 4 (output rows of 16-byte multiples)");
-      if (s[5] > 255 || s[6] > 255) return shape_err("kernel window too large");
+      if (s[5] * s[6] > 31) return shape_err("kernel window larger than 31 taps");
       if (kd.bx != kUmmaThreads || kd.by != 1 || kd.bz != 1) return shape_err("BlockDim must be (192, 1, 1)");
       if (kd.gx != ceil_div(oh * ow, kConvBN) || kd.gy != ceil_div(s[4], kUmmaBM) || kd.gz != s[0])
         return shape_err("GridDim must be (ceil(oh*ow/128), ceil(co/128), n)");
@@ -857,17 +857,19 @@ int bfuse_trace_fused(bfuse_context *ctx, int fusion, int *kernel_of, int *vbloc
 int bfuse_debug_gemm_timeline(bfuse_context *ctx, int kernel, long long *marks, int n) {
   KernelRec *k = get_kernel(ctx, kernel);
   if (!k || !marks || n < MARK_COUNT) return fail(ctx, BFUSE_ERR_INVALID, "bad kernel handle or buffer shorter than 12 marks");
-  if (k->desc.op != BFUSE_OP_GEMM_TF32 && k->desc.op != BFUSE_OP_GEMM_BF16)
-    return fail(ctx, BFUSE_ERR_UNSUPPORTED, "only the tcgen05 GEMM bodies record a timeline");
+  const bool is_conv = k->desc.op == BFUSE_OP_CONV2D_TF32;
+  if (k->desc.op != BFUSE_OP_GEMM_TF32 && k->desc.op != BFUSE_OP_GEMM_BF16 && !is_conv)
+    return fail(ctx, BFUSE_ERR_UNSUPPORTED, "only the tcgen05 GEMM / conv bodies record a timeline");
   cudaSetDevice(ctx->device);
   long long *d = nullptr;
   CK(cudaMalloc(&d, sizeof(long long) * MARK_COUNT));
   cudaMemset(d, 0, sizeof(long long) * MARK_COUNT);
-  GemmUmmaParams *p = reinterpret_cast<GemmUmmaParams *>(k->params);
+  long long **slot = is_conv ? &reinterpret_cast<ConvUmmaParams *>(k->params)->timeline
+                             : &reinterpret_cast<GemmUmmaParams *>(k->params)->timeline;
   int rc = launch_one(ctx, *k, ctx->own);  // warm run
-  p->timeline = d;
+  *slot = d;
   if (!rc) rc = launch_one(ctx, *k, ctx->own);
-  p->timeline = nullptr;
+  *slot = nullptr;
   cudaError_t e = cudaStreamSynchronize(ctx->own);
   if (!rc && e == cudaSuccess) e = cudaMemcpy(marks, d, sizeof(long long) * MARK_COUNT, cudaMemcpyDeviceToHost);
   cudaFree(d);

@@ -68,6 +68,7 @@ def lib():
         L.orc_gemm_nt_bf16.argtypes = [vp, vp, vp] + [C.c_int] * 4
         L.orc_conv2d_nchw_f32.argtypes = [vp, vp, vp] + [C.c_int] * 10
         L.orc_num_threads.restype = C.c_int
+        L.orc_set_num_threads.argtypes = [C.c_int]
         _lib = L
     return _lib
 
@@ -220,3 +221,7 @@ def conv2d_nchw(x, w, stride, pad, tf32=False):
 
 def num_threads():
     return lib().orc_num_threads()
+
+
+def set_num_threads(n):
+    lib().orc_set_num_threads(int(n))

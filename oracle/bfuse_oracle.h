@@ -117,6 +117,8 @@ void orc_conv2d_nchw_f32(const float *x, const float *w, float *y, int n, int ci
 
 /* number of OpenMP threads the loops above use */
 int orc_num_threads(void);
+/* override OMP_NUM_THREADS (launchers such as torchrun export OMP_NUM_THREADS=1) */
+void orc_set_num_threads(int n);
 uint16_t orc_f32_to_bf16(float f);
 float orc_bf16_to_f32(uint16_t h);
 

@@ -26,6 +26,14 @@ int orc_num_threads(void) {
 #endif
 }
 
+void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 float orc_bf16_to_f32(uint16_t h) {
   uint32_t u = (uint32_t)h << 16;
   float f;
