@@ -6,8 +6,8 @@
 //
 // BlockDim = (192, 1, 1): warps 0-3 read the accumulator (one TMEM lane quadrant each), warp 4 is
 // the TMA producer, warp 5 allocates tensor memory and issues the MMAs.  One 128 x BN output tile
-// belongs to `split` CTAs that each multiply a slice of K: GridDim = (split * ceil(N/BN),
-// ceil(M/128), batch).  A tcgen05.mma of 128 x N x 32 bytes takes about the same time for N = 32
+// belongs to `split` CTAs that each multiply a slice of K: GridDim = (split * ceil(M/128),
+// ceil(N/BN), batch).  A tcgen05.mma of 128 x N x 32 bytes takes about the same time for N = 32
 // as for N = 256, so narrow problems are fast only with wide tiles whose K loop is spread over
 // several SMs.  With split > 1 the CTAs of a tile form a thread-block cluster and every CTA owns a
 // share of the tile's 128-byte column chunks: after one cluster barrier (all MMAs of the tile are
@@ -304,7 +304,9 @@ struct GemmUmma {
     const int BN = p.bn, kStageBytes = umma_stage_bytes(BN);
     const uint32_t idesc = umma_idesc(KIND, BN);
     const int split = p.split, kslice = c.block_x() % split;
-    const int n0 = (c.block_x() / split) * BN, m0 = c.block_y() * kUmmaBM, bz = c.block_z();
+    // M tiles vary fastest: the (usually few) CTAs that share a W tile are launched next to each
+    // other, so the tile is fetched from HBM once and the others hit L2
+    const int m0 = (c.block_x() / split) * kUmmaBM, n0 = c.block_y() * BN, bz = c.block_z();
     const int stages = p.stages;
     const int chunks = BN / kOutCols;
 
@@ -369,9 +371,10 @@ struct GemmUmma {
     if (warp == 5) {
       tmem_alloc(smem_u32(tmem_slot), BN);
       if (!c.persistent) tmem_relinquish();
-    } else if (warp < 4) {
-      // the epilogue warps are idle during the main loop: they fetch the tile's bias slice now
-      for (int i = c.tid; i < BN; i += 128) bias_tile[i] = (p.bias && n0 + i < p.N) ? __ldg(p.bias + n0 + i) : 0.f;
+    } else if (warp == 4 && lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&p.map_a) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&p.map_b) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&p.map_out) : "memory");
     }
     tc_fence_before();
     c.sync();
@@ -426,6 +429,10 @@ struct GemmUmma {
       for (int kb = max(0, num_kb - stages); kb < num_kb && ok; ++kb)
         ok = mbar_wait(empty0 + 8 * (kb % stages), (kb / stages) & 1, c.status, UMMA_WAIT_EMPTY_TIMEOUT);
     } else {
+      // the epilogue warps are idle during the main loop: they fetch the tile's bias slice meanwhile
+      // (only they read it, after their own named-barrier-free hand-off below)
+      for (int i = c.tid; i < BN; i += 128) bias_tile[i] = (p.bias && n0 + i < p.N) ? __ldg(p.bias + n0 + i) : 0.f;
+      asm volatile("bar.sync %0, 128;" ::"r"(c.bar_id + 8) : "memory");  // the four epilogue warps only (ids 9 / 10)
       acc_ok = mbar_wait(acc_bar, 0, c.status, UMMA_WAIT_ACC_TIMEOUT);
       tc_fence_after();
       mark(MARK_ACC_READY, c.tid == 0);

@@ -211,7 +211,7 @@ int default_launch(const bfuse_context *ctx, bfuse_kernel_desc *d, std::string *
       const int budget = bn == 256 ? 200 * 1024 : 100 * 1024;
       int stages = std::min({q, kUmmaMaxStages, (budget - kUmmaHeaderBytes) / umma_stage_bytes(bn)});
       stages = std::max({stages, 1, umma_min_stages(bn, split, d->op == BFUSE_OP_GEMM_TF32 ? 4 : 2)});
-      set(split * ceil_div(s[2], bn), ceil_div(s[1], kUmmaBM), s[0], kUmmaThreads, 1, umma_smem_bytes(bn, stages), 4);
+      set(split * ceil_div(s[1], kUmmaBM), ceil_div(s[2], bn), s[0], kUmmaThreads, 1, umma_smem_bytes(bn, stages), 4);
       return BFUSE_OK;
     }
     default:
@@ -398,8 +398,8 @@ int build_params(bfuse_context *ctx, KernelRec &k) {
       const int num_kb = ceil_div(s[3] * eb, kUmmaRowBytes), q = ceil_div(num_kb, split);
       if (split > 8 || (split - 1) * q >= num_kb) return shape_err("shape[5] (split) must be 1..8 with every k-slice non-empty");
       if (kd.bx != kUmmaThreads || kd.by != 1 || kd.bz != 1) return shape_err("BlockDim must be (192, 1, 1)");
-      if (kd.gx != split * ceil_div(s[2], bn) || kd.gy != ceil_div(s[1], kUmmaBM) || kd.gz != s[0])
-        return shape_err("GridDim must be (split * ceil(N/BN), ceil(M/128), batch)");
+      if (kd.gx != split * ceil_div(s[1], kUmmaBM) || kd.gy != ceil_div(s[2], bn) || kd.gz != s[0])
+        return shape_err("GridDim must be (split * ceil(M/128), ceil(N/BN), batch)");
       if (k.smem < (size_t)umma_smem_bytes(bn, umma_min_stages(bn, split, eb)))
         return shape_err("shared memory below the store buffers (and, for a split GEMM, the receive area of the k-slices)");
       k.cluster = split;
