@@ -26,6 +26,14 @@ __device__ __forceinline__ unsigned char *align_smem_1k(unsigned char *p) {
   return p + ((1024u - (a & 1023u)) & 1023u);
 }
 
+// Programmatic dependent launch: every kernel here is launched with the programmatic-stream-
+// serialization attribute, so its CTAs may be scheduled while the previous kernel on the stream is
+// still draining.  grid_dependency_wait() blocks until that kernel has completed and its writes
+// are visible -- nothing before it may touch global memory -- and grid_launch_dependents() lets
+// the next kernel's CTAs start their own prologue early.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 template <class Op>
 __device__ __forceinline__ void run_tile(const typename Op::Params &p, const DispatchTable &t, int k, int vb, int vtid,
                                          int bar_id, unsigned char *smem, int shares_cta = 0) {
@@ -63,6 +71,8 @@ __global__ void __launch_bounds__(cmax(A::kMaxThreads, B::kMaxThreads), pair_min
   extern __shared__ unsigned char smem_raw[];
   unsigned char *smem = align_smem_1k(smem_raw);
   const int tid = threadIdx.x;
+  grid_launch_dependents();
+  grid_dependency_wait();
   if (!t.queue) {
     int k, vb;
     if (!decode_cta(t, blockIdx.x, k, vb)) return;
@@ -108,6 +118,8 @@ __global__ void __launch_bounds__(A::kMaxThreads + B::kMaxThreads, 1)
   extern __shared__ unsigned char smem_raw[];
   unsigned char *smem = align_smem_1k(smem_raw);
   const int tid = threadIdx.x, b = blockIdx.x;
+  grid_launch_dependents();
+  grid_dependency_wait();
   // thread ranges of hfusePattern (Algorithms.cc:23-49): kernel k owns [thr_lo[k], thr_lo[k] + B_k)
   if (tid < t.thr_lo[1]) {
     if (tid < t.n_thr[0] && b < t.n_cta[0]) run_tile<A>(pa, t, 0, b, tid, 1, smem + t.smem_off[0], 1);
@@ -122,6 +134,8 @@ __global__ void __launch_bounds__(A::kMaxThreads, A::kMinBlocks)
     single_kernel(const __grid_constant__ DispatchTable t, const __grid_constant__ typename A::Params pa) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char *smem = align_smem_1k(smem_raw);
+  grid_launch_dependents();
+  grid_dependency_wait();
   if ((int)threadIdx.x < t.n_thr[0]) run_tile<A>(pa, t, 0, blockIdx.x, threadIdx.x, 1, smem);
 }
 
@@ -139,7 +153,8 @@ cudaError_t ensure_smem(Kernel k, size_t smem) {
   return cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
 }
 
-// Launch with `cluster` consecutive CTAs per thread-block cluster (1 = a plain launch).
+// Launch with `cluster` consecutive CTAs per thread-block cluster (1 = no clusters) and with
+// programmatic dependent launch allowed.
 template <class Kernel, class... Args>
 cudaError_t launch_clustered(Kernel kern, unsigned grid, unsigned block, size_t smem, cudaStream_t s, int cluster,
                              Args... args) {
@@ -148,13 +163,15 @@ cudaError_t launch_clustered(Kernel kern, unsigned grid, unsigned block, size_t 
   cfg.blockDim = dim3(block, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = s;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = cluster > 1 ? cluster : 1;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.x = cluster > 1 ? cluster : 1;
+  attr[1].val.clusterDim.y = 1;
+  attr[1].val.clusterDim.z = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = cluster > 1 ? 1 : 0;
+  cfg.numAttrs = cluster > 1 ? 2 : 1;
   return cudaLaunchKernelEx(&cfg, kern, args...);
 }
 
@@ -171,9 +188,8 @@ cudaError_t launch_thread_pair(const DispatchTable &t, const void *pa, const voi
                                size_t smem, cudaStream_t s) {
   cudaError_t e = ensure_smem(fused_thread_kernel<A, B>, smem);
   if (e != cudaSuccess) return e;
-  fused_thread_kernel<A, B><<<grid, block, smem, s>>>(t, *static_cast<const typename A::Params *>(pa),
-                                                       *static_cast<const typename B::Params *>(pb));
-  return cudaGetLastError();
+  return launch_clustered(fused_thread_kernel<A, B>, grid, block, smem, s, 1, t,
+                          *static_cast<const typename A::Params *>(pa), *static_cast<const typename B::Params *>(pb));
 }
 template <class A>
 cudaError_t launch_single(const DispatchTable &t, const void *pa, unsigned grid, unsigned block, size_t smem,

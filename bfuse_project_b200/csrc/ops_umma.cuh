@@ -228,6 +228,8 @@ struct ChunkWriter {
   int m_base, bz;  // first output row of this warp's 32 rows, batch index
   int n_tile0;     // first output column of the tile
 
+  // nbuf is 1, 2, or at least the number of chunks this warp will ever write (then no buffer is
+  // reused and nothing has to be waited for)
   __device__ __forceinline__ uint32_t begin_chunk() {
     if (issued >= nbuf) {  // the buffer about to be overwritten must have been read by its store
       if (lane == 0) {
@@ -287,6 +289,9 @@ struct ChunkWriter {
 };
 
 
+// chunks one epilogue warp writes: all of the tile's chunks, or the owned share of a split tile
+__device__ __forceinline__ int max_owned_or_all(int chunks, int split) { return (chunks + split - 1) / split; }
+
 template <int KIND>
 struct GemmUmma {
   using Params = GemmUmmaParams;
@@ -321,7 +326,10 @@ struct GemmUmma {
     const int max_owned = (chunks + split - 1) / split;                     // store chunks a k-slice finishes
     constexpr uint32_t kChunkPartial = (uint32_t)kOutCols * kUmmaBM * 4;    // fp32 partial of one chunk from one k-slice
     const uint32_t staging = tiles + (uint32_t)umma_recv_bytes(BN, split, kElem);
-    const int nbuf = (stages * kStageBytes - (int)(staging - tiles)) >= 2 * kUmmaStagingBytes ? 2 : 1;
+    // store buffers per epilogue warp: one per chunk when the idle ring has the room (no waits at
+    // all), else two (double buffering), else one
+    const int free_bufs = (stages * kStageBytes - (int)(staging - tiles)) / kUmmaStagingBytes;
+    const int nbuf = free_bufs >= max_owned_or_all(chunks, split) ? max_owned_or_all(chunks, split) : (free_bufs >= 2 ? 2 : 1);
     ChunkWriter<KIND> w{&p.map_out, p.M, p.N, p.causal, staging + (uint32_t)(quad * nbuf) * 4096u, nbuf, lane, 0, m0 + quad * 32, bz, n0};
     long long *const tl = (p.timeline && c.vblock == 0) ? p.timeline : nullptr;
     auto mark = [&](int what, bool who) {
