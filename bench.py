@@ -34,6 +34,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 WORKLOAD = "cfg2_q_k_proj"
+NCU_TRAFFIC_BYTES = 7987968   # dram__bytes_read.sum + dram__bytes_write.sum of the fused kernel, one launch (profiles/)
 L2_BYTES = 126 * 1024 * 1024
 
 
@@ -419,7 +420,9 @@ def main():
         "roofline_pair_us": t_roof_us, "roofline_pair_frac": t_roof_us / us_pair,
         "pairs_per_s": world * 1e6 / us_pair,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                     "frac": achieved / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
+                     "frac": achieved / pk["hbm_gbs"], "traffic": NCU_TRAFFIC_BYTES, "peak_source": pk["source"],
+                     "traffic_note": "dram read + write of one launch from the ncu capture summarised in "
+                                     "profiles/fused_gemm_tf32_pair_cfg2.md; the 3.15 MB of outputs are still in L2 at kernel end",
                      "alg_bytes_per_launch": spec0.bytes, "kernel": info["KernelName"]},
         "cpu_baseline": {"value": cpu_us, "unit": "us", "cores": cores, "kind": "port",
                          "sample": "one full pair (1.2 GFLOP) per run, best of %d runs" % cpu_n},
