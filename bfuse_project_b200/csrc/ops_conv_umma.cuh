@@ -67,20 +67,21 @@ struct ConvUmmaTf32 {
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(c.smem + 8 * (2 * kUmmaMaxStages + 2));
     int2 *tab = reinterpret_cast<int2 *>(c.smem + kUmmaHeaderBytes);
     const uint32_t tiles = smem_u32(c.smem) + kConvHeaderBytes;
-    const int nbuf = stages * kConvStageBytes >= 2 * kUmmaStagingBytes ? 2 : 1;
-    ChunkWriter<0> w{&p.map_out, p.co, ohw, 0, tiles + (uint32_t)(quad * nbuf) * 4096u, nbuf, lane, 0, co0 + quad * 32, img, px0};
+    int nbuf, group;
+    staging_plan(stages * kConvStageBytes / kUmmaStagingBytes, kConvBN / 32, nbuf, group);
+    ChunkWriter<0> w{&p.map_out, p.co, ohw, 0, tiles + (uint32_t)(quad * nbuf) * 4096u, nbuf, lane, 0, co0 + quad * 32, img, px0, 32, group};
 
     long long *const tl = (p.timeline && c.vblock == 0) ? p.timeline : nullptr;
     auto mark = [&](int what, bool who) {
       if (tl && who) tl[what] = (long long)global_ns();
     };
     mark(MARK_START, c.tid == 0);
-    if (c.tid == 0) {
-      for (int s = 0; s < stages; ++s) {
-        mbar_init(full0 + 8 * s, 1 + 128);  // the weight copy's arrive.expect_tx + one arrive per gather thread
-        mbar_init(empty0 + 8 * s, 1);
+    if (warp == 4) {
+      if (lane < stages) {
+        mbar_init(full0 + 8 * lane, 1 + 128);  // the weight copy's arrive.expect_tx + one arrive per gather thread
+        mbar_init(empty0 + 8 * lane, 1);
       }
-      mbar_init(acc_bar, 1);
+      if (lane == 0) mbar_init(acc_bar, 1);
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 5) {
@@ -101,39 +102,46 @@ struct ConvUmmaTf32 {
     const uint32_t tmem_row = tmem_acc + ((uint32_t)(quad * 32) << 16);
     mark(MARK_SETUP_DONE, c.tid == 0);
 
+    // weight producer and MMA issuer: one elected thread each, ring slot / phase / descriptor word
+    // carried incrementally (the issue loop is a dependent chain on one thread; see GemmUmma)
     if (warp == 4) {
-      bool ok = true;
-      for (int kb = 0; kb < num_kb && ok; ++kb) {
-        const int s = kb % stages;
-        ok = mbar_wait(empty0 + 8 * s, ((kb / stages) & 1) ^ 1, c.status, UMMA_WAIT_EMPTY_TIMEOUT);
-        if (ok && lane == 0) {
-          mbar_expect_tx(full0 + 8 * s, kUmmaABytes);
-          tma_load_3d(tiles + s * kConvStageBytes, &p.map_w, full0 + 8 * s, kb * kBK, co0, 0);
+      if (elect_one()) {
+        uint32_t s = 0, ph = 1, dst = tiles, bar = full0;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(empty0 + 8 * s, ph, c.status, UMMA_WAIT_EMPTY_TIMEOUT)) break;
+          mbar_expect_tx(bar, kUmmaABytes);
+          tma_load_3d(dst, &p.map_w, bar, kb * kBK, co0, 0);
+          if (++s == (uint32_t)stages) s = 0, ph ^= 1, dst = tiles, bar = full0;
+          else dst += kConvStageBytes, bar += 8;
         }
-        __syncwarp();
       }
-    } else if (warp == 5) {
-      bool ok = true;
-      for (int kb = 0; kb < num_kb && ok; ++kb) {
-        const int s = kb % stages;
-        ok = mbar_wait(full0 + 8 * s, (kb / stages) & 1, c.status, UMMA_WAIT_FULL_TIMEOUT);
-        fence_async_smem();  // the gathered operand was written through the generic proxy
-        tc_fence_after();
-        if (kb == 0) mark(MARK_FIRST_FULL, lane == 0);
-        if (ok && lane == 0) {
-          const uint64_t a_desc = umma_smem_desc(tiles + s * kConvStageBytes);
-          const uint64_t b_desc = umma_smem_desc(tiles + s * kConvStageBytes + kUmmaABytes);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) umma_ss<0>(tmem_acc, a_desc + 2 * j, b_desc + 2 * j, idesc, (kb | j) != 0);
-          umma_commit(empty0 + 8 * s);
-        }
-        __syncwarp();
-      }
-      if (lane == 0) umma_commit(acc_bar);
-      mark(MARK_LAST_MMA_ISSUED, lane == 0);
       __syncwarp();
-      for (int kb = max(0, num_kb - stages); kb < num_kb && ok; ++kb)
-        ok = mbar_wait(empty0 + 8 * (kb % stages), (kb / stages) & 1, c.status, UMMA_WAIT_EMPTY_TIMEOUT);
+    } else if (warp == 5) {
+      if (elect_one()) {
+        const uint32_t lo0 = ((tiles >> 4) & 0x3fffu) | (1u << 16), stage16 = (uint32_t)kConvStageBytes >> 4;
+        uint32_t s = 0, ph = 0, lo = lo0, accumulate = 0;
+        bool ok = true;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = mbar_wait(full0 + 8 * s, ph, c.status, UMMA_WAIT_FULL_TIMEOUT);
+          if (!ok) break;
+          fence_async_smem();  // the gathered operand was written through the generic proxy
+          tc_fence_after();
+          if (kb == 0) mark(MARK_FIRST_FULL, true);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            umma_ss<0>(tmem_acc, lo + 2 * j, lo + (kUmmaABytes >> 4) + 2 * j, idesc, accumulate);
+            accumulate = 1;
+          }
+          umma_commit(empty0 + 8 * s);
+          if (++s == (uint32_t)stages) s = 0, ph ^= 1, lo = lo0;
+          else lo += stage16;
+        }
+        umma_commit(acc_bar);
+        mark(MARK_LAST_MMA_ISSUED, true);
+        for (int kb = max(0, num_kb - stages); kb < num_kb && ok; ++kb)
+          ok = mbar_wait(empty0 + 8 * (kb % stages), (kb / stages) & 1, c.status, UMMA_WAIT_EMPTY_TIMEOUT);
+      }
+      __syncwarp();
     } else {
       // gather warps: thread r fills row r (one output pixel) of every stage's im2col tile
       const int r = quad * 32 + lane, pix = px0 + r;
@@ -200,12 +208,10 @@ struct ConvUmmaTf32 {
     tc_fence_before();
     c.sync();
     if (warp == 5) tmem_dealloc(tmem_acc, kConvBN);
-    if (c.tid == 0) {
-      for (int s = 0; s < stages; ++s) {
-        mbar_inval(full0 + 8 * s);
-        mbar_inval(empty0 + 8 * s);
-      }
-      mbar_inval(acc_bar);
+    if (c.persistent && c.tid < stages) {  // the next tile of a persistent CTA initialises them again
+      mbar_inval(full0 + 8 * c.tid);
+      mbar_inval(empty0 + 8 * c.tid);
+      if (c.tid == 0) mbar_inval(acc_bar);
     }
     mark(MARK_END, c.tid == 0);
   }

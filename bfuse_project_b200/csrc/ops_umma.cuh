@@ -109,19 +109,29 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-template <int KIND>  // 0: tf32, 1: bf16
-__device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+// One thread of a warp, chosen by the hardware; every lane of the (converged) warp must call it.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.b32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
+// High word of the shared-memory matrix descriptor of a K-major, 128B-swizzled operand tile whose
+// rows are 128 bytes: 8-row groups 1024 bytes apart (stride byte offset, bits 32-45), version 1
+// (bit 46), layout SWIZZLE_128B (bits 61-63).  The low word is (address >> 4) | 1 << 16.
+constexpr uint32_t kUmmaDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+template <int KIND>  // 0: tf32, 1: bf16; a_lo / b_lo: low descriptor words
+__device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t accumulate) {
   if (KIND == 0) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %5, 0;\n\tmov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], da, db, %4, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_lo), "r"(b_lo), "r"(kUmmaDescHi), "r"(idesc), "r"(accumulate)
         : "memory");
   } else {
     asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %5, 0;\n\tmov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_lo), "r"(b_lo), "r"(kUmmaDescHi), "r"(idesc), "r"(accumulate)
         : "memory");
   }
 }
@@ -161,11 +171,6 @@ __device__ __forceinline__ void st_shared_u4(uint32_t addr, uint32_t a, uint32_t
   asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
-// Shared-memory matrix descriptor of a K-major, 128B-swizzled operand tile whose rows are 128
-// bytes: 8-row groups are 1024 bytes apart (stride byte offset), version 1, layout SWIZZLE_128B.
-__device__ __forceinline__ uint64_t umma_smem_desc(uint32_t saddr) {
-  return (uint64_t)((saddr >> 4) & 0x3fffu) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
-}
 // Instruction descriptor: fp32 accumulate, both operands K-major, M = 128, N = bn.
 __host__ __device__ constexpr uint32_t umma_idesc(int kind, int bn) {
   return (1u << 4) | ((kind == 0 ? 2u : 1u) << 7) | ((kind == 0 ? 2u : 1u) << 10) | ((uint32_t)(bn >> 3) << 17) |
@@ -215,42 +220,49 @@ __device__ __forceinline__ void tma_store_wait_read() {
 }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-// The epilogue of one warp: 32 rows x 128-byte chunks go through a 128B-swizzled staging buffer
-// and leave with one TMA store per chunk (full lines, clipped at the M / N edges by the hardware).
-// The epilogue of one warp: 32 rows x 128-byte chunks go through a 128B-swizzled staging buffer and
+// The epilogue of one warp: 32 rows x 128-byte chunks go through 128B-swizzled staging buffers and
 // leave with one TMA store per chunk (full lines, clipped at the tensor's edges by the hardware).
+// Chunks are staged in groups: one proxy fence, one warp barrier and one bulk group per GROUP of
+// chunks, because each of those costs a few hundred nanoseconds of latency that a per-chunk
+// sequence would pay serially.  With a buffer for every chunk of the warp nothing is ever waited
+// for before the end; otherwise the buffers form two half-groups that alternate (one being filled
+// while the other's stores read it).
 template <int KIND>
 struct ChunkWriter {
   const CUtensorMap *map_out;
   int M, N, causal;  // output rows / columns (clipping, mask) of the tensor the map describes
   uint32_t buf0;   // staging buffers of this warp (nbuf x 4096 bytes)
-  int nbuf, lane, issued;
+  int nbuf, lane, issued;  // issued: bulk groups committed so far
   int m_base, bz;  // first output row of this warp's 32 rows, batch index
   int n_tile0;     // first output column of the tile
+  int nb_step;     // columns between consecutive chunks this warp writes
+  int group;       // chunks per bulk group: nbuf (single group) or nbuf / 2
+  int slot = 0, pending = 0, first_nb = 0;
 
-  // nbuf is 1, 2, or at least the number of chunks this warp will ever write (then no buffer is
-  // reused and nothing has to be waited for)
   __device__ __forceinline__ uint32_t begin_chunk() {
-    if (issued >= nbuf) {  // the buffer about to be overwritten must have been read by its store
+    if (pending == 0 && issued * group >= nbuf) {
+      // the half-group about to be overwritten must have been read by its stores
       if (lane == 0) {
-        if (nbuf == 2) tma_store_wait_read<1>();
+        if (group < nbuf) tma_store_wait_read<1>();
         else tma_store_wait_read<0>();
       }
       __syncwarp();
     }
-    return buf0 + (uint32_t)(issued % nbuf) * 4096u;
+    return buf0 + (uint32_t)slot * 4096u;
   }
   // 16 finished fp32 values of this lane's row: columns [nb + sub*16, +16) of the chunk at column nb;
   // bias_tile: this tile's slice of the bias vector in shared memory (zeros without a bias)
   __device__ __forceinline__ void put16(uint32_t buf, int sub, int nb, float (&v)[16], const float *bias_tile) {
     const int col0 = nb + sub * 16, m = m_base + lane;
     if (bias_tile) {
+      // all four loads first: the shared-memory stores below are ordered asm statements, and a load
+      // placed between them would wait out its latency there
       const float4 *b4 = reinterpret_cast<const float4 *>(bias_tile + (col0 - n_tile0));
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float4 b = b4[j];
-        v[4 * j] += b.x, v[4 * j + 1] += b.y, v[4 * j + 2] += b.z, v[4 * j + 3] += b.w;
-      }
+      const float4 ba = b4[0], bb = b4[1], bc = b4[2], bd = b4[3];
+      v[0] += ba.x, v[1] += ba.y, v[2] += ba.z, v[3] += ba.w;
+      v[4] += bb.x, v[5] += bb.y, v[6] += bb.z, v[7] += bb.w;
+      v[8] += bc.x, v[9] += bc.y, v[10] += bc.z, v[11] += bc.w;
+      v[12] += bd.x, v[13] += bd.y, v[14] += bd.z, v[15] += bd.w;
     }
     if (causal && col0 + 15 > m) {
 #pragma unroll
@@ -272,25 +284,44 @@ struct ChunkWriter {
     }
   }
   __device__ __forceinline__ void end_chunk(uint32_t buf, int nb) {
+    (void)buf;
+    if (pending == 0) first_nb = nb;
+    ++pending;
+    if (++slot == nbuf) slot = 0;
+    if (pending == group) flush();
+  }
+  // hands the staged chunks to the TMA: every lane fences its own writes, lane 0 issues the stores
+  __device__ __forceinline__ void flush() {
+    if (pending == 0) return;
     fence_async_smem();
     __syncwarp();
     if (lane == 0) {
-      if (nb < N && m_base < M) tma_store_3d(map_out, buf, nb, m_base, bz);
-      // one group per chunk, even an empty one for a chunk that lies outside the tensor: begin_chunk
-      // counts groups to know when a staging buffer may be overwritten
+      const int first_slot = (slot == 0 ? nbuf : slot) - pending;
+      for (int i = 0; i < pending; ++i) {
+        const int nb = first_nb + i * nb_step;
+        if (nb < N && m_base < M) tma_store_3d(map_out, buf0 + (uint32_t)(first_slot + i) * 4096u, nb, m_base, bz);
+      }
       tma_store_commit();
     }
     ++issued;
+    pending = 0;
   }
   __device__ __forceinline__ void finish() {
+    flush();
     if (lane == 0) tma_store_wait_read<0>();
     __syncwarp();
   }
 };
 
+// staging buffers (per epilogue warp) and chunks per bulk group for `total` chunks when `free_bufs`
+// buffers fit: a buffer per chunk in groups of two (the stores of one pair run while the next pair
+// is staged, and nothing is reused), else two alternating half-groups of up to 4, else one buffer
+__device__ __forceinline__ void staging_plan(int free_bufs, int total, int &nbuf, int &group) {
+  if (free_bufs >= total) nbuf = total, group = min(2, total);
+  else if (free_bufs >= 2) group = min(4, free_bufs / 2), nbuf = 2 * group;
+  else nbuf = 1, group = 1;
+}
 
-// chunks one epilogue warp writes: all of the tile's chunks, or the owned share of a split tile
-__device__ __forceinline__ int max_owned_or_all(int chunks, int split) { return (chunks + split - 1) / split; }
 
 template <int KIND>
 struct GemmUmma {
@@ -326,11 +357,12 @@ struct GemmUmma {
     const int max_owned = (chunks + split - 1) / split;                     // store chunks a k-slice finishes
     constexpr uint32_t kChunkPartial = (uint32_t)kOutCols * kUmmaBM * 4;    // fp32 partial of one chunk from one k-slice
     const uint32_t staging = tiles + (uint32_t)umma_recv_bytes(BN, split, kElem);
-    // store buffers per epilogue warp: one per chunk when the idle ring has the room (no waits at
-    // all), else two (double buffering), else one
+    // store buffers per epilogue warp, as many as the idle ring has room for (see staging_plan)
     const int free_bufs = (stages * kStageBytes - (int)(staging - tiles)) / kUmmaStagingBytes;
-    const int nbuf = free_bufs >= max_owned_or_all(chunks, split) ? max_owned_or_all(chunks, split) : (free_bufs >= 2 ? 2 : 1);
-    ChunkWriter<KIND> w{&p.map_out, p.M, p.N, p.causal, staging + (uint32_t)(quad * nbuf) * 4096u, nbuf, lane, 0, m0 + quad * 32, bz, n0};
+    int nbuf, group;
+    staging_plan(free_bufs, max_owned, nbuf, group);
+    ChunkWriter<KIND> w{&p.map_out, p.M, p.N, p.causal, staging + (uint32_t)(quad * nbuf) * 4096u, nbuf, lane, 0, m0 + quad * 32, bz, n0,
+                        split * kOutCols, group};
     long long *const tl = (p.timeline && c.vblock == 0) ? p.timeline : nullptr;
     auto mark = [&](int what, bool who) {
       if (tl && who) tl[what] = (long long)global_ns();
@@ -361,28 +393,43 @@ struct GemmUmma {
     const int kb0 = kslice * p.kb_per_slice;                 // first K block of this k-slice
     const int num_kb = min(p.kb_per_slice, total_kb - kb0);  // K blocks this CTA multiplies (>= 1)
 
-    if (c.tid == 0) {
-      for (int s = 0; s < stages; ++s) {
-        mbar_init(full0 + 8 * s, 1);
-        mbar_init(empty0 + 8 * s, 1);
+    // The producer warp sets the barriers up itself and starts the first ring pass (every slot is
+    // free, nothing to wait for) before the CTA-wide barrier, so the first operands are already on
+    // their way from HBM while warp 5 allocates tensor memory.
+    const int npre = min(stages, num_kb);
+    if (warp == 4) {
+      if (lane < stages) {
+        mbar_init(full0 + 8 * lane, 1);
+        mbar_init(empty0 + 8 * lane, 1);
       }
-      mbar_init(acc_bar, 1);
-      mbar_init(recv_bar, 1);
+      if (lane == 0) {
+        mbar_init(acc_bar, 1);
+        mbar_init(recv_bar, 1);
+      }
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-      if (split > 1) {
-        // bytes this CTA will receive: one partial per owned chunk from every k-slice (itself included)
-        int owned = 0;
-        for (int ch = kslice; ch < chunks; ch += split) ++owned;
-        mbar_expect_tx(recv_bar, (uint32_t)owned * (uint32_t)split * kChunkPartial);
+      __syncwarp();
+      if (lane == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&p.map_out) : "memory");
+        if (split > 1) {
+          // bytes this CTA will receive: one partial per owned chunk from every k-slice (itself included)
+          int owned = 0;
+          for (int ch = kslice; ch < chunks; ch += split) ++owned;
+          mbar_expect_tx(recv_bar, (uint32_t)owned * (uint32_t)split * kChunkPartial);
+        }
       }
-    }
-    if (warp == 5) {
+      if (elect_one()) {
+        for (int kb = 0; kb < npre; ++kb) {
+          const uint32_t dst = tiles + kb * kStageBytes, bar = full0 + 8 * kb;
+          mbar_expect_tx(bar, kStageBytes);
+          tma_load_3d(dst, &p.map_a, bar, (kb0 + kb) * kBK, m0, bz);
+          tma_load_3d(dst + kUmmaABytes, &p.map_b, bar, (kb0 + kb) * kBK, n0, bz);
+          if (kb == 0) mark(MARK_FIRST_LOAD_ISSUED, true);
+        }
+      }
+      __syncwarp();
+    } else if (warp == 5) {
       tmem_alloc(smem_u32(tmem_slot), BN);
       if (!c.persistent) tmem_relinquish();
-    } else if (warp == 4 && lane == 0) {
-      asm volatile("prefetch.tensormap [%0];" ::"l"(&p.map_a) : "memory");
-      asm volatile("prefetch.tensormap [%0];" ::"l"(&p.map_b) : "memory");
-      asm volatile("prefetch.tensormap [%0];" ::"l"(&p.map_out) : "memory");
     }
     tc_fence_before();
     c.sync();
@@ -391,51 +438,59 @@ struct GemmUmma {
     const uint32_t tmem_row = tmem_acc + ((uint32_t)(quad * 32) << 16);
     mark(MARK_SETUP_DONE, c.tid == 0);
 
-    // Producer and MMA warps run their loops with all 32 lanes (so the warp reaches the closing
-    // barrier converged); lane 0 alone issues the copies / MMAs.
+    // The producer and the MMA issuer are ONE elected thread each (elect.sync, so the compiler knows
+    // the branch is taken by a single thread and keeps descriptors in uniform registers).  Their
+    // loops carry the ring slot, its phase and the low descriptor word incrementally: the issue
+    // loop is a chain of dependent instructions on one thread, and every instruction saved in it is
+    // time the tensor pipe does not idle (4 MMAs of N <= 128 execute faster than a careless loop
+    // iteration issues them).  The other lanes wait at the __syncwarp below.
     bool acc_ok = true;
     if (warp == 4) {
-      bool ok = true;
-      for (int kb = 0; kb < num_kb && ok; ++kb) {
-        const int s = kb % stages;
-        const uint32_t ph = (kb / stages) & 1;
-        ok = mbar_wait(empty0 + 8 * s, ph ^ 1, c.status, UMMA_WAIT_EMPTY_TIMEOUT);
-        if (ok && lane == 0) {
-          mbar_expect_tx(full0 + 8 * s, kStageBytes);
-          const uint32_t a_dst = tiles + s * kStageBytes;
-          tma_load_3d(a_dst, &p.map_a, full0 + 8 * s, (kb0 + kb) * kBK, m0, bz);
-          tma_load_3d(a_dst + kUmmaABytes, &p.map_b, full0 + 8 * s, (kb0 + kb) * kBK, n0, bz);
-          if (kb == 0) mark(MARK_FIRST_LOAD_ISSUED, true);
-          if (kb == num_kb - 1) mark(MARK_LAST_LOAD_ISSUED, true);
+      if (elect_one()) {
+        // second and later ring passes (the first was issued before the barrier): slot 0 again
+        uint32_t s = 0, ph = 0, dst = tiles, bar = full0;
+        int kcoord = (kb0 + npre) * kBK;
+        for (int kb = npre; kb < num_kb; ++kb) {
+          if (!mbar_wait(empty0 + 8 * s, ph, c.status, UMMA_WAIT_EMPTY_TIMEOUT)) break;
+          mbar_expect_tx(bar, kStageBytes);
+          tma_load_3d(dst, &p.map_a, bar, kcoord, m0, bz);
+          tma_load_3d(dst + kUmmaABytes, &p.map_b, bar, kcoord, n0, bz);
+          kcoord += kBK;
+          if (++s == (uint32_t)stages) s = 0, ph ^= 1, dst = tiles, bar = full0;
+          else dst += kStageBytes, bar += 8;
         }
-        __syncwarp();
+        mark(MARK_LAST_LOAD_ISSUED, true);
       }
-    } else if (warp == 5) {
-      bool ok = true;
-      for (int kb = 0; kb < num_kb && ok; ++kb) {
-        const int s = kb % stages;
-        const uint32_t ph = (kb / stages) & 1;
-        ok = mbar_wait(full0 + 8 * s, ph, c.status, UMMA_WAIT_FULL_TIMEOUT);
-        tc_fence_after();
-        if (kb == 0) mark(MARK_FIRST_FULL, lane == 0);
-        if (ok && lane == 0) {
-          const uint64_t a_desc = umma_smem_desc(tiles + s * kStageBytes);
-          const uint64_t b_desc = umma_smem_desc(tiles + s * kStageBytes + kUmmaABytes);
-#pragma unroll
-          for (int j = 0; j < 4; ++j)  // 4 x 32 bytes of K per stage; +2 = 32 bytes in descriptor units
-            umma_ss<KIND>(tmem_acc, a_desc + 2 * j, b_desc + 2 * j, idesc, (kb | j) != 0);
-          umma_commit(empty0 + 8 * s);  // frees the stage once these MMAs have read it
-        }
-        __syncwarp();
-      }
-      if (lane == 0) umma_commit(acc_bar);  // accumulator complete (also arrives if the loop bailed out)
-      mark(MARK_LAST_MMA_ISSUED, lane == 0);
       __syncwarp();
-      // The stage-release arrivals of the last ring pass are asynchronous and nobody consumes them;
-      // wait for them here so that none is still in flight when the barriers are invalidated and
-      // the shared memory is handed to the next tile or the next CTA.
-      for (int kb = max(0, num_kb - stages); kb < num_kb && ok; ++kb)
-        ok = mbar_wait(empty0 + 8 * (kb % stages), (kb / stages) & 1, c.status, UMMA_WAIT_EMPTY_TIMEOUT);
+    } else if (warp == 5) {
+      if (elect_one()) {
+        // descriptor words of stage 0 (see umma_smem_desc); a stage is kStageBytes / 16 further on
+        const uint32_t lo0 = ((tiles >> 4) & 0x3fffu) | (1u << 16), stage16 = (uint32_t)kStageBytes >> 4;
+        uint32_t s = 0, ph = 0, lo = lo0, accumulate = 0;
+        bool ok = true;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = mbar_wait(full0 + 8 * s, ph, c.status, UMMA_WAIT_FULL_TIMEOUT);
+          if (!ok) break;
+          tc_fence_after();
+          if (kb == 0) mark(MARK_FIRST_FULL, true);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {  // 4 x 32 bytes of K per stage; +2 = 32 bytes in descriptor units
+            umma_ss<KIND>(tmem_acc, lo + 2 * j, lo + (kUmmaABytes >> 4) + 2 * j, idesc, accumulate);
+            accumulate = 1;
+          }
+          umma_commit(empty0 + 8 * s);  // frees the stage once these MMAs have read it
+          if (++s == (uint32_t)stages) s = 0, ph ^= 1, lo = lo0;
+          else lo += stage16;
+        }
+        umma_commit(acc_bar);  // accumulator complete (also arrives if the loop bailed out)
+        mark(MARK_LAST_MMA_ISSUED, true);
+        // The stage-release arrivals of the last ring pass are asynchronous and nobody consumes them;
+        // wait for them here so that none is still in flight when the barriers are invalidated and
+        // the shared memory is handed to the next tile or the next CTA.
+        for (int kb = max(0, num_kb - stages); kb < num_kb && ok; ++kb)
+          ok = mbar_wait(empty0 + 8 * (kb % stages), (kb / stages) & 1, c.status, UMMA_WAIT_EMPTY_TIMEOUT);
+      }
+      __syncwarp();
     } else {
       // the epilogue warps are idle during the main loop: they fetch the tile's bias slice meanwhile
       // (only they read it, after their own named-barrier-free hand-off below)
@@ -531,13 +586,13 @@ struct GemmUmma {
     tc_fence_before();
     c.sync();
     if (warp == 5) tmem_dealloc(tmem_acc, BN);
-    if (c.tid == 0) {
-      for (int s = 0; s < stages; ++s) {
-        mbar_inval(full0 + 8 * s);
-        mbar_inval(empty0 + 8 * s);
+    if (c.persistent && c.tid < stages) {  // the next tile of a persistent CTA initialises them again
+      mbar_inval(full0 + 8 * c.tid);
+      mbar_inval(empty0 + 8 * c.tid);
+      if (c.tid == 0) {
+        mbar_inval(acc_bar);
+        mbar_inval(recv_bar);
       }
-      mbar_inval(acc_bar);
-      mbar_inval(recv_bar);
     }
     mark(MARK_END, c.tid == 0);
   }

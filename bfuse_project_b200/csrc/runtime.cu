@@ -53,6 +53,7 @@ struct FusionRec {
   unsigned launch_grid;
   unsigned *queue_ctr;  // device, 2 words (work queue only)
   int regs;
+  int stages[2];        // thread-level fusion only: ring depths that let both windows fit (0: the kernel's own)
 };
 
 struct GraphRec {
@@ -109,28 +110,39 @@ int pick_row_threads(int cols, int vec_elems, int max_vec) {
   return 0;
 }
 
-// A tcgen05.mma (M = 128, 32 bytes of K) takes about 85 ns whether N is 32 or 256, so wide tiles
-// are what makes the tensor pipe efficient: 256 wide when that still yields enough tiles to fill
-// the SMs, otherwise 128 wide with K split in two (wider splits lose more in the cross-CTA
-// reduction than they gain in the main loop; measured on the BERT and Llama projection shapes).
-int default_bn(int batch, int M, int N, int elem, int sm_count) {
-  const int tiles256 = batch * ceil_div(M, kUmmaBM) * ceil_div(N, 256);
-  int bn = (N > 128 && tiles256 >= sm_count / 2) ? 256 : (N > 64 ? 128 : (N > 32 ? 64 : 32));
-  return std::max(bn, 128 / elem);
-}
-
 int umma_min_stages(int bn, int split, int elem) {
   // after the MMAs the ring doubles as the store buffers and, with split > 1, as the receive area
   return ceil_div(umma_epilogue_bytes(bn, split, elem), umma_stage_bytes(bn));
 }
 
-// k-slices per tile: 2 when the tiles alone cannot give this operator about half the SMs (its pair
-// partner takes the other half), else 1; every slice non-empty.
-void default_split(int tiles, int num_kb, int sm_count, int *split, int *kb_per_slice) {
-  const int s = (tiles < sm_count / 2 && num_kb >= 2) ? 2 : 1;
-  const int q = ceil_div(num_kb, s);
-  *split = ceil_div(num_kb, q);
-  *kb_per_slice = q;
+// Tile width and k-slices of a tensor-core GEMM from a small cost model fitted to measurements on
+// B200.  One CTA multiplies a k-block (128 bytes of K per row) in t_kb(BN) -- set by the MMA time for
+// wide tiles and by the bytes the SM can pull from L2 for narrow ones --, pays a fixed prologue +
+// epilogue that grows with BN, and a split tile pays the cross-CTA reduction on top.  The operator
+// is budgeted half of the SMs (its pair partner takes the other half), in whole waves.  Ties go to
+// the wider tile (less L2 traffic).  With bn_fixed / split_fixed > 0 only the other one is chosen.
+void pick_tile(int batch, int M, int N, int K, int elem, int sm_count, int bn_fixed, int split_fixed, int *bn_out, int *split_out) {
+  static const int kBn[4] = {256, 128, 64, 32};
+  static const double kTkbUs[4] = {0.267, 0.213, 0.153, 0.150};
+  const int num_kb = ceil_div(K * elem, kUmmaRowBytes);
+  const int slots = std::max(1, sm_count / 2);
+  double best = 1e30;
+  int best_bn = 128, best_split = 1;
+  for (int i = 0; i < 4; ++i) {
+    const int bn = kBn[i];
+    if (bn_fixed > 0 ? bn != bn_fixed : (bn * elem < 128 || (bn > 32 && bn / 2 >= N && bn / 2 * elem >= 128))) continue;
+    const long long tiles = (long long)batch * ceil_div(M, kUmmaBM) * ceil_div(N, bn);
+    for (int split = 1; split <= 4; split *= 2) {
+      if (split_fixed > 0 ? split != split_fixed : split > num_kb) continue;
+      if (umma_smem_bytes(bn, umma_min_stages(bn, split, elem)) > (bn == 256 ? 200 : 100) * 1024) continue;
+      const long long waves = (tiles * split + slots - 1) / slots;
+      const double per_cta = 1.0 + 0.006 * bn + ceil_div(num_kb, split) * kTkbUs[i] + (split > 1 ? 2.5 + 0.5 * split : 0.0);
+      const double t = (double)waves * per_cta;
+      if (t < best * 0.999) best = t, best_bn = bn, best_split = split;
+    }
+  }
+  *bn_out = bn_fixed > 0 ? bn_fixed : best_bn;
+  *split_out = split_fixed > 0 ? split_fixed : best_split;
 }
 
 int default_launch(const bfuse_context *ctx, bfuse_kernel_desc *d, std::string *err) {
@@ -191,24 +203,22 @@ int default_launch(const bfuse_context *ctx, bfuse_kernel_desc *d, std::string *
     case BFUSE_OP_GEMM_TF32:
     case BFUSE_OP_GEMM_BF16: {
       if (s[0] <= 0 || s[1] <= 0 || s[2] <= 0 || s[3] <= 0) { *err = "gemm: batch, M, N, K must be positive"; return BFUSE_ERR_SHAPE; }
-      const int bn = s[4] ? s[4] : default_bn(s[0], s[1], s[2], d->op == BFUSE_OP_GEMM_TF32 ? 4 : 2, sm);
+      const int eb = d->op == BFUSE_OP_GEMM_TF32 ? 4 : 2;
+      int bn = s[4], split = s[5], q;
+      if (bn <= 0 || split <= 0) pick_tile(s[0], s[1], s[2], s[3], eb, sm, bn, split, &bn, &split);
       if (bn != 32 && bn != 64 && bn != 128 && bn != 256) { *err = "gemm: BN must be 32, 64, 128 or 256"; return BFUSE_ERR_SHAPE; }
       d->shape[4] = bn;
-      const int bk = kUmmaRowBytes / (d->op == BFUSE_OP_GEMM_TF32 ? 4 : 2);
-      const int num_kb = ceil_div(s[3], bk);
-      const int tiles = s[0] * ceil_div(s[1], kUmmaBM) * ceil_div(s[2], bn);
-      int split = s[5], q;
-      if (split <= 0) {
-        default_split(tiles, num_kb, sm, &split, &q);
-      } else {
-        if (split > 8 || split > num_kb) { *err = "gemm: split must be 1..8 and at most the number of K blocks"; return BFUSE_ERR_SHAPE; }
-        q = ceil_div(num_kb, split);
-        split = ceil_div(num_kb, q);
-      }
+      const int num_kb = ceil_div(s[3] * eb, kUmmaRowBytes);
+      if (split > 8 || split > num_kb) { *err = "gemm: split must be 1..8 and at most the number of K blocks"; return BFUSE_ERR_SHAPE; }
+      q = ceil_div(num_kb, split);
+      split = ceil_div(num_kb, q);
       d->shape[5] = split;
-      // ring depth: enough to cover the k-slice, at most 8, within ~100 KB so two CTAs share an SM
-      // (~200 KB for the 256-wide tile), and large enough to hold the partial tile when K is split
-      const int budget = bn == 256 ? 200 * 1024 : 100 * 1024;
+      // ring depth: enough to cover the k-slice, at most 8, and large enough to hold the partial tile
+      // when K is split.  Within ~200 KB when the operator and an equal partner leave every CTA an SM
+      // of its own (operands arriving from HBM need ~1 us of loads in flight per SM) or for the 256-wide
+      // tile, else within ~100 KB so that two CTAs share an SM.
+      const long long ctas = (long long)split * s[0] * ceil_div(s[1], kUmmaBM) * ceil_div(s[2], bn);
+      const int budget = (bn == 256 || 2 * ctas <= sm) ? 200 * 1024 : 100 * 1024;
       int stages = std::min({q, kUmmaMaxStages, (budget - kUmmaHeaderBytes) / umma_stage_bytes(bn)});
       stages = std::max({stages, 1, umma_min_stages(bn, split, d->op == BFUSE_OP_GEMM_TF32 ? 4 : 2)});
       set(split * ceil_div(s[1], kUmmaBM), ceil_div(s[2], bn), s[0], kUmmaThreads, 1, umma_smem_bytes(bn, stages), 4);
@@ -500,11 +510,41 @@ int launch_one(bfuse_context *ctx, KernelRec &k, cudaStream_t s) {
   return BFUSE_OK;
 }
 
+// Shared-memory ring of a tensor-core operator: header bytes, bytes per stage, fewest stages its
+// epilogue can live with, stages it has now.  False for operators without a ring.
+bool ring_info(const KernelRec &k, int *header, int *stage_bytes, int *min_stages, int *stages) {
+  const int *s = k.desc.shape;
+  if (k.desc.op == BFUSE_OP_GEMM_TF32 || k.desc.op == BFUSE_OP_GEMM_BF16) {
+    const int eb = k.desc.op == BFUSE_OP_GEMM_TF32 ? 4 : 2;
+    *header = kUmmaHeaderBytes, *stage_bytes = umma_stage_bytes(s[4]);
+    *min_stages = umma_min_stages(s[4], std::max(1, s[5]), eb);
+    *stages = reinterpret_cast<const GemmUmmaParams *>(k.params)->stages;
+    return true;
+  }
+  if (k.desc.op == BFUSE_OP_CONV2D_TF32) {
+    *header = kConvHeaderBytes, *stage_bytes = kConvStageBytes, *min_stages = 1;
+    *stages = reinterpret_cast<const ConvUmmaParams *>(k.params)->stages;
+    return true;
+  }
+  return false;
+}
+
+// parameter block of `k` with the ring depth replaced (stages > 0), else k's own
+const void *params_with_stages(const KernelRec &k, int stages, unsigned char *scratch) {
+  if (stages <= 0) return k.params;
+  std::memcpy(scratch, k.params, kParamsBytes);
+  if (k.desc.op == BFUSE_OP_CONV2D_TF32) reinterpret_cast<ConvUmmaParams *>(scratch)->stages = stages;
+  else reinterpret_cast<GemmUmmaParams *>(scratch)->stages = stages;
+  return scratch;
+}
+
 int launch_fused_rec(bfuse_context *ctx, FusionRec &f, cudaStream_t s) {
   KernelRec &a = *ctx->kernels[f.k1], &b = *ctx->kernels[f.k2];
   const PairEntry &pe = ctx->pairs[a.desc.op][b.desc.op];
   PairLaunchFn fn = f.plan.table.kind == DISPATCH_THREADS ? pe.thread : pe.block;
-  cudaError_t e = fn(f.plan.table, a.params, b.params, f.launch_grid, (unsigned)f.plan.fused_block, f.smem, s);
+  alignas(64) unsigned char pa[kParamsBytes], pb[kParamsBytes];
+  cudaError_t e = fn(f.plan.table, params_with_stages(a, f.stages[0], pa), params_with_stages(b, f.stages[1], pb), f.launch_grid,
+                     (unsigned)f.plan.fused_block, f.smem, s);
   if (e != cudaSuccess) return fail_cuda(ctx, e, ("launch " + f.name).c_str());
   return BFUSE_OK;
 }
@@ -697,10 +737,26 @@ int bfuse_register_fusion(bfuse_context *ctx, int kernel1, int kernel2, int patt
   // fused kernel name as FusionContext::create builds it (src/Contexts.cc:67-84)
   f->name = a->name + "_" + b->name + (thread_split ? "_fused_hfuse" : "_fused_bfuse");
   // shared memory: union for block-level fusion, sum for thread-level fusion (Matchers.cc:512-519)
+  f->stages[0] = f->stages[1] = 0;
   if (thread_split) {
+    // both windows live side by side; rings registered for a whole SM each are made shallower until
+    // the sum fits (the deeper one first), never below what the operator's epilogue needs
+    size_t win[2] = {a->smem, b->smem};
+    int hdr[2], stg[2], mn[2], st[2];
+    const bool ring[2] = {ring_info(*a, &hdr[0], &stg[0], &mn[0], &st[0]), ring_info(*b, &hdr[1], &stg[1], &mn[1], &st[1])};
+    auto total = [&] { return (win[0] + 1023) / 1024 * 1024 + win[1] + 1024; };
+    while (total() > kMaxSmemPerCta) {
+      int pick = -1;
+      for (int i = 0; i < 2; ++i)
+        if (ring[i] && st[i] > mn[i] && (pick < 0 || win[i] > win[pick])) pick = i;
+      if (pick < 0) break;
+      --st[pick];
+      win[pick] = (size_t)hdr[pick] + (size_t)st[pick] * stg[pick];
+      f->stages[pick] = st[pick];
+    }
     t.smem_off[0] = 0;
-    t.smem_off[1] = (int)((a->smem + 1023) / 1024 * 1024);
-    f->smem = t.smem_off[1] + b->smem + 1024;
+    t.smem_off[1] = (int)((win[0] + 1023) / 1024 * 1024);
+    f->smem = t.smem_off[1] + win[1] + 1024;
   } else {
     f->smem = std::max(a->smem, b->smem) + 1024;
   }
