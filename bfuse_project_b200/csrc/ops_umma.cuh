@@ -41,9 +41,10 @@ enum UmmaStatus : int {
   UMMA_WAIT_PEERS_TIMEOUT = 0x104,
 };
 
-__host__ __device__ constexpr int umma_stage_bytes(int bn) { return kUmmaABytes + bn * kUmmaRowBytes; }
-__host__ __device__ constexpr int umma_smem_bytes(int bn, int stages) {
-  return kUmmaHeaderBytes + stages * umma_stage_bytes(bn);
+// bm: rows of A (and of the output tile) per CTA, 128 or 256
+__host__ __device__ constexpr int umma_stage_bytes(int bn, int bm = kUmmaBM) { return (bm + bn) * kUmmaRowBytes; }
+__host__ __device__ constexpr int umma_smem_bytes(int bn, int stages, int bm = kUmmaBM) {
+  return kUmmaHeaderBytes + stages * umma_stage_bytes(bn, bm);
 }
 
 // ---- PTX wrappers ----------------------------------------------------------------------------
@@ -178,7 +179,7 @@ __host__ __device__ constexpr uint32_t umma_idesc(int kind, int bn) {
 }
 
 struct GemmUmmaParams {
-  alignas(64) CUtensorMap map_a;    // {K, M, batch}, box {128 B of K, 128, 1}, 128B swizzle
+  alignas(64) CUtensorMap map_a;    // {K, M, batch}, box {128 B of K, BM, 1}, 128B swizzle
   alignas(64) CUtensorMap map_b;    // {K, N, batch}, box {128 B of K, BN, 1}, 128B swizzle
   alignas(64) CUtensorMap map_out;  // {N, M, batch}, box {128 B of N, 32, 1}, 128B swizzle (stores)
   const float *bias;                // [N] or nullptr
@@ -189,6 +190,7 @@ struct GemmUmmaParams {
   int bn;            // output-tile width: 32, 64, 128 or 256 (also the TMEM columns allocated)
   int split;         // CTAs (k-slices) per output tile = cluster width; 1: no split
   int kb_per_slice;  // K blocks (of 128 bytes per row) per k-slice
+  int bm;            // output-tile height: 128, or 256 (two MMAs per k-step share the W tile; split == 1 only)
   long long *timeline;  // diagnostic: when non-null, CTA 0 records globaltimer marks here (see UmmaMark)
 };
 
@@ -334,15 +336,45 @@ struct GemmUmma {
   static constexpr int kOutCols = 128 / kElem;       // output columns per 128-byte store chunk
   static constexpr int kSub = kOutCols / 16;         // 16-column accumulator reads per chunk
 
+  // The MMA issue loop of one k-slice, run by a single thread.  TALL: 256-row tile -- rows 128..255
+  // of A (16 KB further on in the stage) against the same W tile into a second accumulator BN
+  // columns on.  A separate instantiation keeps the common loop free of the extra branch and of a
+  // run-time W offset: it is a chain of dependent instructions whose length sets the MMA rate of
+  // narrow tiles.  Returns false when a wait gave up.
+  template <bool TALL>
+  __device__ __forceinline__ static bool issue_mmas(const TileCtx &c, uint32_t tiles, int stage_bytes, int stages, int num_kb,
+                                                    uint32_t full0, uint32_t empty0, uint32_t tmem_acc, uint32_t idesc, int bn,
+                                                    long long *tl) {
+    // low descriptor word of stage 0; a stage is stage_bytes / 16 further on
+    const uint32_t lo0 = ((tiles >> 4) & 0x3fffu) | (1u << 16), stage16 = (uint32_t)stage_bytes >> 4;
+    constexpr uint32_t b_off = (uint32_t)(TALL ? 2 : 1) * (kUmmaABytes >> 4);
+    uint32_t s = 0, ph = 0, lo = lo0, accumulate = 0;
+    for (int kb = 0; kb < num_kb; ++kb) {
+      if (!mbar_wait(full0 + 8 * s, ph, c.status, UMMA_WAIT_FULL_TIMEOUT)) return false;
+      tc_fence_after();
+      if (kb == 0 && tl) tl[MARK_FIRST_FULL] = (long long)global_ns();
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {  // 4 x 32 bytes of K per stage; +2 = 32 bytes in descriptor units
+        umma_ss<KIND>(tmem_acc, lo + 2 * j, lo + b_off + 2 * j, idesc, accumulate);
+        if (TALL) umma_ss<KIND>(tmem_acc + (uint32_t)bn, lo + (kUmmaABytes >> 4) + 2 * j, lo + b_off + 2 * j, idesc, accumulate);
+        accumulate = 1;
+      }
+      umma_commit(empty0 + 8 * s);  // frees the stage once these MMAs have read it
+      if (++s == (uint32_t)stages) s = 0, ph ^= 1, lo = lo0;
+      else lo += stage16;
+    }
+    return true;
+  }
+
   __device__ __forceinline__ static void run(const Params &p, const TileCtx &c) {
     const int warp = c.tid >> 5, lane = c.tid & 31;
     const int quad = (threadIdx.x >> 5) & 3;  // hardware warp w may only touch TMEM lanes [32 * (w % 4), +32)
-    const int BN = p.bn, kStageBytes = umma_stage_bytes(BN);
+    const int BN = p.bn, BM = p.bm, halves = BM / kUmmaBM, kABytes = BM * kUmmaRowBytes, kStageBytes = umma_stage_bytes(BN, BM);
     const uint32_t idesc = umma_idesc(KIND, BN);
     const int split = p.split, kslice = c.block_x() % split;
     // M tiles vary fastest: the (usually few) CTAs that share a W tile are launched next to each
     // other, so the tile is fetched from HBM once and the others hit L2
-    const int m0 = (c.block_x() / split) * kUmmaBM, n0 = c.block_y() * BN, bz = c.block_z();
+    const int m0 = (c.block_x() / split) * BM, n0 = c.block_y() * BN, bz = c.block_z();
     const int stages = p.stages;
     const int chunks = BN / kOutCols;
 
@@ -369,7 +401,7 @@ struct GemmUmma {
     };
     mark(MARK_START, c.tid == 0);
 
-    if (p.causal && n0 > m0 + kUmmaBM - 1) {
+    if (p.causal && n0 > m0 + BM - 1) {
       // tile entirely above the diagonal (for every k-slice of it): only the mask value to write;
       // k-slice 0 fills one buffer once and stores it to every chunk
       if (warp < 4 && kslice == 0) {
@@ -379,9 +411,12 @@ struct GemmUmma {
         for (int j = 0; j < 8; ++j) st_shared_u4(buf + (uint32_t)lane * 128u + j * 16, mask, mask, mask, mask);
         fence_async_smem();
         __syncwarp();
-        if (lane == 0 && w.m_base < p.M) {
-          for (int ch = 0; ch < chunks; ++ch)
-            if (n0 + ch * kOutCols < p.N) tma_store_3d(&p.map_out, buf, n0 + ch * kOutCols, w.m_base, bz);
+        if (lane == 0) {
+          for (int h = 0; h < halves; ++h) {
+            const int mb = w.m_base + h * kUmmaBM;
+            for (int ch = 0; ch < chunks && mb < p.M; ++ch)
+              if (n0 + ch * kOutCols < p.N) tma_store_3d(&p.map_out, buf, n0 + ch * kOutCols, mb, bz);
+          }
           tma_store_commit();
         }
         w.finish();
@@ -422,13 +457,13 @@ struct GemmUmma {
           const uint32_t dst = tiles + kb * kStageBytes, bar = full0 + 8 * kb;
           mbar_expect_tx(bar, kStageBytes);
           tma_load_3d(dst, &p.map_a, bar, (kb0 + kb) * kBK, m0, bz);
-          tma_load_3d(dst + kUmmaABytes, &p.map_b, bar, (kb0 + kb) * kBK, n0, bz);
+          tma_load_3d(dst + kABytes, &p.map_b, bar, (kb0 + kb) * kBK, n0, bz);
           if (kb == 0) mark(MARK_FIRST_LOAD_ISSUED, true);
         }
       }
       __syncwarp();
     } else if (warp == 5) {
-      tmem_alloc(smem_u32(tmem_slot), BN);
+      tmem_alloc(smem_u32(tmem_slot), BN * halves);
       if (!c.persistent) tmem_relinquish();
     }
     tc_fence_before();
@@ -454,7 +489,7 @@ struct GemmUmma {
           if (!mbar_wait(empty0 + 8 * s, ph, c.status, UMMA_WAIT_EMPTY_TIMEOUT)) break;
           mbar_expect_tx(bar, kStageBytes);
           tma_load_3d(dst, &p.map_a, bar, kcoord, m0, bz);
-          tma_load_3d(dst + kUmmaABytes, &p.map_b, bar, kcoord, n0, bz);
+          tma_load_3d(dst + kABytes, &p.map_b, bar, kcoord, n0, bz);
           kcoord += kBK;
           if (++s == (uint32_t)stages) s = 0, ph ^= 1, dst = tiles, bar = full0;
           else dst += kStageBytes, bar += 8;
@@ -464,24 +499,8 @@ struct GemmUmma {
       __syncwarp();
     } else if (warp == 5) {
       if (elect_one()) {
-        // descriptor words of stage 0 (see umma_smem_desc); a stage is kStageBytes / 16 further on
-        const uint32_t lo0 = ((tiles >> 4) & 0x3fffu) | (1u << 16), stage16 = (uint32_t)kStageBytes >> 4;
-        uint32_t s = 0, ph = 0, lo = lo0, accumulate = 0;
-        bool ok = true;
-        for (int kb = 0; kb < num_kb; ++kb) {
-          ok = mbar_wait(full0 + 8 * s, ph, c.status, UMMA_WAIT_FULL_TIMEOUT);
-          if (!ok) break;
-          tc_fence_after();
-          if (kb == 0) mark(MARK_FIRST_FULL, true);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {  // 4 x 32 bytes of K per stage; +2 = 32 bytes in descriptor units
-            umma_ss<KIND>(tmem_acc, lo + 2 * j, lo + (kUmmaABytes >> 4) + 2 * j, idesc, accumulate);
-            accumulate = 1;
-          }
-          umma_commit(empty0 + 8 * s);  // frees the stage once these MMAs have read it
-          if (++s == (uint32_t)stages) s = 0, ph ^= 1, lo = lo0;
-          else lo += stage16;
-        }
+        bool ok = halves == 2 ? issue_mmas<true>(c, tiles, kStageBytes, stages, num_kb, full0, empty0, tmem_acc, idesc, BN, tl)
+                              : issue_mmas<false>(c, tiles, kStageBytes, stages, num_kb, full0, empty0, tmem_acc, idesc, BN, tl);
         umma_commit(acc_bar);  // accumulator complete (also arrives if the loop bailed out)
         mark(MARK_LAST_MMA_ISSUED, true);
         // The stage-release arrivals of the last ring pass are asynchronous and nobody consumes them;
@@ -501,23 +520,29 @@ struct GemmUmma {
       mark(MARK_ACC_READY, c.tid == 0);
       if (acc_ok && split == 1) {
 #pragma unroll 1
-        for (int ch = 0; ch < chunks; ++ch) {
-          const uint32_t buf = w.begin_chunk();
+        for (int h = 0; h < halves; ++h) {  // accumulator h holds output rows [m0 + 128 h, +128)
+          const uint32_t trow = tmem_row + (uint32_t)(h * BN);
+          w.m_base = m0 + h * kUmmaBM + quad * 32;
+#pragma unroll 1
+          for (int ch = 0; ch < chunks; ++ch) {
+            const uint32_t buf = w.begin_chunk();
 #pragma unroll
-          for (int sub = 0; sub < kSub; sub += 2) {  // two accumulator reads in flight per wait
-            uint32_t r0[16], r1[16];
-            tmem_ld_32x16(tmem_row + (ch * kSub + sub) * 16, r0);
-            tmem_ld_32x16(tmem_row + (ch * kSub + sub + 1) * 16, r1);
-            tmem_ld_wait();
-            float v[16];
+            for (int sub = 0; sub < kSub; sub += 2) {  // two accumulator reads in flight per wait
+              uint32_t r0[16], r1[16];
+              tmem_ld_32x16(trow + (ch * kSub + sub) * 16, r0);
+              tmem_ld_32x16(trow + (ch * kSub + sub + 1) * 16, r1);
+              tmem_ld_wait();
+              float v[16];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r0[j]);
-            w.put16(buf, sub, n0 + ch * kOutCols, v, bias_tile);
+              for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r0[j]);
+              w.put16(buf, sub, n0 + ch * kOutCols, v, bias_tile);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r1[j]);
-            w.put16(buf, sub + 1, n0 + ch * kOutCols, v, bias_tile);
+              for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r1[j]);
+              w.put16(buf, sub + 1, n0 + ch * kOutCols, v, bias_tile);
+            }
+            w.end_chunk(buf, n0 + ch * kOutCols);
           }
-          w.end_chunk(buf, n0 + ch * kOutCols);
+          w.flush();  // a group never spans two row blocks
         }
         w.finish();
         mark(MARK_PARTIAL_WRITTEN, c.tid == 0);
@@ -585,7 +610,7 @@ struct GemmUmma {
     }
     tc_fence_before();
     c.sync();
-    if (warp == 5) tmem_dealloc(tmem_acc, BN);
+    if (warp == 5) tmem_dealloc(tmem_acc, BN * halves);
     if (c.persistent && c.tid < stages) {  // the next tile of a persistent CTA initialises them again
       mbar_inval(full0 + 8 * c.tid);
       mbar_inval(empty0 + 8 * c.tid);

@@ -110,9 +110,9 @@ int pick_row_threads(int cols, int vec_elems, int max_vec) {
   return 0;
 }
 
-int umma_min_stages(int bn, int split, int elem) {
+int umma_min_stages(int bn, int split, int elem, int bm = kUmmaBM) {
   // after the MMAs the ring doubles as the store buffers and, with split > 1, as the receive area
-  return ceil_div(umma_epilogue_bytes(bn, split, elem), umma_stage_bytes(bn));
+  return ceil_div(umma_epilogue_bytes(bn, split, elem), umma_stage_bytes(bn, bm));
 }
 
 // Tile width and k-slices of a tensor-core GEMM from a small cost model fitted to measurements on
@@ -204,7 +204,7 @@ int default_launch(const bfuse_context *ctx, bfuse_kernel_desc *d, std::string *
     case BFUSE_OP_GEMM_BF16: {
       if (s[0] <= 0 || s[1] <= 0 || s[2] <= 0 || s[3] <= 0) { *err = "gemm: batch, M, N, K must be positive"; return BFUSE_ERR_SHAPE; }
       const int eb = d->op == BFUSE_OP_GEMM_TF32 ? 4 : 2;
-      int bn = s[4], split = s[5], q;
+      int bn = s[4], split = s[5], bm = s[6], q;
       if (bn <= 0 || split <= 0) pick_tile(s[0], s[1], s[2], s[3], eb, sm, bn, split, &bn, &split);
       if (bn != 32 && bn != 64 && bn != 128 && bn != 256) { *err = "gemm: BN must be 32, 64, 128 or 256"; return BFUSE_ERR_SHAPE; }
       d->shape[4] = bn;
@@ -213,15 +213,22 @@ int default_launch(const bfuse_context *ctx, bfuse_kernel_desc *d, std::string *
       q = ceil_div(num_kb, split);
       split = ceil_div(num_kb, q);
       d->shape[5] = split;
+      // 256-row tiles (two MMAs per k-step share one W tile: a third less operand traffic from L2 per
+      // flop) once the 128-row tiles alone would fill every SM and K is long enough for the main
+      // loop to dominate: that is where L2 -> SM bandwidth, not the tensor pipe, sets the pace of
+      // 128 x 256 tiles (short-K shapes are bound by their output stores and prefer two CTAs per SM)
+      if (bm <= 0) bm = (bn == 256 && split == 1 && num_kb >= 16 && s[1] > kUmmaBM && (long long)s[0] * ceil_div(s[1], kUmmaBM) * ceil_div(s[2], bn) >= sm) ? 256 : kUmmaBM;
+      if ((bm != kUmmaBM && bm != 256) || (bm == 256 && split != 1)) { *err = "gemm: BM must be 128, or 256 with split = 1"; return BFUSE_ERR_SHAPE; }
+      d->shape[6] = bm;
       // ring depth: enough to cover the k-slice, at most 8, and large enough to hold the partial tile
       // when K is split.  Within ~200 KB when the operator and an equal partner leave every CTA an SM
       // of its own (operands arriving from HBM need ~1 us of loads in flight per SM) or for the 256-wide
       // tile, else within ~100 KB so that two CTAs share an SM.
-      const long long ctas = (long long)split * s[0] * ceil_div(s[1], kUmmaBM) * ceil_div(s[2], bn);
+      const long long ctas = (long long)split * s[0] * ceil_div(s[1], bm) * ceil_div(s[2], bn);
       const int budget = (bn == 256 || 2 * ctas <= sm) ? 200 * 1024 : 100 * 1024;
-      int stages = std::min({q, kUmmaMaxStages, (budget - kUmmaHeaderBytes) / umma_stage_bytes(bn)});
-      stages = std::max({stages, 1, umma_min_stages(bn, split, d->op == BFUSE_OP_GEMM_TF32 ? 4 : 2)});
-      set(split * ceil_div(s[1], kUmmaBM), ceil_div(s[2], bn), s[0], kUmmaThreads, 1, umma_smem_bytes(bn, stages), 4);
+      int stages = std::min({q, kUmmaMaxStages, (budget - kUmmaHeaderBytes) / umma_stage_bytes(bn, bm)});
+      stages = std::max({stages, 1, umma_min_stages(bn, split, eb, bm)});
+      set(split * ceil_div(s[1], bm), ceil_div(s[2], bn), s[0], kUmmaThreads, 1, umma_smem_bytes(bn, stages, bm), 4);
       return BFUSE_OK;
     }
     default:
@@ -399,7 +406,7 @@ int build_params(bfuse_context *ctx, KernelRec &k) {
     case BFUSE_OP_GEMM_TF32:
     case BFUSE_OP_GEMM_BF16: {
       const int eb = d.op == BFUSE_OP_GEMM_TF32 ? 4 : 2;
-      const int bn = s[4], split = s[5] > 0 ? s[5] : 1;
+      const int bn = s[4], split = s[5] > 0 ? s[5] : 1, bm = s[6] > 0 ? s[6] : kUmmaBM;
       if (s[0] <= 0 || s[1] <= 0 || s[2] <= 0 || s[3] <= 0) return shape_err("batch, M, N, K must be positive");
       if (bn != 32 && bn != 64 && bn != 128 && bn != 256) return shape_err("shape[4] (BN) must be 32, 64, 128 or 256");
       if (bn * eb < 128) return shape_err("shape[4] (BN) must span at least 128 bytes of output (64 for bf16): stores leave in 128-byte chunks");
@@ -408,14 +415,16 @@ int build_params(bfuse_context *ctx, KernelRec &k) {
       const int num_kb = ceil_div(s[3] * eb, kUmmaRowBytes), q = ceil_div(num_kb, split);
       if (split > 8 || (split - 1) * q >= num_kb) return shape_err("shape[5] (split) must be 1..8 with every k-slice non-empty");
       if (kd.bx != kUmmaThreads || kd.by != 1 || kd.bz != 1) return shape_err("BlockDim must be (192, 1, 1)");
-      if (kd.gx != split * ceil_div(s[1], kUmmaBM) || kd.gy != ceil_div(s[2], bn) || kd.gz != s[0])
-        return shape_err("GridDim must be (split * ceil(M/128), ceil(N/BN), batch)");
-      if (k.smem < (size_t)umma_smem_bytes(bn, umma_min_stages(bn, split, eb)))
+      if ((bm != kUmmaBM && bm != 256) || (bm == 256 && split != 1) || bn * (bm / kUmmaBM) > 512)
+        return shape_err("shape[6] (BM) must be 128, or 256 with split = 1");
+      if (kd.gx != split * ceil_div(s[1], bm) || kd.gy != ceil_div(s[2], bn) || kd.gz != s[0])
+        return shape_err("GridDim must be (split * ceil(M/BM), ceil(N/BN), batch)");
+      if (k.smem < (size_t)umma_smem_bytes(bn, umma_min_stages(bn, split, eb, bm), bm))
         return shape_err("shared memory below the store buffers (and, for a split GEMM, the receive area of the k-slices)");
       k.cluster = split;
       GemmUmmaParams p;
       std::memset(&p, 0, sizeof(p));
-      int rc = encode_map(ctx, &p.map_a, eb, a[0], s[3], s[1], s[0], kUmmaBM);
+      int rc = encode_map(ctx, &p.map_a, eb, a[0], s[3], s[1], s[0], bm);
       if (rc) return rc;
       rc = encode_map(ctx, &p.map_b, eb, a[1], s[3], s[2], s[0], bn);
       if (rc) return rc;
@@ -425,7 +434,8 @@ int build_params(bfuse_context *ctx, KernelRec &k) {
       p.out = a[3];
       p.batch = s[0], p.M = s[1], p.N = s[2], p.K = s[3];
       p.causal = (int)(d.flags & BFUSE_FLAG_CAUSAL);
-      p.stages = std::min<int>(kUmmaMaxStages, (int)((k.smem - kUmmaHeaderBytes) / umma_stage_bytes(bn)));
+      p.stages = std::min<int>(kUmmaMaxStages, (int)((k.smem - kUmmaHeaderBytes) / umma_stage_bytes(bn, bm)));
+      p.bm = bm;
       p.bn = bn;
       p.split = split;
       p.kb_per_slice = q;
@@ -516,8 +526,9 @@ bool ring_info(const KernelRec &k, int *header, int *stage_bytes, int *min_stage
   const int *s = k.desc.shape;
   if (k.desc.op == BFUSE_OP_GEMM_TF32 || k.desc.op == BFUSE_OP_GEMM_BF16) {
     const int eb = k.desc.op == BFUSE_OP_GEMM_TF32 ? 4 : 2;
-    *header = kUmmaHeaderBytes, *stage_bytes = umma_stage_bytes(s[4]);
-    *min_stages = umma_min_stages(s[4], std::max(1, s[5]), eb);
+    const int bm = s[6] > 0 ? s[6] : kUmmaBM;
+    *header = kUmmaHeaderBytes, *stage_bytes = umma_stage_bytes(s[4], bm);
+    *min_stages = umma_min_stages(s[4], std::max(1, s[5]), eb, bm);
     *stages = reinterpret_cast<const GemmUmmaParams *>(k.params)->stages;
     return true;
   }
@@ -739,6 +750,14 @@ int bfuse_register_fusion(bfuse_context *ctx, int kernel1, int kernel2, int patt
   // shared memory: union for block-level fusion, sum for thread-level fusion (Matchers.cc:512-519)
   f->stages[0] = f->stages[1] = 0;
   if (thread_split) {
+    // both operators allocate tensor memory in the same CTA; an allocation that cannot be granted
+    // would block for ever, so the sum has to fit the SM's 512 columns
+    auto tmem_cols = [](const KernelRec &k) {
+      if (k.desc.op == BFUSE_OP_GEMM_TF32 || k.desc.op == BFUSE_OP_GEMM_BF16) return k.desc.shape[4] * std::max(1, k.desc.shape[6] / kUmmaBM);
+      return k.desc.op == BFUSE_OP_CONV2D_TF32 ? kConvBN : 0;
+    };
+    if (tmem_cols(*a) + tmem_cols(*b) > 512)
+      return fail(ctx, BFUSE_ERR_UNSUPPORTED, "thread split: the two operators need more than 512 tensor-memory columns together");
     // both windows live side by side; rings registered for a whole SM each are made shallower until
     // the sum fits (the deeper one first), never below what the operator's epilogue needs
     size_t win[2] = {a->smem, b->smem};

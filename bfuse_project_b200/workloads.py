@@ -92,8 +92,8 @@ def rope(name, rng, seq, heads, dim, theta):
     return KernelSpec(name, OP_ROPE_BF16, (seq, heads, dim), [q, rope_inv_freq(dim, theta), np.zeros_like(q)], [2])
 
 
-def gemm(name, rng, op, batch, M, N, K, bias=False, causal=False, w_std=0.02, a=None, bn=0, split=0):
-    """out[b, M, N] = A[b, M, K] . W[b, N, K]^T (+ bias).  bn / split = 0: chosen by the runtime."""
+def gemm(name, rng, op, batch, M, N, K, bias=False, causal=False, w_std=0.02, a=None, bn=0, split=0, bm=0):
+    """out[b, M, N] = A[b, M, K] . W[b, N, K]^T (+ bias).  bn / split / bm = 0: chosen by the runtime."""
     A = rng.standard_normal((batch, M, K), dtype=np.float32) if a is None else a
     W = (w_std * rng.standard_normal((batch, N, K), dtype=np.float32)).astype(np.float32)
     bvec = rng.standard_normal(N, dtype=np.float32) * 0.1 if bias else None
@@ -103,7 +103,7 @@ def gemm(name, rng, op, batch, M, N, K, bias=False, causal=False, w_std=0.02, a=
         out = np.zeros((batch, M, N), np.uint16)
     else:
         out = np.zeros((batch, M, N), np.float32)
-    shape = (batch, M, N, K, bn, split) if op in (OP_GEMM_TF32, OP_GEMM_BF16) else (batch, M, N, K)
+    shape = (batch, M, N, K, bn, split, bm) if op in (OP_GEMM_TF32, OP_GEMM_BF16) else (batch, M, N, K)
     return KernelSpec(name, op, shape, [A, W, bvec, out], [3], flags=FLAG_CAUSAL if causal else 0,
                       flops=2.0 * batch * M * N * K)
 

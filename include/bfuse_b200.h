@@ -43,9 +43,10 @@ enum {
   BFUSE_OP_ROPE_BF16 = 3,     /* args: q, inv_freq, y            shape: seq, heads, dim                     */
   BFUSE_OP_GEMM_F32_SIMT = 4, /* args: A, W, bias|NULL, out      shape: batch, M, N, K                      */
   BFUSE_OP_CONV2D_F32_SIMT = 5, /* args: x, w, y   shape: n, ci, h, w, co, kh, kw, stride, pad             */
-  BFUSE_OP_GEMM_TF32 = 6,     /* as GEMM_F32_SIMT, tcgen05 kind::tf32; shape[4] = BN tile, shape[5] = k-slices */
-                              /* per tile (a thread-block cluster reduces them); 0 = chosen by the runtime  */
-  BFUSE_OP_GEMM_BF16 = 7,     /* bf16 A, W, out; fp32 accumulate; tcgen05 kind::f16; shape[4], shape[5] same */
+  BFUSE_OP_GEMM_TF32 = 6,     /* as GEMM_F32_SIMT, tcgen05 kind::tf32; shape[4] = BN tile width (32..256),   */
+                              /* shape[5] = k-slices per tile (a thread-block cluster reduces them),        */
+                              /* shape[6] = BM tile height (128, or 256 with one k-slice); 0 = runtime's choice */
+  BFUSE_OP_GEMM_BF16 = 7,     /* bf16 A, W, out; fp32 accumulate; tcgen05 kind::f16; shape[4..6] as above    */
   BFUSE_OP_CONV2D_TF32 = 8,   /* as CONV2D_F32_SIMT on tcgen05 kind::tf32 (implicit GEMM)                   */
   BFUSE_OP_COUNT = 9
 };

@@ -42,6 +42,22 @@ def test_ragged_umma_shapes(rt):
     run_and_check(rt, wl.PairSpec("ragged_bf16", c, d, "bf16", "tensor"), BLOCK_PATTERNS)
 
 
+def test_tall_tiles_share_the_w_tile(rt):
+    """256-row tiles (two accumulators, one W tile per k-step): ragged M and N, bias, causal mask, both
+    operand kinds, beside a 128-row partner; fused == unfused bit for bit, oracle within tolerance."""
+    rng = np.random.default_rng(77)
+    a = wl.gemm("t1", rng, bf.OP_GEMM_TF32, 2, 300, 520, 200, bias=True, w_std=1.0, bn=256, split=1, bm=256)
+    b = wl.gemm("t2", rng, bf.OP_GEMM_TF32, 1, 512, 512, 96, causal=True, w_std=1.0, bn=128, split=1, bm=256)
+    run_and_check(rt, wl.PairSpec("tall_tf32", a, b, "tf32", "hbm"), BLOCK_PATTERNS)
+    c = wl.gemm("t3", rng, bf.OP_GEMM_BF16, 1, 640, 768, 1024, w_std=0.05, bn=256, split=1, bm=256)
+    d = wl.gemm("t4", rng, bf.OP_GEMM_BF16, 1, 130, 136, 72, w_std=0.1, bn=64, split=1, bm=128)
+    pair = run_and_check(rt, wl.PairSpec("tall_bf16", c, d, "bf16", "tensor"), BLOCK_PATTERNS)
+    # two operators of 512 and 64 tensor-memory columns cannot share one CTA
+    with pytest.raises(bf.BfuseError) as e:
+        pair.fusion(bf.THREAD_SPLIT, 1, 1)
+    assert e.value.code == 7
+
+
 @pytest.mark.parametrize("kind", ["tf32", "bf16"])
 def test_split_k_cluster_reduction(rt, kind):
     """k-slices of a tile reduced over distributed shared memory: every split width, ragged M / N,
