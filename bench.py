@@ -36,6 +36,7 @@ sys.path.insert(0, ROOT)
 WORKLOAD = "cfg2_q_k_proj"
 NCU_TRAFFIC_BYTES = 7987968   # dram__bytes_read.sum + dram__bytes_write.sum of the fused kernel, one launch (profiles/)
 L2_BYTES = 126 * 1024 * 1024
+NAIVE_BODY_PAIRS = ("cfg2_q_k_proj", "cfg3_qkt_res_layernorm", "cfg5_conv_branches")   # fp32 pairs with a CUDA-core body
 
 
 def peaks():
@@ -129,6 +130,40 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def run_sweep(args, rt, torch, rank, world, local, pk):
+    """The operator cross-product sweep, its pairs dealt round-robin to the ranks; rank 0 prints one
+    JSON line with the summary (and writes the per-pair table when asked to)."""
+    from bfuse_project_b200 import partition, sweep
+    n_ops = min(args.sweep_limit or len(sweep.SWEEP_OPS), len(sweep.SWEEP_OPS))
+    sets = sweep.build_operands(rt, torch, local, seed=0, ops=sweep.SWEEP_OPS[:n_ops])
+    todo = sweep.pair_indices(n_ops)
+    mine = partition.assign_pairs(todo, world, rank)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    res = sweep.measure(rt, sets, mine, pk["hbm_gbs"], pk["bf16_tflops"] * 0.5)
+    wall = time.perf_counter() - t0
+    assert rt.read_status() == 0, "a bounded device-side wait gave up during the sweep"
+    if world > 1:
+        import torch.distributed as dist
+        gathered, walls = [None] * world, [None] * world
+        dist.all_gather_object(gathered, res)
+        dist.all_gather_object(walls, wall)
+        res, wall = partition.merge_results(gathered), partition.max_over_ranks(walls)
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    line = {"metric": "sweep_wall_s", "value": wall, "unit": "s", "n_gpus": world, "higher_is_better": False, "scaling": "strong",
+            "dtype": "tf32", "data": "synthetic",
+            "config": {"workload": "operator cross-product sweep: %d operators, %d pairs (upper triangle), zig-zag 1:1 fusion vs "
+                                   "back-to-back launches; 3 warm-ups + 30 timed launches per mode" % (n_ops, len(todo)),
+                       "partition": "pair i on rank i mod %d" % world},
+            "sweep": sweep.summarise(res)}
+    if args.sweep_out:
+        with open(args.sweep_out, "w") as f:
+            json.dump({"operators": [{"name": n, "shape": list(sh)} for n, sh in sweep.SWEEP_OPS[:n_ops]], "pairs": res}, f, indent=0)
+    print(json.dumps(line), flush=True)
+
+
 def replay_us(rt, torch, graph, launches, reps=5, warm=3):
     """Microseconds per launch of a CUDA-graph replay, CUDA events on torch's current stream."""
     s = torch.cuda.current_stream().cuda_stream
@@ -174,6 +209,16 @@ def measure_pair(rt, torch, bf, wl, pk, name, device, conv_batch=1, max_reps=24)
     res["roofline_frac"] = res["roofline_us"] / best
     del pairs
     torch.cuda.empty_cache()
+    if name in NAIVE_BODY_PAIRS and conv_batch == 1:
+        # the reference's zig-zag dispatch around plain CUDA-core fp32 bodies of the same operators:
+        # the stand-in for the reference fuser's output at this exact shape (which cannot be generated here)
+        npairs = [wl.DevicePair(rt, wl.make_pair(name, seed=s, tensor_cores=False), device) for s in range(reps)]
+        nf = [p.fusion(bf.ZIGZAG, 1, 1) for p in npairs]
+        res["naive_bodies_zigzag_us"] = replay_us(rt, torch, rt.graph_create(nf, 4), reps)
+        res["naive_bodies_sequential_us"] = replay_us(rt, torch, rt.graph_create(nf, 3), reps)
+        res["speedup_vs_naive_bodies_zigzag"] = res["naive_bodies_zigzag_us"] / best
+        del npairs
+        torch.cuda.empty_cache()
     return res
 
 
@@ -245,6 +290,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="bfuse")
     ap.add_argument("--quick", action="store_true", help="skip the side measurements of the other pairs")
+    ap.add_argument("--sweep", action="store_true", help="run the 42 x 42 operator cross-product sweep instead (pair i on rank i mod N)")
+    ap.add_argument("--sweep-out", default="", help="with --sweep: also write the per-pair table to this JSON file")
+    ap.add_argument("--sweep-limit", type=int, default=0, help="with --sweep: only the first N operators")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
 
@@ -267,6 +315,8 @@ def main():
     pk = peaks()
 
     rt = bf.Runtime(local)
+    if args.sweep:
+        return run_sweep(args, rt, torch, rank, world, local, pk)
     spec0 = wl.make_pair(WORKLOAD, seed=0)
     reps = int(2.2 * L2_BYTES / spec0.bytes) + 1           # instances per step, together > 2 x L2
     specs = [spec0] + [wl.make_pair(WORKLOAD, seed=s) for s in range(1, reps)]

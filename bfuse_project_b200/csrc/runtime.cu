@@ -69,6 +69,7 @@ struct bfuse_context {
   cudaStream_t s1, s2, own;
   cudaEvent_t ev_fork, ev_j1, ev_j2;
   int *d_status;
+  int *h_status;  // pinned mirror: the host-buffer entry points read the status word with the output copies
   EncodeTiledFn encode;
   PairEntry pairs[kNumOps][kNumOps];
   SingleEntry singles[kNumOps];
@@ -632,7 +633,8 @@ int bfuse_create(int device, bfuse_context **out) {
       cudaEventCreateWithFlags(&ctx->ev_fork, cudaEventDisableTiming) != cudaSuccess ||
       cudaEventCreateWithFlags(&ctx->ev_j1, cudaEventDisableTiming) != cudaSuccess ||
       cudaEventCreateWithFlags(&ctx->ev_j2, cudaEventDisableTiming) != cudaSuccess ||
-      cudaMalloc(&ctx->d_status, sizeof(int)) != cudaSuccess || cudaMemset(ctx->d_status, 0, sizeof(int)) != cudaSuccess) {
+      cudaMalloc(&ctx->d_status, sizeof(int)) != cudaSuccess || cudaMemset(ctx->d_status, 0, sizeof(int)) != cudaSuccess ||
+      cudaHostAlloc(&ctx->h_status, sizeof(int), cudaHostAllocDefault) != cudaSuccess) {
     ctx->err = std::string("context set-up failed: ") + cudaGetErrorString(cudaGetLastError());
     return bail(BFUSE_ERR_CUDA);
   }
@@ -649,6 +651,7 @@ int bfuse_destroy(bfuse_context *ctx) {
   for (auto &f : ctx->fusions)
     if (f->queue_ctr) cudaFree(f->queue_ctr);
   cudaFree(ctx->d_status);
+  cudaFreeHost(ctx->h_status);
   cudaEventDestroy(ctx->ev_fork);
   cudaEventDestroy(ctx->ev_j1);
   cudaEventDestroy(ctx->ev_j2);
@@ -981,9 +984,10 @@ static int copy_out(bfuse_context *ctx, KernelRec &k, void *const *host, cudaStr
   return BFUSE_OK;
 }
 static int finish(bfuse_context *ctx, cudaStream_t s) {
+  // the status word rides behind the output copies on the same stream: one synchronisation in all
+  CK(cudaMemcpyAsync(ctx->h_status, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost, s));
   CK(cudaStreamSynchronize(s));
-  int st = 0;
-  CK(cudaMemcpy(&st, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost));
+  const int st = *ctx->h_status;
   if (st) {
     cudaMemset(ctx->d_status, 0, sizeof(int));
     char buf[64];

@@ -1,0 +1,131 @@
+"""The operator cross-product sweep: every operator of the reference's benchmark suite against
+every other one (upper triangle, diagonal included), fused vs back-to-back.
+
+The reference sweeps 42 shapes x 42 shapes at batch 1024 (test-utils/examples/benchmark.yaml:1-88:
+8 dense, 12 batch-matmul, 22 conv2d; pairs (K1, K2 >= K1) as in scripts/profile_test_suite.py:37-46).
+Here the same 42 operators run at the single-sequence sizes of the reference's model studies
+(test-utils/examples/llm.yaml: 512 tokens, per-model head counts; test-utils/examples/resnet-18.yaml
+and the Inception-v3 shapes of benchmark.yaml at one image), on tensor cores where the tcgen05
+bodies cover the shape (dense / batch-matmul: fp32 in, tf32 MMA; conv: tf32 implicit GEMM) and on
+the CUDA-core conv body otherwise.  Inputs are seeded synthetic tensors created on the device.
+
+Timing follows the reference's protocol -- 3 warm-up launches, then 30 timed ones, mean
+(scripts/profile_test_suite.py:10-11) -- on the same buffers every launch, i.e. operands that fit
+stay in L2 as they do in the reference's own loop.
+"""
+import math
+
+from . import (BfuseError, MODE_FUSED, MODE_SEQUENTIAL, OP_CONV2D_F32_SIMT, OP_CONV2D_TF32, OP_GEMM_TF32, ZIGZAG)
+
+# name -> shape.  dense: (M, K, N); bgemm: (batch, M, K, N); conv2d: (N, H, W, CO, CI, KH, KW, stride, pad)
+SWEEP_OPS = (
+    ("dense_0", (512, 768, 768)), ("dense_1", (512, 768, 3072)), ("dense_2", (512, 3072, 768)),
+    ("dense_3", (512, 768, 2304)), ("dense_4", (512, 4096, 4096)), ("dense_5", (512, 4096, 1024)),
+    ("dense_6", (512, 4096, 14336)), ("dense_7", (512, 14336, 4096)),
+    ("bgemm_0", (12, 512, 64, 512)), ("bgemm_1", (12, 512, 512, 64)), ("bgemm_2", (32, 512, 128, 512)),
+    ("bgemm_3", (32, 512, 512, 128)), ("bgemm_4", (16, 256, 64, 256)), ("bgemm_5", (16, 256, 256, 64)),
+    ("bgemm_6", (16, 256, 80, 256)), ("bgemm_7", (16, 256, 256, 80)), ("bgemm_8", (16, 208, 64, 208)),
+    ("bgemm_9", (16, 208, 208, 64)), ("bgemm_10", (16, 208, 80, 208)), ("bgemm_11", (16, 208, 208, 80)),
+    ("conv2d_0", (1, 224, 224, 64, 3, 7, 7, 2, 3)), ("conv2d_1", (1, 56, 56, 64, 64, 3, 3, 1, 1)),
+    ("conv2d_2", (1, 56, 56, 64, 64, 1, 1, 1, 0)), ("conv2d_3", (1, 56, 56, 128, 64, 3, 3, 2, 1)),
+    ("conv2d_4", (1, 28, 28, 128, 128, 3, 3, 1, 1)), ("conv2d_5", (1, 56, 56, 128, 64, 1, 1, 2, 0)),
+    ("conv2d_6", (1, 28, 28, 256, 128, 3, 3, 2, 1)), ("conv2d_7", (1, 14, 14, 256, 256, 3, 3, 1, 1)),
+    ("conv2d_8", (1, 28, 28, 256, 128, 1, 1, 2, 0)), ("conv2d_9", (1, 14, 14, 512, 256, 3, 3, 2, 1)),
+    ("conv2d_10", (1, 7, 7, 512, 512, 3, 3, 1, 1)), ("conv2d_11", (1, 14, 14, 512, 256, 1, 1, 2, 0)),
+    ("conv2d_12", (1, 35, 35, 64, 256, 1, 1, 1, 0)), ("conv2d_13", (1, 35, 35, 48, 256, 1, 1, 1, 0)),
+    ("conv2d_14", (1, 35, 35, 64, 288, 1, 1, 1, 0)), ("conv2d_15", (1, 35, 35, 48, 288, 1, 1, 1, 0)),
+    ("conv2d_16", (1, 35, 35, 384, 288, 3, 3, 2, 0)), ("conv2d_17", (1, 35, 35, 96, 96, 3, 3, 2, 0)),
+    ("conv2d_18", (1, 17, 17, 192, 768, 1, 1, 1, 0)), ("conv2d_19", (1, 17, 17, 128, 768, 1, 1, 1, 0)),
+    ("conv2d_20", (1, 17, 17, 160, 768, 1, 1, 1, 0)), ("conv2d_21", (1, 17, 17, 320, 192, 3, 3, 2, 0)),
+)
+
+
+def pair_indices(n=len(SWEEP_OPS)):
+    """(i, j) with j >= i, in the reference's enumeration order."""
+    return [(i, j) for i in range(n) for j in range(i, n)]
+
+
+def conv_on_tensor_cores(shape):
+    """Whether the tcgen05 implicit-GEMM body takes this conv (its offset table, TMA stride rule
+    and tap mask limit what it covers); otherwise the CUDA-core body runs it."""
+    n, h, w, co, ci, kh, kw, stride, pad = shape
+    oh, ow = (h + 2 * pad - kh) // stride + 1, (w + 2 * pad - kw) // stride + 1
+    k = ci * kh * kw
+    return k % 4 == 0 and k <= 1024 and (oh * ow) % 4 == 0 and kh * kw <= 31
+
+
+class SweepOperand:
+    """One operator of the sweep resident on the device and registered with the runtime."""
+
+    def __init__(self, rt, torch, device, name, shape, gen):
+        self.name, self.shape = name, shape
+        dev = torch.device("cuda", device)
+
+        def randn(*dims, std=1.0):
+            return torch.randn(*dims, device=dev, dtype=torch.float32, generator=gen) * std
+
+        if name.startswith("conv2d"):
+            n, h, w, co, ci, kh, kw, stride, pad = shape
+            oh, ow = (h + 2 * pad - kh) // stride + 1, (w + 2 * pad - kw) // stride + 1
+            self.bufs = [randn(n, ci, h, w), randn(co, ci, kh, kw, std=math.sqrt(2.0 / (ci * kh * kw))),
+                         torch.zeros(n, co, oh, ow, device=dev)]
+            self.op = OP_CONV2D_TF32 if conv_on_tensor_cores(shape) else OP_CONV2D_F32_SIMT
+            self.flops = 2.0 * n * co * oh * ow * ci * kh * kw
+            desc = rt.describe(name, self.op, (n, ci, h, w, co, kh, kw, stride, pad), [b.data_ptr() for b in self.bufs])
+        else:
+            b, (m, k, nn) = (1, shape) if name.startswith("dense") else (shape[0], shape[1:])
+            self.bufs = [randn(b, m, k), randn(b, nn, k, std=0.02 if b == 1 else 1.0), torch.zeros(b, m, nn, device=dev)]
+            self.op = OP_GEMM_TF32
+            self.flops = 2.0 * b * m * nn * k
+            desc = rt.describe(name, self.op, (b, m, nn, k, 0, 0), [self.bufs[0].data_ptr(), self.bufs[1].data_ptr(), None,
+                                                                    self.bufs[2].data_ptr()])
+        self.bytes = sum(t.numel() * t.element_size() for t in self.bufs)
+        self.launch = (desc.GridDim.tuple(), desc.BlockDim.tuple(), desc.smem_bytes)
+        self.kernel = rt.register_kernel(desc)
+
+
+def build_operands(rt, torch, device=0, seed=0, ops=SWEEP_OPS):
+    """Two independent sets of the sweep's operators (the reference's kernel1 / kernel2 sets)."""
+    gen = torch.Generator(device=torch.device("cuda", device))
+    gen.manual_seed(seed)
+    return [[SweepOperand(rt, torch, device, name + suffix, shape, gen) for name, shape in ops] for suffix in ("_k1", "_k2")]
+
+
+def measure(rt, sets, pairs, hbm_gbs, tf32_tflops, pattern=ZIGZAG, warmup=3, iters=30):
+    """{"<k1>|<k2>": {...}} for the given (i, j) pairs: fused and sequential microseconds (mean of
+    `iters` launches after `warmup`), speed-up, and the pair's roofline time."""
+    out = {}
+    for i, j in pairs:
+        a, b = sets[0][i], sets[1][j]
+        key = "%s|%s" % (a.name[:-3], b.name[:-3])   # without the set suffix
+        try:
+            f = rt.register_fusion(a.kernel, b.kernel, pattern, 1, 1)
+        except BfuseError as e:
+            out[key] = {"error": str(e)[:120]}
+            continue
+        fused = rt.time(f, MODE_FUSED, warmup, iters)[0]
+        seq = rt.time(f, MODE_SEQUENTIAL, warmup, iters)[0]
+        roof = max((a.bytes + b.bytes) / (hbm_gbs * 1e3), (a.flops + b.flops) / (tf32_tflops * 1e6))
+        out[key] = {"fused_us": fused, "sequential_us": seq, "speedup_vs_sequential": seq / fused, "roofline_us": roof,
+                    "roofline_frac": roof / fused}
+    return out
+
+
+def summarise(results):
+    """Counts and geometric means over a sweep's result dict."""
+    ok = [v for v in results.values() if "error" not in v]
+    if not ok:
+        return {"pairs": 0, "errors": len(results)}
+    sp = [v["speedup_vs_sequential"] for v in ok]
+    by_kind = {}
+    for k, v in results.items():
+        if "error" in v:
+            continue
+        kinds = "x".join(sorted(n.split("_")[0] for n in k.split("|")))
+        by_kind.setdefault(kinds, []).append(v["speedup_vs_sequential"])
+    gm = lambda xs: math.exp(sum(math.log(x) for x in xs) / len(xs))
+    return {"pairs": len(ok), "errors": len(results) - len(ok), "geomean_speedup_vs_sequential": gm(sp),
+            "min_speedup": min(sp), "max_speedup": max(sp), "pairs_faster_than_sequential": sum(1 for x in sp if x > 1.0),
+            "pairs_5pct_faster": sum(1 for x in sp if x > 1.05), "pairs_5pct_slower": sum(1 for x in sp if x < 0.95),
+            "total_fused_us": sum(v["fused_us"] for v in ok), "total_sequential_us": sum(v["sequential_us"] for v in ok),
+            "geomean_speedup_by_kinds": {k: gm(v) for k, v in sorted(by_kind.items())}}
