@@ -81,6 +81,7 @@ def lib():
             "bfuse_graph_create": [vp, ip, C.c_int, C.c_int, ip], "bfuse_graph_launch": [vp, C.c_int, vp],
             "bfuse_trace_fused": [vp, C.c_int, ip, ip, ip, C.c_int], "bfuse_read_status": [vp, ip],
             "bfuse_debug_gemm_timeline": [vp, C.c_int, C.POINTER(C.c_longlong), C.c_int],
+            "bfuse_debug_fused_timeline": [vp, C.POINTER(C.c_int), C.c_int, C.POINTER(C.c_longlong), C.POINTER(C.c_int)],
             "bfuse_run_kernel": [vp, C.c_int, pp], "bfuse_run_parallel": [vp, C.c_int, pp, pp],
             "bfuse_run_fuse": [vp, C.c_int, pp, pp],
             "bfuse_time": [vp, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_float)],
@@ -288,6 +289,20 @@ class Runtime:
         self._ck(self._L.bfuse_debug_gemm_timeline(self._ctx, kernel, buf, len(names)))
         t0 = buf[0]
         return {n: (buf[i] - t0 if buf[i] else None) for i, n in enumerate(names)}
+
+    def fused_timeline(self, fusions):
+        """Per launch of the list (run back to back, fused mode): int64 array [slots, 3] of nanosecond
+        marks per dispatch slot -- kernel entry, body start, body end (0 where a slot recorded nothing)."""
+        import numpy as np
+        slots = [self.fusion_info(f)["GridDim"][0] for f in fusions]
+        buf = np.zeros((sum(slots), 3), np.int64)
+        self._ck(self._L.bfuse_debug_fused_timeline(self._ctx, (C.c_int * len(fusions))(*fusions), len(fusions),
+                                                     buf.ctypes.data_as(C.POINTER(C.c_longlong)), (C.c_int * len(slots))(*slots)))
+        out, off = [], 0
+        for n in slots:
+            out.append(buf[off:off + n])
+            off += n
+        return out
 
     def read_status(self):
         s = C.c_int()

@@ -46,6 +46,7 @@ struct DispatchTable {
   int smem_off[2];         // byte offset of operator k's shared-memory window
   unsigned int *queue_ctr; // [0] next ticket, [1] CTAs that have drained (persistent queue only)
   int *status;             // device status word; non-zero = a bounded wait gave up
+  unsigned long long *cta_times;  // diagnostic: when non-null, every block-level dispatch slot records 3 globaltimer marks
 };
 
 // Dispatch unit (or ticket) b -> operator k and its virtual unit.  Returns false if b is unmapped.

@@ -34,6 +34,12 @@ __device__ __forceinline__ unsigned char *align_smem_1k(unsigned char *p) {
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
 template <class Op>
 __device__ __forceinline__ void run_tile(const typename Op::Params &p, const DispatchTable &t, int k, int vb, int vtid,
                                          int bar_id, unsigned char *smem, int shares_cta = 0) {
@@ -64,44 +70,61 @@ constexpr int pair_min_blocks() {
                                               : cmin(4, cmax(A::kMinBlocks, B::kMinBlocks));
 }
 
+// A second, register-richer build of pairs with a memory-bound body, launched when its occupancy
+// still holds the whole fused grid (so nothing is lost in waves).  Two memory-bound bodies: 4 CTAs
+// per SM (64 registers) -- under the 40-register cap of the 6-CTA build the two inlined bodies spill.
+// A memory-bound body beside a GEMM / conv body: 2 CTAs per SM (128 registers) -- the 64 registers
+// of the default build make the tensor-core body's epilogue spill.  0: the pair has no second build.
 template <class A, class B>
-__global__ void __launch_bounds__(cmax(A::kMaxThreads, B::kMaxThreads), pair_min_blocks<A, B>())
+constexpr int pair_wide_blocks() {
+  return (A::kMemoryBound && B::kMemoryBound) ? (pair_min_blocks<A, B>() > 4 ? 4 : 0)
+                                              : ((A::kMemoryBound || B::kMemoryBound) && pair_min_blocks<A, B>() > 2 ? 2 : 0);
+}
+
+template <class A, class B, int MINB = pair_min_blocks<A, B>()>
+__global__ void __launch_bounds__(cmax(A::kMaxThreads, B::kMaxThreads), MINB)
     fused_block_kernel(const __grid_constant__ DispatchTable t, const __grid_constant__ typename A::Params pa,
                        const __grid_constant__ typename B::Params pb) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char *smem = align_smem_1k(smem_raw);
   const int tid = threadIdx.x;
+  unsigned long long t_entry = 0;
+  if (t.cta_times) t_entry = global_timer_ns();
   grid_launch_dependents();
   grid_dependency_wait();
-  if (!t.queue) {
-    int k, vb;
-    if (!decode_cta(t, blockIdx.x, k, vb)) return;
-    // guard of the reference: KernelID_ == k && threadIdx.x < B_k (Algorithms.cc:699-717)
-    if (k == 0) {
-      if (tid < t.n_thr[0]) run_tile<A>(pa, t, 0, vb, tid, 1, smem);
-    } else {
-      if (tid < t.n_thr[1]) run_tile<B>(pb, t, 1, vb, tid, 2, smem);
-    }
-    return;
-  }
-  // Persistent CTAs: draw tickets until the queue is empty.  The last CTA to drain resets the
-  // counters, so the next launch on the stream starts from zero without a memset.
+  // One loop serves both launch forms, so each body is inlined once (two copies cost registers and
+  // made the memory-bound pairs spill): a plain launch runs it for CTA blockIdx.x and leaves; a
+  // persistent CTA of the work queue draws tickets until the queue is empty.  The last CTA to drain
+  // resets the counters, so the next launch on the stream starts from zero without a memset.
   __shared__ int ticket_s;
-  for (;;) {
-    if (tid == 0) ticket_s = (int)atomicAdd(t.queue_ctr, 1u);
-    __syncthreads();
-    const int ticket = ticket_s;
-    __syncthreads();
-    if (ticket >= t.total) break;
-    int k, vb;
-    if (!decode_cta(t, ticket, k, vb)) continue;
-    if (k == 0) {
-      if (tid < t.n_thr[0]) run_tile<A>(pa, t, 0, vb, tid, 1, smem);
-    } else {
-      if (tid < t.n_thr[1]) run_tile<B>(pb, t, 1, vb, tid, 2, smem);
+  const bool queue = t.queue != 0;
+  int ticket = blockIdx.x;
+  do {
+    if (queue) {
+      if (tid == 0) ticket_s = (int)atomicAdd(t.queue_ctr, 1u);
+      __syncthreads();
+      ticket = ticket_s;
+      __syncthreads();
+      if (ticket >= t.total) break;
     }
-  }
-  if (tid == 0) {
+    int k, vb;
+    if (decode_cta(t, ticket, k, vb)) {
+      unsigned long long t_body = 0;
+      if (t.cta_times) t_body = global_timer_ns();
+      // guard of the reference: KernelID_ == k && threadIdx.x < B_k (Algorithms.cc:699-717)
+      if (k == 0) {
+        if (tid < t.n_thr[0]) run_tile<A>(pa, t, 0, vb, tid, 1, smem);
+      } else {
+        if (tid < t.n_thr[1]) run_tile<B>(pb, t, 1, vb, tid, 2, smem);
+      }
+      if (t.cta_times && tid == 0) {  // kernel entry, body start (dependency resolved), thread 0 done
+        t.cta_times[3 * (size_t)ticket] = t_entry;
+        t.cta_times[3 * (size_t)ticket + 1] = t_body;
+        t.cta_times[3 * (size_t)ticket + 2] = global_timer_ns();
+      }
+    }
+  } while (queue);
+  if (queue && tid == 0) {
     __threadfence();
     if (atomicAdd(t.queue_ctr + 1, 1u) == gridDim.x - 1) {
       t.queue_ctr[0] = 0;
@@ -198,6 +221,18 @@ cudaError_t launch_single(const DispatchTable &t, const void *pa, unsigned grid,
   if (e != cudaSuccess) return e;
   return launch_clustered(single_kernel<A>, grid, block, smem, s, t.cluster, t,
                           *static_cast<const typename A::Params *>(pa));
+}
+template <class A, class B>
+cudaError_t launch_block_pair_wide(const DispatchTable &t, const void *pa, const void *pb, unsigned grid, unsigned block,
+                                   size_t smem, cudaStream_t s) {
+  cudaError_t e = ensure_smem(fused_block_kernel<A, B, pair_wide_blocks<A, B>()>, smem);
+  if (e != cudaSuccess) return e;
+  return launch_clustered(fused_block_kernel<A, B, pair_wide_blocks<A, B>()>, grid, block, smem, s, t.cluster, t,
+                          *static_cast<const typename A::Params *>(pa), *static_cast<const typename B::Params *>(pb));
+}
+template <class A, class B>
+cudaError_t attr_block_pair_wide(cudaFuncAttributes *a) {
+  return cudaFuncGetAttributes(a, fused_block_kernel<A, B, pair_wide_blocks<A, B>()>);
 }
 template <class A, class B>
 cudaError_t attr_block_pair(cudaFuncAttributes *a) { return cudaFuncGetAttributes(a, fused_block_kernel<A, B>); }

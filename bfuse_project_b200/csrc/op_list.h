@@ -30,6 +30,9 @@ template <> struct OpAt<8> { using type = ConvUmmaTf32; };
 struct PairEntry {
   PairLaunchFn block, thread;
   AttrFn block_attr, thread_attr;
+  PairLaunchFn block_wide;   // the register-richer build of the pair (see pair_wide_blocks), else nullptr
+  AttrFn block_wide_attr;
+  int wide_min_blocks;       // CTAs per SM the wide build is compiled for
 };
 struct SingleEntry {
   SingleLaunchFn launch;

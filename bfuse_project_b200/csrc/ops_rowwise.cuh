@@ -26,7 +26,7 @@ struct SoftmaxF32 {
     float scale;
   };
   static constexpr int kMaxThreads = 256;
-  static constexpr int kMinBlocks = 6;   // 6 x 256 threads per SM: registers per thread <= 40 (32 made the fused kernels spill and ran slower)
+  static constexpr int kMinBlocks = 6;   // 6 x 256 threads per SM: registers per thread <= 40 (32 spills badly; 5 CTAs of 48 registers lose more in waves than the spills cost)
   static constexpr bool kMemoryBound = true;
 
   __device__ __forceinline__ static void run(const Params &p, const TileCtx &c) {
@@ -35,11 +35,15 @@ struct SoftmaxF32 {
     const bool live = row < p.rows;
     const float4 *xr = reinterpret_cast<const float4 *>(p.x + (size_t)row * p.cols);
     float4 v[kRowMaxVec];
+    // every load of the row is issued before the first use of any of them: a use between two loads
+    // would make the second one wait for the first one's trip to DRAM
+#pragma unroll
+    for (int i = 0; i < kRowMaxVec; ++i)
+      if (i < nvec && live) v[i] = ld_stream_f4(xr + i * tpr + lane);
     float m = -INFINITY;
 #pragma unroll
     for (int i = 0; i < kRowMaxVec; ++i) {
       if (i < nvec && live) {
-        v[i] = ld_stream_f4(xr + i * tpr + lane);
         v[i].x *= p.scale, v[i].y *= p.scale, v[i].z *= p.scale, v[i].w *= p.scale;
         m = fmaxf(m, fmaxf(fmaxf(v[i].x, v[i].y), fmaxf(v[i].z, v[i].w)));
       }
@@ -82,7 +86,7 @@ struct LayerNormF32 {
     float eps;
   };
   static constexpr int kMaxThreads = 256;
-  static constexpr int kMinBlocks = 6;   // 6 x 256 threads per SM: registers per thread <= 40 (32 made the fused kernels spill and ran slower)
+  static constexpr int kMinBlocks = 6;   // 6 x 256 threads per SM: registers per thread <= 40 (32 spills badly; 5 CTAs of 48 registers lose more in waves than the spills cost)
   static constexpr bool kMemoryBound = true;
 
   __device__ __forceinline__ static void run(const Params &p, const TileCtx &c) {
@@ -92,19 +96,32 @@ struct LayerNormF32 {
     const float4 *xr = reinterpret_cast<const float4 *>(p.x + (size_t)row * p.cols);
     const float4 *rr = reinterpret_cast<const float4 *>(p.res + (size_t)row * p.cols);
     const bool has_res = p.res != nullptr;
-    float4 v[kRowMaxVec];
-    float s = 0.f;
-#pragma unroll
-    for (int i = 0; i < kRowMaxVec; ++i) {
-      if (i < nvec && live) {
-        v[i] = ld_stream_f4(xr + i * tpr + lane);
-        if (has_res) {
-          const float4 r = ld_stream_f4(rr + i * tpr + lane);
-          v[i].x += r.x, v[i].y += r.y, v[i].z += r.z, v[i].w += r.w;
-        }
-        s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+    const float4 *g4 = reinterpret_cast<const float4 *>(p.gamma);
+    const float4 *b4 = reinterpret_cast<const float4 *>(p.beta);
+    if (c.tid < tpr) {  // one row's worth of threads touches every line of gamma and beta
+      for (int i = 0; i < nvec; ++i) {
+        prefetch_l1(g4 + i * tpr + lane);
+        prefetch_l1(b4 + i * tpr + lane);
       }
     }
+    float4 v[kRowMaxVec];
+    // every load of the row is issued before the first use of any of them (see SoftmaxF32)
+#pragma unroll
+    for (int i = 0; i < kRowMaxVec; ++i)
+      if (i < nvec && live) v[i] = ld_stream_f4(xr + i * tpr + lane);
+    if (has_res) {
+      float4 r[kRowMaxVec];
+#pragma unroll
+      for (int i = 0; i < kRowMaxVec; ++i)
+        if (i < nvec && live) r[i] = ld_stream_f4(rr + i * tpr + lane);
+#pragma unroll
+      for (int i = 0; i < kRowMaxVec; ++i)
+        if (i < nvec && live) v[i].x += r[i].x, v[i].y += r[i].y, v[i].z += r[i].z, v[i].w += r[i].w;
+    }
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < kRowMaxVec; ++i)
+      if (i < nvec && live) s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
     const float mean = row_reduce<OpSum>(s, c, tpr, 0) / (float)p.cols;
     float q = 0.f;
 #pragma unroll
@@ -115,8 +132,6 @@ struct LayerNormF32 {
       }
     }
     const float rstd = 1.f / sqrtf(row_reduce<OpSum>(q, c, tpr, 1) / (float)p.cols + p.eps);
-    const float4 *g4 = reinterpret_cast<const float4 *>(p.gamma);
-    const float4 *b4 = reinterpret_cast<const float4 *>(p.beta);
     float4 *yr = reinterpret_cast<float4 *>(p.y + (size_t)row * p.cols);
 #pragma unroll
     for (int i = 0; i < kRowMaxVec; ++i) {
@@ -151,7 +166,7 @@ struct RmsNormBf16 {
     float eps;
   };
   static constexpr int kMaxThreads = 256;
-  static constexpr int kMinBlocks = 6;   // 6 x 256 threads per SM: registers per thread <= 40 (32 made the fused kernels spill and ran slower)
+  static constexpr int kMinBlocks = 6;   // 6 x 256 threads per SM: registers per thread <= 40 (32 spills badly; 5 CTAs of 48 registers lose more in waves than the spills cost)
   static constexpr bool kMemoryBound = true;
   static constexpr int kMaxVec = 4;  // 8 bf16 per vector
 
@@ -160,12 +175,18 @@ struct RmsNormBf16 {
     const int nvec = p.cols / (8 * tpr);
     const bool live = row < p.rows;
     const uint4 *xr = reinterpret_cast<const uint4 *>(p.x + (size_t)row * p.cols);
+    const uint4 *w4 = reinterpret_cast<const uint4 *>(p.w);
+    if (c.tid < tpr)  // one row's worth of threads touches every line of the weight vector
+      for (int i = 0; i < nvec; ++i) prefetch_l1(w4 + i * tpr + lane);
     uint4 v[kMaxVec];
+    // every load of the row is issued before the first use of any of them (see SoftmaxF32)
+#pragma unroll
+    for (int i = 0; i < kMaxVec; ++i)
+      if (i < nvec && live) v[i] = ld_stream_u4(xr + i * tpr + lane);
     float q = 0.f;
 #pragma unroll
     for (int i = 0; i < kMaxVec; ++i) {
       if (i < nvec && live) {
-        v[i] = ld_stream_u4(xr + i * tpr + lane);
         const uint32_t u[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -175,7 +196,6 @@ struct RmsNormBf16 {
       }
     }
     const float rinv = 1.f / sqrtf(row_reduce<OpSum>(q, c, tpr, 0) / (float)p.cols + p.eps);
-    const uint4 *w4 = reinterpret_cast<const uint4 *>(p.w);
     uint4 *yr = reinterpret_cast<uint4 *>(p.y + (size_t)row * p.cols);
 #pragma unroll
     for (int i = 0; i < kMaxVec; ++i) {
@@ -207,7 +227,7 @@ struct RopeBf16 {
     int seq, heads, dim;
   };
   static constexpr int kMaxThreads = 256;
-  static constexpr int kMinBlocks = 6;   // 6 x 256 threads per SM: registers per thread <= 40 (32 made the fused kernels spill and ran slower)
+  static constexpr int kMinBlocks = 6;   // 6 x 256 threads per SM: registers per thread <= 40 (32 spills badly; 5 CTAs of 48 registers lose more in waves than the spills cost)
   static constexpr bool kMemoryBound = true;
 
   __device__ __forceinline__ static void run(const Params &p, const TileCtx &c) {
@@ -215,14 +235,23 @@ struct RopeBf16 {
     const int tx = c.tid % c.bx, chunk = tx % chunks, hg = tx / chunks, ngroups = c.bx / chunks;
     const int pos = c.vblock * c.by + c.tid / c.bx;
     if (pos >= p.seq) return;
-    float cs[8], sn[8];
+    // The frequency table first (the sin / cos arithmetic waits for it), then all of this thread's
+    // rows as L1 prefetches that tie up no register; the arithmetic runs while they travel and the
+    // loads in the head loop find their lines in L1.  A load first issued after the arithmetic would
+    // queue behind everything the grid already has in flight and cost another trip to DRAM per head.
     const float4 f0 = __ldg(reinterpret_cast<const float4 *>(p.inv_freq) + chunk * 2);
     const float4 f1 = __ldg(reinterpret_cast<const float4 *>(p.inv_freq) + chunk * 2 + 1);
+    const int hpt = p.heads / ngroups, h_begin = hg * hpt, h_end = h_begin + hpt;
+    const size_t o0 = ((size_t)pos * p.heads + h_begin) * p.dim + chunk * 8;
+    for (int h = 0; h < hpt; ++h) {
+      prefetch_l1(p.q + o0 + (size_t)h * p.dim);
+      prefetch_l1(p.q + o0 + (size_t)h * p.dim + half);
+    }
+    float cs[8], sn[8];
     const float fr[8] = {f0.x, f0.y, f0.z, f0.w, f1.x, f1.y, f1.z, f1.w};
 #pragma unroll
     for (int j = 0; j < 8; ++j) sincosf((float)pos * fr[j], &sn[j], &cs[j]);
-    const int hpt = p.heads / ngroups;
-    for (int h = hg * hpt; h < (hg + 1) * hpt; ++h) {
+    for (int h = h_begin; h < h_end; ++h) {
       const size_t o = ((size_t)pos * p.heads + h) * p.dim + chunk * 8;
       const uint4 a4 = ld_stream_u4(reinterpret_cast<const uint4 *>(p.q + o));
       const uint4 b4 = ld_stream_u4(reinterpret_cast<const uint4 *>(p.q + o + half));

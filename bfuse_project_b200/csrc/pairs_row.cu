@@ -7,6 +7,23 @@
 
 namespace bfuse {
 
+template <class A, class B, bool HAS>
+struct WideFiller {
+  static void fill(PairEntry &e) {
+    e.block_wide = nullptr;
+    e.block_wide_attr = nullptr;
+    e.wide_min_blocks = 0;
+  }
+};
+template <class A, class B>
+struct WideFiller<A, B, true> {
+  static void fill(PairEntry &e) {
+    e.block_wide = &launch_block_pair_wide<A, B>;
+    e.block_wide_attr = &attr_block_pair_wide<A, B>;
+    e.wide_min_blocks = pair_wide_blocks<A, B>();
+  }
+};
+
 template <int I, int J>
 struct RowFiller {
   static void fill(PairEntry *row) {
@@ -16,6 +33,7 @@ struct RowFiller {
     row[J].thread = &launch_thread_pair<A, B>;
     row[J].block_attr = &attr_block_pair<A, B>;
     row[J].thread_attr = &attr_thread_pair<A, B>;
+    WideFiller<A, B, (pair_wide_blocks<A, B>() > 0)>::fill(row[J]);
     RowFiller<I, J + 1>::fill(row);
   }
 };

@@ -54,6 +54,7 @@ struct FusionRec {
   unsigned *queue_ctr;  // device, 2 words (work queue only)
   int regs;
   int stages[2];        // thread-level fusion only: ring depths that let both windows fit (0: the kernel's own)
+  bool wide;            // launch the register-richer build of the pair
 };
 
 struct GraphRec {
@@ -550,12 +551,12 @@ const void *params_with_stages(const KernelRec &k, int stages, unsigned char *sc
   return scratch;
 }
 
-int launch_fused_rec(bfuse_context *ctx, FusionRec &f, cudaStream_t s) {
+int launch_fused_rec(bfuse_context *ctx, FusionRec &f, cudaStream_t s, const DispatchTable *table = nullptr) {
   KernelRec &a = *ctx->kernels[f.k1], &b = *ctx->kernels[f.k2];
   const PairEntry &pe = ctx->pairs[a.desc.op][b.desc.op];
-  PairLaunchFn fn = f.plan.table.kind == DISPATCH_THREADS ? pe.thread : pe.block;
+  PairLaunchFn fn = f.plan.table.kind == DISPATCH_THREADS ? pe.thread : (f.wide ? pe.block_wide : pe.block);
   alignas(64) unsigned char pa[kParamsBytes], pb[kParamsBytes];
-  cudaError_t e = fn(f.plan.table, params_with_stages(a, f.stages[0], pa), params_with_stages(b, f.stages[1], pb), f.launch_grid,
+  cudaError_t e = fn(table ? *table : f.plan.table, params_with_stages(a, f.stages[0], pa), params_with_stages(b, f.stages[1], pb), f.launch_grid,
                      (unsigned)f.plan.fused_block, f.smem, s);
   if (e != cudaSuccess) return fail_cuda(ctx, e, ("launch " + f.name).c_str());
   return BFUSE_OK;
@@ -786,8 +787,13 @@ int bfuse_register_fusion(bfuse_context *ctx, int kernel1, int kernel2, int patt
   f->launch_grid = (unsigned)f->plan.fused_grid;
   cudaSetDevice(ctx->device);
   const PairEntry &pe = ctx->pairs[a->desc.op][b->desc.op];
+  // the register-richer build of the pair when its occupancy still holds the whole grid in one wave
+  // (or, for two memory-bound bodies, when the grid is many waves long and waves stop mattering)
+  f->wide = !thread_split && pe.block_wide && !t.queue &&
+            (f->launch_grid <= (unsigned)(pe.wide_min_blocks * ctx->sm_count) ||
+             (pe.wide_min_blocks == 4 && f->launch_grid >= (unsigned)(12 * ctx->sm_count)));
   cudaFuncAttributes attr;
-  cudaError_t e = (thread_split ? pe.thread_attr : pe.block_attr)(&attr);
+  cudaError_t e = (thread_split ? pe.thread_attr : (f->wide ? pe.block_wide_attr : pe.block_attr))(&attr);
   if (e != cudaSuccess) return fail_cuda(ctx, e, "cudaFuncGetAttributes");
   f->regs = attr.numRegs;
   if (t.queue) {
@@ -929,6 +935,38 @@ int bfuse_trace_fused(bfuse_context *ctx, int fusion, int *kernel_of, int *vbloc
   if (e == cudaSuccess) e = cudaMemcpy(sm_of, d + 2 * cnt, sizeof(int) * cnt, cudaMemcpyDeviceToHost);
   cudaFree(d);
   if (e != cudaSuccess) return fail_cuda(ctx, e, "trace");
+  return BFUSE_OK;
+}
+
+int bfuse_debug_fused_timeline(bfuse_context *ctx, const int *fusions, int n, long long *times, const int *slots) {
+  if (!ctx || !fusions || !times || !slots || n <= 0) return BFUSE_ERR_INVALID;
+  size_t total = 0;
+  for (int i = 0; i < n; ++i) {
+    FusionRec *f = get_fusion(ctx, fusions[i]);
+    if (!f) return fail(ctx, BFUSE_ERR_INVALID, "bad fusion handle in list");
+    if (f->plan.table.kind == DISPATCH_THREADS) return fail(ctx, BFUSE_ERR_UNSUPPORTED, "thread-level fusions record no per-CTA times");
+    const int cnt = f->plan.table.queue ? f->plan.table.total * f->plan.table.cluster : (int)f->launch_grid;
+    if (slots[i] < cnt) return fail(ctx, BFUSE_ERR_INVALID, "times array shorter than the fused grid");
+    total += (size_t)slots[i];
+  }
+  cudaSetDevice(ctx->device);
+  unsigned long long *d = nullptr;
+  CK(cudaMalloc(&d, total * 3 * sizeof(unsigned long long)));
+  cudaError_t e = cudaMemsetAsync(d, 0, total * 3 * sizeof(unsigned long long), ctx->own);
+  int rc = BFUSE_OK;
+  size_t off = 0;
+  for (int i = 0; i < n && e == cudaSuccess && !rc; ++i) {
+    FusionRec *f = get_fusion(ctx, fusions[i]);
+    DispatchTable t = f->plan.table;
+    t.cta_times = d + off * 3;
+    rc = launch_fused_rec(ctx, *f, ctx->own, &t);
+    off += (size_t)slots[i];
+  }
+  if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->own);
+  if (e == cudaSuccess) e = cudaMemcpy(times, d, total * 3 * sizeof(unsigned long long), cudaMemcpyDeviceToHost);
+  cudaFree(d);
+  if (rc) return rc;
+  if (e != cudaSuccess) return fail_cuda(ctx, e, "fused timeline");
   return BFUSE_OK;
 }
 

@@ -64,6 +64,12 @@ __device__ __forceinline__ void st_stream_u4(uint4 *p, uint4 v) {
                : "memory");
 }
 
+// Start fetching the line at p into L1 / L2 without tying up a register: for small per-column
+// tables (gamma, beta, weights) that a body needs only after its reductions.  Issued next to the
+// row loads, the fetch shares their trip to DRAM; left to the point of use it would queue behind
+// every load the grid has in flight and cost a second full round trip.
+__device__ __forceinline__ void prefetch_l1(const void *p) { asm volatile("prefetch.global.L1 [%0];" ::"l"(p)); }
+
 struct OpSum {
   __device__ __forceinline__ static float apply(float a, float b) { return a + b; }
 };

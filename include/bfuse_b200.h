@@ -148,6 +148,12 @@ int bfuse_trace_fused(bfuse_context *ctx, int fusion, int *kernel_of, int *vbloc
  * issued, first stage full, last MMA issued, accumulator ready, partial tile written, cluster
  * barrier 1, reduction done, cluster barrier 2, end (12 values; unused marks stay 0). Synchronises. */
 int bfuse_debug_gemm_timeline(bfuse_context *ctx, int kernel, long long *marks, int n);
+/* Diagnostic, no reference counterpart: launch the n block-level fusions back to back on the
+ * context's stream (fused mode), every dispatch slot (CTA, or ticket for WORK_QUEUE) of launch i
+ * recording three global-timer marks in nanoseconds: kernel entry, body start (the dependency on
+ * the previous launch resolved), thread 0 of the body done.  times holds 3 * sum(slots) values,
+ * launch i's slots[i] >= its fused grid entries first to last; unused entries stay 0.  Synchronises. */
+int bfuse_debug_fused_timeline(bfuse_context *ctx, const int *fusions, int n, long long *times, const int *slots);
 /* Read and clear the device status word (0 = no bounded wait gave up). Synchronises. */
 int bfuse_read_status(bfuse_context *ctx, int *status);
 
