@@ -3,28 +3,31 @@
 //
 //   y[n, co, pixel] = sum_k  w[co, k] * im2col(x)[n, pixel, k],   k = (ci, kh, kw) as in w[co][ci][kh][kw]
 //
-// A tile is 128 output channels x 128 output pixels of one image.  The weight operand is K-major in
+// A tile is 128 output channels x BN output pixels of one image (BN = 128, or 64 / 32 for small
+// images, so that a single image still spreads over many SMs).  The weight operand is K-major in
 // global memory and arrives by TMA (128B swizzle).  The im2col operand does not exist in memory:
-// the four epilogue warps, idle during the main loop, gather it (one output pixel per thread, 32
-// values of k per stage) with 4-byte cp.async copies straight into the swizzled K-major layout the
+// the four epilogue warps, idle during the main loop, gather it (128 / BN threads per output pixel,
+// 32 values of k per pixel and stage) with 4-byte cp.async copies straight into the swizzled K-major layout the
 // MMA expects (out-of-image taps are zero-filled by the copy itself), and each thread's
 // cp.async.mbarrier.arrive makes the stage's "full" barrier fire when its copies have landed, so
 // the gather runs several stages ahead of the tensor core.  Per-k input offsets and tap coordinates
 // are tabulated once per CTA in shared memory, so the gather does no divisions.
 //
-// BlockDim = (192, 1, 1); GridDim = (ceil(oh*ow / 128), ceil(co / 128), n).
+// BlockDim = (192, 1, 1); GridDim = (ceil(oh*ow / BN), ceil(co / 128), n).
 #pragma once
 
 #include "ops_umma.cuh"
 
 namespace bfuse {
 
-constexpr int kConvBN = 128;                 // output pixels per tile
+constexpr int kConvBN = 128;                 // output pixels per tile, at most
 constexpr int kConvMaxK = 1024;              // ci * kh * kw the offset table can hold
 constexpr int kConvTableBytes = 8 * 1024;    // int2 {input offset, tap index dy*kw+dx} per k (tap 31 = padding of K)
 constexpr int kConvHeaderBytes = kUmmaHeaderBytes + kConvTableBytes;
-constexpr int kConvStageBytes = kUmmaABytes + kConvBN * kUmmaRowBytes;  // 32 KB
-__host__ __device__ constexpr int conv_umma_smem_bytes(int stages) { return kConvHeaderBytes + stages * kConvStageBytes; }
+__host__ __device__ constexpr int conv_stage_bytes(int bn = kConvBN) { return kUmmaABytes + bn * kUmmaRowBytes; }
+__host__ __device__ constexpr int conv_umma_smem_bytes(int stages, int bn = kConvBN) {
+  return kConvHeaderBytes + stages * conv_stage_bytes(bn);
+}
 
 struct ConvUmmaParams {
   alignas(64) CUtensorMap map_w;    // {K, co, 1}, box {32 fp32, 128, 1}, 128B swizzle
@@ -33,6 +36,7 @@ struct ConvUmmaParams {
   int n, ci, h, wd, co, kh, kw, stride, pad, oh, ow;
   int K;
   int stages;
+  int bn;               // output pixels per tile: 32, 64 or 128
   long long *timeline;  // diagnostic: when non-null, CTA 0 records globaltimer marks (UmmaMark indices)
 };
 
@@ -54,13 +58,60 @@ struct ConvUmmaTf32 {
   static constexpr bool kMemoryBound = false;
   static constexpr int kBK = 32;  // K elements (fp32) per stage row of 128 bytes
 
+  // The im2col gather of one tile by the four epilogue warps (gt = 0..127): 128 / BN threads share a
+  // row (one output pixel) of every stage's tile; consecutive lanes take consecutive pixels, thread
+  // `sub` of a row its sub-th share of the stage's 32 values of k.  A template on BN: the loop is
+  // bound by the issue rate of its copies, and run-time tile arithmetic in it costs a few percent.
+  template <int BN>
+  __device__ __forceinline__ static bool gather(const Params &p, const TileCtx &c, int gt, int px0, int img, int num_kb, int stages,
+                                                uint32_t tiles, uint32_t full0, uint32_t empty0, const int2 *tab, long long *tl) {
+    constexpr int kStageBytes = conv_stage_bytes(BN), kper = kBK * BN / 128;
+    const int r = gt & (BN - 1), sub = gt / BN, pix = px0 + r, ohw = p.oh * p.ow;
+    const bool live = pix < ohw;
+    const int oy = pix / p.ow, ox = pix % p.ow;
+    const int iy0 = oy * p.stride - p.pad, ix0 = ox * p.stride - p.pad;
+    const float *xb = p.x + (size_t)img * p.ci * p.h * p.wd + (ptrdiff_t)iy0 * p.wd + ix0;
+    // which taps of the window fall inside the image for this pixel (bit dy*kw+dx; none for a dead row)
+    uint32_t tapmask = 0;
+    if (live)
+      for (int dy = 0; dy < p.kh; ++dy)
+        for (int dx = 0; dx < p.kw; ++dx)
+          if (iy0 + dy >= 0 && iy0 + dy < p.h && ix0 + dx >= 0 && ix0 + dx < p.wd) tapmask |= 1u << (dy * p.kw + dx);
+    for (int kb = 0; kb < num_kb; ++kb) {
+      const int s = kb % stages;
+      if (!mbar_wait(empty0 + 8 * s, ((kb / stages) & 1) ^ 1, c.status, UMMA_WAIT_EMPTY_TIMEOUT)) return false;
+      const uint32_t brow = tiles + s * kStageBytes + kUmmaABytes + (uint32_t)r * 128u;
+#pragma unroll
+      for (int e0 = sub * kper; e0 < (sub + 1) * kper; e0 += 8) {
+        // look the 8 taps up first (the shared-memory reads overlap), then issue the 8 copies
+        const float *src[8];
+        uint32_t bytes[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int2 t = tab[kb * kBK + e0 + i];
+          const bool in = (tapmask >> t.y) & 1u;
+          src[i] = in ? xb + t.x : p.x;
+          bytes[i] = in ? 4u : 0u;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          cp_async_4(brow + (uint32_t)(((((e0 + i) >> 2) ^ (r & 7)) << 4) + (((e0 + i) & 3) << 2)), src[i], bytes[i]);
+      }
+      cp_async_arrive(full0 + 8 * s);
+      if (tl && gt == 0 && kb == 0) tl[MARK_FIRST_LOAD_ISSUED] = (long long)global_ns();
+      if (tl && gt == 0 && kb == num_kb - 1) tl[MARK_LAST_LOAD_ISSUED] = (long long)global_ns();
+    }
+    return true;
+  }
+
   __device__ __forceinline__ static void run(const Params &p, const TileCtx &c) {
     const int warp = c.tid >> 5, lane = c.tid & 31;
     const int quad = (threadIdx.x >> 5) & 3;
-    const int px0 = c.block_x() * kConvBN, co0 = c.block_y() * kUmmaBM, img = c.block_z();
+    const int BN = p.bn, kStageBytes = conv_stage_bytes(BN);
+    const int px0 = c.block_x() * BN, co0 = c.block_y() * kUmmaBM, img = c.block_z();
     const int stages = p.stages, ohw = p.oh * p.ow, K = p.K;
     const int num_kb = (K + kBK - 1) / kBK;
-    const uint32_t idesc = umma_idesc(0, kConvBN);
+    const uint32_t idesc = umma_idesc(0, BN);
 
     uint64_t *bars = reinterpret_cast<uint64_t *>(c.smem);
     const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * kUmmaMaxStages, acc_bar = empty0 + 8 * kUmmaMaxStages;
@@ -68,7 +119,7 @@ struct ConvUmmaTf32 {
     int2 *tab = reinterpret_cast<int2 *>(c.smem + kUmmaHeaderBytes);
     const uint32_t tiles = smem_u32(c.smem) + kConvHeaderBytes;
     int nbuf, group;
-    staging_plan(stages * kConvStageBytes / kUmmaStagingBytes, kConvBN / 32, nbuf, group);
+    staging_plan(stages * kStageBytes / kUmmaStagingBytes, BN / 32, nbuf, group);
     ChunkWriter<0> w{&p.map_out, p.co, ohw, 0, tiles + (uint32_t)(quad * nbuf) * 4096u, nbuf, lane, 0, co0 + quad * 32, img, px0, 32, group};
 
     long long *const tl = (p.timeline && c.vblock == 0) ? p.timeline : nullptr;
@@ -85,7 +136,7 @@ struct ConvUmmaTf32 {
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 5) {
-      tmem_alloc(smem_u32(tmem_slot), kConvBN);
+      tmem_alloc(smem_u32(tmem_slot), BN);
       if (!c.persistent) tmem_relinquish();
     } else if (warp < 4) {
       // k -> (input offset relative to the pixel's top-left tap, tap row, tap column)
@@ -112,13 +163,13 @@ struct ConvUmmaTf32 {
           mbar_expect_tx(bar, kUmmaABytes);
           tma_load_3d(dst, &p.map_w, bar, kb * kBK, co0, 0);
           if (++s == (uint32_t)stages) s = 0, ph ^= 1, dst = tiles, bar = full0;
-          else dst += kConvStageBytes, bar += 8;
+          else dst += kStageBytes, bar += 8;
         }
       }
       __syncwarp();
     } else if (warp == 5) {
       if (elect_one()) {
-        const uint32_t lo0 = ((tiles >> 4) & 0x3fffu) | (1u << 16), stage16 = (uint32_t)kConvStageBytes >> 4;
+        const uint32_t lo0 = ((tiles >> 4) & 0x3fffu) | (1u << 16), stage16 = (uint32_t)kStageBytes >> 4;
         uint32_t s = 0, ph = 0, lo = lo0, accumulate = 0;
         bool ok = true;
         for (int kb = 0; kb < num_kb; ++kb) {
@@ -143,51 +194,18 @@ struct ConvUmmaTf32 {
       }
       __syncwarp();
     } else {
-      // gather warps: thread r fills row r (one output pixel) of every stage's im2col tile
-      const int r = quad * 32 + lane, pix = px0 + r;
-      const bool live = pix < ohw;
-      const int oy = pix / p.ow, ox = pix % p.ow;
-      const int iy0 = oy * p.stride - p.pad, ix0 = ox * p.stride - p.pad;
-      const float *xb = p.x + (size_t)img * p.ci * p.h * p.wd + (ptrdiff_t)iy0 * p.wd + ix0;
-      // which taps of the window fall inside the image for this pixel (bit dy*kw+dx; none for a dead row)
-      uint32_t tapmask = 0;
-      if (live)
-        for (int dy = 0; dy < p.kh; ++dy)
-          for (int dx = 0; dx < p.kw; ++dx)
-            if (iy0 + dy >= 0 && iy0 + dy < p.h && ix0 + dx >= 0 && ix0 + dx < p.wd) tapmask |= 1u << (dy * p.kw + dx);
-      bool ok = true;
-      for (int kb = 0; kb < num_kb && ok; ++kb) {
-        const int s = kb % stages;
-        ok = mbar_wait(empty0 + 8 * s, ((kb / stages) & 1) ^ 1, c.status, UMMA_WAIT_EMPTY_TIMEOUT);
-        if (!ok) break;
-        const uint32_t brow = tiles + s * kConvStageBytes + kUmmaABytes + (uint32_t)r * 128u;
-#pragma unroll
-        for (int e0 = 0; e0 < kBK; e0 += 8) {
-          // look the 8 taps up first (the shared-memory reads overlap), then issue the 8 copies
-          const float *src[8];
-          uint32_t bytes[8];
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int2 t = tab[kb * kBK + e0 + i];
-            const bool in = (tapmask >> t.y) & 1u;
-            src[i] = in ? xb + t.x : p.x;
-            bytes[i] = in ? 4u : 0u;
-          }
-#pragma unroll
-          for (int i = 0; i < 8; ++i)
-            cp_async_4(brow + (uint32_t)(((((e0 + i) >> 2) ^ (r & 7)) << 4) + (((e0 + i) & 3) << 2)), src[i], bytes[i]);
-        }
-        cp_async_arrive(full0 + 8 * s);
-        if (kb == 0) mark(MARK_FIRST_LOAD_ISSUED, c.tid == 0);
-        if (kb == num_kb - 1) mark(MARK_LAST_LOAD_ISSUED, c.tid == 0);
-      }
+      bool ok;
+      if (BN == 128) ok = gather<128>(p, c, quad * 32 + lane, px0, img, num_kb, stages, tiles, full0, empty0, tab, tl);
+      else if (BN == 64) ok = gather<64>(p, c, quad * 32 + lane, px0, img, num_kb, stages, tiles, full0, empty0, tab, tl);
+      else ok = gather<32>(p, c, quad * 32 + lane, px0, img, num_kb, stages, tiles, full0, empty0, tab, tl);
+      (void)ok;
       // epilogue: accumulator rows are output channels, columns are this tile's pixels
       const bool acc_ok = mbar_wait(acc_bar, 0, c.status, UMMA_WAIT_ACC_TIMEOUT);
       tc_fence_after();
       mark(MARK_ACC_READY, c.tid == 0);
       if (acc_ok) {
 #pragma unroll 1
-        for (int ch = 0; ch < kConvBN / 32; ++ch) {
+        for (int ch = 0; ch < BN / 32; ++ch) {
           const uint32_t buf = w.begin_chunk();
           uint32_t r0[16], r1[16];
           tmem_ld_32x16(tmem_row + ch * 32, r0);
@@ -207,7 +225,7 @@ struct ConvUmmaTf32 {
     }
     tc_fence_before();
     c.sync();
-    if (warp == 5) tmem_dealloc(tmem_acc, kConvBN);
+    if (warp == 5) tmem_dealloc(tmem_acc, BN);
     if (c.persistent && c.tid < stages) {  // the next tile of a persistent CTA initialises them again
       mbar_inval(full0 + 8 * c.tid);
       mbar_inval(empty0 + 8 * c.tid);

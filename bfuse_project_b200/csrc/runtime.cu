@@ -199,7 +199,18 @@ int default_launch(const bfuse_context *ctx, bfuse_kernel_desc *d, std::string *
       const int oh = conv_out(s[2], s[5], s[7], s[8]), ow = conv_out(s[3], s[6], s[7], s[8]);
       if (oh <= 0 || ow <= 0) { *err = "conv2d: empty output"; return BFUSE_ERR_SHAPE; }
       const int num_kb = ceil_div(s[1] * s[5] * s[6], ConvUmmaTf32::kBK);
-      set(ceil_div(oh * ow, kConvBN), ceil_div(s[4], kUmmaBM), s[0], kUmmaThreads, 1, conv_umma_smem_bytes(std::min(num_kb, 3)), 3);
+      // pixels per tile: the widest of 128 / 64 / 32 that still gives the operator about half the
+      // SMs (its pair partner takes the other half); a single small image gets 32-pixel tiles
+      int bn = s[9];
+      if (bn <= 0) {
+        bn = 32;
+        for (int cand = kConvBN; cand > 32; cand /= 2)
+          if ((long long)s[0] * ceil_div(oh * ow, cand) * ceil_div(s[4], kUmmaBM) >= sm / 2) { bn = cand; break; }
+      }
+      if (bn != 32 && bn != 64 && bn != 128) { *err = "conv2d: pixels per tile must be 32, 64 or 128"; return BFUSE_ERR_SHAPE; }
+      d->shape[9] = bn;
+      const int stages = std::max(1, std::min({num_kb, kUmmaMaxStages, (110 * 1024 - kConvHeaderBytes) / conv_stage_bytes(bn)}));   // two CTAs per SM
+      set(ceil_div(oh * ow, bn), ceil_div(s[4], kUmmaBM), s[0], kUmmaThreads, 1, conv_umma_smem_bytes(stages, bn), 3);
       return BFUSE_OK;
     }
     case BFUSE_OP_GEMM_TF32:
@@ -388,9 +399,11 @@ int build_params(bfuse_context *ctx, KernelRec &k) {
       if ((oh * ow) % 4) return shape_err("oh*ow must be a multiple of 4 (output rows of 16-byte multiples)");
       if (s[5] * s[6] > 31) return shape_err("kernel window larger than 31 taps");
       if (kd.bx != kUmmaThreads || kd.by != 1 || kd.bz != 1) return shape_err("BlockDim must be (192, 1, 1)");
-      if (kd.gx != ceil_div(oh * ow, kConvBN) || kd.gy != ceil_div(s[4], kUmmaBM) || kd.gz != s[0])
-        return shape_err("GridDim must be (ceil(oh*ow/128), ceil(co/128), n)");
-      if (k.smem < (size_t)conv_umma_smem_bytes(1)) return shape_err("shared memory below one pipeline stage");
+      const int bn = s[9] > 0 ? s[9] : kConvBN;
+      if (bn != 32 && bn != 64 && bn != 128) return shape_err("shape[9] (pixels per tile) must be 32, 64 or 128");
+      if (kd.gx != ceil_div(oh * ow, bn) || kd.gy != ceil_div(s[4], kUmmaBM) || kd.gz != s[0])
+        return shape_err("GridDim must be (ceil(oh*ow/BN), ceil(co/128), n)");
+      if (k.smem < (size_t)conv_umma_smem_bytes(1, bn)) return shape_err("shared memory below one pipeline stage");
       ConvUmmaParams p;
       std::memset(&p, 0, sizeof(p));
       int rc = encode_map(ctx, &p.map_w, 4, a[1], K, s[4], 1, kUmmaBM);
@@ -400,7 +413,8 @@ int build_params(bfuse_context *ctx, KernelRec &k) {
       p.x = (const float *)a[0];
       p.n = s[0], p.ci = s[1], p.h = s[2], p.wd = s[3], p.co = s[4], p.kh = s[5], p.kw = s[6], p.stride = s[7], p.pad = s[8];
       p.oh = oh, p.ow = ow, p.K = K;
-      p.stages = std::min<int>(kUmmaMaxStages, (int)((k.smem - kConvHeaderBytes) / kConvStageBytes));
+      p.stages = std::min<int>(kUmmaMaxStages, (int)((k.smem - kConvHeaderBytes) / conv_stage_bytes(bn)));
+      p.bn = bn;
       static_assert(sizeof(p) <= kParamsBytes, "parameter block too small");
       std::memcpy(k.params, &p, sizeof(p));
       return BFUSE_OK;
@@ -535,7 +549,7 @@ bool ring_info(const KernelRec &k, int *header, int *stage_bytes, int *min_stage
     return true;
   }
   if (k.desc.op == BFUSE_OP_CONV2D_TF32) {
-    *header = kConvHeaderBytes, *stage_bytes = kConvStageBytes, *min_stages = 1;
+    *header = kConvHeaderBytes, *stage_bytes = conv_stage_bytes(s[9] > 0 ? s[9] : kConvBN), *min_stages = 1;
     *stages = reinterpret_cast<const ConvUmmaParams *>(k.params)->stages;
     return true;
   }
@@ -758,7 +772,7 @@ int bfuse_register_fusion(bfuse_context *ctx, int kernel1, int kernel2, int patt
     // would block for ever, so the sum has to fit the SM's 512 columns
     auto tmem_cols = [](const KernelRec &k) {
       if (k.desc.op == BFUSE_OP_GEMM_TF32 || k.desc.op == BFUSE_OP_GEMM_BF16) return k.desc.shape[4] * std::max(1, k.desc.shape[6] / kUmmaBM);
-      return k.desc.op == BFUSE_OP_CONV2D_TF32 ? kConvBN : 0;
+      return k.desc.op == BFUSE_OP_CONV2D_TF32 ? (k.desc.shape[9] > 0 ? k.desc.shape[9] : kConvBN) : 0;
     };
     if (tmem_cols(*a) + tmem_cols(*b) > 512)
       return fail(ctx, BFUSE_ERR_UNSUPPORTED, "thread split: the two operators need more than 512 tensor-memory columns together");

@@ -167,6 +167,18 @@ def test_conv_tensor_core_ragged_shapes(rt):
     run_and_check(rt, wl.PairSpec("conv_gemm", c, d, "tf32", "hbm"), BLOCK_PATTERNS)
 
 
+def test_conv_pixel_tile_widths(rt):
+    """Every pixel-tile width of the tensor-core conv body (32, 64, 128 pixels; 4, 2, 1 gather threads
+    per pixel) on a padded 3x3 stride-2 conv and a 1x1 conv whose pixel count is not a tile multiple."""
+    rng = np.random.default_rng(21)
+    for bn in (32, 64, 128):
+        a = wl.conv2d("c3x3", rng, bf.OP_CONV2D_TF32, 2, 24, 30, 30, 136, 3, 2, 1, bn=bn)      # 15 x 15 = 225 ... not % 4
+        a = wl.conv2d("c3x3", rng, bf.OP_CONV2D_TF32, 2, 24, 31, 31, 136, 3, 2, 1, bn=bn)      # 16 x 16 = 256 pixels, K = 216
+        b = wl.conv2d("c1x1", rng, bf.OP_CONV2D_TF32, 1, 40, 20, 18, 64, 1, 1, 0, bn=bn)       # 360 pixels, K = 40
+        pair = run_and_check(rt, wl.PairSpec("conv_bn%d" % bn, a, b, "tf32", "hbm"), [(bf.ZIGZAG, 1, 1), (bf.RANGE_SPLIT, 0, 0)])
+        assert pair.spec.a.launch[0][0] == -(-256 // bn) and pair.spec.b.launch[0][0] == -(-360 // bn)
+
+
 def test_conv_tensor_core_matches_cuda_core_body(rt):
     tc = wl.make_pair("cfg5_conv_branches", seed=12, conv_batch=2)
     cc = wl.make_pair("cfg5_conv_branches", seed=12, conv_batch=2, tensor_cores=False)
