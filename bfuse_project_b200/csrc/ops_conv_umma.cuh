@@ -21,17 +21,19 @@
 namespace bfuse {
 
 constexpr int kConvBN = 128;                 // output pixels per tile, at most
-constexpr int kConvMaxK = 1024;              // ci * kh * kw the offset table can hold
-constexpr int kConvTableBytes = 8 * 1024;    // int2 {input offset, tap index dy*kw+dx} per k (tap 31 = padding of K)
-constexpr int kConvHeaderBytes = kUmmaHeaderBytes + kConvTableBytes;
+constexpr int kConvMaxK = 8192;              // ci * kh * kw the offset table may hold (64 KB of shared memory)
+// header of the operator window: barriers etc., then the offset table -- int2 {input offset, tap
+// index dy*kw+dx} per k, K rounded up to whole K blocks (tap 31 = padding) and to 1 KB
+__host__ __device__ constexpr int conv_header_bytes(int K) { return kUmmaHeaderBytes + ((K + 31) / 32 * 32 * 8 + 1023) / 1024 * 1024; }
 __host__ __device__ constexpr int conv_stage_bytes(int bn = kConvBN) { return kUmmaABytes + bn * kUmmaRowBytes; }
-__host__ __device__ constexpr int conv_umma_smem_bytes(int stages, int bn = kConvBN) {
-  return kConvHeaderBytes + stages * conv_stage_bytes(bn);
+__host__ __device__ constexpr int conv_umma_smem_bytes(int stages, int bn, int K) {
+  return conv_header_bytes(K) + stages * conv_stage_bytes(bn);
 }
 
 struct ConvUmmaParams {
   alignas(64) CUtensorMap map_w;    // {K, co, 1}, box {32 fp32, 128, 1}, 128B swizzle
-  alignas(64) CUtensorMap map_out;  // {oh*ow, co, n}, box {32 fp32, 32, 1}, 128B swizzle (stores)
+  alignas(64) CUtensorMap map_out;  // {oh*ow, co, n}, box {32 fp32, 32, 1}, 128B swizzle (stores); unused when oh*ow % 4 != 0
+  float *y;                         // [n, co, oh*ow]: the output rows, for images whose rows are not 16-byte multiples
   const float *x;
   int n, ci, h, wd, co, kh, kw, stride, pad, oh, ow;
   int K;
@@ -117,10 +119,11 @@ struct ConvUmmaTf32 {
     const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * kUmmaMaxStages, acc_bar = empty0 + 8 * kUmmaMaxStages;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(c.smem + 8 * (2 * kUmmaMaxStages + 2));
     int2 *tab = reinterpret_cast<int2 *>(c.smem + kUmmaHeaderBytes);
-    const uint32_t tiles = smem_u32(c.smem) + kConvHeaderBytes;
+    const uint32_t tiles = smem_u32(c.smem) + conv_header_bytes(K);
     int nbuf, group;
     staging_plan(stages * kStageBytes / kUmmaStagingBytes, BN / 32, nbuf, group);
-    ChunkWriter<0> w{&p.map_out, p.co, ohw, 0, tiles + (uint32_t)(quad * nbuf) * 4096u, nbuf, lane, 0, co0 + quad * 32, img, px0, 32, group};
+    ChunkWriter<0> w{&p.map_out, p.co, ohw, 0, tiles + (uint32_t)(quad * nbuf) * 4096u, nbuf, lane, 0, co0 + quad * 32, img, px0, 32, group,
+                     (ohw & 3) ? p.y + (size_t)img * p.co * ohw : nullptr};
 
     long long *const tl = (p.timeline && c.vblock == 0) ? p.timeline : nullptr;
     auto mark = [&](int what, bool who) {

@@ -239,10 +239,13 @@ struct ChunkWriter {
   int n_tile0;     // first output column of the tile
   int nb_step;     // columns between consecutive chunks this warp writes
   int group;       // chunks per bulk group: nbuf (single group) or nbuf / 2
+  // Output rows that are not 16-byte multiples cannot be described to the TMA: the staged chunks
+  // then leave with 4-byte stores, 32 lanes writing 32 consecutive elements of one row (fp32 only).
+  float *direct = nullptr;  // element (0, 0) of this batch entry's output matrix, or nullptr: TMA stores
   int slot = 0, pending = 0, first_nb = 0;
 
   __device__ __forceinline__ uint32_t begin_chunk() {
-    if (pending == 0 && issued * group >= nbuf) {
+    if (!direct && pending == 0 && issued * group >= nbuf) {
       // the half-group about to be overwritten must have been read by its stores
       if (lane == 0) {
         if (group < nbuf) tma_store_wait_read<1>();
@@ -295,6 +298,26 @@ struct ChunkWriter {
   // hands the staged chunks to the TMA: every lane fences its own writes, lane 0 issues the stores
   __device__ __forceinline__ void flush() {
     if (pending == 0) return;
+    if (direct) {
+      __syncwarp();
+      const int first_slot = (slot == 0 ? nbuf : slot) - pending;
+      for (int i = 0; i < pending; ++i) {
+        const int col = first_nb + i * nb_step + lane;
+        const uint32_t b = buf0 + (uint32_t)(first_slot + i) * 4096u;
+        if (col < N) {
+#pragma unroll 4
+          for (int row = 0; row < 32; ++row) {
+            float v;
+            asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(b + (uint32_t)(row * 128 + (((lane >> 2) ^ (row & 7)) << 4) + ((lane & 3) << 2))) : "memory");
+            if (m_base + row < M) direct[(size_t)(m_base + row) * N + col] = v;
+          }
+        }
+      }
+      __syncwarp();  // the buffers may be overwritten
+      ++issued;
+      pending = 0;
+      return;
+    }
     fence_async_smem();
     __syncwarp();
     if (lane == 0) {
@@ -310,7 +333,7 @@ struct ChunkWriter {
   }
   __device__ __forceinline__ void finish() {
     flush();
-    if (lane == 0) tma_store_wait_read<0>();
+    if (!direct && lane == 0) tma_store_wait_read<0>();
     __syncwarp();
   }
 };

@@ -209,8 +209,13 @@ int default_launch(const bfuse_context *ctx, bfuse_kernel_desc *d, std::string *
       }
       if (bn != 32 && bn != 64 && bn != 128) { *err = "conv2d: pixels per tile must be 32, 64 or 128"; return BFUSE_ERR_SHAPE; }
       d->shape[9] = bn;
-      const int stages = std::max(1, std::min({num_kb, kUmmaMaxStages, (110 * 1024 - kConvHeaderBytes) / conv_stage_bytes(bn)}));   // two CTAs per SM
-      set(ceil_div(oh * ow, bn), ceil_div(s[4], kUmmaBM), s[0], kUmmaThreads, 1, conv_umma_smem_bytes(stages, bn), 3);
+      const int K = s[1] * s[5] * s[6];
+      // ring: two CTAs per SM, or the whole SM when the operator and an equal partner leave every CTA
+      // an SM of its own (a long-K conv on few CTAs is bound by the ring's round trip, not by issue rate)
+      const long long ctas = (long long)s[0] * ceil_div(oh * ow, bn) * ceil_div(s[4], kUmmaBM);
+      const int budget = (2 * ctas <= sm ? 200 : 110) * 1024;
+      const int stages = std::max(1, std::min({num_kb, kUmmaMaxStages, (budget - conv_header_bytes(K)) / conv_stage_bytes(bn)}));
+      set(ceil_div(oh * ow, bn), ceil_div(s[4], kUmmaBM), s[0], kUmmaThreads, 1, conv_umma_smem_bytes(stages, bn, K), 3);
       return BFUSE_OK;
     }
     case BFUSE_OP_GEMM_TF32:
@@ -395,25 +400,27 @@ int build_params(bfuse_context *ctx, KernelRec &k) {
       const int oh = conv_out(s[2], s[5], s[7], s[8]), ow = conv_out(s[3], s[6], s[7], s[8]);
       if (oh <= 0 || ow <= 0) return shape_err("empty output");
       const int K = s[1] * s[5] * s[6];
-      if (K > kConvMaxK || K % 4) return shape_err("ci*kh*kw must be a multiple of 4 and at most 1024 (offset table, TMA stride rule)");
-      if ((oh * ow) % 4) return shape_err("oh*ow must be a multiple of 4 (output rows of 16-byte multiples)");
+      if (K > kConvMaxK || K % 4) return shape_err("ci*kh*kw must be a multiple of 4 and at most 8192 (offset table, TMA stride rule)");
       if (s[5] * s[6] > 31) return shape_err("kernel window larger than 31 taps");
       if (kd.bx != kUmmaThreads || kd.by != 1 || kd.bz != 1) return shape_err("BlockDim must be (192, 1, 1)");
       const int bn = s[9] > 0 ? s[9] : kConvBN;
       if (bn != 32 && bn != 64 && bn != 128) return shape_err("shape[9] (pixels per tile) must be 32, 64 or 128");
       if (kd.gx != ceil_div(oh * ow, bn) || kd.gy != ceil_div(s[4], kUmmaBM) || kd.gz != s[0])
         return shape_err("GridDim must be (ceil(oh*ow/BN), ceil(co/128), n)");
-      if (k.smem < (size_t)conv_umma_smem_bytes(1, bn)) return shape_err("shared memory below one pipeline stage");
+      if (k.smem < (size_t)conv_umma_smem_bytes(1, bn, K)) return shape_err("shared memory below one pipeline stage");
       ConvUmmaParams p;
       std::memset(&p, 0, sizeof(p));
       int rc = encode_map(ctx, &p.map_w, 4, a[1], K, s[4], 1, kUmmaBM);
       if (rc) return rc;
-      rc = encode_map(ctx, &p.map_out, 4, a[2], oh * ow, s[4], s[0], 32);
-      if (rc) return rc;
+      if ((oh * ow) % 4 == 0) {  // else the rows are no 16-byte multiples and the body stores them itself
+        rc = encode_map(ctx, &p.map_out, 4, a[2], oh * ow, s[4], s[0], 32);
+        if (rc) return rc;
+      }
+      p.y = (float *)a[2];
       p.x = (const float *)a[0];
       p.n = s[0], p.ci = s[1], p.h = s[2], p.wd = s[3], p.co = s[4], p.kh = s[5], p.kw = s[6], p.stride = s[7], p.pad = s[8];
       p.oh = oh, p.ow = ow, p.K = K;
-      p.stages = std::min<int>(kUmmaMaxStages, (int)((k.smem - kConvHeaderBytes) / conv_stage_bytes(bn)));
+      p.stages = std::min<int>(kUmmaMaxStages, (int)((k.smem - conv_header_bytes(K)) / conv_stage_bytes(bn)));
       p.bn = bn;
       static_assert(sizeof(p) <= kParamsBytes, "parameter block too small");
       std::memcpy(k.params, &p, sizeof(p));
@@ -549,7 +556,7 @@ bool ring_info(const KernelRec &k, int *header, int *stage_bytes, int *min_stage
     return true;
   }
   if (k.desc.op == BFUSE_OP_CONV2D_TF32) {
-    *header = kConvHeaderBytes, *stage_bytes = conv_stage_bytes(s[9] > 0 ? s[9] : kConvBN), *min_stages = 1;
+    *header = conv_header_bytes(s[1] * s[5] * s[6]), *stage_bytes = conv_stage_bytes(s[9] > 0 ? s[9] : kConvBN), *min_stages = 1;
     *stages = reinterpret_cast<const ConvUmmaParams *>(k.params)->stages;
     return true;
   }
@@ -795,7 +802,25 @@ int bfuse_register_fusion(bfuse_context *ctx, int kernel1, int kernel2, int patt
     t.smem_off[1] = (int)((win[0] + 1023) / 1024 * 1024);
     f->smem = t.smem_off[1] + win[1] + 1024;
   } else {
-    f->smem = std::max(a->smem, b->smem) + 1024;
+    // The union is the larger window, and every CTA of the fused grid is charged for it.  A ring that
+    // was sized for a CTA with an SM to itself would then keep the partner's CTAs from sharing SMs:
+    // when the fused grid needs more than one CTA per SM, such rings are made shallower (never below
+    // what the operator's epilogue needs, and only if at least three stages remain) until two CTAs fit.
+    size_t win[2] = {a->smem, b->smem};
+    constexpr size_t kHalfSm = 111 * 1024;
+    if (f->plan.fused_grid > ctx->sm_count && !t.queue) {
+      KernelRec *ks[2] = {a, b};
+      for (int i = 0; i < 2; ++i) {
+        int hdr, stg, mn, st;
+        if (win[i] <= kHalfSm || !ring_info(*ks[i], &hdr, &stg, &mn, &st)) continue;
+        const int fit = (int)((kHalfSm - hdr) / stg);
+        if (fit < st && fit >= std::max(mn, 3)) {  // a ring of fewer than 3 stages is no pipeline: such tiles keep their SM
+          f->stages[i] = fit;
+          win[i] = (size_t)hdr + (size_t)fit * stg;
+        }
+      }
+    }
+    f->smem = std::max(win[0], win[1]) + 1024;
   }
   if (f->smem > kMaxSmemPerCta) return fail(ctx, BFUSE_ERR_SMEM, f->name + ": fused shared memory over the 227 KB per-CTA budget");
   f->launch_grid = (unsigned)f->plan.fused_grid;

@@ -46,12 +46,12 @@ def pair_indices(n=len(SWEEP_OPS)):
 
 
 def conv_on_tensor_cores(shape):
-    """Whether the tcgen05 implicit-GEMM body takes this conv (its offset table, TMA stride rule
-    and tap mask limit what it covers); otherwise the CUDA-core body runs it."""
+    """Whether the tcgen05 implicit-GEMM body takes this conv (the TMA stride rule for the weight
+    rows, its offset table and its tap mask limit what it covers); otherwise the CUDA-core body
+    runs it."""
     n, h, w, co, ci, kh, kw, stride, pad = shape
-    oh, ow = (h + 2 * pad - kh) // stride + 1, (w + 2 * pad - kw) // stride + 1
     k = ci * kh * kw
-    return k % 4 == 0 and k <= 1024 and (oh * ow) % 4 == 0 and kh * kw <= 31
+    return k % 4 == 0 and k <= 8192 and kh * kw <= 31
 
 
 class SweepOperand:

@@ -167,6 +167,21 @@ def test_conv_tensor_core_ragged_shapes(rt):
     run_and_check(rt, wl.PairSpec("conv_gemm", c, d, "tf32", "hbm"), BLOCK_PATTERNS)
 
 
+def test_conv_long_k_and_odd_pixel_counts(rt):
+    """Shapes of the deeper ResNet-18 / Inception-v3 layers: K = ci*kh*kw beyond 1024 (the offset
+    table grows with K), output images whose pixel count is not a multiple of 4 (rows that the TMA
+    cannot describe: the body stores them itself), channel counts that are no tile multiples."""
+    rng = np.random.default_rng(33)
+    a = wl.conv2d("deep3x3", rng, bf.OP_CONV2D_TF32, 1, 512, 7, 7, 512, 3, 1, 1)       # K = 4608, 7 x 7 = 49 pixels
+    b = wl.conv2d("odd1x1", rng, bf.OP_CONV2D_TF32, 2, 256, 35, 35, 48, 1, 1, 0)       # 1225 pixels, 48 channels
+    run_and_check(rt, wl.PairSpec("conv_deep_odd", a, b, "tf32", "hbm"), BLOCK_PATTERNS)
+    c = wl.conv2d("mid3x3", rng, bf.OP_CONV2D_TF32, 1, 128, 28, 28, 128, 3, 1, 1)      # K = 1152, 784 pixels
+    d = wl.conv2d("odd3x3s2", rng, bf.OP_CONV2D_TF32, 1, 96, 35, 35, 96, 3, 2, 0)      # 17 x 17 = 289 pixels, K = 864
+    for bn in (0, 32, 128):
+        c.shape, d.shape = c.shape[:9] + (bn,), d.shape[:9] + (bn,)
+        run_and_check(rt, wl.PairSpec("conv_mid_odd_bn%d" % bn, c, d, "tf32", "hbm"), [(bf.ZIGZAG, 1, 1), (bf.WORK_QUEUE, 1, 1)])
+
+
 def test_conv_pixel_tile_widths(rt):
     """Every pixel-tile width of the tensor-core conv body (32, 64, 128 pixels; 4, 2, 1 gather threads
     per pixel) on a padded 3x3 stride-2 conv and a 1x1 conv whose pixel count is not a tile multiple."""

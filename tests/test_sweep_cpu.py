@@ -24,8 +24,10 @@ def test_conv_body_choice_follows_the_tensor_core_body_limits():
     assert not sweep.conv_on_tensor_cores(shapes["conv2d_0"])      # 7x7 window, K = 147
     assert sweep.conv_on_tensor_cores(shapes["conv2d_3"])          # the ResNet branch pair
     assert sweep.conv_on_tensor_cores(shapes["conv2d_5"])
-    assert not sweep.conv_on_tensor_cores(shapes["conv2d_4"])      # K = 1152 > 1024
-    assert not sweep.conv_on_tensor_cores(shapes["conv2d_12"])     # 35 x 35 outputs, rows not 16-byte multiples
+    assert sweep.conv_on_tensor_cores(shapes["conv2d_4"])          # K = 1152: the offset table grows with K
+    assert sweep.conv_on_tensor_cores(shapes["conv2d_10"])         # K = 4608, 7 x 7 = 49 output pixels
+    assert sweep.conv_on_tensor_cores(shapes["conv2d_12"])         # 35 x 35 outputs: rows stored by the body itself
+    assert sum(sweep.conv_on_tensor_cores(sh) for n, sh in sweep.SWEEP_OPS if n.startswith("conv2d")) == 21
 
 
 def test_summary_counts_and_geomean():
