@@ -222,6 +222,37 @@ def measure_pair(rt, torch, bf, wl, pk, name, device, conv_batch=1, max_reps=24)
     return res
 
 
+def attention_block(rt, torch, bf):
+    """The QK^T -> softmax -> PV chain of a BERT-base / GPT-2 attention block (12 heads, 512 tokens,
+    head size 64, causal), as plain launches and software-pipelined over head groups with horizontally
+    fused steps; CUDA-graph replay on the same buffers (they fit the L2)."""
+    from bfuse_project_b200 import attention
+    try:
+        gen = torch.Generator(device="cuda")
+        gen.manual_seed(0)
+        q, k = (torch.randn(12, 512, 64, device="cuda", generator=gen) for _ in range(2))
+        vt = torch.randn(12, 64, 512, device="cuda", generator=gen)
+        out = {"shape": {"heads": 12, "seq": 512, "head_dim": 64, "causal": True}}
+        one = attention.AttentionBlock(rt, torch, q, k, vt, groups=1)
+        out["one_group_3_launches_us"] = attention.graph_time_us(torch, one.run_sequential)
+        for groups in (2, 4, 6):
+            blk = attention.AttentionBlock(rt, torch, q, k, vt, groups=groups)
+            seq_us = attention.graph_time_us(torch, blk.run_sequential)
+            pip_us = attention.graph_time_us(torch, blk.run_pipelined)
+            blk.run_sequential(torch.cuda.current_stream().cuda_stream)
+            torch.cuda.synchronize()
+            want = blk.out.clone()
+            blk.out.zero_()
+            blk.run_pipelined(torch.cuda.current_stream().cuda_stream)
+            torch.cuda.synchronize()
+            out["groups_%d" % groups] = {"sequential_launches": blk.launches_sequential, "sequential_us": seq_us,
+                                         "pipelined_launches": blk.launches_pipelined, "pipelined_fused_us": pip_us,
+                                         "speedup": seq_us / pip_us, "bit_identical": bool(torch.equal(want, blk.out))}
+        return out
+    except Exception as e:   # reported, not hidden
+        return {"error": str(e)[:300]}
+
+
 def reference_fuser_output(rt, torch, bf, wl, pk):
     """The reference fuser's generated bfuse / hfuse kernels compiled for sm_100a, at their own
     batch-1024 fp32 shapes, beside this runtime's fused pair on the same shapes (fp32 in, tf32 MMA)."""
@@ -484,6 +515,7 @@ def main():
     if not args.quick:
         line["pairs"] = side_pairs
         line["conv_n256_sharded"] = conv256
+        line["attention_block"] = attention_block(rt, torch, bf)
         line["reference_fuser_output"] = reference_fuser_output(rt, torch, bf, wl, pk)
     print(json.dumps(line), flush=True)
     if world > 1:
