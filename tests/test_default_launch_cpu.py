@@ -1,0 +1,61 @@
+"""bfuse_default_launch without a device (context NULL = 148 SMs): the tilings the runtime picks for
+the tensor-core operators -- tile width / height, k-slices, ring depth, conv pixel-tile width."""
+import bfuse_project_b200 as bf
+
+
+def default(op, shape):
+    d = bf.KernelDesc()
+    d.KernelName = b"k"
+    d.op = op
+    for i, v in enumerate(shape):
+        d.shape[i] = v
+    rc = bf.lib().bfuse_default_launch(None, d)
+    assert rc == 0, rc
+    return d
+
+
+def gemm(op, batch, m, n, k, **kw):
+    d = default(op, (batch, m, n, k, kw.get("bn", 0), kw.get("split", 0), kw.get("bm", 0)))
+    return {"grid": d.GridDim.tuple(), "bn": d.shape[4], "split": d.shape[5], "bm": d.shape[6], "smem": d.smem_bytes}
+
+
+def test_projection_pairs_get_narrow_unsplit_tiles_and_a_whole_sm_ring():
+    q = gemm(bf.OP_GEMM_TF32, 1, 512, 768, 768)           # BERT Q / K projection
+    assert (q["bn"], q["split"], q["bm"], q["grid"]) == (64, 1, 128, (4, 12, 1))
+    assert q["smem"] == 2048 + 8 * (128 + 64) * 128        # 48 CTAs and an equal partner: every CTA has an SM
+    kv = gemm(bf.OP_GEMM_BF16, 1, 512, 1024, 4096)         # Llama k / v projection
+    assert (kv["bn"], kv["split"], kv["grid"]) == (64, 1, (4, 16, 1)) and kv["smem"] == 2048 + 8 * 192 * 128
+
+
+def test_large_long_k_gemm_gets_tall_tiles():
+    g = gemm(bf.OP_GEMM_BF16, 1, 512, 14336, 4096)         # Llama gate / up projection
+    assert (g["bn"], g["split"], g["bm"], g["grid"]) == (256, 1, 256, (2, 56, 1))
+    assert g["smem"] == 2048 + 3 * 512 * 128
+    s = gemm(bf.OP_GEMM_TF32, 1024, 512, 512, 64)          # many tiles but two K blocks: bound by its stores
+    assert s["bm"] == 128
+
+
+def test_skinny_long_k_gemm_is_split_over_a_cluster():
+    g = gemm(bf.OP_GEMM_BF16, 1, 128, 128, 8192)
+    assert g["split"] > 1 and g["grid"][0] == g["split"]
+    assert gemm(bf.OP_GEMM_BF16, 1, 128, 128, 8192, split=1)["split"] == 1   # a fixed value is kept
+
+
+def test_explicit_tile_fields_are_validated():
+    d = bf.KernelDesc()
+    d.KernelName, d.op = b"k", bf.OP_GEMM_TF32
+    for i, v in enumerate((1, 512, 512, 512, 48, 1, 0)):
+        d.shape[i] = v
+    assert bf.lib().bfuse_default_launch(None, d) == 2       # BN must be 32, 64, 128 or 256
+    for i, v in enumerate((1, 512, 512, 512, 256, 2, 256)):
+        d.shape[i] = v
+    assert bf.lib().bfuse_default_launch(None, d) == 2       # tall tiles only unsplit
+
+
+def test_conv_pixel_tile_width_follows_the_image_count():
+    one = default(bf.OP_CONV2D_TF32, (1, 64, 56, 56, 128, 3, 3, 2, 1))
+    assert one.shape[9] == 32 and one.GridDim.tuple() == (25, 1, 1)          # 784 pixels of one image
+    many = default(bf.OP_CONV2D_TF32, (256, 64, 56, 56, 128, 3, 3, 2, 1))
+    assert many.shape[9] == 128 and many.GridDim.tuple() == (7, 1, 256)
+    deep = default(bf.OP_CONV2D_TF32, (1, 512, 7, 7, 512, 3, 3, 1, 1))        # K = 4608: the table takes 36 KB
+    assert deep.shape[9] == 32 and deep.GridDim.tuple() == (2, 4, 1) and deep.smem_bytes > 36 * 1024 + 8 * 20 * 1024 - 1
