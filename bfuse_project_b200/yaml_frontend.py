@@ -8,12 +8,13 @@ Schemas (horizontal-fuser/include/fuse/Utils.h:69-112): `kernels.yaml` maps a na
 (src/Contexts.cc:67-84) to a kernel record with the fused dims, HasBarriers true, Reg 32 and
 ExecTime left at its default (src/Fuse.cc:203-220, 358-375).
 
-    python -m bfuse_project_b200.yaml_frontend [-b] kernels.yaml fusions.yaml out.yaml
+    python -m bfuse_project_b200.yaml_frontend [-b] [-y out_dir] fusions.yaml kernels.yaml
 
 `-b` selects block-level fusion (the zig-zag 1:1 pattern the reference uses), without it the
 thread-level split -- the meaning of the reference fuser's own `-b` switch.  No GPU is needed.
 """
 import argparse
+import os
 import sys
 
 import yaml
@@ -85,19 +86,26 @@ def dump_kernels(records, path):
 
 
 def main(argv=None):
-    ap = argparse.ArgumentParser(description="plan the pairs of a fusions.yaml and write the fused-kernel records")
-    ap.add_argument("-b", action="store_true", help="block-level fusion (bfuse); default: thread-level (hfuse)")
-    ap.add_argument("kernels")
-    ap.add_argument("fusions")
-    ap.add_argument("out")
+    """Same switches and argument order as the reference fuser (horizontal-fuser/src/main.cc:20-70):
+    [-b] [-y yaml_output_dir] fusion_config kernel_config [compile_commands]; the record file is
+    `bfuse_kernels.yaml` or `hfuse_kernels.yaml` in the output directory.  `-o` (rewritten sources) and
+    compile_commands are accepted and ignored: there are no sources to rewrite."""
+    ap = argparse.ArgumentParser(prog="yaml_frontend", description="plan the pairs of a fusion config and write the fused-kernel records")
+    ap.add_argument("-b", action="store_true", help="block-level fusion (default: thread-level)")
+    ap.add_argument("-y", default=".", metavar="yaml_output", help="directory for the record file (default: .)")
+    ap.add_argument("-o", default=".", metavar="output", help="accepted for compatibility, unused")
+    ap.add_argument("fusion_config")
+    ap.add_argument("kernel_config")
+    ap.add_argument("compile_commands", nargs="?", help="accepted for compatibility, unused")
     args = ap.parse_args(argv)
+    out = os.path.join(args.y, "bfuse_kernels.yaml" if args.b else "hfuse_kernels.yaml")
     try:
-        recs = fuse_records(load_kernels(args.kernels), load_fusions(args.fusions), block_level=args.b)
-        dump_kernels(recs, args.out)
+        recs = fuse_records(load_kernels(args.kernel_config), load_fusions(args.fusion_config), block_level=args.b)
+        dump_kernels(recs, out)
     except (OSError, ValueError, KeyError, yaml.YAMLError) as e:
         print("yaml_frontend: %s" % e, file=sys.stderr)
         return 1
-    print("%d fused kernels written to %s" % (len(recs), args.out))
+    print("%d fused kernels written to %s" % (len(recs), out))
     return 0
 
 

@@ -58,7 +58,8 @@ def test_command_line_mirrors_the_fuser_switch(golden, tmp_path):
     kp, fp = write_inputs(str(tmp_path), suite)
     out = os.path.join(str(tmp_path), "bfuse_kernels.yaml")
     env = dict(os.environ, PYTHONPATH=ROOT)
-    r = subprocess.run([sys.executable, "-m", "bfuse_project_b200.yaml_frontend", "-b", kp, fp, out], capture_output=True, text=True, env=env)
+    r = subprocess.run([sys.executable, "-m", "bfuse_project_b200.yaml_frontend", "-b", "-y", str(tmp_path), fp, kp, "unused_compile_commands"],
+                       capture_output=True, text=True, env=env)
     assert r.returncode == 0, r.stderr
     doc = yaml.safe_load(open(out))
     a, b, bdims, _ = suite["pairs"][0]
@@ -67,5 +68,5 @@ def test_command_line_mirrors_the_fuser_switch(golden, tmp_path):
     # a fusion naming an unknown kernel is an error exit, not a crash
     with open(fp, "w") as f:
         yaml.safe_dump([{"File": "kernels.cu", "Kernels": ["nope", a]}], f)
-    r = subprocess.run([sys.executable, "-m", "bfuse_project_b200.yaml_frontend", kp, fp, out], capture_output=True, text=True, env=env)
+    r = subprocess.run([sys.executable, "-m", "bfuse_project_b200.yaml_frontend", "-y", str(tmp_path), fp, kp], capture_output=True, text=True, env=env)
     assert r.returncode == 1 and "unknown kernel" in r.stderr
