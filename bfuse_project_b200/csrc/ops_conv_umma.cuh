@@ -13,7 +13,10 @@
 // the gather runs several stages ahead of the tensor core.  Per-k input offsets and tap coordinates
 // are tabulated once per CTA in shared memory, so the gather does no divisions.
 //
-// BlockDim = (192, 1, 1); GridDim = (ceil(oh*ow / BN), ceil(co / 128), n).
+// A long K (deep layers on small images leave few tiles) can be split over the CTAs of a cluster,
+// reduced through distributed shared memory like the GEMM's k-slices.
+//
+// BlockDim = (192, 1, 1); GridDim = (split * ceil(oh*ow / BN), ceil(co / 128), n).
 #pragma once
 
 #include "ops_umma.cuh"
@@ -39,6 +42,8 @@ struct ConvUmmaParams {
   int K;
   int stages;
   int bn;               // output pixels per tile: 32, 64 or 128
+  int split;            // CTAs (k-slices) per tile = cluster width; 1: no split
+  int kb_per_slice;     // K blocks per k-slice
   long long *timeline;  // diagnostic: when non-null, CTA 0 records globaltimer marks (UmmaMark indices)
 };
 
@@ -110,19 +115,26 @@ struct ConvUmmaTf32 {
     const int warp = c.tid >> 5, lane = c.tid & 31;
     const int quad = (threadIdx.x >> 5) & 3;
     const int BN = p.bn, kStageBytes = conv_stage_bytes(BN);
-    const int px0 = c.block_x() * BN, co0 = c.block_y() * kUmmaBM, img = c.block_z();
+    const int split = p.split, kslice = c.block_x() % split;
+    const int px0 = (c.block_x() / split) * BN, co0 = c.block_y() * kUmmaBM, img = c.block_z();
     const int stages = p.stages, ohw = p.oh * p.ow, K = p.K;
-    const int num_kb = (K + kBK - 1) / kBK;
+    const int total_kb = (K + kBK - 1) / kBK;
+    const int kb0 = kslice * p.kb_per_slice;                  // first K block of this k-slice
+    const int num_kb = min(p.kb_per_slice, total_kb - kb0);   // K blocks this CTA multiplies (>= 1)
     const uint32_t idesc = umma_idesc(0, BN);
 
     uint64_t *bars = reinterpret_cast<uint64_t *>(c.smem);
     const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * kUmmaMaxStages, acc_bar = empty0 + 8 * kUmmaMaxStages;
+    const uint32_t recv_bar = acc_bar + 8;  // counts partial sums delivered by the other k-slices
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(c.smem + 8 * (2 * kUmmaMaxStages + 2));
     int2 *tab = reinterpret_cast<int2 *>(c.smem + kUmmaHeaderBytes);
     const uint32_t tiles = smem_u32(c.smem) + conv_header_bytes(K);
+    // once the MMAs are done the ring holds the k-slices' partial sums (split > 1) and the store buffers
+    const int chunks = BN / 32, max_owned = (chunks + split - 1) / split;
+    const uint32_t staging = tiles + (uint32_t)umma_recv_bytes(BN, split, 4);
     int nbuf, group;
-    staging_plan(stages * kStageBytes / kUmmaStagingBytes, BN / 32, nbuf, group);
-    ChunkWriter<0> w{&p.map_out, p.co, ohw, 0, tiles + (uint32_t)(quad * nbuf) * 4096u, nbuf, lane, 0, co0 + quad * 32, img, px0, 32, group,
+    staging_plan((stages * kStageBytes - (int)(staging - tiles)) / kUmmaStagingBytes, max_owned, nbuf, group);
+    ChunkWriter<0> w{&p.map_out, p.co, ohw, 0, staging + (uint32_t)(quad * nbuf) * 4096u, nbuf, lane, 0, co0 + quad * 32, img, px0, split * 32, group,
                      (ohw & 3) ? p.y + (size_t)img * p.co * ohw : nullptr};
 
     long long *const tl = (p.timeline && c.vblock == 0) ? p.timeline : nullptr;
@@ -135,8 +147,18 @@ struct ConvUmmaTf32 {
         mbar_init(full0 + 8 * lane, 1 + 128);  // the weight copy's arrive.expect_tx + one arrive per gather thread
         mbar_init(empty0 + 8 * lane, 1);
       }
-      if (lane == 0) mbar_init(acc_bar, 1);
+      if (lane == 0) {
+        mbar_init(acc_bar, 1);
+        mbar_init(recv_bar, 1);
+      }
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      __syncwarp();
+      if (lane == 0 && split > 1) {
+        // bytes this CTA will receive: one partial per owned 32-pixel chunk from every k-slice (itself included)
+        int owned = 0;
+        for (int ch = kslice; ch < chunks; ch += split) ++owned;
+        mbar_expect_tx(recv_bar, (uint32_t)owned * (uint32_t)split * (32u * kUmmaBM * 4u));
+      }
     }
     if (warp == 5) {
       tmem_alloc(smem_u32(tmem_slot), BN);
@@ -149,7 +171,7 @@ struct ConvUmmaTf32 {
       const int khw = p.kh * p.kw, step_ch = 128 / khw, step_r = 128 % khw;
       const int inv_kw = (65536 + p.kw - 1) / p.kw;
       int ch = c.tid / khw, r = c.tid % khw;
-      for (int k = c.tid; k < num_kb * kBK; k += 128) {
+      for (int k = c.tid; k < total_kb * kBK; k += 128) {
         const int dy = (r * inv_kw) >> 16, dx = r - dy * p.kw;
         tab[k] = k < K ? make_int2((ch * p.h + dy) * p.wd + dx, r) : make_int2(0, 31);
         ch += step_ch, r += step_r;
@@ -165,13 +187,14 @@ struct ConvUmmaTf32 {
 
     // weight producer and MMA issuer: one elected thread each, ring slot / phase / descriptor word
     // carried incrementally (the issue loop is a dependent chain on one thread; see GemmUmma)
+    bool acc_ok = true;
     if (warp == 4) {
       if (elect_one()) {
         uint32_t s = 0, ph = 1, dst = tiles, bar = full0;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(empty0 + 8 * s, ph, c.status, UMMA_WAIT_EMPTY_TIMEOUT)) break;
           mbar_expect_tx(bar, kUmmaABytes);
-          tma_load_3d(dst, &p.map_w, bar, kb * kBK, co0, 0);
+          tma_load_3d(dst, &p.map_w, bar, (kb0 + kb) * kBK, co0, 0);
           if (++s == (uint32_t)stages) s = 0, ph ^= 1, dst = tiles, bar = full0;
           else dst += kStageBytes, bar += 8;
         }
@@ -205,15 +228,16 @@ struct ConvUmmaTf32 {
       __syncwarp();
     } else {
       bool ok;
-      if (BN == 128) ok = gather<128>(p, c, quad * 32 + lane, px0, img, num_kb, stages, tiles, full0, empty0, tab, tl);
-      else if (BN == 64) ok = gather<64>(p, c, quad * 32 + lane, px0, img, num_kb, stages, tiles, full0, empty0, tab, tl);
-      else ok = gather<32>(p, c, quad * 32 + lane, px0, img, num_kb, stages, tiles, full0, empty0, tab, tl);
+      const int2 *tab_slice = tab + kb0 * kBK;
+      if (BN == 128) ok = gather<128>(p, c, quad * 32 + lane, px0, img, num_kb, stages, tiles, full0, empty0, tab_slice, tl);
+      else if (BN == 64) ok = gather<64>(p, c, quad * 32 + lane, px0, img, num_kb, stages, tiles, full0, empty0, tab_slice, tl);
+      else ok = gather<32>(p, c, quad * 32 + lane, px0, img, num_kb, stages, tiles, full0, empty0, tab_slice, tl);
       (void)ok;
       // epilogue: accumulator rows are output channels, columns are this tile's pixels
-      const bool acc_ok = mbar_wait(acc_bar, 0, c.status, UMMA_WAIT_ACC_TIMEOUT);
+      acc_ok = mbar_wait(acc_bar, 0, c.status, UMMA_WAIT_ACC_TIMEOUT);
       tc_fence_after();
       mark(MARK_ACC_READY, c.tid == 0);
-      if (acc_ok) {
+      if (acc_ok && split == 1) {
 #pragma unroll 1
         for (int ch = 0; ch < BN / 32; ++ch) {
           const uint32_t buf = w.begin_chunk();
@@ -233,13 +257,17 @@ struct ConvUmmaTf32 {
         w.finish();
       }
     }
+    if (split > 1) umma_split_reduce<0>(c, BN, split, kslice, tiles, recv_bar, tmem_row, acc_ok, w, px0, nullptr, tl);
     tc_fence_before();
     c.sync();
     if (warp == 5) tmem_dealloc(tmem_acc, BN);
     if (c.persistent && c.tid < stages) {  // the next tile of a persistent CTA initialises them again
       mbar_inval(full0 + 8 * c.tid);
       mbar_inval(empty0 + 8 * c.tid);
-      if (c.tid == 0) mbar_inval(acc_bar);
+      if (c.tid == 0) {
+        mbar_inval(acc_bar);
+        mbar_inval(recv_bar);
+      }
     }
     mark(MARK_END, c.tid == 0);
   }

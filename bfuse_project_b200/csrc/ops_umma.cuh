@@ -348,6 +348,83 @@ __device__ __forceinline__ void staging_plan(int free_bufs, int total, int &nbuf
 }
 
 
+// The cross-CTA reduction of a tile whose K range is split over the `split` CTAs of a cluster
+// (k-slice = rank in the cluster); called by every thread of the operator after the MMAs.  The
+// tile's 128-byte output chunks are dealt to the k-slices round-robin; `tiles` (the ring, idle by
+// now) receives, per owned chunk, one fp32 partial from every k-slice, laid out
+// [16-column group][quarter][row][4 floats].  After one cluster barrier (every k-slice has finished
+// its MMAs, so every ring is free) each CTA pushes its partials straight from tensor memory into
+// the owners' shared memory; an owner waits on its mbarrier, which counts the delivered bytes,
+// sums the k-slices in order (deterministic) and stores the chunk through `w`.
+template <int KIND>
+__device__ __forceinline__ void umma_split_reduce(const TileCtx &c, int BN, int split, int kslice, uint32_t tiles, uint32_t recv_bar,
+                                                  uint32_t tmem_row, bool acc_ok, ChunkWriter<KIND> &w, int n0,
+                                                  const float *bias_tile, long long *tl) {
+  constexpr int kElem = KIND == 0 ? 4 : 2, kOutCols = 128 / kElem, kSub = kOutCols / 16;
+  constexpr uint32_t kChunkPartial = (uint32_t)kOutCols * kUmmaBM * 4;
+  const int warp = c.tid >> 5, lane = c.tid & 31, quad = (threadIdx.x >> 5) & 3;
+  const int chunks = BN / kOutCols, max_owned = (chunks + split - 1) / split;
+  auto mark = [&](int what, bool who) {
+    if (tl && who) tl[what] = (long long)global_ns();
+  };
+  cluster_sync_all();
+  mark(MARK_CLUSTER_SYNC1, c.tid == 0);
+  if (warp >= 4) return;
+  const int row = quad * 32 + lane;
+  if (acc_ok) {
+#pragma unroll 1
+    for (int cc = 0; cc < BN / 16; cc += 2) {
+      uint32_t r0[16], r1[16];
+      tmem_ld_32x16(tmem_row + cc * 16, r0);
+      tmem_ld_32x16(tmem_row + (cc + 1) * 16, r1);
+      tmem_ld_wait();
+      const int ch = cc / kSub, owner = ch % split;
+      const uint32_t slot = tiles + (uint32_t)((ch / split) * split + kslice) * kChunkPartial;
+      const uint32_t dst0 = peer_smem(slot + (uint32_t)((((cc % kSub) * 4) * kUmmaBM + row) * 16), (uint32_t)owner);
+      const uint32_t dst1 = dst0 + 4u * kUmmaBM * 16u;
+      const uint32_t bar = peer_smem(recv_bar, (uint32_t)owner);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        st_async_u4(dst0 + (uint32_t)(j * kUmmaBM * 16), bar, r0[4 * j], r0[4 * j + 1], r0[4 * j + 2], r0[4 * j + 3]);
+        st_async_u4(dst1 + (uint32_t)(j * kUmmaBM * 16), bar, r1[4 * j], r1[4 * j + 1], r1[4 * j + 2], r1[4 * j + 3]);
+      }
+    }
+  }
+  mark(MARK_PARTIAL_WRITTEN, c.tid == 0);
+  // all partials of the chunks this CTA owns have landed (a CTA that owns none expected no bytes)
+  int owned = 0;
+  for (int ch = kslice; ch < chunks; ch += split) ++owned;
+  const bool got = owned == 0 || mbar_wait(recv_bar, 0, c.status, UMMA_WAIT_PEERS_TIMEOUT);
+  mark(MARK_CLUSTER_SYNC2, c.tid == 0);
+  if (got) {
+#pragma unroll 1
+    for (int li = 0; li < max_owned; ++li) {
+      const int ch = li * split + kslice;
+      if (ch >= chunks) break;
+      const uint32_t buf = w.begin_chunk();
+#pragma unroll 1
+      for (int sub = 0; sub < kSub; ++sub) {
+        float acc[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) acc[j] = 0.f;
+#pragma unroll 1
+        for (int peer = 0; peer < split; ++peer) {  // k-slice order: the sum is deterministic
+          const uint32_t src = tiles + (uint32_t)(li * split + peer) * kChunkPartial + (uint32_t)(((sub * 4) * kUmmaBM + row) * 16);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float4 v = ld_shared_f4(src + (uint32_t)(j * kUmmaBM * 16));
+            acc[4 * j] += v.x, acc[4 * j + 1] += v.y, acc[4 * j + 2] += v.z, acc[4 * j + 3] += v.w;
+          }
+        }
+        w.put16(buf, sub, n0 + ch * kOutCols, acc, bias_tile);
+      }
+      w.end_chunk(buf, n0 + ch * kOutCols);
+    }
+    w.finish();
+  }
+  mark(MARK_REDUCED, c.tid == 0);
+}
+
 template <int KIND>
 struct GemmUmma {
   using Params = GemmUmmaParams;
@@ -571,66 +648,7 @@ struct GemmUmma {
         mark(MARK_PARTIAL_WRITTEN, c.tid == 0);
       }
     }
-    if (split > 1) {
-      // (A) every k-slice of the tile has finished its MMAs, so every ring in the cluster is free
-      cluster_sync_all();
-      mark(MARK_CLUSTER_SYNC1, c.tid == 0);
-      if (warp < 4) {
-        const int row = quad * 32 + lane;
-        if (acc_ok) {
-          // push: chunk ch belongs to k-slice ch % split; its receive slot for this k-slice's partial
-          // is [ch / split][kslice], laid out [16-column group][quarter][row][4 floats]
-#pragma unroll 1
-          for (int cc = 0; cc < BN / 16; cc += 2) {
-            uint32_t r0[16], r1[16];
-            tmem_ld_32x16(tmem_row + cc * 16, r0);
-            tmem_ld_32x16(tmem_row + (cc + 1) * 16, r1);
-            tmem_ld_wait();
-            const int ch = cc / kSub, owner = ch % split;
-            const uint32_t slot = tiles + (uint32_t)((ch / split) * split + kslice) * kChunkPartial;
-            const uint32_t dst0 = peer_smem(slot + (uint32_t)((((cc % kSub) * 4) * kUmmaBM + row) * 16), (uint32_t)owner);
-            const uint32_t dst1 = dst0 + 4u * kUmmaBM * 16u;
-            const uint32_t bar = peer_smem(recv_bar, (uint32_t)owner);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              st_async_u4(dst0 + (uint32_t)(j * kUmmaBM * 16), bar, r0[4 * j], r0[4 * j + 1], r0[4 * j + 2], r0[4 * j + 3]);
-              st_async_u4(dst1 + (uint32_t)(j * kUmmaBM * 16), bar, r1[4 * j], r1[4 * j + 1], r1[4 * j + 2], r1[4 * j + 3]);
-            }
-          }
-        }
-        mark(MARK_PARTIAL_WRITTEN, c.tid == 0);
-        // (B) all partials of the chunks this CTA owns have landed
-        const bool got = mbar_wait(recv_bar, 0, c.status, UMMA_WAIT_PEERS_TIMEOUT);
-        mark(MARK_CLUSTER_SYNC2, c.tid == 0);
-        if (got) {
-#pragma unroll 1
-          for (int li = 0; li < max_owned; ++li) {
-            const int ch = li * split + kslice;
-            if (ch >= chunks) break;
-            const uint32_t buf = w.begin_chunk();
-#pragma unroll 1
-            for (int sub = 0; sub < kSub; ++sub) {
-              float acc[16];
-#pragma unroll
-              for (int j = 0; j < 16; ++j) acc[j] = 0.f;
-#pragma unroll 1
-              for (int peer = 0; peer < split; ++peer) {  // k-slice order: the sum is deterministic
-                const uint32_t src = tiles + (uint32_t)(li * split + peer) * kChunkPartial + (uint32_t)(((sub * 4) * kUmmaBM + row) * 16);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  const float4 v = ld_shared_f4(src + (uint32_t)(j * kUmmaBM * 16));
-                  acc[4 * j] += v.x, acc[4 * j + 1] += v.y, acc[4 * j + 2] += v.z, acc[4 * j + 3] += v.w;
-                }
-              }
-              w.put16(buf, sub, n0 + ch * kOutCols, acc, bias_tile);
-            }
-            w.end_chunk(buf, n0 + ch * kOutCols);
-          }
-          w.finish();
-        }
-        mark(MARK_REDUCED, c.tid == 0);
-      }
-    }
+    if (split > 1) umma_split_reduce<KIND>(c, BN, split, kslice, tiles, recv_bar, tmem_row, acc_ok, w, n0, bias_tile, tl);
     tc_fence_before();
     c.sync();
     if (warp == 5) tmem_dealloc(tmem_acc, BN * halves);

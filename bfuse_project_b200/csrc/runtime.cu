@@ -134,9 +134,13 @@ void pick_tile(int batch, int M, int N, int K, int elem, int sm_count, int bn_fi
     const int bn = kBn[i];
     if (bn_fixed > 0 ? bn != bn_fixed : (bn * elem < 128 || (bn > 32 && bn / 2 >= N && bn / 2 * elem >= 128))) continue;
     const long long tiles = (long long)batch * ceil_div(M, kUmmaBM) * ceil_div(N, bn);
-    for (int split = 1; split <= 4; split *= 2) {
-      if (split_fixed > 0 ? split != split_fixed : split > num_kb) continue;
-      if (umma_smem_bytes(bn, umma_min_stages(bn, split, elem)) > (bn == 256 ? 200 : 100) * 1024) continue;
+    // own choice of k-slices: 1 or 4 and no other width, so that any two operators the runtime tiled
+    // can share a launch (a fused launch has one cluster width)
+    const int cand[2] = {split_fixed > 0 ? split_fixed : 1, split_fixed > 0 ? split_fixed : 4};
+    for (int ci = 0; ci < (split_fixed > 0 ? 1 : 2); ++ci) {
+      const int split = cand[ci];
+      if (split > num_kb) continue;
+      if (umma_smem_bytes(bn, umma_min_stages(bn, split, elem)) > ((bn == 256 || 2 * tiles * split <= sm_count) ? 200 : 100) * 1024) continue;
       const long long waves = (tiles * split + slots - 1) / slots;
       const double per_cta = 1.0 + 0.006 * bn + ceil_div(num_kb, split) * kTkbUs[i] + (split > 1 ? 2.5 + 0.5 * split : 0.0);
       const double t = (double)waves * per_cta;
@@ -210,12 +214,25 @@ int default_launch(const bfuse_context *ctx, bfuse_kernel_desc *d, std::string *
       if (bn != 32 && bn != 64 && bn != 128) { *err = "conv2d: pixels per tile must be 32, 64 or 128"; return BFUSE_ERR_SHAPE; }
       d->shape[9] = bn;
       const int K = s[1] * s[5] * s[6];
+      const long long tiles = (long long)s[0] * ceil_div(oh * ow, bn) * ceil_div(s[4], kUmmaBM);
+      // k-slices per tile (a cluster): a deep layer on a small image has few tiles and a long K.  The
+      // runtime's own choice is 1 or 4 -- never another width, so that any two operators it tiled can
+      // share a launch (a fused launch has one cluster width): 4 when the k-slices still fit three
+      // quarters of the SMs and keep at least 4 K blocks each (8-wide clusters measured slower in pairs)
+      int split = s[10];
+      if (split <= 0) split = (tiles * 4 <= 3 * sm / 4 && num_kb >= 16) ? 4 : 1;
+      if (split > 8 || split > num_kb) { *err = "conv2d: k-slices must be 1..8 and at most the number of K blocks"; return BFUSE_ERR_SHAPE; }
+      const int q = ceil_div(num_kb, split);
+      split = ceil_div(num_kb, q);
+      d->shape[10] = split;
       // ring: two CTAs per SM, or the whole SM when the operator and an equal partner leave every CTA
-      // an SM of its own (a long-K conv on few CTAs is bound by the ring's round trip, not by issue rate)
-      const long long ctas = (long long)s[0] * ceil_div(oh * ow, bn) * ceil_div(s[4], kUmmaBM);
+      // an SM of its own (a long-K conv on few CTAs is bound by the ring's round trip, not by issue
+      // rate); deep enough to hold the k-slices' partial sums after the MMAs
+      const long long ctas = tiles * split;
       const int budget = (2 * ctas <= sm ? 200 : 110) * 1024;
-      const int stages = std::max(1, std::min({num_kb, kUmmaMaxStages, (budget - conv_header_bytes(K)) / conv_stage_bytes(bn)}));
-      set(ceil_div(oh * ow, bn), ceil_div(s[4], kUmmaBM), s[0], kUmmaThreads, 1, conv_umma_smem_bytes(stages, bn, K), 3);
+      int stages = std::max(1, std::min({q, kUmmaMaxStages, (budget - conv_header_bytes(K)) / conv_stage_bytes(bn)}));
+      stages = std::max(stages, ceil_div(umma_epilogue_bytes(bn, split, 4), conv_stage_bytes(bn)));
+      set(split * ceil_div(oh * ow, bn), ceil_div(s[4], kUmmaBM), s[0], kUmmaThreads, 1, conv_umma_smem_bytes(stages, bn, K), 3);
       return BFUSE_OK;
     }
     case BFUSE_OP_GEMM_TF32:
@@ -405,9 +422,13 @@ int build_params(bfuse_context *ctx, KernelRec &k) {
       if (kd.bx != kUmmaThreads || kd.by != 1 || kd.bz != 1) return shape_err("BlockDim must be (192, 1, 1)");
       const int bn = s[9] > 0 ? s[9] : kConvBN;
       if (bn != 32 && bn != 64 && bn != 128) return shape_err("shape[9] (pixels per tile) must be 32, 64 or 128");
-      if (kd.gx != ceil_div(oh * ow, bn) || kd.gy != ceil_div(s[4], kUmmaBM) || kd.gz != s[0])
-        return shape_err("GridDim must be (ceil(oh*ow/BN), ceil(co/128), n)");
-      if (k.smem < (size_t)conv_umma_smem_bytes(1, bn, K)) return shape_err("shared memory below one pipeline stage");
+      const int split = s[10] > 0 ? s[10] : 1, num_kb = ceil_div(K, ConvUmmaTf32::kBK), q = ceil_div(num_kb, split);
+      if (split > 8 || (split - 1) * q >= num_kb) return shape_err("shape[10] (k-slices) must be 1..8 with every k-slice non-empty");
+      if (kd.gx != split * ceil_div(oh * ow, bn) || kd.gy != ceil_div(s[4], kUmmaBM) || kd.gz != s[0])
+        return shape_err("GridDim must be (k-slices * ceil(oh*ow/BN), ceil(co/128), n)");
+      if (k.smem < (size_t)conv_umma_smem_bytes(ceil_div(umma_epilogue_bytes(bn, split, 4), conv_stage_bytes(bn)), bn, K))
+        return shape_err("shared memory below the store buffers (and, for a split conv, the receive area of the k-slices)");
+      k.cluster = split;
       ConvUmmaParams p;
       std::memset(&p, 0, sizeof(p));
       int rc = encode_map(ctx, &p.map_w, 4, a[1], K, s[4], 1, kUmmaBM);
@@ -422,6 +443,8 @@ int build_params(bfuse_context *ctx, KernelRec &k) {
       p.oh = oh, p.ow = ow, p.K = K;
       p.stages = std::min<int>(kUmmaMaxStages, (int)((k.smem - conv_header_bytes(K)) / conv_stage_bytes(bn)));
       p.bn = bn;
+      p.split = split;
+      p.kb_per_slice = q;
       static_assert(sizeof(p) <= kParamsBytes, "parameter block too small");
       std::memcpy(k.params, &p, sizeof(p));
       return BFUSE_OK;
@@ -556,7 +579,9 @@ bool ring_info(const KernelRec &k, int *header, int *stage_bytes, int *min_stage
     return true;
   }
   if (k.desc.op == BFUSE_OP_CONV2D_TF32) {
-    *header = conv_header_bytes(s[1] * s[5] * s[6]), *stage_bytes = conv_stage_bytes(s[9] > 0 ? s[9] : kConvBN), *min_stages = 1;
+    const int bn = s[9] > 0 ? s[9] : kConvBN;
+    *header = conv_header_bytes(s[1] * s[5] * s[6]), *stage_bytes = conv_stage_bytes(bn);
+    *min_stages = ceil_div(umma_epilogue_bytes(bn, std::max(1, s[10]), 4), conv_stage_bytes(bn));
     *stages = reinterpret_cast<const ConvUmmaParams *>(k.params)->stages;
     return true;
   }

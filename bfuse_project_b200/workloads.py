@@ -108,11 +108,11 @@ def gemm(name, rng, op, batch, M, N, K, bias=False, causal=False, w_std=0.02, a=
                       flops=2.0 * batch * M * N * K)
 
 
-def conv2d(name, rng, op, n, ci, h, w, co, k, stride, pad, x=None, bn=0):
+def conv2d(name, rng, op, n, ci, h, w, co, k, stride, pad, x=None, bn=0, split=0):
     X = rng.standard_normal((n, ci, h, w), dtype=np.float32) if x is None else x
     Wt = (np.sqrt(2.0 / (ci * k * k)) * rng.standard_normal((co, ci, k, k), dtype=np.float32)).astype(np.float32)
     oh, ow = (h + 2 * pad - k) // stride + 1, (w + 2 * pad - k) // stride + 1
-    shape = (n, ci, h, w, co, k, k, stride, pad, bn) if op == OP_CONV2D_TF32 else (n, ci, h, w, co, k, k, stride, pad)
+    shape = (n, ci, h, w, co, k, k, stride, pad, bn, split) if op == OP_CONV2D_TF32 else (n, ci, h, w, co, k, k, stride, pad)
     return KernelSpec(name, op, shape, [X, Wt, np.zeros((n, co, oh, ow), np.float32)],
                       [2], flops=2.0 * n * co * oh * ow * ci * k * k)
 

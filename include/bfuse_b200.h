@@ -48,7 +48,8 @@ enum {
                               /* shape[6] = BM tile height (128, or 256 with one k-slice); 0 = runtime's choice */
   BFUSE_OP_GEMM_BF16 = 7,     /* bf16 A, W, out; fp32 accumulate; tcgen05 kind::f16; shape[4..6] as above    */
   BFUSE_OP_CONV2D_TF32 = 8,   /* as CONV2D_F32_SIMT on tcgen05 kind::tf32 (implicit GEMM); shape[9] = output */
-                              /* pixels per tile (32, 64, 128; 0 = chosen by the runtime)                   */
+                              /* pixels per tile (32, 64, 128), shape[10] = k-slices per tile (a cluster    */
+                              /* reduces them); 0 = chosen by the runtime                                   */
   BFUSE_OP_COUNT = 9
 };
 

@@ -52,10 +52,23 @@ def test_explicit_tile_fields_are_validated():
     assert bf.lib().bfuse_default_launch(None, d) == 2       # tall tiles only unsplit
 
 
-def test_conv_pixel_tile_width_follows_the_image_count():
-    one = default(bf.OP_CONV2D_TF32, (1, 64, 56, 56, 128, 3, 3, 2, 1))
-    assert one.shape[9] == 32 and one.GridDim.tuple() == (25, 1, 1)          # 784 pixels of one image
+def test_conv_pixel_tile_width_and_k_slices_follow_the_image_count():
+    one = default(bf.OP_CONV2D_TF32, (1, 64, 56, 56, 128, 3, 3, 2, 1))        # 784 pixels of one image, 18 K blocks
+    assert (one.shape[9], one.shape[10]) == (32, 4) and one.GridDim.tuple() == (100, 1, 1)
+    short = default(bf.OP_CONV2D_TF32, (1, 64, 56, 56, 128, 1, 1, 2, 0))      # K = 64: nothing to split
+    assert (short.shape[9], short.shape[10]) == (32, 1) and short.GridDim.tuple() == (25, 1, 1)
     many = default(bf.OP_CONV2D_TF32, (256, 64, 56, 56, 128, 3, 3, 2, 1))
-    assert many.shape[9] == 128 and many.GridDim.tuple() == (7, 1, 256)
-    deep = default(bf.OP_CONV2D_TF32, (1, 512, 7, 7, 512, 3, 3, 1, 1))        # K = 4608: the table takes 36 KB
-    assert deep.shape[9] == 32 and deep.GridDim.tuple() == (2, 4, 1) and deep.smem_bytes > 36 * 1024 + 8 * 20 * 1024 - 1
+    assert (many.shape[9], many.shape[10]) == (128, 1) and many.GridDim.tuple() == (7, 1, 256)
+    deep = default(bf.OP_CONV2D_TF32, (1, 512, 7, 7, 512, 3, 3, 1, 1))        # K = 4608 on 8 tiles: the table takes 36 KB
+    assert (deep.shape[9], deep.shape[10]) == (32, 4) and deep.GridDim.tuple() == (8, 4, 1)
+    assert deep.smem_bytes >= 2048 + 36 * 1024 + 4 * 16 * 1024 + 16 * 1024   # header, table, 4 partial sums, store buffers
+
+
+def test_automatic_k_slices_are_one_or_four():
+    """Any two operators the runtime tiled itself can share a launch: their cluster widths are 1 or 4."""
+    seen = set()
+    for m, n, k in ((128, 128, 8192), (256, 256, 4096), (512, 768, 768), (64, 64, 16384), (128, 512, 2048), (512, 512, 64)):
+        seen.add(gemm(bf.OP_GEMM_BF16, 1, m, n, k)["split"])
+    for sh in ((1, 256, 14, 14, 256, 3, 3, 1, 1), (1, 128, 28, 28, 128, 3, 3, 1, 1), (1, 768, 17, 17, 192, 1, 1, 1, 0), (4, 64, 56, 56, 64, 3, 3, 1, 1)):
+        seen.add(default(bf.OP_CONV2D_TF32, sh).shape[10])
+    assert seen <= {1, 4} and 4 in seen

@@ -182,6 +182,27 @@ def test_conv_long_k_and_odd_pixel_counts(rt):
         run_and_check(rt, wl.PairSpec("conv_mid_odd_bn%d" % bn, c, d, "tf32", "hbm"), [(bf.ZIGZAG, 1, 1), (bf.WORK_QUEUE, 1, 1)])
 
 
+def test_conv_split_k_over_a_cluster(rt):
+    """K of a conv split over 2, 4 and 8 CTAs of a cluster (uneven last slice included), every pixel-tile
+    width, odd pixel counts; the runtime's own choice for a deep layer on a small image is a split one;
+    thread split and the work queue refuse the clustered operator."""
+    rng = np.random.default_rng(55)
+    for split, bn in ((2, 128), (4, 64), (8, 32), (3, 32)):
+        # both operators of a launch need the same cluster width: K block counts (74 and 24) that every split here survives
+        a = wl.conv2d("deep", rng, bf.OP_CONV2D_TF32, 1, 260, 14, 14, 256, 3, 1, 1, bn=bn, split=split)    # K = 2340 (74 blocks, uneven slices), 196 pixels
+        b = wl.conv2d("odd", rng, bf.OP_CONV2D_TF32, 2, 768, 17, 17, 160, 1, 1, 0, bn=bn, split=split)      # K = 768 (24 blocks), 289 pixels
+        pair = run_and_check(rt, wl.PairSpec("conv_split%d" % split, a, b, "tf32", "hbm"), [(bf.ZIGZAG, 1, 1), (bf.RANGE_SPLIT, 0, 0)])
+        assert pair.spec.a.launch[0][0] == split * -(-196 // bn)
+    c = wl.conv2d("auto", rng, bf.OP_CONV2D_TF32, 1, 512, 7, 7, 512, 3, 1, 1)                              # K = 4608 on 8 tiles
+    d = wl.conv2d("plain", rng, bf.OP_CONV2D_TF32, 1, 64, 56, 56, 128, 1, 2, 0)
+    pair = run_and_check(rt, wl.PairSpec("conv_auto_split", c, d, "tf32", "hbm"), [(bf.ZIGZAG, 1, 1), (bf.SM_STRIPED, 0, 0)])
+    assert pair.spec.a.launch[0][0] > 2                      # more CTAs along x than the 2 pixel tiles: K was split
+    for pat in (bf.THREAD_SPLIT, bf.WORK_QUEUE):
+        with pytest.raises(bf.BfuseError) as e:
+            pair.fusion(pat, 1, 1)
+        assert e.value.code == 7
+
+
 def test_conv_pixel_tile_widths(rt):
     """Every pixel-tile width of the tensor-core conv body (32, 64, 128 pixels; 4, 2, 1 gather threads
     per pixel) on a padded 3x3 stride-2 conv and a 1x1 conv whose pixel count is not a tile multiple."""
