@@ -25,7 +25,6 @@ restatement of the same pair (the reference has no CPU operator code of its own)
 import argparse
 import json
 import os
-import subprocess
 import sys
 import threading
 import time
@@ -49,38 +48,55 @@ def peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clock / throttle samples taken during the timed region."""
+    """SM clock and throttle-reason samples taken during the timed region.  The region lasts
+    milliseconds, so the samples come from NVML queries (read-only) polled by a thread every
+    millisecond; `nvidia-smi -lms` would not deliver its first line in time."""
 
-    def __init__(self, index):
-        self.rows, self.proc, self.index = [], None, index
+    REASONS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20), ("sw_power_cap", 0x4))
+
+    def __init__(self, index, uuid=None):
+        self.rows, self.index, self.uuid = [], index, uuid
+        self.nvml, self.handle, self.thread, self.halt = None, None, None, threading.Event()
 
     def start(self):
-        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + q,
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
-                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            threading.Thread(target=self._read, daemon=True).start()
-        except OSError:
-            self.proc = None
+            import pynvml
+            pynvml.nvmlInit()
+            try:
+                self.handle = pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + str(self.uuid)).encode()) if self.uuid else None
+            except pynvml.NVMLError:
+                self.handle = None
+            if self.handle is None:
+                self.handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            self._sample(pynvml)          # one sample before the region starts, so a very short region still has one
+            self.nvml = pynvml
+            self.thread = threading.Thread(target=self._poll, daemon=True)
+            self.thread.start()
+        except Exception:                 # no NVML on this machine: the record says so
+            self.nvml = None
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+    def _sample(self, nv):
+        self.rows.append((int(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM)),
+                          int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle))))
+
+    def _poll(self):
+        while not self.halt.is_set():
+            try:
+                self._sample(self.nvml)
+            except Exception:
+                break
+            self.halt.wait(0.001)
 
     def stop(self):
-        if not self.proc:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
-        self.proc.terminate()
-        rows = [r for r in self.rows if len(r) == 6 and r[0].isdigit()]
-        if not rows:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
-        mhz = sorted(int(r[0]) for r in rows)
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in rows)]
-        return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": int(rows[0][1]), "reasons": reasons, "samples": len(rows)}
+        if not self.nvml:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["NVML unavailable"]}
+        self.halt.set()
+        self.thread.join(timeout=1.0)
+        rows = self.rows[1:] if len(self.rows) > 1 else self.rows
+        mhz = sorted(r[0] for r in rows)
+        reasons = [n for n, bit in self.REASONS if any(r[1] & bit for r in rows)]
+        return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": self.max_mhz, "reasons": reasons, "samples": len(rows)}
 
 
 def cpu_pair_time(spec, budget_s=8.0):
@@ -400,7 +416,7 @@ def main():
         torch.cuda.synchronize()
     trial = {k: timed(g, 3, 3) for k, g in graphs.items()}
     best = min((k for k in trial if k.startswith("fused_")), key=lambda k: trial[k])
-    sampler = ClockSampler(local)
+    sampler = ClockSampler(local, getattr(torch.cuda.get_device_properties(local), "uuid", None))
     if rank == 0:
         sampler.start()
     ms = timed(graphs[best], args.steps, args.warmup)
