@@ -270,6 +270,39 @@ def attention_block(rt, torch, bf):
         return {"error": str(e)[:300]}
 
 
+def model_segments(rt, torch, bf):
+    """Operator lists of model layers walked by the segment driver: ready operators of one body share an
+    n-way launch (Q || K || V, the branches of a down-sampling block, the same operator of independent
+    requests), against one launch per operator; CUDA-graph replay of the whole segment on the same buffers."""
+    from bfuse_project_b200 import attention, segment
+    out = {}
+    for name, build in segment.SEGMENTS.items():
+        try:
+            b, ops = build(rt, torch)
+            seg = segment.Segment(rt, ops)
+            seq_us = attention.graph_time_us(torch, seg.run_sequential)
+            fused_us = attention.graph_time_us(torch, seg.run_fused)
+            stream = torch.cuda.current_stream().cuda_stream
+            names = sorted({w for o in ops for w in o.writes})
+            seg.run_sequential(stream)
+            torch.cuda.synchronize()
+            want = {n: b.buf[n].clone() for n in names}
+            for n in names:
+                b.buf[n].zero_()
+            seg.run_fused(stream)
+            torch.cuda.synchronize()
+            same = all(torch.equal(b.buf[n].view(torch.uint8), want[n].view(torch.uint8)) for n in names)
+            kinds = [k for step in seg.describe() for k, _ in step]
+            out[name] = {"operators": seg.launches_sequential, "fused_launches": seg.launches_fused,
+                         "groups": kinds.count("group"), "pairs": kinds.count("pair"),
+                         "sequential_us": seq_us, "fused_us": fused_us, "speedup": seq_us / fused_us, "bit_identical": bool(same)}
+            del b, ops, seg, want
+            torch.cuda.empty_cache()
+        except Exception as e:   # reported, not hidden
+            out[name] = {"error": str(e)[:300]}
+    return out
+
+
 def reference_fuser_output(rt, torch, bf, wl, pk):
     """The reference fuser's generated bfuse / hfuse kernels compiled for sm_100a, at their own
     batch-1024 fp32 shapes, beside this runtime's fused pair on the same shapes (fp32 in, tf32 MMA)."""
@@ -535,6 +568,7 @@ def main():
         line["pairs"] = side_pairs
         line["conv_n256_sharded"] = conv256
         line["attention_block"] = attention_block(rt, torch, bf)
+        line["model_segments"] = model_segments(rt, torch, bf)
         line["reference_fuser_output"] = reference_fuser_output(rt, torch, bf, wl, pk)
     print(json.dumps(line), flush=True)
     if world > 1:

@@ -91,6 +91,10 @@ def lib():
             "bfuse_plan_map_block": [vp, C.c_int, ip, ip], "bfuse_plan_map_all": [vp, ip, ip, C.c_int],
             "bfuse_plan_map_thread": [vp, C.c_int, C.c_int, C.c_int, ip, ip, ip],
             "bfuse_plan_barrier": [vp, C.c_int, ip, ip],
+            "bfuse_register_group": [vp, ip, C.c_int, C.c_int, C.c_int, C.c_int, ip],
+            "bfuse_group_info": [vp, C.c_int, kd], "bfuse_group_map_block": [vp, C.c_int, C.c_int, ip, ip],
+            "bfuse_launch_group": [vp, C.c_int, vp],
+            "bfuse_plan_group": [C.POINTER(Dim3), C.POINTER(Dim3), C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, ip, ip, ip, C.c_int],
         }
         for name, args in sig.items():
             fn = getattr(L, name)
@@ -155,6 +159,24 @@ class Plan:
         a, b = C.c_int(), C.c_int()
         lib().bfuse_plan_barrier(self._h, kernel, a, b)
         return a.value, b.value
+
+
+def plan_group(kernels, pattern, param_m=1, param_n=1, cluster=1):
+    """The block-dispatch plan of 2..4 kernels in one launch, computed on the CPU.
+    kernels: [gx, gy, gz, bx, by, bz] lists.  Returns (fused_grid, fused_block, kernel_of, vblock_of);
+    padding CTAs of a clustered plan map to -1."""
+    import numpy as np
+    n = len(kernels)
+    g = (Dim3 * n)(*[Dim3(*k[:3]) for k in kernels])
+    b = (Dim3 * n)(*[Dim3(*k[3:]) for k in kernels])
+    fb = C.c_int()
+    ip = C.POINTER(C.c_int)
+    grid = lib().bfuse_plan_group(g, b, n, pattern, param_m, param_n, cluster, fb, None, None, 0)
+    if grid < 0:
+        raise BfuseError(-grid, "group plan rejected")
+    ks, vbs = np.empty(grid, np.int32), np.empty(grid, np.int32)
+    lib().bfuse_plan_group(g, b, n, pattern, param_m, param_n, cluster, fb, ks.ctypes.data_as(ip), vbs.ctypes.data_as(ip), grid)
+    return grid, fb.value, ks, vbs
 
 
 # --------------------------------------------------------------------------------- runtime
@@ -234,6 +256,28 @@ class Runtime:
         h = C.c_int()
         self._ck(self._L.bfuse_register_fusion(self._ctx, k1, k2, pattern, param_m, param_n, h))
         return h.value
+
+    def register_group(self, kernels, pattern, param_m=0, param_n=0):
+        """2..4 registered kernels of one operator body in one fused launch."""
+        arr = (C.c_int * len(kernels))(*kernels)
+        h = C.c_int()
+        self._ck(self._L.bfuse_register_group(self._ctx, arr, len(kernels), pattern, param_m, param_n, h))
+        return h.value
+
+    def group_info(self, group):
+        d = KernelDesc()
+        self._ck(self._L.bfuse_group_info(self._ctx, group, d))
+        return {"KernelName": d.KernelName.decode(), "GridDim": d.GridDim.tuple(), "BlockDim": d.BlockDim.tuple(),
+                "Reg": d.Reg, "smem_bytes": d.smem_bytes, "launched_ctas": d.shape[0]}
+
+    def group_map_block(self, group, b):
+        k, vb = C.c_int(), C.c_int()
+        if self._L.bfuse_group_map_block(self._ctx, group, b, k, vb):
+            return None
+        return k.value, vb.value
+
+    def launch_group(self, group, stream=None):
+        self._ck(self._L.bfuse_launch_group(self._ctx, group, stream))
 
     def fusion_info(self, fusion):
         d = KernelDesc()

@@ -105,4 +105,53 @@ BFUSE_HD bool decode_cta(const DispatchTable &t, int b, int &k, int &vb) {
   return vb < t.n_cta[k];
 }
 
+// ---- n operators of one body in one launch ------------------------------------------------------
+// The reference writes its patterns for n kernels (Algorithms.cc:323-375, 538-587) although its
+// test suite only ever fuses two.  A group is that general form for up to kGroupMax operators that
+// share a body (the Q, K and V projections of one layer, the branches of one block): a rotating
+// region of sum(ratio) units in which residues [ratio_lo[k], ratio_lo[k + 1]) belong to operator
+// k, then what is left of each operator as one contiguous tail, in registration order.
+constexpr int kGroupMax = 4;
+
+struct GroupTable {
+  int n;              // operators in the group (2..kGroupMax)
+  int total;          // dispatch units
+  int cluster;        // CTAs per dispatch unit (see DispatchTable::cluster)
+  int n_cta[kGroupMax], n_thr[kGroupMax];
+  int grid_x[kGroupMax], grid_y[kGroupMax];
+  int blk_x[kGroupMax], blk_y[kGroupMax];
+  int bar_count[kGroupMax];
+  int rot_end, rot, ratio_lo[kGroupMax + 1];
+  int tail_lo[kGroupMax], tail_hi[kGroupMax], tail_base[kGroupMax];
+  int *status;
+};
+
+BFUSE_HD bool decode_group_unit(const GroupTable &t, int b, int &k, int &vb) {
+  if (b < t.rot_end) {
+    const int r = b % t.rot, q = b / t.rot;
+    for (int i = 0; i < t.n; ++i)
+      if (r < t.ratio_lo[i + 1]) {
+        k = i;
+        vb = q * (t.ratio_lo[i + 1] - t.ratio_lo[i]) + (r - t.ratio_lo[i]);
+        return true;
+      }
+    return false;
+  }
+  for (int i = 0; i < t.n; ++i)
+    if (b >= t.tail_lo[i] && b < t.tail_hi[i]) {
+      k = i;
+      vb = b - t.tail_lo[i] + t.tail_base[i];
+      return true;
+    }
+  return false;
+}
+
+BFUSE_HD bool decode_group_cta(const GroupTable &t, int b, int &k, int &vb) {
+  if (t.cluster <= 1) return decode_group_unit(t, b, k, vb);
+  int vu;
+  if (!decode_group_unit(t, b / t.cluster, k, vu)) return false;
+  vb = vu * t.cluster + b % t.cluster;
+  return vb < t.n_cta[k];
+}
+
 }  // namespace bfuse

@@ -9,6 +9,8 @@
 //                              from an atomic counter (persistent work queue);
 //   fused_thread_kernel<A, B>  both operators inside every CTA, split by thread range, each
 //                              synchronising on its own named barrier; shared memory is the sum;
+//   fused_group_kernel<A>      up to four operators of one body in one launch (the reference's
+//                              n-kernel form of the block-level patterns);
 //   single_kernel<A>           the unfused launch of the same body (baselines, bit-exact check);
 //   trace_kernel               the dispatch decode alone, recording what each CTA would run.
 //
@@ -152,6 +154,39 @@ __global__ void __launch_bounds__(A::kMaxThreads + B::kMaxThreads, 1)
   }
 }
 
+// Parameter blocks of a group, indexed by the operator the dispatch decode returns.
+template <class A>
+struct GroupParams {
+  typename A::Params p[kGroupMax];
+};
+
+template <class A>
+__global__ void __launch_bounds__(A::kMaxThreads, A::kMinBlocks)
+    fused_group_kernel(const __grid_constant__ GroupTable t, const __grid_constant__ GroupParams<A> g) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char *smem = align_smem_1k(smem_raw);
+  grid_launch_dependents();
+  grid_dependency_wait();
+  int k, vb;
+  if (!decode_group_cta(t, blockIdx.x, k, vb)) return;
+  const int tid = threadIdx.x;
+  if (tid >= t.n_thr[k]) return;   // guard of the reference: KernelID_ == k && threadIdx.x < B_k
+  TileCtx c;
+  c.vblock = vb;
+  c.tid = tid;
+  c.nthreads = t.n_thr[k];
+  c.bar_id = 1;
+  c.bar_count = t.bar_count[k];
+  c.gx = t.grid_x[k];
+  c.gy = t.grid_y[k];
+  c.bx = t.blk_x[k];
+  c.by = t.blk_y[k];
+  c.smem = smem;
+  c.status = t.status;
+  c.persistent = 0;
+  A::run(g.p[k], c);
+}
+
 template <class A>
 __global__ void __launch_bounds__(A::kMaxThreads, A::kMinBlocks)
     single_kernel(const __grid_constant__ DispatchTable t, const __grid_constant__ typename A::Params pa) {
@@ -168,6 +203,8 @@ typedef cudaError_t (*PairLaunchFn)(const DispatchTable &, const void *pa, const
                                     unsigned block, size_t smem, cudaStream_t);
 typedef cudaError_t (*SingleLaunchFn)(const DispatchTable &, const void *pa, unsigned grid, unsigned block,
                                       size_t smem, cudaStream_t);
+typedef cudaError_t (*GroupLaunchFn)(const GroupTable &, const void *const *params, int n, unsigned grid, unsigned block,
+                                     size_t smem, cudaStream_t);
 typedef cudaError_t (*AttrFn)(cudaFuncAttributes *);
 
 template <class Kernel>
@@ -222,6 +259,17 @@ cudaError_t launch_single(const DispatchTable &t, const void *pa, unsigned grid,
   return launch_clustered(single_kernel<A>, grid, block, smem, s, t.cluster, t,
                           *static_cast<const typename A::Params *>(pa));
 }
+template <class A>
+cudaError_t launch_group(const GroupTable &t, const void *const *params, int n, unsigned grid, unsigned block, size_t smem,
+                         cudaStream_t s) {
+  cudaError_t e = ensure_smem(fused_group_kernel<A>, smem);
+  if (e != cudaSuccess) return e;
+  GroupParams<A> g;
+  for (int i = 0; i < kGroupMax; ++i) g.p[i] = *static_cast<const typename A::Params *>(params[i < n ? i : 0]);
+  return launch_clustered(fused_group_kernel<A>, grid, block, smem, s, t.cluster, t, g);
+}
+template <class A>
+cudaError_t attr_group(cudaFuncAttributes *a) { return cudaFuncGetAttributes(a, fused_group_kernel<A>); }
 template <class A, class B>
 cudaError_t launch_block_pair_wide(const DispatchTable &t, const void *pa, const void *pb, unsigned grid, unsigned block,
                                    size_t smem, cudaStream_t s) {

@@ -37,6 +37,8 @@ struct PairEntry {
 struct SingleEntry {
   SingleLaunchFn launch;
   AttrFn attr;
+  GroupLaunchFn group;       // up to kGroupMax operators of this body in one launch
+  AttrFn group_attr;
   int max_threads;
   size_t params_size;
 };

@@ -48,6 +48,8 @@ void fill_pair_row<BFUSE_ROW>(PairEntry *row, SingleEntry *single) {
   RowFiller<BFUSE_ROW, 0>::fill(row);
   single->launch = &launch_single<A>;
   single->attr = &attr_single<A>;
+  single->group = &launch_group<A>;
+  single->group_attr = &attr_group<A>;
   single->max_threads = A::kMaxThreads;
   single->params_size = sizeof(typename A::Params);
 }

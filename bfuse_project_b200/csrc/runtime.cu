@@ -57,6 +57,16 @@ struct FusionRec {
   bool wide;            // launch the register-richer build of the pair
 };
 
+struct GroupRec {
+  int n;
+  int ks[kGroupMax];
+  GroupPlan plan;
+  std::string name;
+  size_t smem;
+  int regs;
+  int stages[kGroupMax];  // ring depths replaced so that two CTAs share an SM (0: the kernel's own)
+};
+
 struct GraphRec {
   cudaGraphExec_t exec;
   int launches;
@@ -76,6 +86,7 @@ struct bfuse_context {
   SingleEntry singles[kNumOps];
   std::vector<std::unique_ptr<KernelRec>> kernels;
   std::vector<std::unique_ptr<FusionRec>> fusions;
+  std::vector<std::unique_ptr<GroupRec>> groups;
   std::vector<GraphRec> graphs;
   std::string err;
 };
@@ -875,6 +886,121 @@ int bfuse_register_fusion(bfuse_context *ctx, int kernel1, int kernel2, int patt
   ctx->fusions.push_back(std::move(f));
   *fusion = (int)ctx->fusions.size() - 1;
   return BFUSE_OK;
+}
+
+int bfuse_register_group(bfuse_context *ctx, const int *kernels, int n, int pattern, int param_m, int param_n, int *group) {
+  if (!ctx || !kernels || !group) return fail(ctx, BFUSE_ERR_INVALID, "null argument");
+  if (n < 2 || n > kGroupMax) return fail(ctx, BFUSE_ERR_INVALID, "a group holds 2 to 4 kernels");
+  std::unique_ptr<GroupRec> g(new GroupRec());
+  g->n = n;
+  KernelRec *ks[kGroupMax];
+  KernelDims kd[kGroupMax];
+  int cluster = 1;
+  for (int i = 0; i < n; ++i) {
+    ks[i] = get_kernel(ctx, kernels[i]);
+    if (!ks[i]) return fail(ctx, BFUSE_ERR_INVALID, "bad kernel handle");
+    if (ks[i]->desc.op != ks[0]->desc.op) return fail(ctx, BFUSE_ERR_UNSUPPORTED, "the kernels of a group must share one operator body");
+    g->ks[i] = kernels[i];
+    kd[i] = ks[i]->dims;
+    cluster = std::max(cluster, ks[i]->cluster);
+    g->name += (i ? "_" : "") + ks[i]->name;
+  }
+  g->name += "_fused_bfuse";
+  for (int i = 0; i < n; ++i)
+    if (ks[i]->cluster != 1 && ks[i]->cluster != cluster)
+      return fail(ctx, BFUSE_ERR_UNSUPPORTED, "the operators need different cluster widths; register them with equal splits");
+  if (pattern != PATTERN_ZIGZAG && pattern != PATTERN_PROPORTIONAL && pattern != PATTERN_RANGE_SPLIT)
+    return fail(ctx, BFUSE_ERR_UNSUPPORTED, "a group takes the zig-zag, proportional and range-split patterns");
+  if (pattern != PATTERN_RANGE_SPLIT) {
+    if (param_m == 0) param_m = 1;
+    if (param_n == 0) param_n = 1;
+  }
+  std::string err;
+  if (!plan_group(kd, n, pattern, param_m, param_n, &g->plan, &err, cluster)) return fail(ctx, BFUSE_ERR_INVALID, err);
+  g->plan.table.status = ctx->d_status;
+  // shared memory: the union of the windows; rings sized for a whole SM are made shallower when the
+  // fused grid needs two CTAs per SM (same rule as for a pair)
+  constexpr size_t kHalfSm = 111 * 1024;
+  size_t win = 0;
+  for (int i = 0; i < n; ++i) {
+    size_t w = ks[i]->smem;
+    int hdr, stg, mn, st;
+    g->stages[i] = 0;
+    if (g->plan.fused_grid > ctx->sm_count && w > kHalfSm && ring_info(*ks[i], &hdr, &stg, &mn, &st)) {
+      const int fit = (int)((kHalfSm - hdr) / stg);
+      if (fit < st && fit >= std::max(mn, 3)) {
+        g->stages[i] = fit;
+        w = (size_t)hdr + (size_t)fit * stg;
+      }
+    }
+    win = std::max(win, w);
+  }
+  g->smem = win + 1024;
+  if (g->smem > kMaxSmemPerCta) return fail(ctx, BFUSE_ERR_SMEM, g->name + ": fused shared memory over the 227 KB per-CTA budget");
+  cudaSetDevice(ctx->device);
+  cudaFuncAttributes attr;
+  cudaError_t e = ctx->singles[ks[0]->desc.op].group_attr(&attr);
+  if (e != cudaSuccess) return fail_cuda(ctx, e, "cudaFuncGetAttributes");
+  g->regs = attr.numRegs;
+  ctx->groups.push_back(std::move(g));
+  *group = (int)ctx->groups.size() - 1;
+  return BFUSE_OK;
+}
+
+int bfuse_group_info(bfuse_context *ctx, int group, bfuse_kernel_desc *out) {
+  if (!ctx || group < 0 || group >= (int)ctx->groups.size() || !out) return fail(ctx, BFUSE_ERR_INVALID, "bad group handle");
+  const GroupRec &g = *ctx->groups[group];
+  std::memset(out, 0, sizeof(*out));
+  out->KernelName = g.name.c_str();
+  out->HasBarriers = 1;
+  out->GridDim = {g.plan.fused_grid, 1, 1};
+  out->BlockDim = {g.plan.fused_block, 1, 1};
+  out->Reg = g.regs;
+  out->ExecTime = -1.f;
+  out->op = -1;
+  out->smem_bytes = g.smem;
+  out->shape[0] = g.plan.fused_grid;
+  return BFUSE_OK;
+}
+
+int bfuse_group_map_block(const bfuse_context *ctx, int group, int b, int *kernel, int *vblock) {
+  if (!ctx || group < 0 || group >= (int)ctx->groups.size() || !kernel || !vblock || b < 0) return BFUSE_ERR_INVALID;
+  const GroupRec &g = *ctx->groups[group];
+  int k, vb;
+  if (b >= g.plan.fused_grid || !decode_group_cta(g.plan.table, b, k, vb)) return BFUSE_ERR_INVALID;
+  *kernel = k, *vblock = vb;
+  return BFUSE_OK;
+}
+
+int bfuse_launch_group(bfuse_context *ctx, int group, void *stream) {
+  if (!ctx || group < 0 || group >= (int)ctx->groups.size()) return fail(ctx, BFUSE_ERR_INVALID, "bad group handle");
+  GroupRec &g = *ctx->groups[group];
+  alignas(64) unsigned char scratch[kGroupMax][kParamsBytes];
+  const void *params[kGroupMax];
+  for (int i = 0; i < g.n; ++i) params[i] = params_with_stages(*ctx->kernels[g.ks[i]], g.stages[i], scratch[i]);
+  const KernelRec &k0 = *ctx->kernels[g.ks[0]];
+  cudaError_t e = ctx->singles[k0.desc.op].group(g.plan.table, params, g.n, (unsigned)g.plan.fused_grid,
+                                                 (unsigned)g.plan.fused_block, g.smem, (cudaStream_t)stream);
+  if (e != cudaSuccess) return fail_cuda(ctx, e, ("launch " + g.name).c_str());
+  return BFUSE_OK;
+}
+
+int bfuse_plan_group(const bfuse_dim3 *grid, const bfuse_dim3 *block, int n, int pattern, int param_m, int param_n,
+                     int cluster, int *fused_block, int *kernel_of, int *vblock_of, int cap) {
+  if (!grid || !block || n < 2 || n > kGroupMax) return -BFUSE_ERR_INVALID;
+  KernelDims kd[kGroupMax];
+  for (int i = 0; i < n; ++i) kd[i] = KernelDims{grid[i].X, grid[i].Y, grid[i].Z, block[i].X, block[i].Y, block[i].Z};
+  GroupPlan p;
+  std::string err;
+  if (pattern != PATTERN_ZIGZAG && pattern != PATTERN_PROPORTIONAL && pattern != PATTERN_RANGE_SPLIT) return -BFUSE_ERR_UNSUPPORTED;
+  if (!plan_group(kd, n, pattern, param_m, param_n, &p, &err, cluster < 1 ? 1 : cluster)) return -BFUSE_ERR_INVALID;
+  if (fused_block) *fused_block = p.fused_block;
+  for (int b = 0; b < p.fused_grid && b < cap && kernel_of && vblock_of; ++b) {
+    int k, vb;
+    if (decode_group_cta(p.table, b, k, vb)) kernel_of[b] = k, vblock_of[b] = vb;
+    else kernel_of[b] = -1, vblock_of[b] = -1;
+  }
+  return p.fused_grid;
 }
 
 int bfuse_fusion_info(bfuse_context *ctx, int fusion, bfuse_kernel_desc *out) {

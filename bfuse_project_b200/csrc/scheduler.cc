@@ -138,4 +138,75 @@ bool plan_pair(const KernelDims k[2], int pattern, int param_m, int param_n, int
   return true;
 }
 
+bool plan_group(const KernelDims *k, int n, int pattern, int param_m, int param_n, GroupPlan *out, std::string *err,
+                int cluster) {
+  auto fail = [&](const char *m) {
+    if (err) *err = m;
+    return false;
+  };
+  std::memset(out, 0, sizeof(*out));
+  GroupTable &t = out->table;
+  if (n < 2 || n > kGroupMax) return fail("a group holds 2 to 4 operators");
+  if (cluster < 1 || cluster > 8) return fail("cluster width must be 1..8");
+  t.n = n;
+  t.cluster = cluster;
+  out->pattern = pattern;
+  int units[kGroupMax], umin = 0;
+  long long sum = 0;
+  for (int i = 0; i < n; ++i) {
+    if (k[i].gx <= 0 || k[i].gy <= 0 || k[i].gz <= 0 || k[i].bx <= 0 || k[i].by <= 0 || k[i].bz <= 0)
+      return fail("grid and block dims must be positive");
+    if ((long long)k[i].gx * k[i].gy * k[i].gz > 0x0fffffffLL) return fail("grid too large");
+    if (k[i].block() > 1024) return fail("block larger than 1024 threads");
+    t.n_cta[i] = k[i].grid();
+    t.n_thr[i] = k[i].block();
+    t.grid_x[i] = k[i].gx, t.grid_y[i] = k[i].gy;
+    t.blk_x[i] = k[i].bx, t.blk_y[i] = k[i].by;
+    t.bar_count[i] = round_up32(k[i].block());
+    units[i] = (t.n_cta[i] + cluster - 1) / cluster;
+    umin = i == 0 ? units[i] : std::min(umin, units[i]);
+    sum += units[i];
+    out->fused_block = std::max(out->fused_block, t.n_thr[i]);
+  }
+  t.total = (int)sum;
+  out->fused_grid = (int)sum * cluster;
+  int ratio[kGroupMax], rounds = -1;
+  switch (pattern) {
+    case PATTERN_ZIGZAG:
+      if (param_m < 1 || param_n < 1) return fail("zig-zag needs M >= 1 and N >= 1");
+      for (int i = 0; i < n; ++i) {
+        const int q = units[i] / umin;
+        ratio[i] = q < param_m ? q * param_n : param_m * param_n;
+      }
+      break;
+    case PATTERN_PROPORTIONAL: {
+      if (param_m < 1) return fail("proportional zig-zag needs MinOption >= 1");
+      const int unit = std::max(umin / param_m, 1);
+      for (int i = 0; i < n; ++i) ratio[i] = units[i] / unit;
+      break;
+    }
+    case PATTERN_RANGE_SPLIT:
+      for (int i = 0; i < n; ++i) ratio[i] = 1;
+      rounds = 0;
+      break;
+    default:
+      return fail("a group takes the zig-zag, proportional and range-split patterns");
+  }
+  if (rounds < 0)
+    for (int i = 0; i < n; ++i) rounds = rounds < 0 ? units[i] / ratio[i] : std::min(rounds, units[i] / ratio[i]);
+  t.ratio_lo[0] = 0;
+  for (int i = 0; i < n; ++i) t.ratio_lo[i + 1] = t.ratio_lo[i] + ratio[i];
+  t.rot = t.ratio_lo[n];
+  t.rot_end = t.rot * rounds;
+  int at = t.rot_end;
+  for (int i = 0; i < n; ++i) {
+    const int done = ratio[i] * rounds;
+    t.tail_lo[i] = at;
+    t.tail_hi[i] = at + (units[i] - done);
+    t.tail_base[i] = done;
+    at = t.tail_hi[i];
+  }
+  return true;
+}
+
 }  // namespace bfuse

@@ -39,4 +39,16 @@ inline int round_up32(int x) { return (x + 31) / 32 * 32; }
 bool plan_pair(const KernelDims k[2], int pattern, int param_m, int param_n, int total_sm, FusedPlan *out,
                std::string *err, int cluster = 1);
 
+struct GroupPlan {
+  GroupTable table;
+  int fused_grid;   // GridDim.X of the fused launch, a multiple of table.cluster
+  int fused_block;  // BlockDim.X of the fused launch
+  int pattern;
+};
+
+// n operators (2..kGroupMax) in one block-level launch: zig-zag M:N, proportional zig-zag and
+// range split in the reference's n-kernel form (Algorithms.cc:323-375, 538-587, 661-685).
+bool plan_group(const KernelDims *k, int n, int pattern, int param_m, int param_n, GroupPlan *out, std::string *err,
+                int cluster = 1);
+
 }  // namespace bfuse

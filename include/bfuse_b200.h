@@ -128,6 +128,24 @@ int bfuse_fusion_map_block(const bfuse_context *ctx, int fusion, int b, int *ker
 int bfuse_fusion_map_thread(const bfuse_context *ctx, int fusion, int kernel, int b, int t, int *vblock,
                             int *vthread, int *active);
 
+/* n kernels in one fused launch -- the general form the reference's patterns are written in
+ * (a `Kernels:` list of any length, horizontal-fuser/src/Algorithms.cc:323-375, 538-587, 661-685),
+ * here for 2..BFUSE_GROUP_MAX registered kernels that share one operator body (the Q, K and V
+ * projections of a layer; the branches of a block).  Patterns: BFUSE_PATTERN_ZIGZAG (M:N),
+ * BFUSE_PATTERN_PROPORTIONAL, BFUSE_PATTERN_RANGE_SPLIT; others return BFUSE_ERR_UNSUPPORTED, as do
+ * kernels of different bodies or of different cluster widths. */
+#define BFUSE_GROUP_MAX 4
+int bfuse_register_group(bfuse_context *ctx, const int *kernels, int n, int pattern, int param_m, int param_n, int *group);
+/* The fused-kernel record of a group: name "<k1>_<k2>_..._fused_bfuse", fused GridDim / BlockDim, smem, registers. */
+int bfuse_group_info(bfuse_context *ctx, int group, bfuse_kernel_desc *out);
+/* Which kernel (index into the group's list) and virtual block CTA b runs. */
+int bfuse_group_map_block(const bfuse_context *ctx, int group, int b, int *kernel, int *vblock);
+int bfuse_launch_group(bfuse_context *ctx, int group, void *stream);
+/* The scheduler of a group alone (no GPU): kernel and virtual block of every CTA of the fused grid.
+ * Returns the fused grid size (or a negative status); fills at most `cap` entries. */
+int bfuse_plan_group(const bfuse_dim3 *grid, const bfuse_dim3 *block, int n, int pattern, int param_m, int param_n,
+                     int cluster, int *fused_block, int *kernel_of, int *vblock_of, int cap);
+
 /* Device-buffer launches on a caller stream (NULL = default stream). */
 int bfuse_launch_kernel(bfuse_context *ctx, int kernel, void *stream);       /* run_kernel1/2 launch, operation_cu.py:173,191 */
 int bfuse_launch_sequential(bfuse_context *ctx, int fusion, void *stream);   /* k1 then k2 on one stream                       */

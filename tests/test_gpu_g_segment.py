@@ -1,0 +1,106 @@
+"""n-way groups and the model-segment driver on the GPU: the scheduled program (groups, pairs,
+singles) writes the same bits as one launch per operator, and the grouped projections agree with
+the CPU oracle within the tensor-core tolerance."""
+import numpy as np
+import pytest
+
+import bfuse_project_b200 as bf
+import oracle
+from bfuse_project_b200 import segment as sg
+
+pytestmark = pytest.mark.gpu
+
+
+def _written(builder, ops):
+    return sorted({w for o in ops for w in o.writes})
+
+
+def _run_both(rt, torch, builder, ops, pattern=bf.ZIGZAG, max_group=4):
+    seg = sg.Segment(rt, ops, pattern=pattern, max_group=max_group)
+    stream = torch.cuda.current_stream().cuda_stream
+    names = _written(builder, ops)
+    seg.run_sequential(stream)
+    torch.cuda.synchronize()
+    want = {n: builder.buf[n].clone() for n in names}
+    for n in names:
+        builder.buf[n].zero_()
+    seg.run_fused(stream)
+    torch.cuda.synchronize()
+    assert rt.read_status() == 0
+    for n in names:
+        assert torch.equal(builder.buf[n].view(torch.uint8), want[n].view(torch.uint8)), n
+    return seg
+
+
+def test_qkv_three_way_group_matches_unfused_and_oracle():
+    import torch
+    rt = bf.Runtime(0)
+    b, ops = sg.bert_layer(rt, torch, seq=256, hidden=384, heads=6, ffn=1024, seed=3)
+    seg = _run_both(rt, torch, b, ops)
+    assert seg.describe()[0] == [("group", ["q_proj", "k_proj", "v_proj"])]
+    assert seg.launches_sequential == 11 and seg.launches_fused == 9
+    x = b.buf["x"].cpu().numpy()
+    for n in "qkv":
+        want = oracle.gemm_nt(x[None], b.buf["w" + n].cpu().numpy()[None], b.buf["b" + n].cpu().numpy(), tf32=True)[0]
+        got = b.buf[n].cpu().numpy()
+        rms = np.sqrt((want.astype(np.float64) ** 2).mean())
+        assert np.abs(got - want).max() <= 5e-3 * rms + 5e-3 * np.abs(want).max(), n
+    # the group's record and its dispatch: every virtual block of every kernel exactly once
+    kind, handle, idx = seg.steps[0][0]
+    info = rt.group_info(handle)
+    assert info["KernelName"] == "q_proj_k_proj_v_proj_fused_bfuse"
+    grid = info["GridDim"][0]
+    seen = {}
+    for cta in range(grid):
+        m = rt.group_map_block(handle, cta)
+        if m is not None:
+            seen.setdefault(m[0], []).append(m[1])
+    assert sorted(seen) == [0, 1, 2] and all(sorted(v) == list(range(len(v))) for v in seen.values())
+    assert rt.group_map_block(handle, grid) is None
+    rt.close()
+
+
+@pytest.mark.parametrize("pattern", [bf.ZIGZAG, bf.PROPORTIONAL, bf.RANGE_SPLIT])
+def test_requests_grouped_four_ways_every_pattern(pattern):
+    """Four independent requests of a (reduced) BERT layer: every operator runs as a 4-way group --
+    tcgen05 GEMMs (clustered where the runtime split K), batch-matmuls, softmax and LayerNorm."""
+    import torch
+    rt = bf.Runtime(0)
+    b, ops = sg.bert_layer(rt, torch, replicas=4, seq=128, hidden=256, heads=4, ffn=512, seed=4)
+    seg = _run_both(rt, torch, b, ops, pattern=pattern)
+    assert seg.launches_sequential == 44 and seg.launches_fused == 11
+    rt.close()
+
+
+def test_llama_projections_and_resnet_stages_full_size():
+    import torch
+    rt = bf.Runtime(0)
+    b, ops = sg.llama_layer_projections(rt, torch, seed=5)
+    seg = _run_both(rt, torch, b, ops)
+    assert ("group", ["q_proj", "k_proj", "v_proj"]) in seg.describe()[1]
+    assert ("group", ["rope_q", "rope_k"]) in seg.describe()[2]
+    b2, ops2 = sg.resnet18_stages(rt, torch, batch=2, seed=6)
+    seg2 = _run_both(rt, torch, b2, ops2)
+    assert seg2.launches_fused == 12
+    rt.close()
+
+
+def test_group_registration_errors():
+    import torch
+    rt = bf.Runtime(0)
+    b, ops = sg.bert_layer(rt, torch, seq=128, hidden=256, heads=4, ffn=512, seed=7)
+    by_name = {o.name: o.kernel for o in ops}
+    with pytest.raises(bf.BfuseError) as e:       # different bodies
+        rt.register_group([by_name["q_proj"], by_name["softmax"]], bf.ZIGZAG, 1, 1)
+    assert e.value.code == 7
+    for pat in (bf.SM_STRIPED, bf.THREAD_SPLIT, bf.WORK_QUEUE):
+        with pytest.raises(bf.BfuseError) as e:
+            rt.register_group([by_name["q_proj"], by_name["k_proj"]], pat, 1, 1)
+        assert e.value.code == 7
+    with pytest.raises(bf.BfuseError) as e:
+        rt.register_group([by_name["q_proj"]], bf.ZIGZAG, 1, 1)
+    assert e.value.code == 1
+    with pytest.raises(bf.BfuseError) as e:
+        rt.register_group([by_name["q_proj"], 10 ** 6], bf.ZIGZAG, 1, 1)
+    assert e.value.code == 1
+    rt.close()

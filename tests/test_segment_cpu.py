@@ -1,0 +1,120 @@
+"""Host logic of the n-way groups and of the model-segment driver (no GPU)."""
+import numpy as np
+import pytest
+
+import bfuse_project_b200 as bf
+import oracle
+from bfuse_project_b200 import segment as sg
+
+
+def _random_kernels(rng, n):
+    return [[int(rng.integers(1, 40)), int(rng.integers(1, 6)), int(rng.integers(1, 4)),
+             int(rng.integers(1, 257)), int(rng.integers(1, 3)), 1] for _ in range(n)]
+
+
+def test_group_plans_match_the_oracle_for_two_to_four_kernels():
+    """Zig-zag M:N, proportional and range split of 2, 3 and 4 kernels: fused dims and the kernel /
+    virtual block of every CTA equal the oracle's if / else-if chain (Algorithms.cc:323-375, 538-587)."""
+    rng = np.random.default_rng(11)
+    for _ in range(400):
+        ks = _random_kernels(rng, int(rng.integers(2, 5)))
+        M, N, opt = int(rng.integers(1, 4)), int(rng.integers(1, 4)), int(rng.integers(1, 4))
+        for pat, name, kw, pm, pn in ((bf.ZIGZAG, "zigzag", dict(M=M, N=N), M, N),
+                                      (bf.PROPORTIONAL, "proportional", dict(min_option=opt), opt, 1),
+                                      (bf.RANGE_SPLIT, "range_split", {}, 0, 0)):
+            p = oracle.plan(name, ks, **kw)
+            grid, block, kernel_of, vblock_of = bf.plan_group(ks, pat, pm, pn)
+            want_k, want_vb = oracle.block_table(p)
+            assert (grid, block) == (p.fused_grid, p.fused_block)
+            assert np.array_equal(kernel_of, want_k) and np.array_equal(vblock_of, want_vb)
+
+
+def test_group_of_two_equals_the_pair_plan():
+    rng = np.random.default_rng(12)
+    for _ in range(200):
+        ks = _random_kernels(rng, 2)
+        for pat, pm, pn in ((bf.ZIGZAG, 2, 3), (bf.PROPORTIONAL, 2, 1), (bf.RANGE_SPLIT, 0, 0)):
+            grid, block, kernel_of, vblock_of = bf.plan_group(ks, pat, pm, pn)
+            plan = bf.Plan(ks, pat, pm, pn)
+            pk, pvb = plan.map_all()
+            assert grid == plan.fused_grid[0] and block == plan.fused_block[0]
+            assert np.array_equal(kernel_of, pk) and np.array_equal(vblock_of, pvb)
+
+
+def test_clustered_group_keeps_clusters_whole_and_covers_every_block():
+    ks = [[12, 1, 1, 192, 1, 1], [7, 1, 1, 192, 1, 1], [20, 1, 1, 192, 1, 1]]   # 7 CTAs: one padded cluster of 4
+    grid, block, kernel_of, vblock_of = bf.plan_group(ks, bf.ZIGZAG, 1, 1, cluster=4)
+    assert grid % 4 == 0 and grid == 4 * (3 + 2 + 5)
+    for c in range(grid // 4):
+        owners = {int(k) for k in kernel_of[4 * c:4 * c + 4] if k >= 0}
+        assert len(owners) == 1
+        vbs = [int(v) for v in vblock_of[4 * c:4 * c + 4] if v >= 0]
+        assert vbs == list(range(vbs[0], vbs[0] + len(vbs))) and vbs[0] % 4 == 0
+    for k, (g, *_rest) in enumerate(ks):
+        assert sorted(int(v) for kk, v in zip(kernel_of, vblock_of) if kk == k) == list(range(g))
+    assert int((kernel_of < 0).sum()) == 1   # the padding CTA of the 7-block kernel
+
+
+def test_group_rejects_bad_input():
+    ks = [[4, 1, 1, 64, 1, 1]] * 3
+    for bad in (lambda: bf.plan_group(ks[:1], bf.ZIGZAG), lambda: bf.plan_group(ks * 2, bf.ZIGZAG),
+                lambda: bf.plan_group(ks, bf.SM_STRIPED, 148, 0), lambda: bf.plan_group(ks, bf.THREAD_SPLIT),
+                lambda: bf.plan_group(ks, bf.ZIGZAG, 0, 1)):
+        with pytest.raises(bf.BfuseError):
+            bad()
+
+
+def _ops(spec):
+    return [sg.SegmentOp(n, op, i, r, w) for i, (n, op, r, w) in enumerate(spec)]
+
+
+def test_dependencies_cover_raw_war_waw():
+    ops = _ops([("w1", 0, ["a"], ["b"]), ("r1", 0, ["b"], ["c"]), ("waw", 0, ["a"], ["b"]), ("war", 1, ["z"], ["a"]),
+                ("free", 1, ["q"], ["r"])])
+    deps = sg.dependencies(ops)
+    assert deps[1] == {0} and deps[2] == {0, 1} and deps[3] == {0, 2} and deps[4] == set()
+
+
+def test_schedule_respects_dependencies_and_groups_by_body():
+    for name, build in sg.SEGMENTS.items():
+        _, ops = build(None, None)
+        deps = sg.dependencies(ops)
+        steps = sg.schedule(ops)
+        seen, step_of = [], {}
+        for si, step in enumerate(steps):
+            for kind, idx in step:
+                assert 1 <= len(idx) <= 4
+                assert (kind == "single") == (len(idx) == 1)
+                if kind == "group":
+                    assert len({ops[i].op for i in idx}) == 1
+                if kind == "pair":
+                    assert len(idx) == 2 and ops[idx[0]].op != ops[idx[1]].op
+                for i in idx:
+                    step_of[i] = si
+                seen.extend(idx)
+        assert sorted(seen) == list(range(len(ops))), name
+        for j, d in enumerate(deps):
+            assert all(step_of[i] < step_of[j] for i in d), name
+
+
+def test_bert_layer_fuses_qkv_three_ways_and_replicas_across_requests():
+    _, ops = sg.bert_layer(None, None)
+    steps = sg.schedule(ops)
+    assert steps[0] == [("group", [0, 1, 2])] and [ops[i].name for i in (0, 1, 2)] == ["q_proj", "k_proj", "v_proj"]
+    assert sum(len(s) for s in steps) == len(ops) - 2
+    _, ops4 = sg.bert_layer(None, None, replicas=4)
+    steps4 = sg.schedule(ops4)
+    assert len(ops4) == 44 and sum(len(s) for s in steps4) == 11
+    assert [len(idx) for _, idx in steps4[0]] == [4, 4, 4]
+
+
+def test_rule_and_group_width_are_honoured():
+    ops = _ops([("c%d" % i, bf.OP_CONV2D_F32_SIMT, ["x"], ["y%d" % i]) for i in range(3)] +
+               [("s", bf.OP_SOFTMAX_F32, ["x"], ["p"]), ("l", bf.OP_LAYERNORM_F32, ["x"], ["q"])])
+    steps = sg.schedule(ops)
+    kinds = sorted(k for k, _ in steps[0])
+    assert kinds == ["pair", "single", "single", "single"]        # CUDA-core convs stay alone; softmax pairs with LayerNorm
+    five = _ops([("g%d" % i, bf.OP_GEMM_TF32, ["x"], ["y%d" % i]) for i in range(5)])
+    assert [len(i) for _, i in sg.schedule(five)[0]] == [3, 2]
+    assert [len(i) for _, i in sg.schedule(five, max_group=2)[0]] == [2, 2, 1]
+    assert [k for k, _ in sg.schedule(five, max_group=1)[0]] == ["single"] * 5
