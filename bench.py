@@ -293,9 +293,18 @@ def model_segments(rt, torch, bf):
             torch.cuda.synchronize()
             same = all(torch.equal(b.buf[n].view(torch.uint8), want[n].view(torch.uint8)) for n in names)
             kinds = [k for step in seg.describe() for k, _ in step]
+            steps = []   # every shared launch alone, against its operators back to back
+            for step, names in zip(seg.steps, seg.describe()):
+                for (kind, h, idx), (_, nm) in zip(step, names):
+                    if kind == "single":
+                        continue
+                    one = attention.graph_time_us(torch, lambda st, kind=kind, h=h: (rt.launch_group if kind == "group" else rt.launch_fused)(h, st))
+                    b2b = attention.graph_time_us(torch, lambda st, idx=idx: [rt.launch_kernel(ops[i].kernel, st) for i in idx])
+                    steps.append({"kind": kind, "operators": nm, "one_launch_us": one, "back_to_back_us": b2b})
             out[name] = {"operators": seg.launches_sequential, "fused_launches": seg.launches_fused,
                          "groups": kinds.count("group"), "pairs": kinds.count("pair"),
-                         "sequential_us": seq_us, "fused_us": fused_us, "speedup": seq_us / fused_us, "bit_identical": bool(same)}
+                         "sequential_us": seq_us, "fused_us": fused_us, "speedup": seq_us / fused_us, "bit_identical": bool(same),
+                         "steps": steps}
             del b, ops, seg, want
             torch.cuda.empty_cache()
         except Exception as e:   # reported, not hidden
