@@ -251,11 +251,11 @@ def attention_block(rt, torch, bf):
         vt = torch.randn(12, 64, 512, device="cuda", generator=gen)
         out = {"shape": {"heads": 12, "seq": 512, "head_dim": 64, "causal": True}}
         one = attention.AttentionBlock(rt, torch, q, k, vt, groups=1)
-        out["one_group_3_launches_us"] = attention.graph_time_us(torch, one.run_sequential)
+        out["one_group_3_launches_us"] = attention.graph_time_us(torch, one.run_sequential, repeat=4)
         for groups in (2, 4, 6):
             blk = attention.AttentionBlock(rt, torch, q, k, vt, groups=groups)
-            seq_us = attention.graph_time_us(torch, blk.run_sequential)
-            pip_us = attention.graph_time_us(torch, blk.run_pipelined)
+            seq_us = attention.graph_time_us(torch, blk.run_sequential, repeat=4)
+            pip_us = attention.graph_time_us(torch, blk.run_pipelined, repeat=4)
             blk.run_sequential(torch.cuda.current_stream().cuda_stream)
             torch.cuda.synchronize()
             want = blk.out.clone()
@@ -273,18 +273,19 @@ def attention_block(rt, torch, bf):
 def model_segments(rt, torch, bf):
     """Operator lists of model layers walked by the segment driver: ready operators of one body share an
     n-way launch (Q || K || V, the branches of a down-sampling block, the same operator of independent
-    requests), against one launch per operator; CUDA-graph replay of the whole segment on the same buffers."""
+    requests), against one launch per operator, each tiled for the whole GPU; CUDA-graph replay of the whole
+    segment on the same buffers."""
     from bfuse_project_b200 import attention, segment
     out = {}
     for name, build in segment.SEGMENTS.items():
         try:
             b, ops = build(rt, torch)
             seg = segment.Segment(rt, ops)
-            seq_us = attention.graph_time_us(torch, seg.run_sequential)
-            fused_us = attention.graph_time_us(torch, seg.run_fused)
+            seq_us = attention.graph_time_us(torch, seg.run_sequential, repeat=4)
+            fused_us = attention.graph_time_us(torch, seg.run_fused, repeat=4)
             stream = torch.cuda.current_stream().cuda_stream
             names = sorted({w for o in ops for w in o.writes})
-            seg.run_sequential(stream)
+            seg.run_unfused(stream)     # the fused program's kernels one by one
             torch.cuda.synchronize()
             want = {n: b.buf[n].clone() for n in names}
             for n in names:
@@ -298,8 +299,8 @@ def model_segments(rt, torch, bf):
                 for (kind, h, idx), (_, nm) in zip(step, names):
                     if kind == "single":
                         continue
-                    one = attention.graph_time_us(torch, lambda st, kind=kind, h=h: (rt.launch_group if kind == "group" else rt.launch_fused)(h, st))
-                    b2b = attention.graph_time_us(torch, lambda st, idx=idx: [rt.launch_kernel(ops[i].kernel, st) for i in idx])
+                    one = attention.graph_time_us(torch, lambda st, kind=kind, h=h: (rt.launch_group if kind == "group" else rt.launch_fused)(h, st), repeat=10)
+                    b2b = attention.graph_time_us(torch, lambda st, idx=idx: [rt.launch_kernel(seg.alone[i], st) for i in idx], repeat=10)
                     steps.append({"kind": kind, "operators": nm, "one_launch_us": one, "back_to_back_us": b2b})
             out[name] = {"operators": seg.launches_sequential, "fused_launches": seg.launches_fused,
                          "groups": kinds.count("group"), "pairs": kinds.count("pair"),

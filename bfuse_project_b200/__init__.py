@@ -20,6 +20,11 @@ MAX_ARGS, MAX_SHAPE = 6, 12
 OP_SOFTMAX_F32, OP_LAYERNORM_F32, OP_RMSNORM_BF16, OP_ROPE_BF16 = 0, 1, 2, 3
 OP_GEMM_F32_SIMT, OP_CONV2D_F32_SIMT, OP_GEMM_TF32, OP_GEMM_BF16, OP_CONV2D_TF32 = 4, 5, 6, 7, 8
 FLAG_CAUSAL = 1
+
+
+def flag_share(n):
+    """Hint for the default tiling: n operators (1..4) will share the launch; 1 = the operator runs alone."""
+    return int(n) << 8
 # dispatch patterns
 ZIGZAG, PROPORTIONAL, SM_STRIPED, THREAD_SPLIT, RANGE_SPLIT, WORK_QUEUE = 0, 1, 2, 3, 4, 5
 PATTERN_NAMES = {ZIGZAG: "zigzag", PROPORTIONAL: "proportional", SM_STRIPED: "sm_striped",

@@ -97,8 +97,10 @@ class AttentionBlock:
                     self.rt.launch_kernel(handle, stream)
 
 
-def graph_time_us(torch, launch, replays=20, warm=3):
-    """Microseconds per call of `launch(stream)` replayed from a CUDA graph (device time, CUDA events)."""
+def graph_time_us(torch, launch, replays=20, warm=3, repeat=1):
+    """Microseconds per call of `launch(stream)` replayed from a CUDA graph (device time, CUDA events).
+    repeat: calls captured per graph -- replays of a graph start about 2 us apart at the earliest, so a
+    program of a few microseconds is captured several times over to be timed to better than that."""
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(side):
@@ -106,7 +108,8 @@ def graph_time_us(torch, launch, replays=20, warm=3):
     torch.cuda.synchronize()
     g = torch.cuda.CUDAGraph()
     with torch.cuda.graph(g, stream=side):
-        launch(torch.cuda.current_stream().cuda_stream)
+        for _ in range(repeat):
+            launch(torch.cuda.current_stream().cuda_stream)
     for _ in range(warm):
         g.replay()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -115,4 +118,4 @@ def graph_time_us(torch, launch, replays=20, warm=3):
         g.replay()
     e1.record()
     torch.cuda.synchronize()
-    return e0.elapsed_time(e1) * 1e3 / replays
+    return e0.elapsed_time(e1) * 1e3 / (replays * repeat)

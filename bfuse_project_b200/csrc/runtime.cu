@@ -132,13 +132,13 @@ int umma_min_stages(int bn, int split, int elem, int bm = kUmmaBM) {
 // B200.  One CTA multiplies a k-block (128 bytes of K per row) in t_kb(BN) -- set by the MMA time for
 // wide tiles and by the bytes the SM can pull from L2 for narrow ones --, pays a fixed prologue +
 // epilogue that grows with BN, and a split tile pays the cross-CTA reduction on top.  The operator
-// is budgeted half of the SMs (its pair partner takes the other half), in whole waves.  Ties go to
+// is budgeted its share of the SMs (half: its pair partner takes the other half), in whole waves.  Ties go to
 // the wider tile (less L2 traffic).  With bn_fixed / split_fixed > 0 only the other one is chosen.
-void pick_tile(int batch, int M, int N, int K, int elem, int sm_count, int bn_fixed, int split_fixed, int *bn_out, int *split_out) {
+void pick_tile(int batch, int M, int N, int K, int elem, int sm_count, int share, int bn_fixed, int split_fixed, int *bn_out, int *split_out) {
   static const int kBn[4] = {256, 128, 64, 32};
   static const double kTkbUs[4] = {0.267, 0.213, 0.153, 0.150};
   const int num_kb = ceil_div(K * elem, kUmmaRowBytes);
-  const int slots = std::max(1, sm_count / 2);
+  const int slots = std::max(1, sm_count / share);
   double best = 1e30;
   int best_bn = 128, best_split = 1;
   for (int i = 0; i < 4; ++i) {
@@ -151,7 +151,7 @@ void pick_tile(int batch, int M, int N, int K, int elem, int sm_count, int bn_fi
     for (int ci = 0; ci < (split_fixed > 0 ? 1 : 2); ++ci) {
       const int split = cand[ci];
       if (split > num_kb) continue;
-      if (umma_smem_bytes(bn, umma_min_stages(bn, split, elem)) > ((bn == 256 || 2 * tiles * split <= sm_count) ? 200 : 100) * 1024) continue;
+      if (umma_smem_bytes(bn, umma_min_stages(bn, split, elem)) > ((bn == 256 || share * tiles * split <= sm_count) ? 200 : 100) * 1024) continue;
       const long long waves = (tiles * split + slots - 1) / slots;
       const double per_cta = 1.0 + 0.006 * bn + ceil_div(num_kb, split) * kTkbUs[i] + (split > 1 ? 2.5 + 0.5 * split : 0.0);
       const double t = (double)waves * per_cta;
@@ -172,6 +172,8 @@ int default_launch(const bfuse_context *ctx, bfuse_kernel_desc *d, std::string *
     d->HasBarriers = 1;
   };
   const int sm = ctx ? ctx->sm_count : 148;
+  // operators that will share the launch (BFUSE_FLAG_SHARE): 2 unless told otherwise -- a pair
+  const int share = ((d->flags >> 8) & 7u) ? (int)((d->flags >> 8) & 7u) : 2;
   switch (d->op) {
     case BFUSE_OP_SOFTMAX_F32:
     case BFUSE_OP_LAYERNORM_F32: {
@@ -220,7 +222,7 @@ int default_launch(const bfuse_context *ctx, bfuse_kernel_desc *d, std::string *
       if (bn <= 0) {
         bn = 32;
         for (int cand = kConvBN; cand > 32; cand /= 2)
-          if ((long long)s[0] * ceil_div(oh * ow, cand) * ceil_div(s[4], kUmmaBM) >= sm / 2) { bn = cand; break; }
+          if ((long long)s[0] * ceil_div(oh * ow, cand) * ceil_div(s[4], kUmmaBM) >= sm / share) { bn = cand; break; }
       }
       if (bn != 32 && bn != 64 && bn != 128) { *err = "conv2d: pixels per tile must be 32, 64 or 128"; return BFUSE_ERR_SHAPE; }
       d->shape[9] = bn;
@@ -231,7 +233,7 @@ int default_launch(const bfuse_context *ctx, bfuse_kernel_desc *d, std::string *
       // share a launch (a fused launch has one cluster width): 4 when the k-slices still fit three
       // quarters of the SMs and keep at least 4 K blocks each (8-wide clusters measured slower in pairs)
       int split = s[10];
-      if (split <= 0) split = (tiles * 4 <= 3 * sm / 4 && num_kb >= 16) ? 4 : 1;
+      if (split <= 0) split = (tiles * 4 * share <= 3 * sm / 2 && num_kb >= 16) ? 4 : 1;
       if (split > 8 || split > num_kb) { *err = "conv2d: k-slices must be 1..8 and at most the number of K blocks"; return BFUSE_ERR_SHAPE; }
       const int q = ceil_div(num_kb, split);
       split = ceil_div(num_kb, q);
@@ -240,7 +242,7 @@ int default_launch(const bfuse_context *ctx, bfuse_kernel_desc *d, std::string *
       // an SM of its own (a long-K conv on few CTAs is bound by the ring's round trip, not by issue
       // rate); deep enough to hold the k-slices' partial sums after the MMAs
       const long long ctas = tiles * split;
-      const int budget = (2 * ctas <= sm ? 200 : 110) * 1024;
+      const int budget = (share * ctas <= sm ? 200 : 110) * 1024;
       int stages = std::max(1, std::min({q, kUmmaMaxStages, (budget - conv_header_bytes(K)) / conv_stage_bytes(bn)}));
       stages = std::max(stages, ceil_div(umma_epilogue_bytes(bn, split, 4), conv_stage_bytes(bn)));
       set(split * ceil_div(oh * ow, bn), ceil_div(s[4], kUmmaBM), s[0], kUmmaThreads, 1, conv_umma_smem_bytes(stages, bn, K), 3);
@@ -251,7 +253,7 @@ int default_launch(const bfuse_context *ctx, bfuse_kernel_desc *d, std::string *
       if (s[0] <= 0 || s[1] <= 0 || s[2] <= 0 || s[3] <= 0) { *err = "gemm: batch, M, N, K must be positive"; return BFUSE_ERR_SHAPE; }
       const int eb = d->op == BFUSE_OP_GEMM_TF32 ? 4 : 2;
       int bn = s[4], split = s[5], bm = s[6], q;
-      if (bn <= 0 || split <= 0) pick_tile(s[0], s[1], s[2], s[3], eb, sm, bn, split, &bn, &split);
+      if (bn <= 0 || split <= 0) pick_tile(s[0], s[1], s[2], s[3], eb, sm, share, bn, split, &bn, &split);
       if (bn != 32 && bn != 64 && bn != 128 && bn != 256) { *err = "gemm: BN must be 32, 64, 128 or 256"; return BFUSE_ERR_SHAPE; }
       d->shape[4] = bn;
       const int num_kb = ceil_div(s[3] * eb, kUmmaRowBytes);
@@ -263,7 +265,15 @@ int default_launch(const bfuse_context *ctx, bfuse_kernel_desc *d, std::string *
       // flop) once the 128-row tiles alone would fill every SM and K is long enough for the main
       // loop to dominate: that is where L2 -> SM bandwidth, not the tensor pipe, sets the pace of
       // 128 x 256 tiles (short-K shapes are bound by their output stores and prefer two CTAs per SM)
-      if (bm <= 0) bm = (bn == 256 && split == 1 && num_kb >= 16 && s[1] > kUmmaBM && (long long)s[0] * ceil_div(s[1], kUmmaBM) * ceil_div(s[2], bn) >= sm) ? 256 : kUmmaBM;
+      if (bm <= 0) {
+        const long long tiles = (long long)s[0] * ceil_div(s[1], kUmmaBM) * ceil_div(s[2], bn);
+        const long long slots = std::max(1, sm / share);
+        // ... or, for an operator that runs alone (its waves are real ones), when halving the CTA count
+        // halves the waves: with every SM busy a 256-row tile takes about 1.9x a 128-row one
+        const long long waves = (tiles + slots - 1) / slots, waves_tall = ((tiles + 1) / 2 + slots - 1) / slots;
+        bm = (bn == 256 && split == 1 && num_kb >= 16 && s[1] > kUmmaBM &&
+              (tiles >= 2 * slots || (share == 1 && 19 * waves_tall < 10 * waves))) ? 256 : kUmmaBM;
+      }
       if ((bm != kUmmaBM && bm != 256) || (bm == 256 && split != 1)) { *err = "gemm: BM must be 128, or 256 with split = 1"; return BFUSE_ERR_SHAPE; }
       d->shape[6] = bm;
       // ring depth: enough to cover the k-slice, at most 8, and large enough to hold the partial tile
@@ -271,7 +281,7 @@ int default_launch(const bfuse_context *ctx, bfuse_kernel_desc *d, std::string *
       // of its own (operands arriving from HBM need ~1 us of loads in flight per SM) or for the 256-wide
       // tile, else within ~100 KB so that two CTAs share an SM.
       const long long ctas = (long long)split * s[0] * ceil_div(s[1], bm) * ceil_div(s[2], bn);
-      const int budget = (bn == 256 || 2 * ctas <= sm) ? 200 * 1024 : 100 * 1024;
+      const int budget = (bn == 256 || share * ctas <= sm) ? 200 * 1024 : 100 * 1024;
       int stages = std::min({q, kUmmaMaxStages, (budget - kUmmaHeaderBytes) / umma_stage_bytes(bn, bm)});
       stages = std::max({stages, 1, umma_min_stages(bn, split, eb, bm)});
       set(split * ceil_div(s[1], bm), ceil_div(s[2], bn), s[0], kUmmaThreads, 1, umma_smem_bytes(bn, stages, bm), 4);

@@ -13,8 +13,11 @@ inputs are ready --
     * two ready operators of different bodies as one fused pair;
     * what is left alone.
 
-`run_sequential` is the unfused program (one launch per operator, program order); `run_fused` the
-scheduled one.  Both write the same buffers with the same bodies, so their results are bit-identical.
+`run_sequential` is the unfused program (one launch per operator, program order, every operator
+tiled for the whole GPU); `run_fused` the scheduled one, its operators tiled for their share of the
+launch.  `run_unfused` launches the fused program's kernels one by one: same bodies, same tilings, so
+bit-identical results (the two tilings of an operator can differ in their k-slices, i.e. in the order
+of a sum).
 Element-wise glue of the models (ReLU / GELU / SiLU, batch-norm, reshapes and transposes) has no
 operator body here: buffers are reinterpreted in the layout the next operator wants, which keeps
 every operator's shape and the dependency structure of the layer, not its numerical function.
@@ -22,15 +25,26 @@ every operator's shape and the dependency structure of the layer, not its numeri
 import math
 
 from . import (FLAG_CAUSAL, OP_CONV2D_F32_SIMT, OP_CONV2D_TF32, OP_GEMM_BF16, OP_GEMM_TF32, OP_LAYERNORM_F32,
-               OP_RMSNORM_BF16, OP_ROPE_BF16, OP_SOFTMAX_F32, ZIGZAG, BfuseError)
+               OP_RMSNORM_BF16, OP_ROPE_BF16, OP_SOFTMAX_F32, ZIGZAG, BfuseError, flag_share)
 
 
 class SegmentOp:
-    """One operator of a segment: a registered kernel plus the names of the buffers it reads / writes."""
+    """One operator of a segment: its body, the names of the buffers it reads / writes and, when it is
+    bound to device buffers, what `Runtime.describe` needs to register it (`spec` = (shape, pointers,
+    keyword arguments)).  `kernel` is a ready-made kernel handle for callers that registered it themselves."""
 
-    def __init__(self, name, op, kernel, reads, writes):
-        self.name, self.op, self.kernel = name, op, kernel
+    def __init__(self, name, op, kernel, reads, writes, spec=None):
+        self.name, self.op, self.kernel, self.spec = name, op, kernel, spec
         self.reads, self.writes = frozenset(reads), frozenset(writes)
+
+    def register(self, rt, share):
+        """Kernel handle of this operator tiled for `share` operators in one launch (1: alone)."""
+        if self.spec is None:
+            return self.kernel
+        shape, ptrs, kw = self.spec
+        kw = dict(kw)
+        kw["flags"] = kw.get("flags", 0) | flag_share(share)
+        return rt.register_kernel(rt.describe(self.name, self.op, shape, ptrs, **kw))
 
 
 def dependencies(ops):
@@ -95,27 +109,34 @@ def schedule(ops, max_group=4, rule=default_rule):
 
 
 class Segment:
-    """A scheduled segment bound to a runtime: registers the groups / pairs of `schedule` and launches them."""
+    """A scheduled segment bound to a runtime.  Every operator is registered twice: tiled for the whole
+    GPU (the program of one launch per operator, and operators the schedule leaves alone) and tiled for
+    its share of the launch it was scheduled into."""
 
     def __init__(self, rt, ops, pattern=ZIGZAG, max_group=4, rule=default_rule):
         self.rt, self.ops = rt, list(ops)
+        self.alone = [o.register(rt, 1) for o in self.ops]
+        self.shared = list(self.alone)
         self.steps = []
         m = 1 if pattern == ZIGZAG else 0
         for step in schedule(self.ops, max_group, rule):
             out = []
             for kind, idx in step:
-                ks = [self.ops[i].kernel for i in idx]
+                if kind == "single":
+                    out.append(("single", self.alone[idx[0]], idx))
+                    continue
+                ks = [self.ops[i].register(rt, len(idx)) for i in idx]
                 try:
                     if kind == "group":
                         out.append(("group", rt.register_group(ks, pattern, m, m), idx))
-                    elif kind == "pair":
-                        out.append(("pair", rt.register_fusion(ks[0], ks[1], pattern, m, m), idx))
                     else:
-                        out.append(("single", ks[0], idx))
+                        out.append(("pair", rt.register_fusion(ks[0], ks[1], pattern, m, m), idx))
+                    for i, k in zip(idx, ks):
+                        self.shared[i] = k
                 except BfuseError as e:
                     if e.code not in (3, 7):      # shared memory over budget / combination not supported: run them alone
                         raise
-                    out.extend(("single", k, [i]) for k, i in zip(ks, idx))
+                    out.extend(("single", self.alone[i], [i]) for i in idx)
             self.steps.append(out)
 
     @property
@@ -131,8 +152,14 @@ class Segment:
         return [[(kind, [self.ops[i].name for i in idx]) for kind, _, idx in step] for step in self.steps]
 
     def run_sequential(self, stream=None):
-        for o in self.ops:
-            self.rt.launch_kernel(o.kernel, stream)
+        """One launch per operator in program order, each tiled for the whole GPU."""
+        for k in self.alone:
+            self.rt.launch_kernel(k, stream)
+
+    def run_unfused(self, stream=None):
+        """One launch per operator with the tilings of the fused program: its bit-exact reference."""
+        for k in self.shared:
+            self.rt.launch_kernel(k, stream)
 
     def run_fused(self, stream=None):
         for step in self.steps:
@@ -191,8 +218,7 @@ class _Builder:
             self.ops.append(SegmentOp(name, op, len(self.ops), reads, writes))
             return
         ptrs = [None if a is None else self.buf[a].data_ptr() for a in args]
-        k = self.rt.register_kernel(self.rt.describe(name, op, shape, ptrs, **kw))
-        self.ops.append(SegmentOp(name, op, k, reads, writes))
+        self.ops.append(SegmentOp(name, op, None, reads, writes, spec=(shape, ptrs, kw)))
 
     def dense(self, name, x, w, bias, y, M, N, K, op=OP_GEMM_TF32, batch=1, causal=False):
         self._add(name, op, (batch, M, N, K, 0, 0, 0), [x, w, bias, y], [x, w] + ([bias] if bias else []), [y],

@@ -55,6 +55,9 @@ enum {
 
 /* operator flags */
 #define BFUSE_FLAG_CAUSAL 1u /* GEMM: out[b,m,n] = -FLT_MAX where n > m */
+/* Hint to bfuse_default_launch: n operators (1..4) will share the launch, so tile this one for 1/n of
+ * the SMs; 1 = it runs alone.  Absent = 2, a pair.  Never changes results except through the k-slices. */
+#define BFUSE_FLAG_SHARE(n) ((unsigned)(n) << 8)
 
 /* block-dispatch patterns (horizontal-fuser/src/Algorithms.cc) */
 enum {
