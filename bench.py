@@ -158,6 +158,7 @@ def run_sweep(args, rt, torch, rank, world, local, pk):
     t0 = time.perf_counter()
     res = sweep.measure(rt, sets, mine, pk["hbm_gbs"], pk["bf16_tflops"] * 0.5)
     wall = time.perf_counter() - t0
+    alone = sweep.alone_times(rt, sets) if rank == 0 else None      # for the pair-selection model, outside the wall time
     assert rt.read_status() == 0, "a bounded device-side wait gave up during the sweep"
     if world > 1:
         import torch.distributed as dist
@@ -174,9 +175,12 @@ def run_sweep(args, rt, torch, rank, world, local, pk):
                                    "back-to-back launches; 3 warm-ups + 30 timed launches per mode" % (n_ops, len(todo)),
                        "partition": "pair i on rank i mod %d" % world},
             "sweep": sweep.summarise(res)}
+    from bfuse_project_b200 import pairing
+    line["pairing_model"] = pairing.evaluate(sweep.pairing_records(sets, res, alone, rt.sm_count))
     if args.sweep_out:
         with open(args.sweep_out, "w") as f:
-            json.dump({"operators": [{"name": n, "shape": list(sh)} for n, sh in sweep.SWEEP_OPS[:n_ops]], "pairs": res}, f, indent=0)
+            json.dump({"operators": [{"name": n, "shape": list(sh), "alone_us": alone[i], "launch": [list(x) if isinstance(x, tuple) else x for x in sets[0][i].launch]}
+                                     for i, (n, sh) in enumerate(sweep.SWEEP_OPS[:n_ops])], "pairs": res}, f, indent=0)
     print(json.dumps(line), flush=True)
 
 

@@ -288,7 +288,7 @@ class Runtime:
         d = KernelDesc()
         self._ck(self._L.bfuse_fusion_info(self._ctx, fusion, d))
         return {"KernelName": d.KernelName.decode(), "GridDim": d.GridDim.tuple(), "BlockDim": d.BlockDim.tuple(),
-                "Reg": d.Reg, "smem_bytes": d.smem_bytes, "launched_ctas": d.shape[0]}
+                "Reg": d.Reg, "smem_bytes": d.smem_bytes, "launched_ctas": d.shape[0], "resident_ctas": d.shape[1]}
 
     def map_block(self, fusion, b):
         k, vb = C.c_int(), C.c_int()

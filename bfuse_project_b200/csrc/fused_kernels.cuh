@@ -18,6 +18,8 @@
 // that keeps the lighter operator's occupancy without starving the heavier body of registers.
 #pragma once
 
+#include <cstdlib>
+
 #include "dispatch.h"
 #include "tile.h"
 
@@ -206,11 +208,19 @@ typedef cudaError_t (*SingleLaunchFn)(const DispatchTable &, const void *pa, uns
 typedef cudaError_t (*GroupLaunchFn)(const GroupTable &, const void *const *params, int n, unsigned grid, unsigned block,
                                      size_t smem, cudaStream_t);
 typedef cudaError_t (*AttrFn)(cudaFuncAttributes *);
+typedef int (*ClusterCapFn)(unsigned block, size_t smem, int cluster);
 
 template <class Kernel>
 cudaError_t ensure_smem(Kernel k, size_t smem) {
   if (smem <= 48 * 1024) return cudaSuccess;
   return cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+}
+
+// Diagnostic switch: with BFUSE_NO_PDL set in the environment the launches do not ask for programmatic
+// dependent launch, to tell its effect on a timeline from everything else.
+inline bool pdl_allowed() {
+  static const bool on = std::getenv("BFUSE_NO_PDL") == nullptr;
+  return on;
 }
 
 // Launch with `cluster` consecutive CTAs per thread-block cluster (1 = no clusters) and with
@@ -225,7 +235,7 @@ cudaError_t launch_clustered(Kernel kern, unsigned grid, unsigned block, size_t 
   cfg.stream = s;
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_allowed() ? 1 : 0;
   attr[1].id = cudaLaunchAttributeClusterDimension;
   attr[1].val.clusterDim.x = cluster > 1 ? cluster : 1;
   attr[1].val.clusterDim.y = 1;
@@ -233,6 +243,42 @@ cudaError_t launch_clustered(Kernel kern, unsigned grid, unsigned block, size_t 
   cfg.attrs = attr;
   cfg.numAttrs = cluster > 1 ? 2 : 1;
   return cudaLaunchKernelEx(&cfg, kern, args...);
+}
+
+// Thread-block clusters of `cluster` CTAs of this kernel that can be resident at once (a cluster must
+// fit one GPC, so this is less than SMs * CTAs-per-SM / cluster); -1 when the query fails.
+template <class Kernel>
+int max_resident_clusters(Kernel kern, unsigned block, size_t smem, int cluster) {
+  if (ensure_smem(kern, smem) != cudaSuccess) return -1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)cluster, 1, 1);
+  cfg.blockDim = dim3(block, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)cluster;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  return n;
+}
+template <class A, class B>
+int clusters_block_pair(unsigned block, size_t smem, int cluster) {
+  return max_resident_clusters(fused_block_kernel<A, B>, block, smem, cluster);
+}
+template <class A, class B>
+int clusters_block_pair_wide(unsigned block, size_t smem, int cluster) {
+  return max_resident_clusters(fused_block_kernel<A, B, pair_wide_blocks<A, B>()>, block, smem, cluster);
+}
+template <class A>
+int clusters_group(unsigned block, size_t smem, int cluster) {
+  return max_resident_clusters(fused_group_kernel<A>, block, smem, cluster);
 }
 
 template <class A, class B>

@@ -33,12 +33,14 @@ struct PairEntry {
   PairLaunchFn block_wide;   // the register-richer build of the pair (see pair_wide_blocks), else nullptr
   AttrFn block_wide_attr;
   int wide_min_blocks;       // CTAs per SM the wide build is compiled for
+  ClusterCapFn block_clusters;  // clusters of the block-level kernel that can be resident at once
 };
 struct SingleEntry {
   SingleLaunchFn launch;
   AttrFn attr;
   GroupLaunchFn group;       // up to kGroupMax operators of this body in one launch
   AttrFn group_attr;
+  ClusterCapFn group_clusters;
   int max_threads;
   size_t params_size;
 };

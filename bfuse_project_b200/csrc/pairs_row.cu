@@ -33,6 +33,7 @@ struct RowFiller {
     row[J].thread = &launch_thread_pair<A, B>;
     row[J].block_attr = &attr_block_pair<A, B>;
     row[J].thread_attr = &attr_thread_pair<A, B>;
+    row[J].block_clusters = &clusters_block_pair<A, B>;
     WideFiller<A, B, (pair_wide_blocks<A, B>() > 0)>::fill(row[J]);
     RowFiller<I, J + 1>::fill(row);
   }
@@ -50,6 +51,7 @@ void fill_pair_row<BFUSE_ROW>(PairEntry *row, SingleEntry *single) {
   single->attr = &attr_single<A>;
   single->group = &launch_group<A>;
   single->group_attr = &attr_group<A>;
+  single->group_clusters = &clusters_group<A>;
   single->max_threads = A::kMaxThreads;
   single->params_size = sizeof(typename A::Params);
 }

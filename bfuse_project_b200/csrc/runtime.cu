@@ -854,7 +854,14 @@ int bfuse_register_fusion(bfuse_context *ctx, int kernel1, int kernel2, int patt
     // what the operator's epilogue needs, and only if at least three stages remain) until two CTAs fit.
     size_t win[2] = {a->smem, b->smem};
     constexpr size_t kHalfSm = 111 * 1024;
-    if (f->plan.fused_grid > ctx->sm_count && !t.queue) {
+    // clusters have to fit a GPC each, so fewer CTAs than SMs can be resident at one CTA per SM: ask
+    bool second_wave = f->plan.fused_grid > ctx->sm_count;
+    if (!second_wave && cluster > 1 && std::max(win[0], win[1]) > kHalfSm) {
+      cudaSetDevice(ctx->device);
+      const int cap = ctx->pairs[a->desc.op][b->desc.op].block_clusters((unsigned)f->plan.fused_block, std::max(win[0], win[1]) + 1024, cluster);
+      second_wave = cap > 0 && f->plan.fused_grid / cluster > cap;
+    }
+    if (second_wave && !t.queue) {
       KernelRec *ks[2] = {a, b};
       for (int i = 0; i < 2; ++i) {
         int hdr, stg, mn, st;
@@ -931,12 +938,19 @@ int bfuse_register_group(bfuse_context *ctx, const int *kernels, int n, int patt
   // shared memory: the union of the windows; rings sized for a whole SM are made shallower when the
   // fused grid needs two CTAs per SM (same rule as for a pair)
   constexpr size_t kHalfSm = 111 * 1024;
-  size_t win = 0;
+  size_t win = 0, widest = 0;
+  for (int i = 0; i < n; ++i) widest = std::max(widest, ks[i]->smem);
+  bool second_wave = g->plan.fused_grid > ctx->sm_count;
+  if (!second_wave && cluster > 1 && widest > kHalfSm) {   // clusters fit a GPC each: fewer resident CTAs than SMs
+    cudaSetDevice(ctx->device);
+    const int cap = ctx->singles[ks[0]->desc.op].group_clusters((unsigned)g->plan.fused_block, widest + 1024, cluster);
+    second_wave = cap > 0 && g->plan.fused_grid / cluster > cap;
+  }
   for (int i = 0; i < n; ++i) {
     size_t w = ks[i]->smem;
     int hdr, stg, mn, st;
     g->stages[i] = 0;
-    if (g->plan.fused_grid > ctx->sm_count && w > kHalfSm && ring_info(*ks[i], &hdr, &stg, &mn, &st)) {
+    if (second_wave && w > kHalfSm && ring_info(*ks[i], &hdr, &stg, &mn, &st)) {
       const int fit = (int)((kHalfSm - hdr) / stg);
       if (fit < st && fit >= std::max(mn, 3)) {
         g->stages[i] = fit;
@@ -1026,6 +1040,14 @@ int bfuse_fusion_info(bfuse_context *ctx, int fusion, bfuse_kernel_desc *out) {
   out->op = -1;
   out->smem_bytes = f->smem;
   out->shape[0] = (int)f->launch_grid;  // CTAs actually launched (differs from GridDim for the work queue)
+  // CTAs of this kernel the device can hold at once (whole clusters), 0 when not known
+  out->shape[1] = 0;
+  if (f->plan.table.kind != DISPATCH_THREADS && !f->wide) {
+    const int cl = std::max(1, f->plan.table.cluster);
+    cudaSetDevice(ctx->device);
+    const int cap = ctx->pairs[ctx->kernels[f->k1]->desc.op][ctx->kernels[f->k2]->desc.op].block_clusters((unsigned)f->plan.fused_block, f->smem, cl);
+    if (cap > 0) out->shape[1] = cap * cl;
+  }
   return BFUSE_OK;
 }
 

@@ -15,7 +15,8 @@ stay in L2 as they do in the reference's own loop.
 """
 import math
 
-from . import (BfuseError, MODE_FUSED, MODE_SEQUENTIAL, OP_CONV2D_F32_SIMT, OP_CONV2D_TF32, OP_GEMM_TF32, ZIGZAG)
+from . import (BfuseError, MODE_FUSED, MODE_KERNEL1, MODE_SEQUENTIAL, OP_CONV2D_F32_SIMT, OP_CONV2D_TF32, OP_GEMM_TF32, RANGE_SPLIT,
+               ZIGZAG)
 
 # name -> shape.  dense: (M, K, N); bgemm: (batch, M, K, N); conv2d: (N, H, W, CO, CI, KH, KW, stride, pad)
 SWEEP_OPS = (
@@ -89,6 +90,30 @@ def build_operands(rt, torch, device=0, seed=0, ops=SWEEP_OPS):
     gen = torch.Generator(device=torch.device("cuda", device))
     gen.manual_seed(seed)
     return [[SweepOperand(rt, torch, device, name + suffix, shape, gen) for name, shape in ops] for suffix in ("_k1", "_k2")]
+
+
+def alone_times(rt, sets, warmup=3, iters=30):
+    """Microseconds of every operator of the first set launched alone (same protocol as the pairs)."""
+    out = []
+    for a, b in zip(sets[0], sets[1]):
+        f = rt.register_fusion(a.kernel, b.kernel, RANGE_SPLIT, 0, 0)     # any fusion of the operator: mode 0 times kernel 1 alone
+        out.append(rt.time(f, MODE_KERNEL1, warmup, iters)[0])
+    return out
+
+
+def pairing_records(sets, results, alone, sm_count):
+    """The sweep's measurements in the form `pairing.evaluate` takes."""
+    by_name = {a.name[:-3]: i for i, a in enumerate(sets[0])}
+    recs = []
+    for key, v in results.items():
+        if "error" in v:
+            continue
+        i, j = (by_name[n] for n in key.split("|"))
+        la, lb = sets[0][i].launch, sets[1][j].launch
+        dims = lambda l: (l[0][0] * l[0][1] * l[0][2], l[1][0] * l[1][1] * l[1][2], l[2])
+        recs.append({"t_a": alone[i], "t_b": alone[j], "launch_a": dims(la), "launch_b": dims(lb), "sm_count": sm_count,
+                     "fused_us": v["fused_us"], "sequential_us": v["sequential_us"]})
+    return recs
 
 
 def measure(rt, sets, pairs, hbm_gbs, tf32_tflops, pattern=ZIGZAG, warmup=3, iters=30):

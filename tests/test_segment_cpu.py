@@ -118,3 +118,23 @@ def test_rule_and_group_width_are_honoured():
     assert [len(i) for _, i in sg.schedule(five)[0]] == [3, 2]
     assert [len(i) for _, i in sg.schedule(five, max_group=2)[0]] == [2, 2, 1]
     assert [k for k, _ in sg.schedule(five, max_group=1)[0]] == ["single"] * 5
+
+
+def test_pairing_model_arithmetic():
+    from bfuse_project_b200 import pairing
+    assert pairing.ctas_per_sm(192, 198656) == 1 and pairing.ctas_per_sm(192, 100352) == 2
+    assert pairing.ctas_per_sm(256, 256) == 8 and pairing.ctas_per_sm(1024, 0) == 2
+    assert pairing.ctas_per_sm(256, 256, regs_per_thread=64) == 4
+    assert pairing.fill(48, 192, 198656) == pytest.approx(48 / 148) and pairing.fill(1000, 192, 198656) == 1.0
+    # two operators that each leave two thirds of the SMs idle overlap completely: the longer one plus the overhead
+    a = pairing.advise(8.0, 6.0, (48, 192, 198656), (48, 192, 198656))
+    assert a["predicted_fused_us"] == pytest.approx(8.0 + pairing.OVERHEAD_US) and a["fuse"]
+    # two operators that fill the GPU alone gain nothing
+    b = pairing.advise(50.0, 50.0, (300, 192, 198656), (300, 192, 198656))
+    assert b["predicted_fused_us"] == pytest.approx(101.0) and not b["fuse"]
+    recs = [dict(t_a=8.0, t_b=6.0, launch_a=(48, 192, 198656), launch_b=(48, 192, 198656), fused_us=9.0, sequential_us=14.0),
+            dict(t_a=50.0, t_b=50.0, launch_a=(300, 192, 198656), launch_b=(300, 192, 198656), fused_us=102.0, sequential_us=100.0),
+            dict(t_a=50.0, t_b=50.0, launch_a=(300, 192, 198656), launch_b=(300, 192, 198656), fused_us=95.0, sequential_us=100.0)]
+    ev = pairing.evaluate(recs)
+    assert (ev["pairs"], ev["advice_fuse_and_pays"], ev["advice_alone_and_slower"], ev["advice_alone_but_pays"]) == (3, 1, 1, 1)
+    assert ev["median_rel_err"] == pytest.approx(1.0 / 102.0)
