@@ -38,6 +38,11 @@ __device__ __forceinline__ unsigned char *align_smem_1k(unsigned char *p) {
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// Whole warp, converged: this CTA will not allocate tensor memory (any more).
+__device__ __forceinline__ void relinquish_tmem_permit() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+
 __device__ __forceinline__ unsigned long long global_timer_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -94,8 +99,21 @@ __global__ void __launch_bounds__(cmax(A::kMaxThreads, B::kMaxThreads), MINB)
   const int tid = threadIdx.x;
   unsigned long long t_entry = 0;
   if (t.cta_times) t_entry = global_timer_ns();
-  grid_launch_dependents();
-  grid_dependency_wait();
+  // A kernel that contains tcgen05.alloc gets its CTAs launched one at a time per SM: the next CTA
+  // starts only once the resident one has given up its permit to allocate tensor memory, and a CTA
+  // that never allocates holds it until it exits.  So the CTAs of an operator without tensor memory
+  // give the permit up before anything else (measured: 4 such CTAs per SM ran one after the other).
+  if constexpr (A::kUsesTmem != B::kUsesTmem) {
+    if (!t.queue && tid < 32) {
+      int k0, vb0;
+      const bool mapped = decode_cta(t, blockIdx.x, k0, vb0);
+      if (!mapped || (k0 == 0 ? !A::kUsesTmem : !B::kUsesTmem)) relinquish_tmem_permit();
+    }
+  }
+  if (t.queue) {   // the ticket counter is global memory; otherwise the body waits and lets the next kernel in (TileCtx::dependency_wait)
+    grid_dependency_wait();
+    grid_launch_dependents();
+  }
   // One loop serves both launch forms, so each body is inlined once (two copies cost registers and
   // made the memory-bound pairs spill): a plain launch runs it for CTA blockIdx.x and leaves; a
   // persistent CTA of the work queue draws tickets until the queue is empty.  The last CTA to drain
@@ -121,7 +139,7 @@ __global__ void __launch_bounds__(cmax(A::kMaxThreads, B::kMaxThreads), MINB)
       } else {
         if (tid < t.n_thr[1]) run_tile<B>(pb, t, 1, vb, tid, 2, smem);
       }
-      if (t.cta_times && tid == 0) {  // kernel entry, body start (dependency resolved), thread 0 done
+      if (t.cta_times && tid == 0) {  // kernel entry, body start (its set-up may overlap the previous kernel), thread 0 done
         t.cta_times[3 * (size_t)ticket] = t_entry;
         t.cta_times[3 * (size_t)ticket + 1] = t_body;
         t.cta_times[3 * (size_t)ticket + 2] = global_timer_ns();
@@ -145,14 +163,18 @@ __global__ void __launch_bounds__(A::kMaxThreads + B::kMaxThreads, 1)
   extern __shared__ unsigned char smem_raw[];
   unsigned char *smem = align_smem_1k(smem_raw);
   const int tid = threadIdx.x, b = blockIdx.x;
-  grid_launch_dependents();
-  grid_dependency_wait();
+  // the bodies wait for the previous kernel and let the next one in themselves (TileCtx::dependency_wait)
   // thread ranges of hfusePattern (Algorithms.cc:23-49): kernel k owns [thr_lo[k], thr_lo[k] + B_k)
+  // An operator keeps its permit to allocate tensor memory only while the other one may still need it
+  // (both allocate); when just one of them uses tensor memory it gives the permit up as it would alone,
+  // and a CTA past that operator's grid gives it up on its behalf, so that the SM can start its next CTA.
   if (tid < t.thr_lo[1]) {
-    if (tid < t.n_thr[0] && b < t.n_cta[0]) run_tile<A>(pa, t, 0, b, tid, 1, smem + t.smem_off[0], 1);
+    if (tid < t.n_thr[0] && b < t.n_cta[0]) run_tile<A>(pa, t, 0, b, tid, 1, smem + t.smem_off[0], B::kUsesTmem ? 1 : 0);
+    else if (A::kUsesTmem && !B::kUsesTmem && b >= t.n_cta[0] && tid < 32) relinquish_tmem_permit();
   } else {
     const int vt = tid - t.thr_lo[1];
-    if (vt < t.n_thr[1] && b < t.n_cta[1]) run_tile<B>(pb, t, 1, b, vt, 2, smem + t.smem_off[1], 1);
+    if (vt < t.n_thr[1] && b < t.n_cta[1]) run_tile<B>(pb, t, 1, b, vt, 2, smem + t.smem_off[1], A::kUsesTmem ? 1 : 0);
+    else if (B::kUsesTmem && !A::kUsesTmem && b >= t.n_cta[1] && vt < 32) relinquish_tmem_permit();
   }
 }
 
@@ -167,8 +189,7 @@ __global__ void __launch_bounds__(A::kMaxThreads, A::kMinBlocks)
     fused_group_kernel(const __grid_constant__ GroupTable t, const __grid_constant__ GroupParams<A> g) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char *smem = align_smem_1k(smem_raw);
-  grid_launch_dependents();
-  grid_dependency_wait();
+  // the body waits for the previous kernel and lets the next one in itself (TileCtx::dependency_wait)
   int k, vb;
   if (!decode_group_cta(t, blockIdx.x, k, vb)) return;
   const int tid = threadIdx.x;
@@ -194,8 +215,7 @@ __global__ void __launch_bounds__(A::kMaxThreads, A::kMinBlocks)
     single_kernel(const __grid_constant__ DispatchTable t, const __grid_constant__ typename A::Params pa) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char *smem = align_smem_1k(smem_raw);
-  grid_launch_dependents();
-  grid_dependency_wait();
+  // the body waits for the previous kernel and lets the next one in itself (TileCtx::dependency_wait)
   if ((int)threadIdx.x < t.n_thr[0]) run_tile<A>(pa, t, 0, blockIdx.x, threadIdx.x, 1, smem);
 }
 

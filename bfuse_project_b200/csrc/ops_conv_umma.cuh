@@ -63,6 +63,7 @@ struct ConvUmmaTf32 {
   static constexpr int kMaxThreads = kUmmaThreads;
   static constexpr int kMinBlocks = 1;
   static constexpr bool kMemoryBound = false;
+  static constexpr bool kUsesTmem = true;   // allocates tensor memory (see fused_block_kernel)
   static constexpr int kBK = 32;  // K elements (fp32) per stage row of 128 bytes
 
   // The im2col gather of one tile by the four epilogue warps (gt = 0..127): 128 / BN threads share a
@@ -127,6 +128,12 @@ struct ConvUmmaTf32 {
     const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * kUmmaMaxStages, acc_bar = empty0 + 8 * kUmmaMaxStages;
     const uint32_t recv_bar = acc_bar + 8;  // counts partial sums delivered by the other k-slices
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(c.smem + 8 * (2 * kUmmaMaxStages + 2));
+    // tensor memory first: the SM starts its next CTA of this kernel only once this one has given up
+    // its permit to allocate
+    if (warp == 5) {
+      tmem_alloc(smem_u32(tmem_slot), BN);
+      if (!c.persistent) tmem_relinquish();
+    }
     int2 *tab = reinterpret_cast<int2 *>(c.smem + kUmmaHeaderBytes);
     const uint32_t tiles = smem_u32(c.smem) + conv_header_bytes(K);
     // once the MMAs are done the ring holds the k-slices' partial sums (split > 1) and the store buffers
@@ -160,10 +167,7 @@ struct ConvUmmaTf32 {
         mbar_expect_tx(recv_bar, (uint32_t)owned * (uint32_t)split * (32u * kUmmaBM * 4u));
       }
     }
-    if (warp == 5) {
-      tmem_alloc(smem_u32(tmem_slot), BN);
-      if (!c.persistent) tmem_relinquish();
-    } else if (warp < 4) {
+    if (warp < 4) {
       // k -> (input offset relative to the pixel's top-left tap, tap index dy*kw+dx).  Thread t fills
       // entries t, t + 128, ...: (channel, tap) advance by the decomposition of 128, and tap -> (dy, dx)
       // is a multiply-shift (exact for taps < 32), so the loop has no division -- four chained ones
@@ -178,6 +182,7 @@ struct ConvUmmaTf32 {
         if (r >= khw) r -= khw, ++ch;
       }
     }
+    c.dependency_wait();   // nothing above touches global memory: barriers, tensor memory and the table overlap the previous kernel
     tc_fence_before();
     c.sync();
     tc_fence_after();

@@ -28,8 +28,10 @@ struct SoftmaxF32 {
   static constexpr int kMaxThreads = 256;
   static constexpr int kMinBlocks = 6;   // 6 x 256 threads per SM: registers per thread <= 40 (32 spills badly; 5 CTAs of 48 registers lose more in waves than the spills cost)
   static constexpr bool kMemoryBound = true;
+  static constexpr bool kUsesTmem = false;   // allocates tensor memory (see fused_block_kernel)
 
   __device__ __forceinline__ static void run(const Params &p, const TileCtx &c) {
+    c.dependency_wait();
     const int tpr = c.bx, lane = c.tid % tpr, row = c.vblock * c.by + c.tid / tpr;
     const int nvec = p.cols / (4 * tpr);
     const bool live = row < p.rows;
@@ -88,8 +90,10 @@ struct LayerNormF32 {
   static constexpr int kMaxThreads = 256;
   static constexpr int kMinBlocks = 6;   // 6 x 256 threads per SM: registers per thread <= 40 (32 spills badly; 5 CTAs of 48 registers lose more in waves than the spills cost)
   static constexpr bool kMemoryBound = true;
+  static constexpr bool kUsesTmem = false;   // allocates tensor memory (see fused_block_kernel)
 
   __device__ __forceinline__ static void run(const Params &p, const TileCtx &c) {
+    c.dependency_wait();
     const int tpr = c.bx, lane = c.tid % tpr, row = c.vblock * c.by + c.tid / tpr;
     const int nvec = p.cols / (4 * tpr);
     const bool live = row < p.rows;
@@ -168,9 +172,11 @@ struct RmsNormBf16 {
   static constexpr int kMaxThreads = 256;
   static constexpr int kMinBlocks = 6;   // 6 x 256 threads per SM: registers per thread <= 40 (32 spills badly; 5 CTAs of 48 registers lose more in waves than the spills cost)
   static constexpr bool kMemoryBound = true;
+  static constexpr bool kUsesTmem = false;   // allocates tensor memory (see fused_block_kernel)
   static constexpr int kMaxVec = 4;  // 8 bf16 per vector
 
   __device__ __forceinline__ static void run(const Params &p, const TileCtx &c) {
+    c.dependency_wait();
     const int tpr = c.bx, lane = c.tid % tpr, row = c.vblock * c.by + c.tid / tpr;
     const int nvec = p.cols / (8 * tpr);
     const bool live = row < p.rows;
@@ -229,8 +235,10 @@ struct RopeBf16 {
   static constexpr int kMaxThreads = 256;
   static constexpr int kMinBlocks = 6;   // 6 x 256 threads per SM: registers per thread <= 40 (32 spills badly; 5 CTAs of 48 registers lose more in waves than the spills cost)
   static constexpr bool kMemoryBound = true;
+  static constexpr bool kUsesTmem = false;   // allocates tensor memory (see fused_block_kernel)
 
   __device__ __forceinline__ static void run(const Params &p, const TileCtx &c) {
+    c.dependency_wait();
     const int half = p.dim >> 1, chunks = half >> 3;
     const int tx = c.tid % c.bx, chunk = tx % chunks, hg = tx / chunks, ngroups = c.bx / chunks;
     const int pos = c.vblock * c.by + c.tid / c.bx;

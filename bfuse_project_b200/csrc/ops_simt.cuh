@@ -63,8 +63,10 @@ struct GemmSimtF32 {
   static constexpr int kMaxThreads = 256;
   static constexpr int kMinBlocks = 2;
   static constexpr bool kMemoryBound = false;
+  static constexpr bool kUsesTmem = false;   // allocates tensor memory (see fused_block_kernel)
 
   __device__ __forceinline__ static void run(const Params &p, const TileCtx &c) {
+    c.dependency_wait();
     const int n0 = c.block_x() * kSimtTile, m0 = c.block_y() * kSimtTile, bz = c.block_z();
     const int tx = c.tid & 15, ty = c.tid >> 4;
     float *out = p.out + (size_t)bz * p.M * p.N;
@@ -110,8 +112,10 @@ struct ConvSimtF32 {
   static constexpr int kMaxThreads = 256;
   static constexpr int kMinBlocks = 2;
   static constexpr bool kMemoryBound = false;
+  static constexpr bool kUsesTmem = false;   // allocates tensor memory (see fused_block_kernel)
 
   __device__ __forceinline__ static void run(const Params &p, const TileCtx &c) {
+    c.dependency_wait();
     const int px0 = c.block_x() * kSimtTile, co0 = c.block_y() * kSimtTile;
     const int tx = c.tid & 15, ty = c.tid >> 4;
     const int K = p.ci * p.kh * p.kw, ohw = p.oh * p.ow, npix = p.n * ohw, khw = p.kh * p.kw;

@@ -431,6 +431,7 @@ struct GemmUmma {
   static constexpr int kMaxThreads = kUmmaThreads;
   static constexpr int kMinBlocks = 1;
   static constexpr bool kMemoryBound = false;
+  static constexpr bool kUsesTmem = true;   // allocates tensor memory (see fused_block_kernel)
   static constexpr int kElem = KIND == 0 ? 4 : 2;
   static constexpr int kBK = kUmmaRowBytes / kElem;  // K elements per stage
   static constexpr int kOutCols = 128 / kElem;       // output columns per 128-byte store chunk
@@ -483,6 +484,15 @@ struct GemmUmma {
     uint64_t *bars = reinterpret_cast<uint64_t *>(c.smem);
     const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * kUmmaMaxStages, acc_bar = empty0 + 8 * kUmmaMaxStages;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(c.smem + 8 * (2 * kUmmaMaxStages + 2));
+    // Tensor memory first: the SM starts its next CTA of this kernel only when this one has given up
+    // its permit to allocate, so every instruction before that delays a co-resident CTA.  A tile
+    // entirely above the diagonal of a causal product needs no accumulator.
+    const bool masked_tile = p.causal && n0 > m0 + BM - 1;
+    if (warp == 5) {
+      if (!masked_tile) tmem_alloc(smem_u32(tmem_slot), BN * halves);
+      if (!c.persistent) tmem_relinquish();
+    }
+    c.dependency_wait();   // the producer's first loads and everything after read global memory
     const uint32_t tiles = smem_u32(c.smem) + kUmmaHeaderBytes;
     const uint32_t recv_bar = acc_bar + 8;                                  // counts partial sums delivered by peers
     float *bias_tile = reinterpret_cast<float *>(c.smem + 1024);            // BN floats
@@ -501,7 +511,7 @@ struct GemmUmma {
     };
     mark(MARK_START, c.tid == 0);
 
-    if (p.causal && n0 > m0 + BM - 1) {
+    if (masked_tile) {
       // tile entirely above the diagonal (for every k-slice of it): only the mask value to write;
       // k-slice 0 fills one buffer once and stores it to every chunk
       if (warp < 4 && kslice == 0) {
@@ -562,9 +572,6 @@ struct GemmUmma {
         }
       }
       __syncwarp();
-    } else if (warp == 5) {
-      tmem_alloc(smem_u32(tmem_slot), BN * halves);
-      if (!c.persistent) tmem_relinquish();
     }
     tc_fence_before();
     c.sync();

@@ -27,6 +27,17 @@ struct TileCtx {
   int persistent;       // 1: more tensor-memory allocations may follow in this CTA (work queue: the next
                         // tile; thread split: the other operator), so the allocation permit must be kept
 
+  // Programmatic dependent launch: the CTA may have started while the previous kernel on the stream
+  // was still running.  Every thread calls this before its first access to global memory; what comes
+  // before it (tensor-memory allocation, barrier set-up, tables in shared memory) overlaps that
+  // kernel's tail.  Returns at once when there is nothing to wait for.
+  // Only then is the next kernel allowed to start its CTAs: were it allowed earlier, CTAs of several
+  // queued launches would pile up on whatever SMs had room first, holding tensor memory and slots.
+  __device__ __forceinline__ void dependency_wait() const {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  }
+
   __device__ __forceinline__ void sync() const {
     asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(bar_count) : "memory");
   }
