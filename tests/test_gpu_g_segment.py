@@ -112,3 +112,26 @@ def test_group_registration_errors():
         rt.register_group([by_name["q_proj"], 10 ** 6], bf.ZIGZAG, 1, 1)
     assert e.value.code == 1
     rt.close()
+
+
+def test_trace_files_of_a_pair(tmp_path):
+    """The five per-mode timing files of one pair, named and laid out as the reference's analysis expects."""
+    import torch
+    from bfuse_project_b200 import trace_csv
+    rt = bf.Runtime(0)
+    b, ops = sg.bert_layer(rt, torch, seq=128, hidden=256, heads=4, ffn=512, seed=9)
+    seg = sg.Segment(rt, ops)
+    k = {o.name: h for o, h in zip(ops, seg.alone)}
+    paths = trace_csv.emit_pair(rt, torch, str(tmp_path), 2, 5, k["softmax"], k["ln1"], "softmax", "ln1", warmup=3, trials=5)
+    names = sorted(p.rsplit("/", 1)[1] for p in paths)
+    assert names == ["0_2_0_cuda_gpu_trace.csv", "1_0_5_cuda_gpu_trace.csv", "2_2_5_cuda_gpu_trace.csv", "3_2_5_cuda_gpu_trace.csv",
+                     "4_2_5_cuda_gpu_trace.csv"]
+    for p in paths:
+        rows = trace_csv.read_gpu_trace(p)
+        mode = int(p.rsplit("/", 1)[1][0])
+        assert len(rows) == (16 if mode == 2 else 8)
+        assert all(d > 0 for _, d, _ in rows) and all(rows[i][0] <= rows[i + 1][0] for i in range(len(rows) - 1))
+        want = {0: {"softmax"}, 1: {"ln1"}, 2: {"softmax", "ln1"}, 3: {"softmax_ln1_fused_hfuse"}, 4: {"softmax_ln1_fused_bfuse"}}[mode]
+        assert {n for _, _, n in rows} == want
+    assert rt.read_status() == 0
+    rt.close()

@@ -70,3 +70,20 @@ def test_command_line_mirrors_the_fuser_switch(golden, tmp_path):
         yaml.safe_dump([{"File": "kernels.cu", "Kernels": ["nope", a]}], f)
     r = subprocess.run([sys.executable, "-m", "bfuse_project_b200.yaml_frontend", "-y", str(tmp_path), fp, kp], capture_output=True, text=True, env=env)
     assert r.returncode == 1 and "unknown kernel" in r.stderr
+
+
+def test_gpu_trace_csv_round_trip_in_the_reference_layout(tmp_path):
+    """The per-launch timing files carry the header of nsys' cuda_gpu_trace report and parse back to the
+    fields the reference's analysis keeps (start / duration in ms, name); its statistic -- skip the
+    first three rows of a kernel, average the rest (analyze_test_suite.py:104-122) -- comes out right."""
+    from bfuse_project_b200 import trace_csv
+    rows = [dict(start_ns=1000 * i, duration_ns=(50000 if i < 3 else 8000 + i), name="a_b_fused_bfuse", grid=(96, 1, 1),
+                 block=(192, 1, 1), regs=114, smem=199680) for i in range(10)]
+    p = tmp_path / "4_0_1_cuda_gpu_trace.csv"
+    trace_csv.write_gpu_trace(str(p), rows)
+    first = p.read_text().splitlines()[0]
+    assert first.startswith("Start (ns),Duration (ns),CorrId,GrdX,GrdY,GrdZ,BlkX,BlkY,BlkZ,Reg/Trd") and first.endswith(",Strm,Name")
+    back = trace_csv.read_gpu_trace(str(p))
+    assert len(back) == 10 and back[4] == (0.004, 0.008004, "a_b_fused_bfuse")
+    kept = [d for i, (_, d, n) in enumerate(back) if n == "a_b_fused_bfuse" and i >= 3]
+    assert abs(sum(kept) / len(kept) - (8000 + 6.0) / 1e6) < 1e-12
