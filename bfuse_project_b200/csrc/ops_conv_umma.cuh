@@ -160,6 +160,10 @@ struct ConvUmmaTf32 {
       }
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
       __syncwarp();
+      if (lane == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&p.map_w) : "memory");
+        if ((ohw & 3) == 0) asm volatile("prefetch.tensormap [%0];" ::"l"(&p.map_out) : "memory");
+      }
       if (lane == 0 && split > 1) {
         // bytes this CTA will receive: one partial per owned 32-pixel chunk from every k-slice (itself included)
         int owned = 0;

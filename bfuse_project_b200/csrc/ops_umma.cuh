@@ -492,7 +492,6 @@ struct GemmUmma {
       if (!masked_tile) tmem_alloc(smem_u32(tmem_slot), BN * halves);
       if (!c.persistent) tmem_relinquish();
     }
-    c.dependency_wait();   // the producer's first loads and everything after read global memory
     const uint32_t tiles = smem_u32(c.smem) + kUmmaHeaderBytes;
     const uint32_t recv_bar = acc_bar + 8;                                  // counts partial sums delivered by peers
     float *bias_tile = reinterpret_cast<float *>(c.smem + 1024);            // BN floats
@@ -512,6 +511,7 @@ struct GemmUmma {
     mark(MARK_START, c.tid == 0);
 
     if (masked_tile) {
+      c.dependency_wait();
       // tile entirely above the diagonal (for every k-slice of it): only the mask value to write;
       // k-slice 0 fills one buffer once and stores it to every chunk
       if (warp < 4 && kslice == 0) {
@@ -554,6 +554,8 @@ struct GemmUmma {
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
       __syncwarp();
       if (lane == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&p.map_a) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&p.map_b) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&p.map_out) : "memory");
         if (split > 1) {
           // bytes this CTA will receive: one partial per owned chunk from every k-slice (itself included)
@@ -562,6 +564,7 @@ struct GemmUmma {
           mbar_expect_tx(recv_bar, (uint32_t)owned * (uint32_t)split * kChunkPartial);
         }
       }
+      c.dependency_wait();   // all of the above ran while the previous kernel drained; the loads below read its output
       if (elect_one()) {
         for (int kb = 0; kb < npre; ++kb) {
           const uint32_t dst = tiles + kb * kStageBytes, bar = full0 + 8 * kb;
@@ -572,6 +575,8 @@ struct GemmUmma {
         }
       }
       __syncwarp();
+    } else {
+      c.dependency_wait();
     }
     tc_fence_before();
     c.sync();
