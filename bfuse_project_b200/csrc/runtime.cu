@@ -1040,7 +1040,8 @@ int bfuse_fusion_info(bfuse_context *ctx, int fusion, bfuse_kernel_desc *out) {
   out->op = -1;
   out->smem_bytes = f->smem;
   out->shape[0] = (int)f->launch_grid;  // CTAs actually launched (differs from GridDim for the work queue)
-  // CTAs of this kernel the device can hold at once (whole clusters), 0 when not known
+  // CTAs of this kernel resident at once according to the occupancy calculator (whole clusters; one CTA per SM
+  // for kernels that allocate tensor memory), 0 when not asked
   out->shape[1] = 0;
   if (f->plan.table.kind != DISPATCH_THREADS && !f->wide) {
     const int cl = std::max(1, f->plan.table.cluster);

@@ -121,7 +121,8 @@ int bfuse_register_fusion(bfuse_context *ctx, int kernel1, int kernel2, int patt
                           int *fusion);
 /* The record fuse::bfuse / hfuse write to {b,h}fuse_kernels.yaml (src/Fuse.cc:203-220,358-375):
  * name "<k1>_<k2>_fused_{bfuse,hfuse}", fused GridDim / BlockDim, plus smem and registers;
- * shape[0] = CTAs launched, shape[1] = CTAs of the kernel the device can hold at once (0: unknown).
+ * shape[0] = CTAs launched, shape[1] = CTAs of the kernel resident at once according to cudaOccupancyMaxActiveClusters,
+ * which counts one CTA per SM for kernels that allocate tensor memory (0: not asked).
  * out->KernelName points into the context and stays valid until bfuse_destroy. */
 int bfuse_fusion_info(bfuse_context *ctx, int fusion, bfuse_kernel_desc *out);
 /* Which operator and virtual block CTA (or queue ticket) b runs: the if / else-if chain the

@@ -225,3 +225,18 @@ def test_conv_tensor_core_matches_cuda_core_body(rt):
     for k in range(2):
         rms = np.sqrt(np.mean(b[k][0].astype(np.float64) ** 2))
         assert np.abs(a[k][0] - b[k][0]).max() <= 5e-3 * (np.abs(b[k][0]).max() + rms)
+
+
+def test_clustered_pair_that_would_need_a_second_wave_gets_half_sm_rings(rt):
+    """A conv split over clusters of 4 (100 CTAs) beside a 40-CTA conv whose ring was sized for a whole
+    SM: 140 CTAs, but clusters of 4 at one CTA per SM do not fit 148 SMs, so the runtime halves the rings;
+    the record reports what the occupancy calculator answered, and the results stay bit-identical to the unfused launches."""
+    rng = np.random.default_rng(91)
+    a = wl.conv2d("deep", rng, bf.OP_CONV2D_TF32, 1, 128, 28, 28, 128, 3, 1, 1)       # K = 1152: split 4, 25 x 4 CTAs
+    b = wl.conv2d("wide", rng, bf.OP_CONV2D_TF32, 1, 256, 35, 35, 64, 1, 1, 0)        # 1225 pixels, K = 256: 39 CTAs, whole-SM ring
+    pair = run_and_check(rt, wl.PairSpec("cluster_capacity", a, b, "tf32", "hbm"), [(bf.ZIGZAG, 1, 1)])
+    assert pair.spec.a.launch[0][0] == 100 and pair.spec.b.launch[0][0] == 39
+    info = rt.fusion_info(pair.fusion(bf.ZIGZAG, 1, 1))
+    assert info["GridDim"][0] == 140 and info["smem_bytes"] <= 112 * 1024 + 1024
+    # the occupancy calculator counts one CTA per SM for kernels that allocate tensor memory: whole clusters of 4 on 148 SMs
+    assert 0 < info["resident_ctas"] <= rt.sm_count and info["resident_ctas"] % 4 == 0 and info["resident_ctas"] < info["GridDim"][0]
