@@ -89,6 +89,7 @@ def lib():
             "bfuse_debug_fused_timeline": [vp, C.POINTER(C.c_int), C.c_int, C.POINTER(C.c_longlong), C.POINTER(C.c_int)],
             "bfuse_run_kernel": [vp, C.c_int, pp], "bfuse_run_parallel": [vp, C.c_int, pp, pp],
             "bfuse_run_fuse": [vp, C.c_int, pp, pp],
+            "bfuse_run_fuse_batch": [vp, ip, C.c_int, C.POINTER(pp), C.POINTER(pp)],
             "bfuse_time": [vp, C.c_int, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_float)],
             "bfuse_plan_create": [C.POINTER(Dim3), C.POINTER(Dim3), C.c_int, C.c_int, C.c_int, pp],
             "bfuse_plan_create_clustered": [C.POINTER(Dim3), C.POINTER(Dim3), C.c_int, C.c_int, C.c_int, C.c_int, pp],
@@ -374,6 +375,16 @@ class Runtime:
 
     def run_fuse(self, fusion, host1, host2):
         self._ck(self._L.bfuse_run_fuse(self._ctx, fusion, self._host_args(host1), self._host_args(host2)))
+
+    def run_fuse_batch(self, fusions, hosts1, hosts2):
+        """run_fuse over fusions with separate device buffers; transfers in both directions overlap the kernels
+        (pinned host arrays needed for that).  hosts1[i] / hosts2[i]: the host arrays of fusion i's two kernels."""
+        n = len(fusions)
+        pp = C.POINTER(C.c_void_p)
+        keep1, keep2 = [self._host_args(h) for h in hosts1], [self._host_args(h) for h in hosts2]
+        a1 = (pp * n)(*[C.cast(k, pp) for k in keep1])
+        a2 = (pp * n)(*[C.cast(k, pp) for k in keep2])
+        self._ck(self._L.bfuse_run_fuse_batch(self._ctx, (C.c_int * n)(*fusions), n, a1, a2))
 
     def time(self, fusion, mode, warmup=3, iters=30):
         """(mean_us over back-to-back launches, min_us over individually bracketed launches)."""

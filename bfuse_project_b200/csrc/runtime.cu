@@ -1280,6 +1280,41 @@ static int run_pair(bfuse_context *ctx, int fusion, void *const *h1, void *const
   if (!rc) rc = copy_out(ctx, b, h2, ctx->own);
   return rc ? rc : finish(ctx, ctx->own);
 }
+int bfuse_run_fuse_batch(bfuse_context *ctx, const int *fusions, int n, void *const *const *h1, void *const *const *h2) {
+  if (!ctx || !fusions || !h1 || !h2 || n <= 0) return fail(ctx, BFUSE_ERR_INVALID, "null argument");
+  for (int i = 0; i < n; ++i) {
+    if (!get_fusion(ctx, fusions[i]) || !h1[i] || !h2[i]) return fail(ctx, BFUSE_ERR_INVALID, "bad fusion handle in batch");
+    for (int j = 0; j < i; ++j)
+      if (fusions[j] == fusions[i]) return fail(ctx, BFUSE_ERR_INVALID, "a fusion may appear once per batch: its device buffers would race");
+  }
+  cudaSetDevice(ctx->device);
+  // s1 carries the copies in, the context's own stream the launches, s2 the copies out
+  std::vector<cudaEvent_t> ev(2 * (size_t)n, nullptr);
+  int rc = BFUSE_OK;
+  for (size_t i = 0; i < ev.size() && !rc; ++i)
+    if (cudaEventCreateWithFlags(&ev[i], cudaEventDisableTiming) != cudaSuccess) rc = fail(ctx, BFUSE_ERR_CUDA, "cudaEventCreate");
+  for (int i = 0; i < n && !rc; ++i) {
+    FusionRec &f = *get_fusion(ctx, fusions[i]);
+    KernelRec &a = *ctx->kernels[f.k1], &b = *ctx->kernels[f.k2];
+    rc = copy_in(ctx, a, h1[i], ctx->s1);
+    if (!rc) rc = copy_in(ctx, b, h2[i], ctx->s1);
+    if (rc) break;
+    cudaEventRecord(ev[2 * i], ctx->s1);
+    cudaStreamWaitEvent(ctx->own, ev[2 * i], 0);
+    rc = launch_fused_rec(ctx, f, ctx->own);
+    if (rc) break;
+    cudaEventRecord(ev[2 * i + 1], ctx->own);
+    cudaStreamWaitEvent(ctx->s2, ev[2 * i + 1], 0);
+    rc = copy_out(ctx, a, h1[i], ctx->s2);
+    if (!rc) rc = copy_out(ctx, b, h2[i], ctx->s2);
+  }
+  cudaStreamSynchronize(ctx->s1);
+  cudaStreamSynchronize(ctx->own);
+  const int rc2 = finish(ctx, ctx->s2);   // status word behind the last copies out, then one synchronisation
+  for (cudaEvent_t e : ev)
+    if (e) cudaEventDestroy(e);
+  return rc ? rc : rc2;
+}
 int bfuse_run_parallel(bfuse_context *ctx, int fusion, void *const *h1, void *const *h2) { return run_pair(ctx, fusion, h1, h2, 2); }
 int bfuse_run_fuse(bfuse_context *ctx, int fusion, void *const *h1, void *const *h2) { return run_pair(ctx, fusion, h1, h2, 4); }
 

@@ -188,6 +188,13 @@ int bfuse_read_status(bfuse_context *ctx, int *status);
 int bfuse_run_kernel(bfuse_context *ctx, int kernel, void *const *host_args);                    /* run_kernel1/2 */
 int bfuse_run_parallel(bfuse_context *ctx, int fusion, void *const *host_args1, void *const *host_args2); /* run_parallel */
 int bfuse_run_fuse(bfuse_context *ctx, int fusion, void *const *host_args1, void *const *host_args2);     /* run_fuse     */
+/* run_fuse over n fusions that own different device buffers (the benchmark's `-n N` loop over independent
+ * pairs, tests/benchmark/main.cu): the copies in of fusion i + 1, the fused launch of fusion i and the copies out
+ * of fusion i - 1 run on three streams, so host <-> device transfers in both directions overlap the kernels.
+ * host_args1[i] / host_args2[i] are the argument lists bfuse_run_fuse takes; pinned host memory is needed for the
+ * overlap.  Returns after everything has completed; a fusion listed twice is rejected (its buffers would race). */
+int bfuse_run_fuse_batch(bfuse_context *ctx, const int *fusions, int n, void *const *const *host_args1,
+                         void *const *const *host_args2);
 
 /* Timing in the spirit of scripts/profile_test_suite.py:10-11 + analyze_test_suite.py:103-123
  * (warm-ups, then the mean over 30 launches): `warmup` untimed launches, then a CUDA graph of `iters`

@@ -171,3 +171,32 @@ def test_rejected_registrations(rt):
     with pytest.raises(bf.BfuseError) as e:
         rt.register_kernel(d)
     assert e.value.code == 3
+
+
+def test_run_fuse_batch_matches_one_call_per_pair(rt):
+    """The batched host-buffer entry point (copies in, launches and copies out of neighbouring pairs on
+    three streams) returns the same bits as one synchronous run_fuse per pair; duplicates are refused."""
+    specs = [wl.make_pair("cfg1_softmax_layernorm", seed=s, scale=0.25) for s in range(3)] + \
+            [wl.make_pair("cfg2_q_k_proj", seed=7, scale=0.25)]
+    pairs = [wl.DevicePair(rt, sp) for sp in specs]
+    fus = [p.fusion(bf.ZIGZAG, 1, 1) for p in pairs]
+
+    def host_copy(sp):
+        return [[None if a is None else a.copy() for a in ks.host] for ks in (sp.a, sp.b)]
+
+    want = []
+    for p, f in zip(pairs, fus):
+        h = host_copy(p.spec)
+        rt.run_fuse(f, h[0], h[1])
+        want.append(h)
+        p.clear_outputs()
+    got = [host_copy(p.spec) for p in pairs]
+    rt.run_fuse_batch(fus, [h[0] for h in got], [h[1] for h in got])
+    for p, w, g in zip(pairs, want, got):
+        for k, ks in enumerate((p.spec.a, p.spec.b)):
+            for i in ks.outputs:
+                assert np.array_equal(w[k][i].view(np.uint8), g[k][i].view(np.uint8))
+                assert np.any(g[k][i].view(np.uint8) != 0)
+    with pytest.raises(bf.BfuseError) as e:
+        rt.run_fuse_batch([fus[0], fus[0]], [got[0][0], got[0][0]], [got[0][1], got[0][1]])
+    assert e.value.code == 1
