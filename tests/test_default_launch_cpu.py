@@ -72,3 +72,30 @@ def test_automatic_k_slices_are_one_or_four():
     for sh in ((1, 256, 14, 14, 256, 3, 3, 1, 1), (1, 128, 28, 28, 128, 3, 3, 1, 1), (1, 768, 17, 17, 192, 1, 1, 1, 0), (4, 64, 56, 56, 64, 3, 3, 1, 1)):
         seen.add(default(bf.OP_CONV2D_TF32, sh).shape[10])
     assert seen <= {1, 4} and 4 in seen
+
+
+def test_share_hint_budgets_the_sms_per_co_runner():
+    """BFUSE_FLAG_SHARE(n): the operator is tiled for 1 / n of the SMs (absent: a pair, n = 2)."""
+    def g(op, shape, share):
+        d = bf.KernelDesc()
+        d.KernelName, d.op, d.flags = b"k", op, bf.flag_share(share) if share else 0
+        for i, v in enumerate(shape):
+            d.shape[i] = v
+        assert bf.lib().bfuse_default_launch(None, d) == 0
+        return d.GridDim.tuple(), d.shape[4], d.shape[5], d.shape[6]
+    q = (1, 512, 4096, 4096, 0, 0, 0)                                  # Llama q projection, bf16
+    assert g(bf.OP_GEMM_BF16, q, 0) == g(bf.OP_GEMM_BF16, q, 2)        # no hint = a pair
+    assert g(bf.OP_GEMM_BF16, q, 1) == ((4, 32, 1), 128, 1, 128)       # alone: 128 CTAs of 128 x 128
+    assert g(bf.OP_GEMM_BF16, q, 2) == ((4, 16, 1), 256, 1, 128)
+    assert g(bf.OP_GEMM_BF16, q, 3) == ((4, 16, 1), 256, 1, 128)       # a third of the SMs: still 128-row tiles (no second wave to save)
+    gate = (1, 512, 14336, 4096, 0, 0, 0)
+    assert g(bf.OP_GEMM_BF16, gate, 1) == ((2, 56, 1), 256, 1, 256)    # alone, 224 tiles = 2 waves: 256-row tiles make it one
+    assert g(bf.OP_GEMM_BF16, gate, 2) == ((2, 56, 1), 256, 1, 256)
+    ffn2 = (1, 512, 768, 3072, 0, 0, 0)                                # BERT FFN down projection, tf32: long K, few tiles
+    assert g(bf.OP_GEMM_TF32, ffn2, 1)[2] == 4 and g(bf.OP_GEMM_TF32, ffn2, 4)[2] == 1   # k-slices only while SMs are idle
+    conv = (1, 64, 56, 56, 128, 3, 3, 2, 1)                            # 784 pixels, 18 K blocks
+    d = bf.KernelDesc()
+    d.KernelName, d.op, d.flags = b"k", bf.OP_CONV2D_TF32, bf.flag_share(4)
+    for i, v in enumerate(conv):
+        d.shape[i] = v
+    assert bf.lib().bfuse_default_launch(None, d) == 0 and d.shape[10] == 1 and d.shape[9] == 32   # a quarter of the SMs: 25 tiles fill it unsplit
