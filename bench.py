@@ -156,7 +156,9 @@ def run_sweep(args, rt, torch, rank, world, local, pk):
     mine = partition.assign_pairs(todo, world, rank)
     torch.cuda.synchronize()
     t0 = time.perf_counter()
-    res = sweep.measure(rt, sets, mine, pk["hbm_gbs"], pk["bf16_tflops"] * 0.5)
+    import bfuse_project_b200 as bfm
+    pattern = {"zigzag": bfm.ZIGZAG, "range": bfm.RANGE_SPLIT, "striped": bfm.SM_STRIPED, "proportional": bfm.PROPORTIONAL}[args.sweep_pattern]
+    res = sweep.measure(rt, sets, mine, pk["hbm_gbs"], pk["bf16_tflops"] * 0.5, pattern=pattern)
     wall = time.perf_counter() - t0
     alone = sweep.alone_times(rt, sets) if rank == 0 else None      # for the pair-selection model, outside the wall time
     assert rt.read_status() == 0, "a bounded device-side wait gave up during the sweep"
@@ -171,8 +173,8 @@ def run_sweep(args, rt, torch, rank, world, local, pk):
         return
     line = {"metric": "sweep_wall_s", "value": wall, "unit": "s", "n_gpus": world, "higher_is_better": False, "scaling": "strong",
             "dtype": "tf32", "data": "synthetic",
-            "config": {"workload": "operator cross-product sweep: %d operators, %d pairs (upper triangle), zig-zag 1:1 fusion vs "
-                                   "back-to-back launches; 3 warm-ups + 30 timed launches per mode" % (n_ops, len(todo)),
+            "config": {"workload": "operator cross-product sweep: %d operators, %d pairs (upper triangle), %s fusion vs "
+                                   "back-to-back launches; 3 warm-ups + 30 timed launches per mode" % (n_ops, len(todo), args.sweep_pattern),
                        "partition": "pair i on rank i mod %d" % world},
             "sweep": sweep.summarise(res)}
     from bfuse_project_b200 import pairing
@@ -388,6 +390,8 @@ def main():
     ap.add_argument("--sweep", action="store_true", help="run the 42 x 42 operator cross-product sweep instead (pair i on rank i mod N)")
     ap.add_argument("--sweep-out", default="", help="with --sweep: also write the per-pair table to this JSON file")
     ap.add_argument("--sweep-limit", type=int, default=0, help="with --sweep: only the first N operators")
+    ap.add_argument("--sweep-pattern", default="zigzag", choices=["zigzag", "range", "striped", "proportional"],
+                    help="with --sweep: the block-level pattern of the fused launches")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
 

@@ -15,8 +15,8 @@ stay in L2 as they do in the reference's own loop.
 """
 import math
 
-from . import (BfuseError, MODE_FUSED, MODE_KERNEL1, MODE_SEQUENTIAL, OP_CONV2D_F32_SIMT, OP_CONV2D_TF32, OP_GEMM_TF32, RANGE_SPLIT,
-               ZIGZAG)
+from . import (BfuseError, MODE_FUSED, MODE_KERNEL1, MODE_SEQUENTIAL, OP_CONV2D_F32_SIMT, OP_CONV2D_TF32, OP_GEMM_TF32, PROPORTIONAL,
+               RANGE_SPLIT, ZIGZAG)
 
 # name -> shape.  dense: (M, K, N); bgemm: (batch, M, K, N); conv2d: (N, H, W, CO, CI, KH, KW, stride, pad)
 SWEEP_OPS = (
@@ -124,7 +124,8 @@ def measure(rt, sets, pairs, hbm_gbs, tf32_tflops, pattern=ZIGZAG, warmup=3, ite
         a, b = sets[0][i], sets[1][j]
         key = "%s|%s" % (a.name[:-3], b.name[:-3])   # without the set suffix
         try:
-            f = rt.register_fusion(a.kernel, b.kernel, pattern, 1, 1)
+            mn = 1 if pattern in (ZIGZAG, PROPORTIONAL) else 0     # range split takes no parameter, SM-striped the device's SM count
+            f = rt.register_fusion(a.kernel, b.kernel, pattern, mn, mn)
         except BfuseError as e:
             out[key] = {"error": str(e)[:120]}
             continue
