@@ -135,3 +135,47 @@ def test_trace_files_of_a_pair(tmp_path):
         assert {n for _, _, n in rows} == want
     assert rt.read_status() == 0
     rt.close()
+
+
+def test_group_with_clustered_members():
+    """A group whose members split K over clusters of 4, beside an unsplit member that is scheduled in
+    padded clusters: same bits as the unfused launches, every virtual block exactly once."""
+    import torch
+    rt = bf.Runtime(0)
+    b = sg._Builder(rt, torch, seed=11)
+    M, N, K = 256, 192, 1024
+    b.tensor("x", (M, K))
+    for i, (bn, split) in enumerate(((64, 4), (128, 4), (64, 1))):
+        b.tensor("w%d" % i, (N, K), std=0.05)
+        b.tensor("y%d" % i, (M, N), zero=True)
+        b._add("g%d" % i, bf.OP_GEMM_TF32, (1, M, N, K, bn, split, 0), ["x", "w%d" % i, None, "y%d" % i], ["x", "w%d" % i], ["y%d" % i])
+    ks = [o.register(rt, 3) for o in b.ops]
+    stream = torch.cuda.current_stream().cuda_stream
+    for k in ks:
+        rt.launch_kernel(k, stream)
+    torch.cuda.synchronize()
+    want = [b.buf["y%d" % i].clone() for i in range(3)]
+    for pattern in (bf.ZIGZAG, bf.RANGE_SPLIT):
+        for i in range(3):
+            b.buf["y%d" % i].zero_()
+        g = rt.register_group(ks, pattern, 1 if pattern == bf.ZIGZAG else 0, 1 if pattern == bf.ZIGZAG else 0)
+        rt.launch_group(g, stream)
+        torch.cuda.synchronize()
+        assert rt.read_status() == 0
+        for i in range(3):
+            assert torch.equal(b.buf["y%d" % i], want[i]) and bool(want[i].abs().sum() > 0)
+        info = rt.group_info(g)
+        assert info["GridDim"][0] % 4 == 0
+        seen = {}
+        for cta in range(info["GridDim"][0]):
+            m = rt.group_map_block(g, cta)
+            if m is not None:
+                seen.setdefault(m[0], []).append(m[1])
+        assert all(sorted(v) == list(range(len(v))) for v in seen.values()) and sorted(seen) == [0, 1, 2]
+    ref = (b.buf["x"].double() @ b.buf["w0"].double().T).float()
+    assert float((want[0] - ref).abs().max()) <= 5e-3 * float(ref.abs().max())
+    with pytest.raises(bf.BfuseError) as e:       # clusters of 2 and of 4 cannot share a launch
+        odd = sg.SegmentOp("g2", bf.OP_GEMM_TF32, None, ["x"], ["y2"], spec=((1, M, N, K, 64, 2, 0), [b.buf["x"].data_ptr(), b.buf["w2"].data_ptr(), None, b.buf["y2"].data_ptr()], {}))
+        rt.register_group([ks[0], odd.register(rt, 2)], bf.ZIGZAG, 1, 1)
+    assert e.value.code == 7
+    rt.close()
