@@ -175,8 +175,9 @@ int bfuse_trace_fused(bfuse_context *ctx, int fusion, int *kernel_of, int *vbloc
 int bfuse_debug_gemm_timeline(bfuse_context *ctx, int kernel, long long *marks, int n);
 /* Diagnostic, no reference counterpart: launch the n block-level fusions back to back on the
  * context's stream (fused mode), every dispatch slot (CTA, or ticket for WORK_QUEUE) of launch i
- * recording three global-timer marks in nanoseconds: kernel entry, body start (the dependency on
- * the previous launch resolved), thread 0 of the body done.  times holds 3 * sum(slots) values,
+ * recording three global-timer marks in nanoseconds: kernel entry, body start (the body sets itself
+ * up and then waits for the previous launch, so this may precede that launch's end), thread 0 of
+ * the body done.  times holds 3 * sum(slots) values,
  * launch i's slots[i] >= its fused grid entries first to last; unused entries stay 0.  Synchronises. */
 int bfuse_debug_fused_timeline(bfuse_context *ctx, const int *fusions, int n, long long *times, const int *slots);
 /* Read and clear the device status word (0 = no bounded wait gave up). Synchronises. */
@@ -188,8 +189,8 @@ int bfuse_read_status(bfuse_context *ctx, int *status);
 int bfuse_run_kernel(bfuse_context *ctx, int kernel, void *const *host_args);                    /* run_kernel1/2 */
 int bfuse_run_parallel(bfuse_context *ctx, int fusion, void *const *host_args1, void *const *host_args2); /* run_parallel */
 int bfuse_run_fuse(bfuse_context *ctx, int fusion, void *const *host_args1, void *const *host_args2);     /* run_fuse     */
-/* run_fuse over n fusions that own different device buffers (the benchmark's `-n N` loop over independent
- * pairs, tests/benchmark/main.cu): the copies in of fusion i + 1, the fused launch of fusion i and the copies out
+/* run_fuse over n fusions that own different device buffers (the harness' `-n num_iterations` loop around
+ * run_fuse, tests/benchmark/main.cc:183-200, for independent pairs instead of one repeated): the copies in of fusion i + 1, the fused launch of fusion i and the copies out
  * of fusion i - 1 run on three streams, so host <-> device transfers in both directions overlap the kernels.
  * host_args1[i] / host_args2[i] are the argument lists bfuse_run_fuse takes; pinned host memory is needed for the
  * overlap.  Returns after everything has completed; a fusion listed twice is rejected (its buffers would race). */
