@@ -146,9 +146,11 @@ void pick_tile(int batch, int M, int N, int K, int elem, int sm_count, int share
     if (bn_fixed > 0 ? bn != bn_fixed : (bn * elem < 128 || (bn > 32 && bn / 2 >= N && bn / 2 * elem >= 128))) continue;
     const long long tiles = (long long)batch * ceil_div(M, kUmmaBM) * ceil_div(N, bn);
     // own choice of k-slices: 1 or 4 and no other width, so that any two operators the runtime tiled
-    // can share a launch (a fused launch has one cluster width)
-    const int cand[2] = {split_fixed > 0 ? split_fixed : 1, split_fixed > 0 ? split_fixed : 4};
-    for (int ci = 0; ci < (split_fixed > 0 ? 1 : 2); ++ci) {
+    // can share a launch (a fused launch has one cluster width); an operator that runs alone may also take 2
+    // when K is very long (the model underrates what a split costs: at 64 K blocks two slices measured 25 us
+    // against 16 us unsplit and at 128 K blocks 36 us against 34 us, at 224 K blocks 58 us against 74 us with four)
+    const int cand[3] = {split_fixed > 0 ? split_fixed : 1, 4, 2};
+    for (int ci = 0; ci < (split_fixed > 0 ? 1 : (share == 1 && num_kb >= 192 ? 3 : 2)); ++ci) {
       const int split = cand[ci];
       if (split > num_kb) continue;
       if (umma_smem_bytes(bn, umma_min_stages(bn, split, elem)) > ((bn == 256 || share * tiles * split <= sm_count) ? 200 : 100) * 1024) continue;

@@ -99,3 +99,17 @@ def test_share_hint_budgets_the_sms_per_co_runner():
     for i, v in enumerate(conv):
         d.shape[i] = v
     assert bf.lib().bfuse_default_launch(None, d) == 0 and d.shape[10] == 1 and d.shape[9] == 32   # a quarter of the SMs: 25 tiles fill it unsplit
+
+
+def test_lone_long_k_gemm_may_take_two_k_slices():
+    """An operator that runs alone (share 1) may split a very long K in two; operators that share a launch keep 1 or 4."""
+    def split(op, shape, share):
+        d = bf.KernelDesc()
+        d.KernelName, d.op, d.flags = b"k", op, bf.flag_share(share)
+        for i, v in enumerate(shape):
+            d.shape[i] = v
+        assert bf.lib().bfuse_default_launch(None, d) == 0
+        return d.shape[5]
+    down = (1, 512, 4096, 14336, 0, 0, 0)                       # Llama down projection: 224 K blocks in bf16
+    assert split(bf.OP_GEMM_BF16, down, 1) == 2 and split(bf.OP_GEMM_BF16, down, 2) in (1, 4)
+    assert split(bf.OP_GEMM_TF32, (1, 512, 4096, 4096, 0, 0, 0), 1) == 1      # 128 K blocks: unsplit is as fast
