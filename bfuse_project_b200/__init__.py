@@ -84,6 +84,9 @@ def lib():
             "bfuse_launch_parallel": [vp, C.c_int, vp], "bfuse_launch_fused": [vp, C.c_int, vp],
             "bfuse_launch_list": [vp, ip, C.c_int, C.c_int, vp],
             "bfuse_graph_create": [vp, ip, C.c_int, C.c_int, ip], "bfuse_graph_launch": [vp, C.c_int, vp],
+            "bfuse_graph_destroy": [vp, C.c_int], "bfuse_unregister_kernel": [vp, C.c_int],
+            "bfuse_unregister_fusion": [vp, C.c_int], "bfuse_unregister_group": [vp, C.c_int],
+            "bfuse_set_dependent_launch": [vp, C.c_int],
             "bfuse_trace_fused": [vp, C.c_int, ip, ip, ip, C.c_int], "bfuse_read_status": [vp, ip],
             "bfuse_debug_gemm_timeline": [vp, C.c_int, C.POINTER(C.c_longlong), C.c_int],
             "bfuse_debug_fused_timeline": [vp, C.POINTER(C.c_int), C.c_int, C.POINTER(C.c_longlong), C.POINTER(C.c_int)],
@@ -254,6 +257,22 @@ class Runtime:
         self._ck(self._L.bfuse_register_kernel(self._ctx, desc, h))
         return h.value
 
+    def unregister_kernel(self, kernel):
+        self._ck(self._L.bfuse_unregister_kernel(self._ctx, kernel))
+
+    def unregister_fusion(self, fusion):
+        self._ck(self._L.bfuse_unregister_fusion(self._ctx, fusion))
+
+    def unregister_group(self, group):
+        self._ck(self._L.bfuse_unregister_group(self._ctx, group))
+
+    def graph_destroy(self, graph):
+        self._ck(self._L.bfuse_graph_destroy(self._ctx, graph))
+
+    def set_dependent_launch(self, enabled):
+        """Diagnostic: False launches every later kernel without programmatic dependent launch."""
+        self._ck(self._L.bfuse_set_dependent_launch(self._ctx, 1 if enabled else 0))
+
     def set_kernel_args(self, kernel, args):
         arr = (C.c_void_p * len(args))(*args)
         self._ck(self._L.bfuse_set_kernel_args(self._ctx, kernel, arr, len(args)))
@@ -289,7 +308,8 @@ class Runtime:
         d = KernelDesc()
         self._ck(self._L.bfuse_fusion_info(self._ctx, fusion, d))
         return {"KernelName": d.KernelName.decode(), "GridDim": d.GridDim.tuple(), "BlockDim": d.BlockDim.tuple(),
-                "Reg": d.Reg, "smem_bytes": d.smem_bytes, "launched_ctas": d.shape[0], "resident_ctas": d.shape[1]}
+                "Reg": d.Reg, "smem_bytes": d.smem_bytes, "launched_ctas": d.shape[0], "resident_ctas": d.shape[1],
+                "retiled_unsplit": (bool(d.shape[2]), bool(d.shape[3]))}
 
     def map_block(self, fusion, b):
         k, vb = C.c_int(), C.c_int()

@@ -47,6 +47,7 @@ struct DispatchTable {
   unsigned int *queue_ctr; // [0] next ticket, [1] CTAs that have drained (persistent queue only)
   int *status;             // device status word; non-zero = a bounded wait gave up
   unsigned long long *cta_times;  // diagnostic: when non-null, every block-level dispatch slot records 3 globaltimer marks
+  int no_pdl;              // host side only: launch without the programmatic-dependent-launch attribute
 };
 
 // Dispatch unit (or ticket) b -> operator k and its virtual unit.  Returns false if b is unmapped.
@@ -124,6 +125,7 @@ struct GroupTable {
   int rot_end, rot, ratio_lo[kGroupMax + 1];
   int tail_lo[kGroupMax], tail_hi[kGroupMax], tail_base[kGroupMax];
   int *status;
+  int no_pdl;         // host side only: launch without the programmatic-dependent-launch attribute
 };
 
 BFUSE_HD bool decode_group_unit(const GroupTable &t, int b, int &k, int &vb) {

@@ -18,8 +18,6 @@
 // that keeps the lighter operator's occupancy without starving the heavier body of registers.
 #pragma once
 
-#include <cstdlib>
-
 #include "dispatch.h"
 #include "tile.h"
 
@@ -112,7 +110,13 @@ __global__ void __launch_bounds__(cmax(A::kMaxThreads, B::kMaxThreads), MINB)
   }
   if (t.queue) {   // the ticket counter is global memory; otherwise the body waits and lets the next kernel in (TileCtx::dependency_wait)
     grid_dependency_wait();
-    grid_launch_dependents();
+    // A persistent CTA of a tensor-core body allocates tensor memory again for every ticket, and that
+    // allocation is the one wait without a bound.  CTAs of a following kernel, started early, would
+    // allocate their columns before their own griddepcontrol.wait and then sit on this SM until this
+    // grid has finished -- while a persistent CTA here waits for columns: a circular wait.  So a queue
+    // launch with a tensor-memory operator never lets the next kernel in early (its CTAs start when
+    // this grid's CTAs have exited); two memory-bound bodies keep the early trigger.
+    if constexpr (!A::kUsesTmem && !B::kUsesTmem) grid_launch_dependents();
   }
   // One loop serves both launch forms, so each body is inlined once (two copies cost registers and
   // made the memory-bound pairs spill): a plain launch runs it for CTA blockIdx.x and leaves; a
@@ -236,17 +240,12 @@ cudaError_t ensure_smem(Kernel k, size_t smem) {
   return cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
 }
 
-// Diagnostic switch: with BFUSE_NO_PDL set in the environment the launches do not ask for programmatic
-// dependent launch, to tell its effect on a timeline from everything else.
-inline bool pdl_allowed() {
-  static const bool on = std::getenv("BFUSE_NO_PDL") == nullptr;
-  return on;
-}
-
 // Launch with `cluster` consecutive CTAs per thread-block cluster (1 = no clusters) and with
-// programmatic dependent launch allowed.
+// programmatic dependent launch allowed unless the dispatch table says otherwise (no_pdl, set from the
+// context's switch bfuse_set_dependent_launch: a diagnostic to tell the overlap's effect on a timeline
+// from everything else).
 template <class Kernel, class... Args>
-cudaError_t launch_clustered(Kernel kern, unsigned grid, unsigned block, size_t smem, cudaStream_t s, int cluster,
+cudaError_t launch_clustered(Kernel kern, unsigned grid, unsigned block, size_t smem, cudaStream_t s, int cluster, bool pdl,
                              Args... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid, 1, 1);
@@ -255,7 +254,7 @@ cudaError_t launch_clustered(Kernel kern, unsigned grid, unsigned block, size_t 
   cfg.stream = s;
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = pdl_allowed() ? 1 : 0;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl ? 1 : 0;
   attr[1].id = cudaLaunchAttributeClusterDimension;
   attr[1].val.clusterDim.x = cluster > 1 ? cluster : 1;
   attr[1].val.clusterDim.y = 1;
@@ -306,7 +305,7 @@ cudaError_t launch_block_pair(const DispatchTable &t, const void *pa, const void
                               size_t smem, cudaStream_t s) {
   cudaError_t e = ensure_smem(fused_block_kernel<A, B>, smem);
   if (e != cudaSuccess) return e;
-  return launch_clustered(fused_block_kernel<A, B>, grid, block, smem, s, t.cluster, t,
+  return launch_clustered(fused_block_kernel<A, B>, grid, block, smem, s, t.cluster, !t.no_pdl, t,
                           *static_cast<const typename A::Params *>(pa), *static_cast<const typename B::Params *>(pb));
 }
 template <class A, class B>
@@ -314,7 +313,7 @@ cudaError_t launch_thread_pair(const DispatchTable &t, const void *pa, const voi
                                size_t smem, cudaStream_t s) {
   cudaError_t e = ensure_smem(fused_thread_kernel<A, B>, smem);
   if (e != cudaSuccess) return e;
-  return launch_clustered(fused_thread_kernel<A, B>, grid, block, smem, s, 1, t,
+  return launch_clustered(fused_thread_kernel<A, B>, grid, block, smem, s, 1, !t.no_pdl, t,
                           *static_cast<const typename A::Params *>(pa), *static_cast<const typename B::Params *>(pb));
 }
 template <class A>
@@ -322,7 +321,7 @@ cudaError_t launch_single(const DispatchTable &t, const void *pa, unsigned grid,
                           cudaStream_t s) {
   cudaError_t e = ensure_smem(single_kernel<A>, smem);
   if (e != cudaSuccess) return e;
-  return launch_clustered(single_kernel<A>, grid, block, smem, s, t.cluster, t,
+  return launch_clustered(single_kernel<A>, grid, block, smem, s, t.cluster, !t.no_pdl, t,
                           *static_cast<const typename A::Params *>(pa));
 }
 template <class A>
@@ -332,7 +331,7 @@ cudaError_t launch_group(const GroupTable &t, const void *const *params, int n, 
   if (e != cudaSuccess) return e;
   GroupParams<A> g;
   for (int i = 0; i < kGroupMax; ++i) g.p[i] = *static_cast<const typename A::Params *>(params[i < n ? i : 0]);
-  return launch_clustered(fused_group_kernel<A>, grid, block, smem, s, t.cluster, t, g);
+  return launch_clustered(fused_group_kernel<A>, grid, block, smem, s, t.cluster, !t.no_pdl, t, g);
 }
 template <class A>
 cudaError_t attr_group(cudaFuncAttributes *a) { return cudaFuncGetAttributes(a, fused_group_kernel<A>); }
@@ -341,7 +340,7 @@ cudaError_t launch_block_pair_wide(const DispatchTable &t, const void *pa, const
                                    size_t smem, cudaStream_t s) {
   cudaError_t e = ensure_smem(fused_block_kernel<A, B, pair_wide_blocks<A, B>()>, smem);
   if (e != cudaSuccess) return e;
-  return launch_clustered(fused_block_kernel<A, B, pair_wide_blocks<A, B>()>, grid, block, smem, s, t.cluster, t,
+  return launch_clustered(fused_block_kernel<A, B, pair_wide_blocks<A, B>()>, grid, block, smem, s, t.cluster, !t.no_pdl, t,
                           *static_cast<const typename A::Params *>(pa), *static_cast<const typename B::Params *>(pb));
 }
 template <class A, class B>

@@ -25,6 +25,7 @@
 
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 
 #include "../../include/bfuse_b200.h"
 #include "fused_kernels.cuh"
@@ -41,7 +42,9 @@ constexpr int kMaxDevices = 64;
 static __device__ __align__(256) unsigned int g_noalloc_scratch[kScratchWords];
 
 struct DeviceSetup {
-  bool ready;
+  std::once_flag once;    // the first call on a device fills the rest; concurrent first calls wait for it
+  int status;             // BFUSE_OK, or why the set-up failed (kept: later calls report it again)
+  const char *why;
   unsigned int *scratch;  // device address of g_noalloc_scratch on this device
   int sm_count;
   int ctas_per_sm;
@@ -51,15 +54,6 @@ DeviceSetup g_setup[kMaxDevices];
 int reject(int code, const char *msg) {
   fprintf(stderr, "bfuse_softmax_layernorm_queue_noalloc: %s\n", msg);
   return code;
-}
-
-// threads per row: the same rule as the registered path's default tiling
-int row_threads(int cols) {
-  for (int tpr = 32; tpr <= 256; tpr *= 2)
-    if (cols % (4 * tpr) == 0 && cols / (4 * tpr) <= 4) return tpr;
-  for (int tpr = 256; tpr >= 1; tpr /= 2)
-    if (cols % (4 * tpr) == 0 && cols / (4 * tpr) <= kRowMaxVec) return tpr;
-  return 0;
 }
 
 bool misaligned(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) != 0; }
@@ -75,7 +69,7 @@ extern "C" int bfuse_softmax_layernorm_queue_noalloc(const float *sm_x, float *s
       misaligned(ln_beta) || misaligned(ln_y))
     return reject(BFUSE_ERR_INVALID, "buffers must be 16-byte aligned");
   if (sm_rows <= 0 || sm_cols <= 0 || ln_rows <= 0 || ln_cols <= 0) return reject(BFUSE_ERR_SHAPE, "rows and cols must be positive");
-  const int tpr_a = row_threads(sm_cols), tpr_b = row_threads(ln_cols);
+  const int tpr_a = pick_row_threads(sm_cols, 4, kRowMaxVec), tpr_b = pick_row_threads(ln_cols, 4, kRowMaxVec);  // the registered path's rule
   if (!tpr_a || !tpr_b) return reject(BFUSE_ERR_SHAPE, "cols must be a multiple of 4 * (power-of-two threads per row), at most 4096");
   const int rpc_a = 256 / tpr_a, rpc_b = 256 / tpr_b;
   const long long ctas_a = ((long long)sm_rows + rpc_a - 1) / rpc_a, ctas_b = ((long long)ln_rows + rpc_b - 1) / rpc_b;
@@ -87,25 +81,26 @@ extern "C" int bfuse_softmax_layernorm_queue_noalloc(const float *sm_x, float *s
   if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) return reject(BFUSE_ERR_DEVICE, "no current CUDA device");
   DeviceSetup &su = g_setup[dev];
   auto kernel = fused_block_kernel<SoftmaxF32, LayerNormF32>;
-  if (!su.ready) {
+  std::call_once(su.once, [&] {
     // once per device, with that device current: the array's name is a host-side handle, the
     // kernel needs its device address
+    su.status = BFUSE_OK;
     void *ptr = nullptr;
-    e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
-    if (e != cudaSuccess || !ptr) return reject(BFUSE_ERR_CUDA, cudaGetErrorString(e));
+    cudaError_t e1 = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+    if (e1 != cudaSuccess || !ptr) { su.status = BFUSE_ERR_CUDA, su.why = cudaGetErrorString(e1); return; }
     int major = 0, sms = 0;
     cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    if (major != 10 || sms <= 0) return reject(BFUSE_ERR_DEVICE, "not an sm_100 device");
+    if (major != 10 || sms <= 0) { su.status = BFUSE_ERR_DEVICE, su.why = "not an sm_100 device"; return; }
     cudaFuncAttributes attr;
-    e = cudaFuncGetAttributes(&attr, kernel);
-    if (e != cudaSuccess) return reject(BFUSE_ERR_CUDA, cudaGetErrorString(e));
+    e1 = cudaFuncGetAttributes(&attr, kernel);
+    if (e1 != cudaSuccess) { su.status = BFUSE_ERR_CUDA, su.why = cudaGetErrorString(e1); return; }
     const int by_regs = 65536 / (attr.numRegs * 256 > 0 ? attr.numRegs * 256 : 1);
     su.ctas_per_sm = by_regs < 1 ? 1 : (by_regs > 8 ? 8 : by_regs);
     su.sm_count = sms;
     su.scratch = static_cast<unsigned int *>(ptr);
-    su.ready = true;
-  }
+  });
+  if (su.status != BFUSE_OK) return reject(su.status, su.why);
 
   const KernelDims kd[2] = {{(int)ctas_a, 1, 1, tpr_a, rpc_a, 1}, {(int)ctas_b, 1, 1, tpr_b, rpc_b, 1}};
   FusedPlan plan;

@@ -43,10 +43,15 @@ struct KernelRec {
   int cluster;  // CTAs per thread-block cluster the body needs (split-K GEMM), else 1
   int nargs;
   ArgInfo arg[BFUSE_MAX_ARGS];
+  int alias_of;  // >= 0: a hidden re-tiling (one k-slice) of that registered kernel, owned by a fusion
+  int users;     // live fusions / groups that launch this kernel
 };
 
 struct FusionRec {
-  int k1, k2;
+  int k1, k2;           // the kernels the fusion launches (hidden unsplit re-tilings when retiled[k])
+  int reg1, reg2;       // the kernels it was registered with
+  bool retiled[2];
+  int users;            // live graphs that captured it
   FusedPlan plan;
   std::string name;
   size_t smem;
@@ -70,6 +75,7 @@ struct GroupRec {
 struct GraphRec {
   cudaGraphExec_t exec;
   int launches;
+  std::vector<int> fusions;  // captured fusions: they cannot be released while the graph lives
 };
 
 }  // namespace
@@ -82,6 +88,8 @@ struct bfuse_context {
   int *d_status;
   int *h_status;  // pinned mirror: the host-buffer entry points read the status word with the output copies
   EncodeTiledFn encode;
+  bool no_pdl;     // diagnostic switch: launch without programmatic dependent launch
+  std::vector<cudaEvent_t> batch_events;  // reused by bfuse_run_fuse_batch (two per pair)
   PairEntry pairs[kNumOps][kNumOps];
   SingleEntry singles[kNumOps];
   std::vector<std::unique_ptr<KernelRec>> kernels;
@@ -113,15 +121,6 @@ bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 int conv_out(int in, int k, int stride, int pad) { return (in + 2 * pad - k) / stride + 1; }
 
 // ---- default tilings (what the reference reads back from TVM, configure_kernels.py:73-99) --------
-
-int pick_row_threads(int cols, int vec_elems, int max_vec) {
-  // smallest power-of-two thread count per row (>= 32) that keeps <= 4 vectors per thread
-  for (int tpr = 32; tpr <= 256; tpr *= 2)
-    if (cols % (vec_elems * tpr) == 0 && cols / (vec_elems * tpr) <= std::min(4, max_vec)) return tpr;
-  for (int tpr = 256; tpr >= 1; tpr /= 2)
-    if (cols % (vec_elems * tpr) == 0 && cols / (vec_elems * tpr) <= max_vec) return tpr;
-  return 0;
-}
 
 int umma_min_stages(int bn, int split, int elem, int bm = kUmmaBM) {
   // after the MMAs the ring doubles as the store buffers and, with split > 1, as the receive area
@@ -560,8 +559,19 @@ void fill_rows(bfuse_context *ctx) {
   if constexpr (I + 1 < kNumOps) fill_rows<I + 1>(ctx);
 }
 
-KernelRec *get_kernel(bfuse_context *ctx, int h) {
+KernelRec *get_kernel(bfuse_context *ctx, int h) {   // nullptr for a bad or released handle
   return (ctx && h >= 0 && h < (int)ctx->kernels.size()) ? ctx->kernels[h].get() : nullptr;
+}
+GroupRec *get_group(const bfuse_context *ctx, int h) {
+  return (ctx && h >= 0 && h < (int)ctx->groups.size()) ? ctx->groups[h].get() : nullptr;
+}
+// first released slot of a handle table, else a new one at the end
+template <class T>
+int free_slot(std::vector<std::unique_ptr<T>> &v) {
+  for (size_t i = 0; i < v.size(); ++i)
+    if (!v[i]) return (int)i;
+  v.emplace_back();
+  return (int)v.size() - 1;
 }
 FusionRec *get_fusion(const bfuse_context *ctx, int h) {
   return (ctx && h >= 0 && h < (int)ctx->fusions.size()) ? ctx->fusions[h].get() : nullptr;
@@ -578,6 +588,7 @@ DispatchTable single_table(const bfuse_context *ctx, const KernelRec &k) {
   t.total = t.n_cta[0];
   t.cluster = k.cluster;
   t.status = ctx->d_status;
+  t.no_pdl = ctx->no_pdl;
   return t;
 }
 
@@ -625,6 +636,12 @@ int launch_fused_rec(bfuse_context *ctx, FusionRec &f, cudaStream_t s, const Dis
   const PairEntry &pe = ctx->pairs[a.desc.op][b.desc.op];
   PairLaunchFn fn = f.plan.table.kind == DISPATCH_THREADS ? pe.thread : (f.wide ? pe.block_wide : pe.block);
   alignas(64) unsigned char pa[kParamsBytes], pb[kParamsBytes];
+  DispatchTable with_switch;
+  if (ctx->no_pdl) {
+    with_switch = table ? *table : f.plan.table;
+    with_switch.no_pdl = 1;
+    table = &with_switch;
+  }
   cudaError_t e = fn(table ? *table : f.plan.table, params_with_stages(a, f.stages[0], pa), params_with_stages(b, f.stages[1], pb), f.launch_grid,
                      (unsigned)f.plan.fused_block, f.smem, s);
   if (e != cudaSuccess) return fail_cuda(ctx, e, ("launch " + f.name).c_str());
@@ -679,6 +696,7 @@ int bfuse_create(int device, bfuse_context **out) {
     return code;
   };
   ctx->device = device;
+  ctx->no_pdl = false;
   cudaDeviceProp prop;
   if (cudaSetDevice(device) != cudaSuccess || cudaGetDeviceProperties(&prop, device) != cudaSuccess) {
     ctx->err = "no usable CUDA device " + std::to_string(device);
@@ -719,7 +737,8 @@ int bfuse_destroy(bfuse_context *ctx) {
   for (auto &g : ctx->graphs)
     if (g.exec) cudaGraphExecDestroy(g.exec);
   for (auto &f : ctx->fusions)
-    if (f->queue_ctr) cudaFree(f->queue_ctr);
+    if (f && f->queue_ctr) cudaFree(f->queue_ctr);
+  for (cudaEvent_t e : ctx->batch_events) cudaEventDestroy(e);
   cudaFree(ctx->d_status);
   cudaFreeHost(ctx->h_status);
   cudaEventDestroy(ctx->ev_fork);
@@ -773,11 +792,13 @@ int bfuse_register_kernel(bfuse_context *ctx, const bfuse_kernel_desc *desc, int
   k->nargs = describe_args(k->desc, k->arg, &err);
   if (k->nargs < 0) return fail(ctx, BFUSE_ERR_INVALID, err);
   if (desc->nargs != k->nargs) return fail(ctx, BFUSE_ERR_INVALID, k->name + ": wrong number of arguments for this operator");
+  k->alias_of = -1;
+  k->users = 0;
   cudaSetDevice(ctx->device);
   const int rc = build_params(ctx, *k);
   if (rc) return rc;
-  ctx->kernels.push_back(std::move(k));
-  *kernel = (int)ctx->kernels.size() - 1;
+  *kernel = free_slot(ctx->kernels);
+  ctx->kernels[*kernel] = std::move(k);
   return BFUSE_OK;
 }
 
@@ -792,15 +813,72 @@ int bfuse_set_kernel_args(bfuse_context *ctx, int kernel, void *const *args, int
   if (rc) {
     std::memcpy(k->desc.args, saved, sizeof(saved));
     build_params(ctx, *k);
+    return rc;
   }
-  return rc;
+  // hidden unsplit re-tilings of this kernel (thread-split / work-queue fusions) follow it
+  for (auto &other : ctx->kernels)
+    if (other && other->alias_of == kernel) {
+      std::memcpy(other->desc.args, k->desc.args, sizeof(saved));
+      const int rc2 = build_params(ctx, *other);
+      if (rc2) return rc2;
+    }
+  return BFUSE_OK;
 }
 
 int bfuse_register_fusion(bfuse_context *ctx, int kernel1, int kernel2, int pattern, int param_m, int param_n, int *fusion) {
   KernelRec *a = get_kernel(ctx, kernel1), *b = get_kernel(ctx, kernel2);
   if (!a || !b || !fusion) return fail(ctx, BFUSE_ERR_INVALID, "bad kernel handle");
+  if (a->alias_of >= 0 || b->alias_of >= 0) return fail(ctx, BFUSE_ERR_INVALID, "bad kernel handle");
   std::unique_ptr<FusionRec> f(new FusionRec());
-  f->k1 = kernel1, f->k2 = kernel2;
+  f->k1 = f->reg1 = kernel1, f->k2 = f->reg2 = kernel2;
+  f->retiled[0] = f->retiled[1] = false;
+  f->users = 0;
+  // Thread split and the work queue cannot host operators launched as clusters (a cluster's CTAs must
+  // start together; a persistent CTA or a thread range is no cluster).  An operator whose tiling splits
+  // K over a cluster is therefore re-tiled with one k-slice for such a fusion -- a hidden kernel record
+  // owned by the fusion, same buffers and tile width -- and the fusion's record says so.  Every launch
+  // mode of this fusion (fused, sequential, parallel) then uses the unsplit tiling, so fused == unfused
+  // still holds bit for bit within the fusion; the k-split kernel launched by its own handle sums in a
+  // different order.
+  struct Undo {   // hidden records are dropped again if the registration fails further down
+    bfuse_context *c;
+    int h[2] = {-1, -1};
+    bool keep = false;
+    ~Undo() {
+      for (int x : h)
+        if (x >= 0 && !keep) c->kernels[x].reset();
+    }
+  } undo{ctx};
+  if (pattern == PATTERN_THREAD_SPLIT || pattern == PATTERN_WORK_QUEUE) {
+    KernelRec **side[2] = {&a, &b};
+    int *handle[2] = {&f->k1, &f->k2};
+    for (int i = 0; i < 2; ++i) {
+      KernelRec *orig = *side[i];
+      if (orig->cluster <= 1) continue;
+      std::unique_ptr<KernelRec> alt(new KernelRec(*orig));
+      const bool conv = orig->desc.op == BFUSE_OP_CONV2D_TF32;
+      alt->desc.shape[conv ? 10 : 5] = 1;
+      if (!conv) alt->desc.shape[6] = 0;   // tile height: the runtime's choice for the unsplit form
+      alt->desc.KernelName = nullptr;
+      std::string err;
+      int rc = default_launch(ctx, &alt->desc, &err);
+      if (rc) return fail(ctx, rc, orig->name + " (re-tiled with one k-slice): " + err);
+      alt->dims = {alt->desc.GridDim.X, alt->desc.GridDim.Y, alt->desc.GridDim.Z, alt->desc.BlockDim.X, alt->desc.BlockDim.Y, alt->desc.BlockDim.Z};
+      alt->smem = alt->desc.smem_bytes;
+      alt->alias_of = *handle[i];
+      alt->users = 0;
+      rc = build_params(ctx, *alt);
+      if (rc) return rc;
+      const int slot = free_slot(ctx->kernels);
+      ctx->kernels[slot] = std::move(alt);
+      undo.h[i] = slot;
+      *handle[i] = slot;
+      *side[i] = ctx->kernels[slot].get();
+      f->retiled[i] = true;
+    }
+    // free_slot may have grown the table: the unique_ptrs moved, the records they own did not
+    a = ctx->kernels[f->k1].get(), b = ctx->kernels[f->k2].get();
+  }
   const KernelDims kd[2] = {a->dims, b->dims};
   if (pattern == PATTERN_SM_STRIPED && param_m == 0) param_m = ctx->sm_count;
   if (pattern != PATTERN_SM_STRIPED && pattern != PATTERN_THREAD_SPLIT && pattern != PATTERN_RANGE_SPLIT) {
@@ -811,8 +889,6 @@ int bfuse_register_fusion(bfuse_context *ctx, int kernel1, int kernel2, int patt
   const int cluster = std::max(a->cluster, b->cluster);
   if ((a->cluster != 1 && a->cluster != cluster) || (b->cluster != 1 && b->cluster != cluster))
     return fail(ctx, BFUSE_ERR_UNSUPPORTED, "the two operators need different cluster widths; register them with equal splits");
-  if (cluster > 1 && (pattern == PATTERN_THREAD_SPLIT || pattern == PATTERN_WORK_QUEUE))
-    return fail(ctx, BFUSE_ERR_UNSUPPORTED, "thread split and the work queue cannot host operators launched as clusters (register the GEMM with split = 1)");
   std::string err;
   if (!plan_pair(kd, pattern, param_m, param_n, param_m, &f->plan, &err, cluster)) return fail(ctx, BFUSE_ERR_INVALID, err);
   DispatchTable &t = f->plan.table;
@@ -902,8 +978,10 @@ int bfuse_register_fusion(bfuse_context *ctx, int kernel1, int kernel2, int patt
     CK(cudaMemset(f->queue_ctr, 0, 2 * sizeof(unsigned)));
     t.queue_ctr = f->queue_ctr;
   }
-  ctx->fusions.push_back(std::move(f));
-  *fusion = (int)ctx->fusions.size() - 1;
+  undo.keep = true;
+  ++ctx->kernels[f->reg1]->users, ++ctx->kernels[f->reg2]->users;
+  *fusion = free_slot(ctx->fusions);
+  ctx->fusions[*fusion] = std::move(f);
   return BFUSE_OK;
 }
 
@@ -917,7 +995,7 @@ int bfuse_register_group(bfuse_context *ctx, const int *kernels, int n, int patt
   int cluster = 1;
   for (int i = 0; i < n; ++i) {
     ks[i] = get_kernel(ctx, kernels[i]);
-    if (!ks[i]) return fail(ctx, BFUSE_ERR_INVALID, "bad kernel handle");
+    if (!ks[i] || ks[i]->alias_of >= 0) return fail(ctx, BFUSE_ERR_INVALID, "bad kernel handle");
     if (ks[i]->desc.op != ks[0]->desc.op) return fail(ctx, BFUSE_ERR_UNSUPPORTED, "the kernels of a group must share one operator body");
     g->ks[i] = kernels[i];
     kd[i] = ks[i]->dims;
@@ -968,13 +1046,14 @@ int bfuse_register_group(bfuse_context *ctx, const int *kernels, int n, int patt
   cudaError_t e = ctx->singles[ks[0]->desc.op].group_attr(&attr);
   if (e != cudaSuccess) return fail_cuda(ctx, e, "cudaFuncGetAttributes");
   g->regs = attr.numRegs;
-  ctx->groups.push_back(std::move(g));
-  *group = (int)ctx->groups.size() - 1;
+  for (int i = 0; i < n; ++i) ++ks[i]->users;
+  *group = free_slot(ctx->groups);
+  ctx->groups[*group] = std::move(g);
   return BFUSE_OK;
 }
 
 int bfuse_group_info(bfuse_context *ctx, int group, bfuse_kernel_desc *out) {
-  if (!ctx || group < 0 || group >= (int)ctx->groups.size() || !out) return fail(ctx, BFUSE_ERR_INVALID, "bad group handle");
+  if (!get_group(ctx, group) || !out) return fail(ctx, BFUSE_ERR_INVALID, "bad group handle");
   const GroupRec &g = *ctx->groups[group];
   std::memset(out, 0, sizeof(*out));
   out->KernelName = g.name.c_str();
@@ -990,7 +1069,7 @@ int bfuse_group_info(bfuse_context *ctx, int group, bfuse_kernel_desc *out) {
 }
 
 int bfuse_group_map_block(const bfuse_context *ctx, int group, int b, int *kernel, int *vblock) {
-  if (!ctx || group < 0 || group >= (int)ctx->groups.size() || !kernel || !vblock || b < 0) return BFUSE_ERR_INVALID;
+  if (!get_group(ctx, group) || !kernel || !vblock || b < 0) return BFUSE_ERR_INVALID;
   const GroupRec &g = *ctx->groups[group];
   int k, vb;
   if (b >= g.plan.fused_grid || !decode_group_cta(g.plan.table, b, k, vb)) return BFUSE_ERR_INVALID;
@@ -999,12 +1078,13 @@ int bfuse_group_map_block(const bfuse_context *ctx, int group, int b, int *kerne
 }
 
 int bfuse_launch_group(bfuse_context *ctx, int group, void *stream) {
-  if (!ctx || group < 0 || group >= (int)ctx->groups.size()) return fail(ctx, BFUSE_ERR_INVALID, "bad group handle");
+  if (!get_group(ctx, group)) return fail(ctx, BFUSE_ERR_INVALID, "bad group handle");
   GroupRec &g = *ctx->groups[group];
   alignas(64) unsigned char scratch[kGroupMax][kParamsBytes];
   const void *params[kGroupMax];
   for (int i = 0; i < g.n; ++i) params[i] = params_with_stages(*ctx->kernels[g.ks[i]], g.stages[i], scratch[i]);
   const KernelRec &k0 = *ctx->kernels[g.ks[0]];
+  g.plan.table.no_pdl = ctx->no_pdl;
   cudaError_t e = ctx->singles[k0.desc.op].group(g.plan.table, params, g.n, (unsigned)g.plan.fused_grid,
                                                  (unsigned)g.plan.fused_block, g.smem, (cudaStream_t)stream);
   if (e != cudaSuccess) return fail_cuda(ctx, e, ("launch " + g.name).c_str());
@@ -1045,6 +1125,9 @@ int bfuse_fusion_info(bfuse_context *ctx, int fusion, bfuse_kernel_desc *out) {
   // CTAs of this kernel resident at once according to the occupancy calculator (whole clusters; one CTA per SM
   // for kernels that allocate tensor memory), 0 when not asked
   out->shape[1] = 0;
+  // operator 1 / 2 runs here in a one-k-slice re-tiling of the registered kernel (thread split, work queue)
+  out->shape[2] = f->retiled[0] ? 1 : 0;
+  out->shape[3] = f->retiled[1] ? 1 : 0;
   if (f->plan.table.kind != DISPATCH_THREADS && !f->wide) {
     const int cl = std::max(1, f->plan.table.cluster);
     cudaSetDevice(ctx->device);
@@ -1124,17 +1207,72 @@ int bfuse_graph_create(bfuse_context *ctx, const int *fusions, int n, int mode, 
     return rc;
   }
   if (e != cudaSuccess) return fail_cuda(ctx, e, "cudaStreamEndCapture");
-  GraphRec gr{nullptr, n * (mode == 2 || mode == 3 ? 2 : 1)};
+  GraphRec gr{nullptr, n * (mode == 2 || mode == 3 ? 2 : 1), std::vector<int>(fusions, fusions + n)};
   e = cudaGraphInstantiate(&gr.exec, g, 0);
   cudaGraphDestroy(g);
   if (e != cudaSuccess) return fail_cuda(ctx, e, "cudaGraphInstantiate");
-  ctx->graphs.push_back(gr);
-  *graph = (int)ctx->graphs.size() - 1;
+  for (int h : gr.fusions) ++ctx->fusions[h]->users;
+  int slot = -1;
+  for (size_t i = 0; i < ctx->graphs.size() && slot < 0; ++i)
+    if (!ctx->graphs[i].exec) slot = (int)i;
+  if (slot < 0) {
+    ctx->graphs.emplace_back();
+    slot = (int)ctx->graphs.size() - 1;
+  }
+  ctx->graphs[slot] = std::move(gr);
+  *graph = slot;
+  return BFUSE_OK;
+}
+
+int bfuse_graph_destroy(bfuse_context *ctx, int graph) {
+  if (!ctx || graph < 0 || graph >= (int)ctx->graphs.size() || !ctx->graphs[graph].exec) return fail(ctx, BFUSE_ERR_INVALID, "bad graph handle");
+  cudaSetDevice(ctx->device);
+  GraphRec &g = ctx->graphs[graph];
+  CK(cudaGraphExecDestroy(g.exec));
+  g.exec = nullptr;
+  for (int h : g.fusions)
+    if (FusionRec *f = get_fusion(ctx, h)) --f->users;
+  g.fusions.clear();
+  return BFUSE_OK;
+}
+
+// ---- release (finalize_kernel1/2 of the reference harness, operation_cu.py:146-162) ------------------
+
+int bfuse_unregister_fusion(bfuse_context *ctx, int fusion) {
+  FusionRec *f = get_fusion(ctx, fusion);
+  if (!f) return fail(ctx, BFUSE_ERR_INVALID, "bad fusion handle");
+  if (f->users > 0) return fail(ctx, BFUSE_ERR_INVALID, f->name + ": still captured by a graph; destroy the graph first");
+  cudaSetDevice(ctx->device);
+  if (f->queue_ctr) {
+    // the counters may still be in use by a launch in flight
+    CK(cudaDeviceSynchronize());
+    CK(cudaFree(f->queue_ctr));
+  }
+  if (f->retiled[0]) ctx->kernels[f->k1].reset();
+  if (f->retiled[1]) ctx->kernels[f->k2].reset();
+  --ctx->kernels[f->reg1]->users, --ctx->kernels[f->reg2]->users;
+  ctx->fusions[fusion].reset();
+  return BFUSE_OK;
+}
+
+int bfuse_unregister_group(bfuse_context *ctx, int group) {
+  GroupRec *g = get_group(ctx, group);
+  if (!g) return fail(ctx, BFUSE_ERR_INVALID, "bad group handle");
+  for (int i = 0; i < g->n; ++i) --ctx->kernels[g->ks[i]]->users;
+  ctx->groups[group].reset();
+  return BFUSE_OK;
+}
+
+int bfuse_unregister_kernel(bfuse_context *ctx, int kernel) {
+  KernelRec *k = get_kernel(ctx, kernel);
+  if (!k || k->alias_of >= 0) return fail(ctx, BFUSE_ERR_INVALID, "bad kernel handle");
+  if (k->users > 0) return fail(ctx, BFUSE_ERR_INVALID, k->name + ": still used by a fusion or group; release those first");
+  ctx->kernels[kernel].reset();
   return BFUSE_OK;
 }
 
 int bfuse_graph_launch(bfuse_context *ctx, int graph, void *stream) {
-  if (!ctx || graph < 0 || graph >= (int)ctx->graphs.size()) return BFUSE_ERR_INVALID;
+  if (!ctx || graph < 0 || graph >= (int)ctx->graphs.size() || !ctx->graphs[graph].exec) return BFUSE_ERR_INVALID;
   CK(cudaGraphLaunch(ctx->graphs[graph].exec, (cudaStream_t)stream));
   return BFUSE_OK;
 }
@@ -1219,23 +1357,43 @@ int bfuse_debug_gemm_timeline(bfuse_context *ctx, int kernel, long long *marks, 
   return BFUSE_OK;
 }
 
+// After a bounded wait gave up, a persistent launch may have left its ticket counters non-zero (the
+// last CTA to drain resets them, and a CTA that bailed out may have skipped tickets): every later
+// launch of that fusion would then find the queue "empty" and do nothing.  Start them from zero again.
+static void reset_queue_counters(bfuse_context *ctx) {
+  for (auto &f : ctx->fusions)
+    if (f && f->queue_ctr) cudaMemset(f->queue_ctr, 0, 2 * sizeof(unsigned));
+}
+
 int bfuse_read_status(bfuse_context *ctx, int *status) {
   if (!ctx || !status) return BFUSE_ERR_INVALID;
   cudaSetDevice(ctx->device);
   CK(cudaDeviceSynchronize());
   CK(cudaMemcpy(status, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost));
-  if (*status) CK(cudaMemset(ctx->d_status, 0, sizeof(int)));
+  if (*status) {
+    CK(cudaMemset(ctx->d_status, 0, sizeof(int)));
+    reset_queue_counters(ctx);
+  }
+  return BFUSE_OK;
+}
+
+int bfuse_set_dependent_launch(bfuse_context *ctx, int enabled) {
+  if (!ctx) return BFUSE_ERR_INVALID;
+  ctx->no_pdl = !enabled;
   return BFUSE_OK;
 }
 
 // ---- host-buffer entry points (H2D, launch, sync, D2H) --------------------------------------------
 
 static int copy_in(bfuse_context *ctx, KernelRec &k, void *const *host, cudaStream_t s) {
-  for (int i = 0; i < k.nargs; ++i)
-    if (!k.arg[i].is_output && k.desc.args[i]) {
-      if (!host[i]) return fail(ctx, BFUSE_ERR_INVALID, k.name + ": missing host input buffer");
-      CK(cudaMemcpyAsync(k.desc.args[i], host[i], k.arg[i].bytes, cudaMemcpyHostToDevice, s));
-    }
+  // small buffers (bias, per-column tables) first: each copy pays a fixed few microseconds, which
+  // then overlap the previous pair's large transfer instead of trailing this pair's
+  for (int pass = 0; pass < 2; ++pass)
+    for (int i = 0; i < k.nargs; ++i)
+      if (!k.arg[i].is_output && k.desc.args[i] && (k.arg[i].bytes <= 65536) == (pass == 0)) {
+        if (!host[i]) return fail(ctx, BFUSE_ERR_INVALID, k.name + ": missing host input buffer");
+        CK(cudaMemcpyAsync(k.desc.args[i], host[i], k.arg[i].bytes, cudaMemcpyHostToDevice, s));
+      }
   return BFUSE_OK;
 }
 static int copy_out(bfuse_context *ctx, KernelRec &k, void *const *host, cudaStream_t s) {
@@ -1253,6 +1411,7 @@ static int finish(bfuse_context *ctx, cudaStream_t s) {
   const int st = *ctx->h_status;
   if (st) {
     cudaMemset(ctx->d_status, 0, sizeof(int));
+    reset_queue_counters(ctx);
     char buf[64];
     snprintf(buf, sizeof(buf), "device status 0x%x: a bounded wait gave up", st);
     return fail(ctx, BFUSE_ERR_TIMEOUT, buf);
@@ -1291,10 +1450,14 @@ int bfuse_run_fuse_batch(bfuse_context *ctx, const int *fusions, int n, void *co
   }
   cudaSetDevice(ctx->device);
   // s1 carries the copies in, the context's own stream the launches, s2 the copies out
-  std::vector<cudaEvent_t> ev(2 * (size_t)n, nullptr);
+  // (two events per pair, kept in the context and reused by later calls)
+  std::vector<cudaEvent_t> &ev = ctx->batch_events;
   int rc = BFUSE_OK;
-  for (size_t i = 0; i < ev.size() && !rc; ++i)
-    if (cudaEventCreateWithFlags(&ev[i], cudaEventDisableTiming) != cudaSuccess) rc = fail(ctx, BFUSE_ERR_CUDA, "cudaEventCreate");
+  while (ev.size() < 2 * (size_t)n && !rc) {
+    cudaEvent_t e = nullptr;
+    if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) rc = fail(ctx, BFUSE_ERR_CUDA, "cudaEventCreate");
+    else ev.push_back(e);
+  }
   for (int i = 0; i < n && !rc; ++i) {
     FusionRec &f = *get_fusion(ctx, fusions[i]);
     KernelRec &a = *ctx->kernels[f.k1], &b = *ctx->kernels[f.k2];
@@ -1313,8 +1476,6 @@ int bfuse_run_fuse_batch(bfuse_context *ctx, const int *fusions, int n, void *co
   cudaStreamSynchronize(ctx->s1);
   cudaStreamSynchronize(ctx->own);
   const int rc2 = finish(ctx, ctx->s2);   // status word behind the last copies out, then one synchronisation
-  for (cudaEvent_t e : ev)
-    if (e) cudaEventDestroy(e);
   return rc ? rc : rc2;
 }
 int bfuse_run_parallel(bfuse_context *ctx, int fusion, void *const *h1, void *const *h2) { return run_pair(ctx, fusion, h1, h2, 2); }

@@ -33,6 +33,18 @@ struct FusedPlan {
 
 inline int round_up32(int x) { return (x + 31) / 32 * 32; }
 
+// Threads per row of the row-wise bodies' default tiling: the smallest power of two (>= 32) that
+// keeps at most 4 vectors of `vec_elems` elements per thread, else the largest one within the
+// body's per-thread budget of `max_vec` vectors; 0 when cols cannot be tiled.  One definition for the
+// registered path and the allocation-free entry point, whose outputs must stay bit-identical.
+inline int pick_row_threads(int cols, int vec_elems, int max_vec) {
+  for (int tpr = 32; tpr <= 256; tpr *= 2)
+    if (cols % (vec_elems * tpr) == 0 && cols / (vec_elems * tpr) <= (max_vec < 4 ? max_vec : 4)) return tpr;
+  for (int tpr = 256; tpr >= 1; tpr /= 2)
+    if (cols % (vec_elems * tpr) == 0 && cols / (vec_elems * tpr) <= max_vec) return tpr;
+  return 0;
+}
+
 // Returns false and sets err on invalid input.  For PATTERN_WORK_QUEUE the table describes the
 // ticket order (zig-zag param_m : param_n); the caller sizes the persistent grid.
 // cluster > 1 schedules units of `cluster` consecutive CTAs (see decode_cta in dispatch.h).

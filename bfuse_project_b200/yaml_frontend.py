@@ -63,7 +63,9 @@ def fuse_records(kernels, fusions, block_level=True, pattern=None, param_m=1, pa
                 raise KeyError("fusion refers to unknown kernel %s" % n)
         dims = [list(kernels[n]["GridDim"]) + list(kernels[n]["BlockDim"]) for n in names]
         plan = Plan(dims, pattern, param_m, param_n)
-        name = "_".join(kernels[n]["KernelName"] for n in names) + suffix
+        # the fused name is built from the kernels.yaml map keys listed in the fusion, not from the KernelName
+        # fields (horizontal-fuser/src/Contexts.cc:67-84: FusedKernelName += KName + '_')
+        name = "_".join(names) + suffix
         out[name] = {"KernelName": name, "HasBarriers": True, "GridDim": plan.fused_grid, "BlockDim": plan.fused_block,
                      "Reg": 32, "ExecTime": -1.0}
     return out
@@ -72,7 +74,7 @@ def fuse_records(kernels, fusions, block_level=True, pattern=None, param_m=1, pa
 def dump_kernels(records, path):
     """Write records in the reference's output schema (ExecTime omitted at its default, as llvm::yaml does)."""
     doc = {}
-    for name, r in records.items():
+    for name, r in sorted(records.items()):   # the reference keeps its records in a std::map: written sorted by name
         e = {"KernelName": r["KernelName"], "HasBarriers": bool(r["HasBarriers"]),
              "GridDim": dict(zip("XYZ", (int(v) for v in r["GridDim"]))),
              "BlockDim": dict(zip("XYZ", (int(v) for v in r["BlockDim"]))), "Reg": int(r["Reg"])}

@@ -114,6 +114,15 @@ int bfuse_arg_info(const bfuse_context *ctx, const bfuse_kernel_desc *desc, int 
 int bfuse_register_kernel(bfuse_context *ctx, const bfuse_kernel_desc *desc, int *kernel);
 /* Rebind the device buffers of a registered kernel (same shapes). */
 int bfuse_set_kernel_args(bfuse_context *ctx, int kernel, void *const *args, int nargs);
+/* Release a kernel / fusion / group (finalize_kernel1/2 of the reference harness,
+ * test-utils/test-suite-files/operation_cu.py:146-162): frees what the runtime holds for it (records,
+ * work-queue counters) and makes the handle invalid; later registrations may reuse it.  The caller's
+ * buffers are untouched.  Order: graphs that captured a fusion first (bfuse_graph_destroy), then
+ * fusions and groups, then their kernels; out of order returns BFUSE_ERR_INVALID and releases nothing.
+ * Releasing a work-queue fusion synchronises the device. */
+int bfuse_unregister_kernel(bfuse_context *ctx, int kernel);
+int bfuse_unregister_fusion(bfuse_context *ctx, int fusion);
+int bfuse_unregister_group(bfuse_context *ctx, int group);
 
 /* fusions.yaml entry {Kernels: [k1, k2]} + pattern -> fused handle: the work of fuse::bfuse /
  * fuse::hfuse (horizontal-fuser/include/fuse/Fuse.h:43-49, src/Fuse.cc:64-221,223-376). */
@@ -123,6 +132,11 @@ int bfuse_register_fusion(bfuse_context *ctx, int kernel1, int kernel2, int patt
  * name "<k1>_<k2>_fused_{bfuse,hfuse}", fused GridDim / BlockDim, plus smem and registers;
  * shape[0] = CTAs launched, shape[1] = CTAs of the kernel resident at once according to cudaOccupancyMaxActiveClusters,
  * which counts one CTA per SM for kernels that allocate tensor memory (0: not asked).
+ * shape[2] / shape[3] = 1 when kernel 1 / 2 runs in this fusion with ONE k-slice although it was
+ * registered with several: BFUSE_PATTERN_THREAD_SPLIT and BFUSE_PATTERN_WORK_QUEUE cannot host
+ * operators launched as thread-block clusters, so such an operator is re-tiled unsplit for the fusion
+ * (all launch modes of the fusion use that tiling; its sums differ in the last bits from the k-split
+ * kernel launched through its own handle).
  * out->KernelName points into the context and stays valid until bfuse_destroy. */
 int bfuse_fusion_info(bfuse_context *ctx, int fusion, bfuse_kernel_desc *out);
 /* Which operator and virtual block CTA (or queue ticket) b runs: the if / else-if chain the
@@ -164,6 +178,7 @@ int bfuse_launch_list(bfuse_context *ctx, const int *fusions, int n, int mode, v
  * kernels last a few microseconds the per-launch host cost otherwise dominates. */
 int bfuse_graph_create(bfuse_context *ctx, const int *fusions, int n, int mode, int *graph);
 int bfuse_graph_launch(bfuse_context *ctx, int graph, void *stream);
+int bfuse_graph_destroy(bfuse_context *ctx, int graph);
 /* Run the fused grid with a recording body: per CTA the operator, virtual block and SM id it saw
  * (the %smid printf of legacy/tests/thread_pooling_test/temp2.cu:7-9, as data).  Arrays hold
  * fused-grid entries; for WORK_QUEUE they are indexed by ticket.  Synchronises. */
@@ -180,8 +195,14 @@ int bfuse_debug_gemm_timeline(bfuse_context *ctx, int kernel, long long *marks, 
  * the body done.  times holds 3 * sum(slots) values,
  * launch i's slots[i] >= its fused grid entries first to last; unused entries stay 0.  Synchronises. */
 int bfuse_debug_fused_timeline(bfuse_context *ctx, const int *fusions, int n, long long *times, const int *slots);
-/* Read and clear the device status word (0 = no bounded wait gave up). Synchronises. */
+/* Read and clear the device status word (0 = no bounded wait gave up). Synchronises.  A non-zero
+ * status also restarts the ticket counters of every work-queue fusion from zero. */
 int bfuse_read_status(bfuse_context *ctx, int *status);
+/* Diagnostic, no reference counterpart: enabled = 0 makes every later launch of this context go
+ * without the programmatic-dependent-launch attribute (a kernel's CTAs then start only when the
+ * previous kernel on the stream has finished), to tell that overlap's effect on a timeline from
+ * everything else.  Default: enabled. */
+int bfuse_set_dependent_launch(bfuse_context *ctx, int enabled);
 
 /* Host-buffer entry points with the reference harness' semantics: H2D of every input, launch,
  * device sync, D2H of every output.  host_args follow each kernel's argument order; pointers for

@@ -219,7 +219,9 @@ def yaml_dims(ref, suite):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("BFUSE_REFERENCE_DIR", "")
+    if not os.path.isdir(os.path.join(ref, "tests", "benchmark", "cuda")):
+        sys.exit("usage: make_dispatch_golden.py <reference checkout>   (or set BFUSE_REFERENCE_DIR)")
     out = {"source": "parsed from the reference's generated kernels and YAML outputs; see this script",
            "br_fields": list(BR_FIELDS)}
 

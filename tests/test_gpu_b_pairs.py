@@ -39,6 +39,11 @@ def run_and_check(rt, spec, patterns, check_oracle=True):
             if e.code != 7:   # only "pattern unsupported for clustered operators" may be skipped
                 raise
             continue
+        if any(rt.fusion_info(fusion)["retiled_unsplit"]):
+            # an operator registered with several k-slices runs unsplit under this pattern: its sums differ in
+            # the last bits from the k-split kernel launched alone, so the check is the fusion's own sequential mode
+            check_retiled(rt, pair, pat)
+            continue
         ran.append(pat)
         pair.clear_outputs()
         rt.launch_fused(fusion)
@@ -56,6 +61,24 @@ def run_and_check(rt, spec, patterns, check_oracle=True):
     for k in range(2):
         assert np.array_equal(par[k][0].view(np.uint8), unfused[k][0].view(np.uint8))
     return pair
+
+
+def check_retiled(rt, pair, pat):
+    """Thread split / work queue with an operator that was registered with several k-slices: the fusion
+    runs a one-k-slice re-tiling of it and says so; within the fusion fused == sequential bit for bit,
+    and the result agrees with the oracle within tolerance."""
+    fusion = pair.fusion(pat, 1, 1)
+    assert any(rt.fusion_info(fusion)["retiled_unsplit"])
+    pair.clear_outputs()
+    rt.launch_sequential(fusion)
+    seq = pair.read_outputs()
+    pair.clear_outputs()
+    rt.launch_fused(fusion)
+    fused = pair.read_outputs()
+    assert rt.read_status() == 0
+    for k, ks in enumerate((pair.spec.a, pair.spec.b)):
+        assert np.array_equal(seq[k][0].view(np.uint8), fused[k][0].view(np.uint8)), (bf.PATTERN_NAMES[pat], k)
+        check_against_oracle(ks, fused[k], "%s/%s retiled" % (pair.spec.name, ks.name))
 
 
 @pytest.mark.parametrize("name", ["cfg1_softmax_layernorm", "cfg4c_rmsnorm_rope"])
@@ -171,6 +194,87 @@ def test_rejected_registrations(rt):
     with pytest.raises(bf.BfuseError) as e:
         rt.register_kernel(d)
     assert e.value.code == 3
+
+
+def test_release_of_kernels_fusions_groups_and_graphs(rt):
+    """bfuse_unregister_* / bfuse_graph_destroy (finalize_kernel1/2 of the reference harness): out-of-order
+    releases are refused and release nothing, released handles are dead and get reused, a work-queue
+    fusion's counters are freed (device memory in use returns to where it was), and the caller's buffers
+    and the other registrations are untouched."""
+    import torch
+    spec = wl.make_pair("cfg1_softmax_layernorm", seed=5, scale=0.25)
+    pair = wl.DevicePair(rt, spec)
+    k1, k2 = pair.kernels
+    keep = rt.register_fusion(k1, k2, bf.ZIGZAG, 1, 1)
+    rt.launch_fused(keep)
+    want = pair.read_outputs()
+    torch.cuda.synchronize()
+    queue = rt.register_fusion(k1, k2, bf.WORK_QUEUE, 1, 1)
+    graph = rt.graph_create([queue], bf.MODE_FUSED)
+    with pytest.raises(bf.BfuseError) as e:       # captured by a live graph
+        rt.unregister_fusion(queue)
+    assert e.value.code == 1
+    with pytest.raises(bf.BfuseError) as e:       # used by live fusions
+        rt.unregister_kernel(k1)
+    assert e.value.code == 1
+    pair.clear_outputs()
+    rt.graph_launch(graph)                        # both refusals released nothing
+    got = pair.read_outputs()
+    assert all(np.array_equal(got[k][0], want[k][0]) for k in range(2))
+    rt.graph_destroy(graph)
+    with pytest.raises(bf.BfuseError):
+        rt.graph_launch(graph)
+    rt.unregister_fusion(queue)
+    for call in (rt.launch_fused, rt.fusion_info, rt.unregister_fusion):
+        with pytest.raises(bf.BfuseError) as e:   # the handle is dead
+            call(queue)
+        assert e.value.code == 1
+    # re-registering in a loop does not grow what the runtime holds: handles are reused
+    seen = set()
+    for _ in range(50):
+        f = rt.register_fusion(k1, k2, bf.WORK_QUEUE, 1, 1)
+        seen.add(f)
+        rt.unregister_fusion(f)
+    assert len(seen) == 1
+    # a group pins its kernels the same way
+    pa = wl.DevicePair(rt, wl.make_pair("cfg1_softmax_layernorm", seed=6, scale=0.25))
+    group = rt.register_group([k1, pa.kernels[0]], bf.ZIGZAG, 1, 1)
+    with pytest.raises(bf.BfuseError):
+        rt.unregister_kernel(pa.kernels[0])
+    rt.unregister_group(group)
+    with pytest.raises(bf.BfuseError):
+        rt.launch_group(group)
+    rt.unregister_kernel(pa.kernels[0])
+    with pytest.raises(bf.BfuseError):
+        rt.launch_kernel(pa.kernels[0])
+    # the fusion that was kept still runs and gives the same bits
+    pair.clear_outputs()
+    rt.launch_fused(keep)
+    got = pair.read_outputs()
+    assert rt.read_status() == 0
+    assert all(np.array_equal(got[k][0], want[k][0]) for k in range(2))
+    rt.unregister_fusion(keep)
+    rt.unregister_kernel(k1)
+    rt.unregister_kernel(k2)
+
+
+def test_dependent_launch_switch_changes_no_result(rt):
+    """bfuse_set_dependent_launch(0): launches without programmatic dependent launch write the same bits."""
+    spec = wl.make_pair("cfg3_qkt_res_layernorm", seed=8, scale=0.25)
+    pair = wl.DevicePair(rt, spec)
+    f = pair.fusion(bf.ZIGZAG, 1, 1)
+    rt.launch_fused(f)
+    want = pair.read_outputs()
+    rt.set_dependent_launch(False)
+    try:
+        pair.clear_outputs()
+        rt.launch_fused(f)
+        rt.launch_kernel(pair.kernels[0])
+        got = pair.read_outputs()
+    finally:
+        rt.set_dependent_launch(True)
+    assert rt.read_status() == 0
+    assert all(np.array_equal(got[k][0].view(np.uint8), want[k][0].view(np.uint8)) for k in range(2))
 
 
 def test_run_fuse_batch_matches_one_call_per_pair(rt):

@@ -5,7 +5,7 @@ import pytest
 import bfuse_project_b200 as bf
 from bfuse_project_b200 import workloads as wl
 from pair_oracle import check_against_oracle
-from test_gpu_b_pairs import BLOCK_PATTERNS, run_and_check
+from test_gpu_b_pairs import BLOCK_PATTERNS, check_retiled, run_and_check
 
 pytestmark = pytest.mark.gpu
 
@@ -85,10 +85,9 @@ def test_split_gemm_with_unsplit_partner_and_unsupported_patterns(rt):
     a = wl.gemm("g1", rng, bf.OP_GEMM_TF32, 1, 256, 256, 256, w_std=1.0, bn=256, split=4)
     b = wl.layernorm("ln", rng, 100, 768, 1e-5, residual=True)   # 25 CTAs: clusters of 4 get padding CTAs
     pair = run_and_check(rt, wl.PairSpec("split_ln", a, b, "tf32", "hbm"), [(bf.ZIGZAG, 1, 1), (bf.RANGE_SPLIT, 0, 0)])
-    for pat in (bf.THREAD_SPLIT, bf.WORK_QUEUE):
-        with pytest.raises(bf.BfuseError) as e:
-            pair.fusion(pat, 1, 1)
-        assert e.value.code == 7
+    assert rt.fusion_info(pair.fusion(bf.ZIGZAG, 1, 1))["retiled_unsplit"] == (False, False)
+    for pat in (bf.THREAD_SPLIT, bf.WORK_QUEUE):   # no clusters there: the GEMM runs with one k-slice instead
+        check_retiled(rt, pair, pat)
     c = wl.gemm("g3", rng, bf.OP_GEMM_TF32, 1, 256, 256, 256, w_std=1.0, bn=256, split=2)
     mixed = wl.DevicePair(rt, wl.PairSpec("mixed", a, c, "tf32", "hbm"))
     with pytest.raises(bf.BfuseError) as e:   # different cluster widths cannot share a launch
@@ -198,9 +197,7 @@ def test_conv_split_k_over_a_cluster(rt):
     pair = run_and_check(rt, wl.PairSpec("conv_auto_split", c, d, "tf32", "hbm"), [(bf.ZIGZAG, 1, 1), (bf.SM_STRIPED, 0, 0)])
     assert pair.spec.a.launch[0][0] > 2                      # more CTAs along x than the 2 pixel tiles: K was split
     for pat in (bf.THREAD_SPLIT, bf.WORK_QUEUE):
-        with pytest.raises(bf.BfuseError) as e:
-            pair.fusion(pat, 1, 1)
-        assert e.value.code == 7
+        check_retiled(rt, pair, pat)
 
 
 def test_conv_pixel_tile_widths(rt):

@@ -87,3 +87,22 @@ def test_gpu_trace_csv_round_trip_in_the_reference_layout(tmp_path):
     assert len(back) == 10 and back[4] == (0.004, 0.008004, "a_b_fused_bfuse")
     kept = [d for i, (_, d, n) in enumerate(back) if n == "a_b_fused_bfuse" and i >= 3]
     assert abs(sum(kept) / len(kept) - (8000 + 6.0) / 1e6) < 1e-12
+
+
+def test_fused_names_come_from_the_map_keys_and_records_are_sorted(tmp_path):
+    """The reference builds a fused name from the kernels.yaml map keys a fusion lists, not from the
+    KernelName fields (Contexts.cc:67-84), and writes its records sorted by name (a std::map)."""
+    from bfuse_project_b200 import yaml_frontend as yf
+    dims = {"GridDim": {"X": 8, "Y": 1, "Z": 1}, "BlockDim": {"X": 128, "Y": 1, "Z": 1}, "Reg": 32, "HasBarriers": True}
+    kernels = {"zeta": dict(dims, KernelName="real_kernel_z"), "alpha": dict(dims, KernelName="real_kernel_a"),
+               "mid": dict(dims, KernelName="real_kernel_m")}
+    kp, fp, out = (str(tmp_path / n) for n in ("kernels.yaml", "fusions.yaml", "bfuse_kernels.yaml"))
+    with open(kp, "w") as f:
+        yaml.safe_dump(kernels, f)
+    with open(fp, "w") as f:
+        yaml.safe_dump([{"File": "k.cu", "Kernels": ["zeta", "alpha"]}, {"File": "k.cu", "Kernels": ["alpha", "mid"]}], f)
+    recs = yf.fuse_records(yf.load_kernels(kp), yf.load_fusions(fp), block_level=True)
+    assert set(recs) == {"zeta_alpha_fused_bfuse", "alpha_mid_fused_bfuse"}
+    yf.dump_kernels(recs, out)
+    names = [ln[:-1] for ln in open(out).read().splitlines() if ln.endswith("_fused_bfuse:")]
+    assert names == ["alpha_mid_fused_bfuse", "zeta_alpha_fused_bfuse"]
