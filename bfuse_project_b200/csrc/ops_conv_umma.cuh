@@ -5,13 +5,25 @@
 //
 // A tile is 128 output channels x BN output pixels of one image (BN = 128, or 64 / 32 for small
 // images, so that a single image still spreads over many SMs).  The weight operand is K-major in
-// global memory and arrives by TMA (128B swizzle).  The im2col operand does not exist in memory:
-// the four epilogue warps, idle during the main loop, gather it (128 / BN threads per output pixel,
-// 32 values of k per pixel and stage) with 4-byte cp.async copies straight into the swizzled K-major layout the
-// MMA expects (out-of-image taps are zero-filled by the copy itself), and each thread's
-// cp.async.mbarrier.arrive makes the stage's "full" barrier fire when its copies have landed, so
-// the gather runs several stages ahead of the tensor core.  Per-k input offsets and tap coordinates
-// are tabulated once per CTA in shared memory, so the gather does no divisions.
+// global memory and arrives by TMA (128B swizzle).  The im2col operand does not exist in memory; the
+// four epilogue warps, idle during the main loop, build it in the swizzled K-major layout the MMA
+// expects (128 / BN threads per output pixel, 32 values of k per pixel and stage), in one of two ways:
+//
+//   staged (image rows of 16-byte multiples): the input rows a tile needs -- every row its output
+//     pixels' windows touch, full width, a few channels at a time -- arrive by tiled TMA loads over
+//     the NCHW tensor into a ring of raw slots (padding is the TMA's out-of-bounds zero fill; a
+//     one-row window with a stride loads only the rows it uses through the map's element stride),
+//     and the warps repack shared memory -> shared memory: per 16-byte chunk of a pixel's row one
+//     16-byte table read (four byte offsets), four 4-byte reads of the raw slot and one 16-byte
+//     store.  A direct TMA load of the taps is not possible: a tap's first column is  dx - pad, and a
+//     tiled TMA copy must start at a multiple of 16 bytes;
+//   gathered (any other row length): 4-byte cp.async copies from global memory straight into the
+//     operand (out-of-image taps zero-filled by the copy), bound by the issue rate of those copies --
+//     about four times slower per K block than the staged form.
+//
+// Either way the stage's "full" barrier fires when the weights have landed and every repack thread has
+// arrived, so the operand is built several stages ahead of the tensor core.  Per-k offsets are
+// tabulated once per CTA in shared memory, so neither loop divides.
 //
 // A long K (deep layers on small images leave few tiles) can be split over the CTAs of a cluster,
 // reduced through distributed shared memory like the GEMM's k-slices.
@@ -29,13 +41,68 @@ constexpr int kConvMaxK = 8192;              // ci * kh * kw the offset table ma
 // index dy*kw+dx} per k, K rounded up to whole K blocks (tap 31 = padding) and to 1 KB
 __host__ __device__ constexpr int conv_header_bytes(int K) { return kUmmaHeaderBytes + ((K + 31) / 32 * 32 * 8 + 1023) / 1024 * 1024; }
 __host__ __device__ constexpr int conv_stage_bytes(int bn = kConvBN) { return kUmmaABytes + bn * kUmmaRowBytes; }
-__host__ __device__ constexpr int conv_umma_smem_bytes(int stages, int bn, int K) {
-  return conv_header_bytes(K) + stages * conv_stage_bytes(bn);
+// operator window: header (barriers, offset table), the raw ring of a staged conv, then the operand ring
+__host__ __device__ constexpr int conv_umma_smem_bytes(int stages, int bn, int K, int raw_bytes = 0) {
+  return conv_header_bytes(K) + raw_bytes + stages * conv_stage_bytes(bn);
+}
+
+constexpr int kConvMaxRawSlots = 4;
+constexpr int kConvRawBarOffset = 256;   // byte offset of the raw ring's barriers in the header: full[4], then empty[4]
+constexpr int kConvZeroOffset = 512;     // 16 bytes of zeros in the header: what the repack reads for k >= K
+
+// Geometry of the raw-input staging of a conv (shared by the host, which sizes shared memory and
+// encodes the tensor map, and the kernel).  A slot holds `cc` channels x `rows` staged rows x
+// `pitch` floats; staged row j, column i of a tile is input row y0 + j * ey, column x_start + i * ex,
+// where y0 = (first output row of the tile) * stride - pad.
+struct ConvStaging {
+  int slots;        // ring depth (0: the conv is gathered from global memory instead)
+  int cc;           // channels per slot (a power of two >= 4, so a slot holds a multiple of 4 values of k)
+  int rows, pitch;  // staged rows per channel, floats per staged row (a multiple of 4)
+  int ex, ey;       // element strides of the load: ey > 1 for one-row windows with a stride; ex is always 1 (the TMA
+                    // has no traversal stride in the innermost dimension)
+  int step_x, step_y;  // staged columns / rows between neighbouring output pixels / output rows
+  int x_start;      // tensor column of staged column 0 (a multiple of 4, <= -pad)
+  int x_off;        // staged column of tap dx = 0 of output column 0
+  int slot_bytes;   // cc * rows * pitch * 4: what one TMA load delivers
+  int slot_pitch;   // slot_bytes rounded up to 128
+};
+
+// Fills `st` for an image of h x wd and a kh x kw window; returns false when the conv cannot be staged
+// (rows that are no 16-byte multiples cannot be described to the TMA; a box is at most 256 wide / high).
+__host__ __device__ inline bool conv_staging(int ci, int h, int wd, int kh, int kw, int stride, int pad, int oh, int ow, int bn,
+                                             ConvStaging *st) {
+  (void)h;
+  st->slots = 0;
+  if (wd % 4) return false;
+  st->ey = (kh == 1 && stride <= 8) ? stride : 1;   // a traversal stride is at most 8
+  st->ex = 1;
+  const int out_rows = min(oh, (bn - 1 + ow - 1) / ow + 1);   // output rows that bn consecutive pixels can touch
+  st->step_y = st->ey == 1 ? stride : 1;
+  st->step_x = st->ex == 1 ? stride : 1;
+  st->rows = (out_rows - 1) * st->step_y + (st->ey == 1 ? kh : 1);
+  st->x_start = st->ex == 1 ? -((pad + 3) / 4 * 4) : 0;
+  const int cols = st->ex == 1 ? (ow - 1) * stride - pad + kw - st->x_start : ow;
+  st->pitch = (cols + 3) / 4 * 4;
+  st->x_off = st->ex == 1 ? -pad - st->x_start : 0;
+  if (st->pitch > 256 || st->rows * st->ey > 256) return false;
+  const int plane = st->rows * st->pitch * 4;
+  // channels per slot: about 16 KB, and enough values of k (cc * kh * kw >= 16) that one K block touches
+  // at most three slots -- the repack releases the slots it passed only at the end of a K block, so a K
+  // block must not need more slots than the ring holds
+  int cc = 64;
+  while (cc > 4 && (cc * plane > 16 * 1024 || cc / 2 >= ci) && (cc / 2) * kh * kw >= 16) cc /= 2;
+  if (cc * kh * kw < 16 || cc * plane > 24 * 1024) return false;
+  st->cc = cc;
+  st->slot_bytes = cc * plane;
+  st->slot_pitch = (st->slot_bytes + 127) / 128 * 128;
+  st->slots = 3;
+  return true;
 }
 
 struct ConvUmmaParams {
   alignas(64) CUtensorMap map_w;    // {K, co, 1}, box {32 fp32, 128, 1}, 128B swizzle
   alignas(64) CUtensorMap map_out;  // {oh*ow, co, n}, box {32 fp32, 32, 1}, 128B swizzle (stores); unused when oh*ow % 4 != 0
+  alignas(64) CUtensorMap map_x;    // staged convs: {wd, h, ci, n}, box {pitch, rows * ey, cc, 1}, element strides {1, ey, 1, 1}
   float *y;                         // [n, co, oh*ow]: the output rows, for images whose rows are not 16-byte multiples
   const float *x;
   int n, ci, h, wd, co, kh, kw, stride, pad, oh, ow;
@@ -44,8 +111,12 @@ struct ConvUmmaParams {
   int bn;               // output pixels per tile: 32, 64 or 128
   int split;            // CTAs (k-slices) per tile = cluster width; 1: no split
   int kb_per_slice;     // K blocks per k-slice
+  ConvStaging st;       // st.slots == 0: gathered from global memory
   long long *timeline;  // diagnostic: when non-null, CTA 0 records globaltimer marks (UmmaMark indices)
 };
+
+// bytes of the raw ring, rounded so that the operand ring behind it stays 1 KB aligned (128B swizzle)
+__host__ __device__ constexpr int conv_raw_bytes(int slots, int slot_pitch) { return (slots * slot_pitch + 1023) / 1024 * 1024; }
 
 // 4-byte asynchronous copy global -> shared; src_bytes = 0 writes zeros instead
 __device__ __forceinline__ void cp_async_4(uint32_t dst, const float *src, uint32_t src_bytes) {
@@ -58,10 +129,42 @@ __device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+// has phase `parity` of the barrier completed?  Never blocks.
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ float ld_shared_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ int4 ld_shared_i4(uint32_t addr) {
+  int4 v;
+  asm volatile("ld.shared.v4.s32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+
 struct ConvUmmaTf32 {
   using Params = ConvUmmaParams;
   static constexpr int kMaxThreads = kUmmaThreads;
-  static constexpr int kMinBlocks = 1;
+  static constexpr int kMinBlocks = 2;      // two CTAs per SM: one tile's epilogue runs under the other's main loop
   static constexpr bool kMemoryBound = false;
   static constexpr bool kUsesTmem = true;   // allocates tensor memory (see fused_block_kernel)
   static constexpr int kBK = 32;  // K elements (fp32) per stage row of 128 bytes
@@ -78,7 +181,8 @@ struct ConvUmmaTf32 {
     const bool live = pix < ohw;
     const int oy = pix / p.ow, ox = pix % p.ow;
     const int iy0 = oy * p.stride - p.pad, ix0 = ox * p.stride - p.pad;
-    const float *xb = p.x + (size_t)img * p.ci * p.h * p.wd + (ptrdiff_t)iy0 * p.wd + ix0;
+    const float *const x0 = p.x;   // read once: the loop's asm statements make the compiler re-read parameters otherwise
+    const float *xb = x0 + (size_t)img * p.ci * p.h * p.wd + (ptrdiff_t)iy0 * p.wd + ix0;
     // which taps of the window fall inside the image for this pixel (bit dy*kw+dx; none for a dead row)
     uint32_t tapmask = 0;
     if (live)
@@ -98,7 +202,7 @@ struct ConvUmmaTf32 {
         for (int i = 0; i < 8; ++i) {
           const int2 t = tab[kb * kBK + e0 + i];
           const bool in = (tapmask >> t.y) & 1u;
-          src[i] = in ? xb + t.x : p.x;
+          src[i] = in ? xb + t.x : x0;
           bytes[i] = in ? 4u : 0u;
         }
 #pragma unroll
@@ -112,6 +216,112 @@ struct ConvUmmaTf32 {
     return true;
   }
 
+  // The im2col operand of one tile built from the raw ring by the four epilogue warps (gt = 0..127).
+  // Thread layout as in gather(): consecutive lanes take consecutive pixels, thread `sub` of a pixel its
+  // share of the stage's 32 values of k, in 16-byte chunks of four.  tab[k] is the byte offset of k's
+  // (channel within the slot, dy, dx) inside a slot, relative to the pixel's window origin.  All threads
+  // walk the same sequence of k, so the slot bookkeeping (which ring slot holds k, its phase) is
+  // uniform per warp; a warp arrives on a slot's "empty" barrier once it has moved past the slot.
+  //
+  // A K block is done in four straight-line phases -- slot bookkeeping and waits (the only branches),
+  // then every table read, then every raw read, then the stores -- because the compiler lets
+  // outstanding shared-memory reads complete at every branch: with a branch per chunk each chunk paid
+  // its own two round trips to shared memory (about 150 clocks per chunk, 1200 per K block; in
+  // phases the K block costs what its ~100 shared-memory wavefronts per warp cost).  A chunk past K
+  // (K padded up to a whole K block) reads a 16-byte zero area instead of branching around the reads:
+  // the weights' padding is zero too, but 0 x garbage must not be NaN.
+  template <int BN>
+  __device__ __forceinline__ static bool repack(const Params &p, const TileCtx &c, int gt, int px0, int kb0, int num_kb, int stages,
+                                                uint32_t tiles, uint32_t full0, uint32_t empty0, uint32_t raw0, uint32_t raw_full0,
+                                                uint32_t raw_empty0, uint32_t tab, uint32_t zeros, long long *tl) {
+    constexpr int kStageBytes = conv_stage_bytes(BN), kper = kBK * BN / 128, kChunks = kper / 4;
+    // Every parameter the loop needs is read into registers here: the loop is full of asm statements
+    // that clobber memory, after each of which the compiler would otherwise read the parameter block again.
+    const ConvStaging st = p.st;
+    const int K = p.K, ow = p.ow;
+    const uint32_t slot_pitch = (uint32_t)st.slot_pitch;
+    int *const status = c.status;
+    const int r = gt & (BN - 1), sub = gt / BN, pix = px0 + r, ohw = p.oh * ow;
+    // a row past the image reads the window of pixel 0 of the tile: finite values, and its output
+    // columns are clipped by the store
+    const int oy0 = px0 / ow;
+    int oy = pix / ow, ox = pix - oy * ow;
+    if (pix >= ohw) oy = oy0, ox = px0 - oy0 * ow;
+    const uint32_t pixoff = (uint32_t)(((oy - oy0) * st.step_y * st.pitch + ox * st.step_x + st.x_off) * 4);
+    const int kslot = st.cc * p.kh * p.kw, nslots = st.slots;
+    // ring slot (index, phase) that holds the next k, k's position inside it, first slot not yet released
+    int kin = kb0 * kBK + sub * kper - (kb0 * kBK / kslot) * kslot;
+    uint32_t rs = 0, rph = 0, rel_s = 0;
+    bool have = false;
+    const uint32_t swz = (uint32_t)(r & 7);
+    const bool lane0 = (gt & 31) == 0;
+    uint32_t s = 0, ph = 1;
+    for (int kb = 0; kb < num_kb; ++kb) {
+      // (a wait's outcome is made uniform over the warp: its lanes meet at __syncwarp below, and one
+      // that gave up a poll earlier than its neighbours must not leave them waiting there)
+      if (!__all_sync(0xffffffffu, mbar_wait(empty0 + 8 * s, ph, status, UMMA_WAIT_EMPTY_TIMEOUT))) return false;
+      const uint32_t brow = tiles + s * kStageBytes + kUmmaABytes + (uint32_t)r * 128u;
+      const int k0 = (kb0 + kb) * kBK + sub * kper;
+      // phase 0: which slot holds each chunk (waiting for slots not seen yet); no shared-memory reads
+      uint32_t src[kChunks], tix[kChunks];
+      int rel = 0;
+#pragma unroll
+      for (int i = 0; i < kChunks; ++i) {
+        const int k = k0 + 4 * i;
+        if (k < K) {
+          while (kin >= kslot) {   // k lies in a later slot: pass the current one
+            kin -= kslot, ++rel, have = false;
+            if (++rs == (uint32_t)nslots) rs = 0, rph ^= 1;
+          }
+          if (!have) {
+            if (!__all_sync(0xffffffffu, mbar_wait(raw_full0 + 8 * rs, rph, status, UMMA_WAIT_FULL_TIMEOUT))) return false;
+            have = true;
+          }
+          src[i] = raw0 + rs * slot_pitch + pixoff;
+          tix[i] = tab + (uint32_t)(k - kb0 * kBK) * 4u;
+        } else {
+          src[i] = zeros;   // with the table entry of k = kb0 * 32 replaced by offsets 0 below
+          tix[i] = 0;
+        }
+        kin += 4;
+      }
+      // phase 1: the table entries (four byte offsets per chunk)
+      int4 off[kChunks];
+#pragma unroll
+      for (int i = 0; i < kChunks; ++i) off[i] = ld_shared_i4(tix[i] ? tix[i] : tab);
+      // phase 2: the raw values
+      float v[kChunks][4];
+#pragma unroll
+      for (int i = 0; i < kChunks; ++i) {
+        const bool pad = tix[i] == 0;
+        v[i][0] = ld_shared_f32(src[i] + (pad ? 0u : (uint32_t)off[i].x));
+        v[i][1] = ld_shared_f32(src[i] + (pad ? 4u : (uint32_t)off[i].y));
+        v[i][2] = ld_shared_f32(src[i] + (pad ? 8u : (uint32_t)off[i].z));
+        v[i][3] = ld_shared_f32(src[i] + (pad ? 12u : (uint32_t)off[i].w));
+      }
+      // phase 3: the operand row's 16-byte chunks
+#pragma unroll
+      for (int i = 0; i < kChunks; ++i)
+        st_shared_u4(brow + ((((uint32_t)(sub * kChunks + i)) ^ swz) << 4), __float_as_uint(v[i][0]), __float_as_uint(v[i][1]),
+                     __float_as_uint(v[i][2]), __float_as_uint(v[i][3]));
+      kin += kBK - kper;   // the other threads of this pixel take the rest of the K block
+      fence_async_smem();  // the operand was written through the generic proxy; the MMA reads it through the async proxy
+      __syncwarp();
+      // One arrival per warp (its lanes walk the same k): 128 arrivals on one barrier word serialise.
+      // The raw reads above have completed (their values were stored), so the slots passed on the way are free.
+      if (lane0) {
+        mbar_arrive(full0 + 8 * s);
+        for (int i = 0; i < rel; ++i) mbar_arrive(raw_empty0 + 8 * (rel_s + i < (uint32_t)nslots ? rel_s + i : rel_s + i - nslots));
+      }
+      rel_s += rel;
+      if (rel_s >= (uint32_t)nslots) rel_s -= nslots;
+      if (tl && gt == 0 && kb == 0) tl[MARK_FIRST_LOAD_ISSUED] = (long long)global_ns();
+      if (tl && gt == 0 && kb == num_kb - 1) tl[MARK_LAST_LOAD_ISSUED] = (long long)global_ns();
+      if (++s == (uint32_t)stages) s = 0, ph ^= 1;
+    }
+    return true;
+  }
+
   __device__ __forceinline__ static void run(const Params &p, const TileCtx &c) {
     const int warp = c.tid >> 5, lane = c.tid & 31;
     const int quad = (threadIdx.x >> 5) & 3;
@@ -119,6 +329,7 @@ struct ConvUmmaTf32 {
     const int split = p.split, kslice = c.block_x() % split;
     const int px0 = (c.block_x() / split) * BN, co0 = c.block_y() * kUmmaBM, img = c.block_z();
     const int stages = p.stages, ohw = p.oh * p.ow, K = p.K;
+    int *const status = c.status;
     const int total_kb = (K + kBK - 1) / kBK;
     const int kb0 = kslice * p.kb_per_slice;                  // first K block of this k-slice
     const int num_kb = min(p.kb_per_slice, total_kb - kb0);   // K blocks this CTA multiplies (>= 1)
@@ -135,7 +346,10 @@ struct ConvUmmaTf32 {
       if (!c.persistent) tmem_relinquish();
     }
     int2 *tab = reinterpret_cast<int2 *>(c.smem + kUmmaHeaderBytes);
-    const uint32_t tiles = smem_u32(c.smem) + conv_header_bytes(K);
+    const bool staged = p.st.slots > 0;
+    const uint32_t raw_full0 = full0 + kConvRawBarOffset, raw_empty0 = raw_full0 + 8 * kConvMaxRawSlots;
+    const uint32_t raw0 = smem_u32(c.smem) + conv_header_bytes(K);                     // the raw ring of a staged conv
+    const uint32_t tiles = raw0 + (uint32_t)conv_raw_bytes(p.st.slots, p.st.slot_pitch);  // the operand ring
     // once the MMAs are done the ring holds the k-slices' partial sums (split > 1) and the store buffers
     const int chunks = BN / 32, max_owned = (chunks + split - 1) / split;
     const uint32_t staging = tiles + (uint32_t)umma_recv_bytes(BN, split, 4);
@@ -151,18 +365,24 @@ struct ConvUmmaTf32 {
     mark(MARK_START, c.tid == 0);
     if (warp == 4) {
       if (lane < stages) {
-        mbar_init(full0 + 8 * lane, 1 + 128);  // the weight copy's arrive.expect_tx + one arrive per gather thread
+        mbar_init(full0 + 8 * lane, staged ? 1 + 4 : 1 + 128);  // the weight copy's arrive.expect_tx + one arrive per gather thread / repack warp
         mbar_init(empty0 + 8 * lane, 1);
       }
       if (lane == 0) {
         mbar_init(acc_bar, 1);
         mbar_init(recv_bar, 1);
       }
+      if (lane == 0) st_shared_u4(full0 + kConvZeroOffset, 0u, 0u, 0u, 0u);
+      if (lane < p.st.slots) {
+        mbar_init(raw_full0 + 8 * lane, 1);      // the slot's TMA load (arrive.expect_tx)
+        mbar_init(raw_empty0 + 8 * lane, 4);     // every repack warp, once it has moved past the slot
+      }
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
       __syncwarp();
       if (lane == 0) {
         asm volatile("prefetch.tensormap [%0];" ::"l"(&p.map_w) : "memory");
         if ((ohw & 3) == 0) asm volatile("prefetch.tensormap [%0];" ::"l"(&p.map_out) : "memory");
+        if (staged) asm volatile("prefetch.tensormap [%0];" ::"l"(&p.map_x) : "memory");
       }
       if (lane == 0 && split > 1) {
         // bytes this CTA will receive: one partial per owned 32-pixel chunk from every k-slice (itself included)
@@ -178,12 +398,26 @@ struct ConvUmmaTf32 {
       // per entry made this set-up take 11 us for K = 4608.
       const int khw = p.kh * p.kw, step_ch = 128 / khw, step_r = 128 % khw;
       const int inv_kw = (65536 + p.kw - 1) / p.kw;
-      int ch = c.tid / khw, r = c.tid % khw;
-      for (int k = c.tid; k < total_kb * kBK; k += 128) {
-        const int dy = (r * inv_kw) >> 16, dx = r - dy * p.kw;
-        tab[k] = k < K ? make_int2((ch * p.h + dy) * p.wd + dx, r) : make_int2(0, 31);
-        ch += step_ch, r += step_r;
-        if (r >= khw) r -= khw, ++ch;
+      if (!staged) {
+        int ch = c.tid / khw, r = c.tid % khw;
+        for (int k = c.tid; k < total_kb * kBK; k += 128) {
+          const int dy = (r * inv_kw) >> 16, dx = r - dy * p.kw;
+          tab[k] = k < K ? make_int2((ch * p.h + dy) * p.wd + dx, r) : make_int2(0, 31);
+          ch += step_ch, r += step_r;
+          if (r >= khw) r -= khw, ++ch;
+        }
+      } else {
+        // staged: this k-slice's range only, entry j <-> k = kb0 * 32 + j, as the byte offset of
+        // (channel within its slot, dy, dx) inside a raw slot
+        int *tab4 = reinterpret_cast<int *>(tab);
+        const int plane = p.st.rows * p.st.pitch, k_lo = kb0 * kBK + c.tid;
+        int ch = k_lo / khw, r = k_lo - ch * khw;
+        for (int j = c.tid; j < num_kb * kBK; j += 128) {
+          const int dy = (r * inv_kw) >> 16, dx = r - dy * p.kw;
+          tab4[j] = (((ch & (p.st.cc - 1)) * plane) + dy * p.st.pitch + dx) * 4;
+          ch += step_ch, r += step_r;
+          if (r >= khw) r -= khw, ++ch;
+        }
       }
     }
     c.dependency_wait();   // nothing above touches global memory: barriers, tensor memory and the table overlap the previous kernel
@@ -198,7 +432,8 @@ struct ConvUmmaTf32 {
     // carried incrementally (the issue loop is a dependent chain on one thread; see GemmUmma)
     bool acc_ok = true;
     if (warp == 4) {
-      if (elect_one()) {
+      const bool leader = elect_one();
+      if (leader && !staged) {
         uint32_t s = 0, ph = 1, dst = tiles, bar = full0;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(empty0 + 8 * s, ph, c.status, UMMA_WAIT_EMPTY_TIMEOUT)) break;
@@ -206,6 +441,47 @@ struct ConvUmmaTf32 {
           tma_load_3d(dst, &p.map_w, bar, (kb0 + kb) * kBK, co0, 0);
           if (++s == (uint32_t)stages) s = 0, ph ^= 1, dst = tiles, bar = full0;
           else dst += kStageBytes, bar += 8;
+        }
+      } else if (leader) {
+        // Staged: one thread feeds two rings -- the raw slots (input rows of `cc` channels, one tiled TMA
+        // load each) and the weight half of the operand stages -- by polling both "empty" barriers, so
+        // neither ring's back-pressure holds the other up.  Raw slots first: the repack needs them a
+        // stage earlier.
+        const int cc = p.st.cc, kslot = cc * p.kh * p.kw, x_start = p.st.x_start, nslots = p.st.slots;
+        const uint32_t slot_bytes = (uint32_t)p.st.slot_bytes, slot_pitch = (uint32_t)p.st.slot_pitch;
+        const int k_end = min(K, (kb0 + num_kb) * kBK);
+        int g = kb0 * kBK / kslot;
+        const int g_end = (k_end - 1) / kslot + 1;
+        const int y_start = (px0 / p.ow) * p.stride - p.pad;
+        uint32_t ws = 0, wph = 1, wdst = tiles, wbar = full0, rs = 0, rph = 1, idle = 0;
+        int kb = 0;
+        uint64_t t0 = 0;
+        while (kb < num_kb || g < g_end) {
+          bool progress = false;
+          if (g < g_end && mbar_test(raw_empty0 + 8 * rs, rph)) {
+            mbar_expect_tx(raw_full0 + 8 * rs, slot_bytes);
+            tma_load_4d(raw0 + rs * slot_pitch, &p.map_x, raw_full0 + 8 * rs, x_start, y_start, g * cc, img);
+            ++g, progress = true;
+            if (++rs == (uint32_t)nslots) rs = 0, rph ^= 1;
+          }
+          if (kb < num_kb && mbar_test(empty0 + 8 * ws, wph)) {
+            mbar_expect_tx(wbar, kUmmaABytes);
+            tma_load_3d(wdst, &p.map_w, wbar, (kb0 + kb) * kBK, co0, 0);
+            ++kb, progress = true;
+            if (++ws == (uint32_t)stages) ws = 0, wph ^= 1, wdst = tiles, wbar = full0;
+            else wdst += kStageBytes, wbar += 8;
+          }
+          if (progress) {
+            idle = 0, t0 = 0;
+          } else if ((++idle & 1023u) == 0) {   // bounded like every other wait: ~1 s without progress
+            if (status && *reinterpret_cast<volatile int *>(status) != 0) break;
+            const uint64_t now = global_ns();
+            if (t0 == 0) t0 = now;
+            if (now - t0 > 1000000000ull) {
+              if (status) atomicExch(status, (int)UMMA_WAIT_EMPTY_TIMEOUT);
+              break;
+            }
+          }
         }
       }
       __syncwarp();
@@ -215,7 +491,7 @@ struct ConvUmmaTf32 {
         uint32_t s = 0, ph = 0, lo = lo0, accumulate = 0;
         bool ok = true;
         for (int kb = 0; kb < num_kb; ++kb) {
-          ok = mbar_wait(full0 + 8 * s, ph, c.status, UMMA_WAIT_FULL_TIMEOUT);
+          ok = mbar_wait(full0 + 8 * s, ph, status, UMMA_WAIT_FULL_TIMEOUT);
           if (!ok) break;
           fence_async_smem();  // the gathered operand was written through the generic proxy
           tc_fence_after();
@@ -237,10 +513,18 @@ struct ConvUmmaTf32 {
       __syncwarp();
     } else {
       bool ok;
-      const int2 *tab_slice = tab + kb0 * kBK;
-      if (BN == 128) ok = gather<128>(p, c, quad * 32 + lane, px0, img, num_kb, stages, tiles, full0, empty0, tab_slice, tl);
-      else if (BN == 64) ok = gather<64>(p, c, quad * 32 + lane, px0, img, num_kb, stages, tiles, full0, empty0, tab_slice, tl);
-      else ok = gather<32>(p, c, quad * 32 + lane, px0, img, num_kb, stages, tiles, full0, empty0, tab_slice, tl);
+      const int gt = quad * 32 + lane;
+      if (staged) {
+        const uint32_t tab_s = smem_u32(tab), zeros = full0 + kConvZeroOffset;
+        if (BN == 128) ok = repack<128>(p, c, gt, px0, kb0, num_kb, stages, tiles, full0, empty0, raw0, raw_full0, raw_empty0, tab_s, zeros, tl);
+        else if (BN == 64) ok = repack<64>(p, c, gt, px0, kb0, num_kb, stages, tiles, full0, empty0, raw0, raw_full0, raw_empty0, tab_s, zeros, tl);
+        else ok = repack<32>(p, c, gt, px0, kb0, num_kb, stages, tiles, full0, empty0, raw0, raw_full0, raw_empty0, tab_s, zeros, tl);
+      } else {
+        const int2 *tab_slice = tab + kb0 * kBK;
+        if (BN == 128) ok = gather<128>(p, c, gt, px0, img, num_kb, stages, tiles, full0, empty0, tab_slice, tl);
+        else if (BN == 64) ok = gather<64>(p, c, gt, px0, img, num_kb, stages, tiles, full0, empty0, tab_slice, tl);
+        else ok = gather<32>(p, c, gt, px0, img, num_kb, stages, tiles, full0, empty0, tab_slice, tl);
+      }
       (void)ok;
       // epilogue: accumulator rows are output channels, columns are this tile's pixels
       acc_ok = mbar_wait(acc_bar, 0, c.status, UMMA_WAIT_ACC_TIMEOUT);
@@ -277,6 +561,10 @@ struct ConvUmmaTf32 {
         mbar_inval(acc_bar);
         mbar_inval(recv_bar);
       }
+    }
+    if (c.persistent && c.tid < p.st.slots) {
+      mbar_inval(raw_full0 + 8 * c.tid);
+      mbar_inval(raw_empty0 + 8 * c.tid);
     }
     mark(MARK_END, c.tid == 0);
   }

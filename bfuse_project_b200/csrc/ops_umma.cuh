@@ -78,6 +78,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int *st
         : "memory");
     if (ok) return true;
     if ((it & 1023u) == 1023u) {
+      // once any wait of the launch has given up, the others follow at once: a failed launch then ends
+      // after about one second in all, not one second per CTA
+      if (status && *reinterpret_cast<volatile int *>(status) != 0) return false;
       const uint64_t now = global_ns();
       if (t0 == 0) t0 = now;
       if (now - t0 > 1000000000ull) {

@@ -22,7 +22,7 @@ using namespace bfuse;
 namespace {
 
 constexpr size_t kMaxSmemPerCta = 227 * 1024 - 256;  // opt-in dynamic limit minus the kernels' few static bytes
-constexpr int kParamsBytes = 512;
+constexpr int kParamsBytes = 640;
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -243,10 +243,28 @@ int default_launch(const bfuse_context *ctx, bfuse_kernel_desc *d, std::string *
       // an SM of its own (a long-K conv on few CTAs is bound by the ring's round trip, not by issue
       // rate); deep enough to hold the k-slices' partial sums after the MMAs
       const long long ctas = tiles * split;
-      const int budget = (share * ctas <= sm ? 200 : 110) * 1024;
-      int stages = std::max(1, std::min({q, kUmmaMaxStages, (budget - conv_header_bytes(K)) / conv_stage_bytes(bn)}));
+      // How the im2col operand is built, shape[11]: 1 = staged (input rows by TMA into a raw ring, repacked in
+      // shared memory), 2 = gathered from global memory, 0 = the runtime's choice -- gathered: it needs no raw
+      // ring, so a third CTA fits an SM, and with the whole grid streaming weights and input out of L2 that
+      // occupancy was worth more than the cheaper operand path at every batch size measured (batch 256:
+      // 3 x 3 branch alone 191 us gathered at three CTAs per SM, 216 us staged at two).
+      ConvStaging st;
+      st.slots = 0;
+      if (s[11] == 1 && !conv_staging(s[1], s[2], s[3], s[5], s[6], s[7], s[8], oh, ow, bn, &st)) {
+        *err = "conv2d: shape[11] = 1 (staged operand) needs image rows of 16-byte multiples and a window whose rows fit a 24 KB slot";
+        return BFUSE_ERR_SHAPE;
+      }
+      if (s[11] < 0 || s[11] > 2) { *err = "conv2d: shape[11] (operand mode) must be 0, 1 or 2"; return BFUSE_ERR_SHAPE; }
+      d->shape[11] = st.slots ? 1 : 2;
+      // ring budget: the whole SM when the operator and an equal partner leave every CTA an SM of its own, else
+      // two CTAs per SM (staged) or three (gathered)
+      const int budget = (share * ctas <= sm ? 200 : (st.slots ? 110 : 74)) * 1024;
+      if (st.slots && budget > 150 * 1024) st.slots = kConvMaxRawSlots;   // a CTA with an SM to itself: deeper raw ring
+      const int raw = conv_raw_bytes(st.slots, st.slot_pitch);
+      int stages = std::max(1, std::min({q, kUmmaMaxStages, (budget - conv_header_bytes(K) - raw) / conv_stage_bytes(bn)}));
       stages = std::max(stages, ceil_div(umma_epilogue_bytes(bn, split, 4), conv_stage_bytes(bn)));
-      set(split * ceil_div(oh * ow, bn), ceil_div(s[4], kUmmaBM), s[0], kUmmaThreads, 1, conv_umma_smem_bytes(stages, bn, K), 3);
+      if (st.slots) stages = std::max(stages, 2);   // the repack of stage s + 1 runs while the MMAs read stage s
+      set(split * ceil_div(oh * ow, bn), ceil_div(s[4], kUmmaBM), s[0], kUmmaThreads, 1, conv_umma_smem_bytes(stages, bn, K, raw), 3);
       return BFUSE_OK;
     }
     case BFUSE_OP_GEMM_TF32:
@@ -448,13 +466,39 @@ int build_params(bfuse_context *ctx, KernelRec &k) {
       if (split > 8 || (split - 1) * q >= num_kb) return shape_err("shape[10] (k-slices) must be 1..8 with every k-slice non-empty");
       if (kd.gx != split * ceil_div(oh * ow, bn) || kd.gy != ceil_div(s[4], kUmmaBM) || kd.gz != s[0])
         return shape_err("GridDim must be (k-slices * ceil(oh*ow/BN), ceil(co/128), n)");
-      if (k.smem < (size_t)conv_umma_smem_bytes(ceil_div(umma_epilogue_bytes(bn, split, 4), conv_stage_bytes(bn)), bn, K))
-        return shape_err("shared memory below the store buffers (and, for a split conv, the receive area of the k-slices)");
       k.cluster = split;
       ConvUmmaParams p;
       std::memset(&p, 0, sizeof(p));
+      // Staged (input rows by TMA into a raw ring, repacked in shared memory) when the geometry allows
+      // it and the registered window has room for the raw ring beside the smallest operand ring;
+      // else gathered from global memory.  The raw ring is 3 slots deep, 4 when room is left for a
+      // whole-SM operand ring as well.
+      const int min_stages = ceil_div(umma_epilogue_bytes(bn, split, 4), conv_stage_bytes(bn));
+      if (s[11] < 0 || s[11] > 2) return shape_err("shape[11] (operand mode) must be 0 (the runtime's choice), 1 (staged) or 2 (gathered)");
+      if (s[11] == 1 && !conv_staging(s[1], s[2], s[3], s[5], s[6], s[7], s[8], oh, ow, bn, &p.st))
+        return shape_err("shape[11] = 1 (staged operand) needs image rows of 16-byte multiples and a window whose rows fit a 24 KB slot");
+      if (s[11] == 1) {
+        if (k.smem >= (size_t)conv_umma_smem_bytes(std::max(min_stages, 4), bn, K, conv_raw_bytes(kConvMaxRawSlots, p.st.slot_pitch)) &&
+            k.smem > 150 * 1024)
+          p.st.slots = kConvMaxRawSlots;
+        if (k.smem < (size_t)conv_umma_smem_bytes(std::max(min_stages, 2), bn, K, conv_raw_bytes(p.st.slots, p.st.slot_pitch)))
+          return shape_err("shape[11] = 1 (staged operand): shared memory below the raw ring plus two operand stages");
+      }
+      const int raw = conv_raw_bytes(p.st.slots, p.st.slot_pitch);
+      if (k.smem < (size_t)conv_umma_smem_bytes(min_stages, bn, K, raw))
+        return shape_err("shared memory below the store buffers (and, for a split conv, the receive area of the k-slices)");
       int rc = encode_map(ctx, &p.map_w, 4, a[1], K, s[4], 1, kUmmaBM);
       if (rc) return rc;
+      if (p.st.slots) {
+        // the NCHW input as {w, h, ci, n}; a box is one slot: pitch x rows x cc elements, rows taken with element stride ey
+        const cuuint64_t dims[4] = {(cuuint64_t)s[3], (cuuint64_t)s[2], (cuuint64_t)s[1], (cuuint64_t)s[0]};
+        const cuuint64_t strides[3] = {(cuuint64_t)s[3] * 4, (cuuint64_t)s[3] * s[2] * 4, (cuuint64_t)s[3] * s[2] * s[1] * 4};
+        const cuuint32_t box[4] = {(cuuint32_t)p.st.pitch, (cuuint32_t)(p.st.rows * p.st.ey), (cuuint32_t)p.st.cc, 1};
+        const cuuint32_t estr[4] = {1, (cuuint32_t)p.st.ey, 1, 1};
+        const CUresult r = ctx->encode(&p.map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, a[0], dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                       CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return fail(ctx, BFUSE_ERR_CUDA, "cuTensorMapEncodeTiled (conv input) failed (" + std::to_string((int)r) + ")");
+      }
       if ((oh * ow) % 4 == 0) {  // else the rows are no 16-byte multiples and the body stores them itself
         rc = encode_map(ctx, &p.map_out, 4, a[2], oh * ow, s[4], s[0], 32);
         if (rc) return rc;
@@ -463,7 +507,7 @@ int build_params(bfuse_context *ctx, KernelRec &k) {
       p.x = (const float *)a[0];
       p.n = s[0], p.ci = s[1], p.h = s[2], p.wd = s[3], p.co = s[4], p.kh = s[5], p.kw = s[6], p.stride = s[7], p.pad = s[8];
       p.oh = oh, p.ow = ow, p.K = K;
-      p.stages = std::min<int>(kUmmaMaxStages, (int)((k.smem - conv_header_bytes(K)) / conv_stage_bytes(bn)));
+      p.stages = std::min<int>(kUmmaMaxStages, (int)((k.smem - conv_header_bytes(K) - raw) / conv_stage_bytes(bn)));
       p.bn = bn;
       p.split = split;
       p.kb_per_slice = q;
@@ -614,9 +658,10 @@ bool ring_info(const KernelRec &k, int *header, int *stage_bytes, int *min_stage
   }
   if (k.desc.op == BFUSE_OP_CONV2D_TF32) {
     const int bn = s[9] > 0 ? s[9] : kConvBN;
-    *header = conv_header_bytes(s[1] * s[5] * s[6]), *stage_bytes = conv_stage_bytes(bn);
-    *min_stages = ceil_div(umma_epilogue_bytes(bn, std::max(1, s[10]), 4), conv_stage_bytes(bn));
-    *stages = reinterpret_cast<const ConvUmmaParams *>(k.params)->stages;
+    const ConvUmmaParams *cp = reinterpret_cast<const ConvUmmaParams *>(k.params);
+    *header = conv_header_bytes(s[1] * s[5] * s[6]) + conv_raw_bytes(cp->st.slots, cp->st.slot_pitch), *stage_bytes = conv_stage_bytes(bn);
+    *min_stages = std::max(cp->st.slots ? 2 : 1, ceil_div(umma_epilogue_bytes(bn, std::max(1, s[10]), 4), conv_stage_bytes(bn)));
+    *stages = cp->stages;
     return true;
   }
   return false;
@@ -1363,6 +1408,18 @@ int bfuse_debug_gemm_timeline(bfuse_context *ctx, int kernel, long long *marks, 
 static void reset_queue_counters(bfuse_context *ctx) {
   for (auto &f : ctx->fusions)
     if (f && f->queue_ctr) cudaMemset(f->queue_ctr, 0, 2 * sizeof(unsigned));
+}
+
+int bfuse_debug_conv_staging(const int *shape, int bn, int *out, int n) {
+  if (!shape || !out || n < 12) return BFUSE_ERR_INVALID;
+  const int *s = shape;
+  const int oh = conv_out(s[2], s[5], s[7], s[8]), ow = conv_out(s[3], s[6], s[7], s[8]);
+  ConvStaging st;
+  std::memset(&st, 0, sizeof(st));
+  const bool ok = oh > 0 && ow > 0 && conv_staging(s[1], s[2], s[3], s[5], s[6], s[7], s[8], oh, ow, bn, &st);
+  const int v[12] = {ok ? st.slots : 0, st.cc, st.rows, st.pitch, st.ex, st.ey, st.step_x, st.step_y, st.x_start, st.x_off, st.slot_bytes, st.slot_pitch};
+  std::memcpy(out, v, sizeof(v));
+  return BFUSE_OK;
 }
 
 int bfuse_read_status(bfuse_context *ctx, int *status) {

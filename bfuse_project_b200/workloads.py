@@ -108,11 +108,12 @@ def gemm(name, rng, op, batch, M, N, K, bias=False, causal=False, w_std=0.02, a=
                       flops=2.0 * batch * M * N * K)
 
 
-def conv2d(name, rng, op, n, ci, h, w, co, k, stride, pad, x=None, bn=0, split=0):
+def conv2d(name, rng, op, n, ci, h, w, co, k, stride, pad, x=None, bn=0, split=0, mode=0):
     X = rng.standard_normal((n, ci, h, w), dtype=np.float32) if x is None else x
     Wt = (np.sqrt(2.0 / (ci * k * k)) * rng.standard_normal((co, ci, k, k), dtype=np.float32)).astype(np.float32)
     oh, ow = (h + 2 * pad - k) // stride + 1, (w + 2 * pad - k) // stride + 1
-    shape = (n, ci, h, w, co, k, k, stride, pad, bn, split) if op == OP_CONV2D_TF32 else (n, ci, h, w, co, k, k, stride, pad)
+    # mode: how the tensor-core body builds its im2col operand (0 the runtime's choice, 1 staged, 2 gathered)
+    shape = (n, ci, h, w, co, k, k, stride, pad, bn, split, mode) if op == OP_CONV2D_TF32 else (n, ci, h, w, co, k, k, stride, pad)
     return KernelSpec(name, op, shape, [X, Wt, np.zeros((n, co, oh, ow), np.float32)],
                       [2], flops=2.0 * n * co * oh * ow * ci * k * k)
 
@@ -124,7 +125,7 @@ def pair_names():
             "cfg4b_k_v_proj", "cfg4c_rmsnorm_rope", "cfg5_conv_branches"]
 
 
-def make_pair(name, seed=0, scale=1.0, tensor_cores=True, conv_batch=1, split=0):
+def make_pair(name, seed=0, scale=1.0, tensor_cores=True, conv_batch=1, split=0, conv_mode=0):
     """Build one pair.  scale < 1 shrinks the row / token dimension for quick tests (512 tokens ->
     512 * scale); tensor_cores=False swaps the tcgen05 GEMM bodies for the CUDA-core fp32 bodies;
     split = 1 keeps the tcgen05 GEMMs un-split (needed under thread split and the work queue)."""
@@ -157,7 +158,7 @@ def make_pair(name, seed=0, scale=1.0, tensor_cores=True, conv_batch=1, split=0)
     if name == "cfg5_conv_branches":
         x = rng.standard_normal((conv_batch, 64, 56, 56), dtype=np.float32)
         op = OP_CONV2D_TF32 if tensor_cores else OP_CONV2D_F32_SIMT
-        return PairSpec(name, conv2d("conv3x3_s2", rng, op, conv_batch, 64, 56, 56, 128, 3, 2, 1, x=x),
+        return PairSpec(name, conv2d("conv3x3_s2", rng, op, conv_batch, 64, 56, 56, 128, 3, 2, 1, x=x, mode=conv_mode),
                         conv2d("conv1x1_s2", rng, op, conv_batch, 64, 56, 56, 128, 1, 2, 0, x=x),
                         "tf32" if tensor_cores else "f32", "hbm", "ResNet-18 3x3 s2 conv || 1x1 s2 downsample (same input)")
     raise KeyError(name)
@@ -214,3 +215,56 @@ class DevicePair:
         for ks, bufs in ((self.spec.a, self.buffers[0]), (self.spec.b, self.buffers[1])):
             res.append([bufs[i].cpu().numpy().view(ks.host[i].dtype).reshape(ks.host[i].shape) for i in ks.outputs])
         return res
+
+
+class ConvBranchBatch:
+    """The ResNet-18 branch pair (3x3 stride-2 conv || 1x1 stride-2 downsample, 64 -> 128 channels on
+    56 x 56 images) over ONE seeded batch of n images resident on a GPU, with both outputs.  A shard
+    -- images [first, first + count), the partition of `partition.shard_batch` -- is a pair of kernels
+    registered on the same buffers at a pointer offset: every shard reads its slice of the one batch and
+    writes its slice of the one output, each with the whole (328 KB) weights, and no shard touches
+    another's bytes."""
+
+    CI, H, W, CO, OH, OW = 64, 56, 56, 128, 28, 28
+
+    def __init__(self, rt, torch, device, n, seed=0, mode=0):
+        self.rt, self.torch, self.n, self.mode = rt, torch, n, mode
+        dev = torch.device("cuda", device)
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(seed)
+        self.x = torch.randn(n, self.CI, self.H, self.W, device=dev, generator=gen)
+        self.w3 = torch.randn(self.CO, self.CI, 3, 3, device=dev, generator=gen) * float(np.sqrt(2.0 / (self.CI * 9)))
+        self.w1 = torch.randn(self.CO, self.CI, 1, 1, device=dev, generator=gen) * float(np.sqrt(2.0 / self.CI))
+        self.y3 = torch.zeros(n, self.CO, self.OH, self.OW, device=dev)
+        self.y1 = torch.zeros(n, self.CO, self.OH, self.OW, device=dev)
+        self._shards = {}
+
+    def bytes(self, count=None):
+        """Algorithmic bytes of the pair over `count` images: each operator's inputs read once (the shared
+        input counted per operator) and its output written once."""
+        c = self.n if count is None else count
+        return 4 * (2 * c * self.CI * self.H * self.W + self.w3.numel() + self.w1.numel() + 2 * c * self.CO * self.OH * self.OW)
+
+    def flops(self, count=None):
+        c = self.n if count is None else count
+        return 2.0 * c * self.CO * self.OH * self.OW * self.CI * (9 + 1)
+
+    def shard(self, first, count):
+        """(kernel handle 3x3, kernel handle 1x1) of the shard, registered once."""
+        key = (first, count)
+        if key not in self._shards:
+            if first < 0 or count <= 0 or first + count > self.n:
+                raise ValueError("shard outside the batch")
+            xo = self.x.data_ptr() + 4 * first * self.CI * self.H * self.W
+            yo = 4 * first * self.CO * self.OH * self.OW
+            d3 = self.rt.describe("conv3x3_s2", OP_CONV2D_TF32, (count, self.CI, self.H, self.W, self.CO, 3, 3, 2, 1, 0, 0, self.mode),
+                                  [xo, self.w3.data_ptr(), self.y3.data_ptr() + yo])
+            d1 = self.rt.describe("conv1x1_s2", OP_CONV2D_TF32, (count, self.CI, self.H, self.W, self.CO, 1, 1, 2, 0, 0, 0, self.mode if self.mode != 1 else 0),
+                                  [xo, self.w1.data_ptr(), self.y1.data_ptr() + yo])
+            self.launch = [(d.GridDim.tuple(), d.BlockDim.tuple(), d.smem_bytes) for d in (d3, d1)]
+            self._shards[key] = (self.rt.register_kernel(d3), self.rt.register_kernel(d1))
+        return self._shards[key]
+
+    def clear_outputs(self):
+        self.y3.zero_()
+        self.y1.zero_()

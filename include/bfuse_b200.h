@@ -49,7 +49,9 @@ enum {
   BFUSE_OP_GEMM_BF16 = 7,     /* bf16 A, W, out; fp32 accumulate; tcgen05 kind::f16; shape[4..6] as above    */
   BFUSE_OP_CONV2D_TF32 = 8,   /* as CONV2D_F32_SIMT on tcgen05 kind::tf32 (implicit GEMM); shape[9] = output */
                               /* pixels per tile (32, 64, 128), shape[10] = k-slices per tile (a cluster    */
-                              /* reduces them); 0 = chosen by the runtime                                   */
+                              /* reduces them), shape[11] = how the im2col operand is built: 1 staged (input */
+                              /* rows by TMA into shared memory, repacked there; needs rows of 16-byte       */
+                              /* multiples), 2 gathered from global memory; 0 = chosen by the runtime        */
   BFUSE_OP_COUNT = 9
 };
 
@@ -195,6 +197,13 @@ int bfuse_debug_gemm_timeline(bfuse_context *ctx, int kernel, long long *marks, 
  * the body done.  times holds 3 * sum(slots) values,
  * launch i's slots[i] >= its fused grid entries first to last; unused entries stay 0.  Synchronises. */
 int bfuse_debug_fused_timeline(bfuse_context *ctx, const int *fusions, int n, long long *times, const int *slots);
+/* Diagnostic, no reference counterpart, no GPU needed: how the tensor-core conv body would stage the input
+ * of a conv of shape {n, ci, h, w, co, kh, kw, stride, pad} with bn output pixels per tile.  out (12 ints):
+ * ring slots (0: the conv is gathered from global memory instead), channels per slot, staged rows,
+ * floats per staged row, element strides x / y of the load, staged columns / rows between neighbouring
+ * output pixels / rows, tensor column of staged column 0, staged column of tap 0 of output column 0,
+ * bytes per slot, slot pitch in bytes. */
+int bfuse_debug_conv_staging(const int *shape, int bn, int *out, int n);
 /* Read and clear the device status word (0 = no bounded wait gave up). Synchronises.  A non-zero
  * status also restarts the ticket counters of every work-queue fusion from zero. */
 int bfuse_read_status(bfuse_context *ctx, int *status);

@@ -94,3 +94,31 @@ def test_fused_timeline_marks_every_slot_in_launch_order(rt, pair):
         assert (m > 0).all() and (m[:, 0] <= m[:, 1]).all() and (m[:, 1] <= m[:, 2]).all()
     assert marks[1][:, 2].min() >= marks[0][:, 2].max() and marks[2][:, 2].min() >= marks[1][:, 2].max()
     assert rt.read_status() == 0
+
+
+def test_which_operators_share_an_sm(rt):
+    """The effect the patterns exist for is which operators end up on the same SM (the reference looks at
+    it through %smid logs, tests/interleave_scheduler/test/test_scheduler.py:40-120).  The hardware deals
+    consecutive CTAs to the two SMs of a TPC in turn, so under strict 1 : 1 alternation even CTAs -- one
+    operator -- land on even SMs and odd CTAs on odd SMs: no SM hosts both operators, the pattern acts as
+    a split of every TPC.  Runs of two (M = 1, N = 2) put both operators on at least 80 % of the SMs.
+    The range split gives the whole first round of CTAs to the first operator."""
+    rng = np.random.default_rng(2)
+    a = wl.softmax("sm", rng, 6144, 512, 0.125)       # 768 CTAs
+    b = wl.layernorm("ln", rng, 3072, 768, 1e-5)      # 768 CTAs
+    pair = wl.DevicePair(rt, wl.PairSpec("mix", a, b, "f32", "hbm"))
+    assert a.launch[0][0] == b.launch[0][0] == 768
+
+    def sms_with_both(pattern, m, n):
+        kern, _, sm = rt.trace_fused(pair.fusion(pattern, m, n))
+        both = sum(len(set(kern[sm == s].tolist())) == 2 for s in range(rt.sm_count))
+        return both / rt.sm_count, kern, sm
+
+    runs_of_two, _, _ = sms_with_both(bf.ZIGZAG, 1, 2)
+    strict, kern, sm = sms_with_both(bf.ZIGZAG, 1, 1)
+    print("SMs that host both operators: zig-zag 2:2 %.2f, 1:1 %.2f" % (runs_of_two, strict))
+    assert runs_of_two >= 0.8
+    assert strict <= 0.2
+    assert all(len(set((np.nonzero(sm == s)[0] % 2).tolist())) <= 1 for s in range(rt.sm_count))   # an SM sees CTAs of one parity
+    _, kern, sm = sms_with_both(bf.RANGE_SPLIT, 0, 0)
+    assert set(kern[:rt.sm_count].tolist()) == {0}
