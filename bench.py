@@ -4,27 +4,30 @@ unfused launches of the same bodies, fraction of the pair's roofline.
 
     python bench.py --gpus N --steps K --warmup W [--impl reference]
 
-Workload (config.workload): the BERT-base Q-projection || K-projection pair -- two independent
-[512x768]x[768x768]+bias GEMMs, fp32 in, tf32 tensor cores, fp32 accumulate -- on seeded synthetic
-inputs.  One "step" is one pass over R independent instances of the pair (distinct buffers, like
-the layers of a model) replayed from a CUDA graph; R is chosen so the instances together are
-larger than twice the 126 MB L2, so every launch reads its operands from HBM.  Multi-GPU: each fused
-pair runs on one GPU and there is no exchange step, so the headline pair runs as replicas (every
-rank the same step on its own GPU, max over ranks reported); the partitioned workloads ride along
-in the same line: `pairs` (the other BASELINE pairs, pair i measured on rank i mod N) and
-`conv_n256_sharded` (the ResNet branch pair at batch 256, images split evenly across the ranks, no
-collective, time = max over ranks).  `reference_fuser_output` times the reference fuser's own
-generated kernels (baseline/_ref/*.cubin, batch-1024 fp32 shapes) beside this runtime's pair at
-the same shapes.
+Workload (config.workload): the largest single-GPU configuration -- the ResNet-18 branch pair, a 3x3
+stride-2 conv || a 1x1 stride-2 downsample conv, 64 -> 128 channels, over ONE seeded batch of 256
+images [64, 56, 56] (fp32 in, tf32 tensor cores, fp32 accumulate; 617 MB of algorithmic traffic).  With
+--gpus N the images are split across the ranks (rank r takes the slice partition.shard_batch gives it,
+no collective on the data path), so the job is the same 256 images at every N: strong scaling.  One
+"step" is one fused launch over the rank's shard; consecutive steps rotate over R instances of the
+shard (distinct buffers) so that the steps' inputs together exceed twice the 126 MB L2.  `value` =
+microseconds per fused pair over the whole batch (the slowest rank), inputs resident in HBM; `e2e` =
+the same metric through bfuse_run_fuse_batch with pinned HOST buffers (H2D of the shard, fused launches,
+D2H of both outputs inside the timed region, the transfers of neighbouring sub-shards overlapping).
 
-One JSON line on stdout (rank 0).  `value` = microseconds per fused pair, inputs resident in HBM;
-`e2e` = the same metric through bfuse_run_fuse_batch with pinned HOST buffers (H2D of every input,
-launch, D2H of every output inside the timed region; transfers of neighbouring pairs overlap).  `--impl reference` times the CPU
-restatement of the same pair (the reference has no CPU operator code of its own) on the host cores.
+The other BASELINE pairs ride along as side measurements (pair i on rank i mod N); `per_config`, the
+LAST key of the line, holds every configuration's best fused / sequential microseconds, roofline fraction
+and pattern.  `reference_fuser_output` times the reference fuser's own generated kernels
+(baseline/_ref/*.cubin, batch-1024 fp32 shapes) beside this runtime's pair at the same shapes.
+`--impl reference` times the CPU restatement of the same pair (the reference has no CPU operator code of
+its own) on the host cores, on a stated sample of the images.
+
+One JSON line on stdout (rank 0).
 """
 import argparse
 import json
 import os
+import re
 import sys
 import threading
 import time
@@ -32,10 +35,24 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-WORKLOAD = "cfg2_q_k_proj"
-NCU_TRAFFIC_BYTES = 7954944   # dram__bytes_read.sum + dram__bytes_write.sum of the fused kernel, one launch (profiles/)
+WORKLOAD = "cfg5_conv_branches_n256"
+WORKLOAD_DESC = (WORKLOAD + ": ResNet-18 3x3 s2 conv || 1x1 s2 downsample, 64->128 channels, one seeded batch of 256 x [64,56,56] "
+                 "fp32 NCHW, tf32 MMA with fp32 accumulate; images split across the GPUs")
+BATCH = 256
+CONV_PROFILE = os.path.join(ROOT, "profiles", "fused_conv_tf32_pair_cfg5.md")
 L2_BYTES = 126 * 1024 * 1024
 NAIVE_BODY_PAIRS = ("cfg2_q_k_proj", "cfg3_qkt_res_layernorm", "cfg5_conv_branches")   # fp32 pairs with a CUDA-core body
+CPU_SAMPLE_IMAGES = 32
+
+
+def dram_bytes_per_image():
+    """DRAM read + write bytes per image of the fused conv kernel, from the line `dram_bytes_per_image: N`
+    of the committed ncu summary (the capture runs a smaller batch; traffic grows in proportion to it)."""
+    try:
+        m = re.search(r"dram_bytes_per_image:\s*([0-9.eE+]+)", open(CONV_PROFILE).read())
+        return float(m.group(1)) if m else None
+    except OSError:
+        return None
 
 
 def peaks():
@@ -99,48 +116,67 @@ class ClockSampler:
         return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": self.max_mhz, "reasons": reasons, "samples": len(rows)}
 
 
-def cpu_pair_time(spec, budget_s=8.0):
-    """Time the oracle's plain loops (OpenMP) on one instance of the pair; microseconds per pair."""
+def cpu_conv_pair(images, seed=0, runs=1):
+    """The oracle's plain loops (C + OpenMP, all host cores) over `images` images of the seeded batch, both
+    convs back to back; (best seconds over `runs`, threads used).  The batch comes from numpy's default_rng --
+    the CPU arm needs the values' distribution, not the device generator's bits."""
+    import numpy as np
     import oracle
     oracle.set_num_threads(len(os.sched_getaffinity(0)))   # all host cores, whatever OMP_NUM_THREADS a launcher exported
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((images, 64, 56, 56), dtype=np.float32)
+    w3 = (np.sqrt(2.0 / 576) * rng.standard_normal((128, 64, 3, 3), dtype=np.float32)).astype(np.float32)
+    w1 = (np.sqrt(2.0 / 64) * rng.standard_normal((128, 64, 1, 1), dtype=np.float32)).astype(np.float32)
+    best = None
+    for _ in range(runs):
+        t0 = time.perf_counter()
+        oracle.conv2d_nchw(x, w3, 2, 1)
+        oracle.conv2d_nchw(x, w1, 2, 0)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return best, oracle.num_threads()
+
+
+def cpu_pair_time(spec, budget_s=8.0):
+    """Time the oracle's plain loops (OpenMP) on one instance of a pair; microseconds per pair."""
+    import oracle
+    oracle.set_num_threads(len(os.sched_getaffinity(0)))
     oracle_outputs = _load_pair_oracle().oracle_outputs
     oracle_outputs(spec.a), oracle_outputs(spec.b)  # warm-up
     best, n, t_end = None, 0, time.perf_counter() + budget_s
-    while n < 5 or (time.perf_counter() < t_end and n < 50):
+    while n < 3 or (time.perf_counter() < t_end and n < 50):
         t0 = time.perf_counter()
         oracle_outputs(spec.a)
         oracle_outputs(spec.b)
         dt = time.perf_counter() - t0
         best = dt if best is None else min(best, dt)
         n += 1
-        if time.perf_counter() > t_end and n >= 5:
-            break
     return best * 1e6, n, oracle.num_threads()
 
 
 def run_reference(args):
-    """CPU arm: the oracle port of the same pair on the host cores (rank 0 only)."""
+    """CPU arm: the oracle port of the same pair on the host cores (rank 0 only).  One step = the pair over
+    CPU_SAMPLE_IMAGES images of the batch, scaled to the 256 images of the job."""
     if int(os.environ.get("RANK", "0")) != 0:
         return
-    from bfuse_project_b200 import workloads as wl
-    spec = wl.make_pair(WORKLOAD, seed=0)
-    us, n, cores = None, 0, 0
-    samples = []
+    cores = 0
     for _ in range(args.warmup):
-        cpu_pair_time(spec, 0.0)
+        cpu_conv_pair(CPU_SAMPLE_IMAGES)
+    samples = []
     for _ in range(args.steps):
-        u, n, cores = cpu_pair_time(spec, 2.0)
-        samples.append(u)
+        sec, cores = cpu_conv_pair(CPU_SAMPLE_IMAGES)
+        samples.append(sec * 1e6 * BATCH / CPU_SAMPLE_IMAGES)
     us = sum(samples) / len(samples)
     line = {
         "impl": "reference", "metric": "fused_pair_us", "value": us, "unit": "us", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": us / 1e3, "higher_is_better": False,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD + ": BERT-base Q||K projection, 2x([512x768]x[768x768]+bias)",
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD_DESC,
                    "note": "the reference ships no CPU operator code; this is the plain C/OpenMP restatement "
-                           "(oracle/), both GEMMs back to back, best of >=5 runs per step"},
+                           "(oracle/), both convs back to back on all host cores"},
         "cpu_baseline": {"value": us, "unit": "us", "cores": cores, "kind": "port",
-                         "sample": "one full pair per run (1.2 GFLOP), best of %d runs per step" % n},
+                         "sample": "%d of the 256 images per step (%.2f GFLOP), time scaled by %d" % (
+                             CPU_SAMPLE_IMAGES, CPU_SAMPLE_IMAGES * 0.1285, BATCH // CPU_SAMPLE_IMAGES)},
         "e2e": {"value": us, "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -200,12 +236,42 @@ def replay_us(rt, torch, graph, launches, reps=5, warm=3):
     return e0.elapsed_time(e1) * 1e3 / (reps * launches)
 
 
-MODES = (("fused_zigzag", "ZIGZAG", 4), ("fused_range", "RANGE_SPLIT", 4), ("fused_striped", "SM_STRIPED", 4),
-         ("fused_queue", "WORK_QUEUE", 4), ("fused_thread_split", "THREAD_SPLIT", 4), ("sequential", "ZIGZAG", 3),
-         ("parallel", "ZIGZAG", 2))
+# (label, pattern, harness mode, M, N); zig-zag in runs of two puts both operators on every SM, strict
+# alternation sends them to alternate SMs (the hardware deals consecutive CTAs to the two SMs of a TPC)
+MODES = (("fused_zigzag", "ZIGZAG", 4, 1, 1), ("fused_zigzag2", "ZIGZAG", 4, 1, 2), ("fused_range", "RANGE_SPLIT", 4, 0, 0),
+         ("fused_striped", "SM_STRIPED", 4, 0, 0), ("fused_queue", "WORK_QUEUE", 4, 1, 1), ("fused_thread_split", "THREAD_SPLIT", 4, 0, 0),
+         ("sequential", "ZIGZAG", 3, 1, 1), ("parallel", "ZIGZAG", 2, 1, 1))
 
 
-def measure_pair(rt, torch, bf, wl, pk, name, device, conv_batch=1, max_reps=24):
+class L2Flusher:
+    """Writes a buffer larger than the L2 so that the next launch starts cold."""
+
+    def __init__(self, torch, device):
+        self.buf = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=torch.device("cuda", device))
+
+    def flush(self):
+        self.buf.fill_(1)
+
+
+def isolated_us(rt, torch, flusher, launch, n=5):
+    """Microseconds of ONE launch, CUDA events around it, L2 flushed before: what a caller sees who launches
+    the pair once, as opposed to the amortised figure of a graph replay over many instances."""
+    stream = torch.cuda.current_stream().cuda_stream
+    best = None
+    for _ in range(n):
+        flusher.flush()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        launch(stream)
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3
+        best = us if best is None else min(best, us)
+    return best
+
+
+def measure_pair(rt, torch, bf, wl, pk, name, device, conv_batch=1, max_reps=24, flusher=None):
     """Fused (every pattern that can host the pair) / sequential / two-stream microseconds of one
     BASELINE pair, replayed over enough instances to exceed twice the L2."""
     spec = wl.make_pair(name, seed=0, conv_batch=conv_batch)
@@ -213,18 +279,26 @@ def measure_pair(rt, torch, bf, wl, pk, name, device, conv_batch=1, max_reps=24)
     pairs = [wl.DevicePair(rt, spec if s == 0 else wl.make_pair(name, seed=s, conv_batch=conv_batch), device) for s in range(reps)]
     res = {"instances": reps, "alg_bytes": spec.bytes, "alg_flops": spec.flops, "dtype": spec.dtype,
            "launch": [list(spec.a.launch[0]) + list(spec.a.launch[1]), list(spec.b.launch[0]) + list(spec.b.launch[1])]}
-    for label, pattern, mode in MODES:
+    for label, pattern, mode, m, n in MODES:
         pat = getattr(bf, pattern)
-        mn = 1 if pat in (bf.ZIGZAG, bf.WORK_QUEUE) else 0
         try:
-            fus = [p.fusion(pat, mn, mn) for p in pairs]
+            fus = [p.fusion(pat, m, n) for p in pairs]
         except bf.BfuseError as e:
             if e.code not in (3, 7):
                 raise
-            continue   # the pattern cannot host this pair (clustered operators; thread split: windows or TMEM over budget)
-        res[label + "_us"] = replay_us(rt, torch, rt.graph_create(fus, mode), reps)
-    best = min(v for k, v in res.items() if k.startswith("fused_"))
+            continue   # the pattern cannot host this pair (thread split: windows or tensor memory over budget)
+        g = rt.graph_create(fus, mode)
+        res[label + "_us"] = replay_us(rt, torch, g, reps)
+        rt.graph_destroy(g)
+    best_label = min((k for k in res if k.startswith("fused_")), key=lambda k: res[k])
+    best = res[best_label]
     res["best_fused_us"] = best
+    res["best_pattern"] = best_label[len("fused_"):-len("_us")]
+    if flusher is not None:
+        lab = [x for x in MODES if "fused_" + res["best_pattern"] == x[0]][0]
+        f0 = pairs[0].fusion(getattr(bf, lab[1]), lab[3], lab[4])
+        res["isolated_fused_us"] = isolated_us(rt, torch, flusher, lambda st: rt.launch_fused(f0, st))
+        res["isolated_sequential_us"] = isolated_us(rt, torch, flusher, lambda st: rt.launch_sequential(f0, st))
     res["speedup_vs_sequential"] = res["sequential_us"] / best
     res["speedup_vs_parallel_streams"] = res["parallel_us"] / best
     tensor_peak = pk["bf16_tflops"] * (1e6 if spec.dtype == "bf16" else 0.5e6)   # flop per us; tf32 = half of bf16
@@ -380,6 +454,56 @@ def reference_fuser_output(rt, torch, bf, wl, pk):
     return out
 
 
+def bind_to_gpu_numa_node(torch, local):
+    """Pin this process (and so the pinned buffers it allocates next, by first touch) to the CPUs of the NUMA
+    node the GPU hangs off, read from sysfs for the GPU's PCI address; returns what was found."""
+    info = {"pci": None, "numa_node": None, "cpus": None}
+    try:
+        bus = torch.cuda.get_device_properties(local).pci_bus_id
+        dom = getattr(torch.cuda.get_device_properties(local), "pci_domain_id", 0)
+        dev = getattr(torch.cuda.get_device_properties(local), "pci_device_id", 0)
+        addr = "%04x:%02x:%02x.0" % (dom, bus, dev)
+        info["pci"] = addr
+        base = "/sys/bus/pci/devices/" + addr
+        node = int(open(base + "/numa_node").read())
+        info["numa_node"] = node
+        cpus = set()
+        for part in open(base + "/local_cpulist").read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        cpus &= os.sched_getaffinity(0)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+            info["cpus"] = len(cpus)
+    except Exception as e:   # no sysfs entry (containers): stay where the launcher put us, and say so
+        info["note"] = str(e)[:80]
+    return info
+
+
+def copy_bandwidth(torch, host_in, dev_in, dev_outs, host_outs, reps=3):
+    """Plain pinned-memory copies of the e2e step's bytes -- the input in, both outputs out -- in both directions at
+    once on two streams: what the link delivers with no kernel in between (GB/s per direction, microseconds)."""
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    best = None
+    for _ in range(reps):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        with torch.cuda.stream(s1):
+            dev_in.copy_(host_in, non_blocking=True)
+        with torch.cuda.stream(s2):
+            for h, d in zip(host_outs, dev_outs):
+                h.copy_(d, non_blocking=True)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    out_bytes = sum(h.numel() * h.element_size() for h in host_outs)
+    return {"h2d_gbs": host_in.numel() * host_in.element_size() / best / 1e9, "d2h_gbs": out_bytes / best / 1e9, "copies_alone_us": best * 1e6}
+
+
+PATTERNS = (("zigzag", "ZIGZAG", 1, 1), ("zigzag2", "ZIGZAG", 1, 2), ("range", "RANGE_SPLIT", 0, 0), ("striped", "SM_STRIPED", 0, 0),
+            ("queue", "WORK_QUEUE", 1, 1), ("thread_split", "THREAD_SPLIT", 0, 0))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -392,6 +516,7 @@ def main():
     ap.add_argument("--sweep-limit", type=int, default=0, help="with --sweep: only the first N operators")
     ap.add_argument("--sweep-pattern", default="zigzag", choices=["zigzag", "range", "striped", "proportional"],
                     help="with --sweep: the block-level pattern of the fused launches")
+    ap.add_argument("--batch", type=int, default=BATCH, help="images of the conv batch (256: the BASELINE configuration; smaller for profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
 
@@ -402,12 +527,14 @@ def main():
     import torch
 
     import bfuse_project_b200 as bf
+    from bfuse_project_b200 import partition
     from bfuse_project_b200 import workloads as wl
 
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     torch.cuda.set_device(local)
+    numa = bind_to_gpu_numa_node(torch, local)
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
@@ -416,137 +543,158 @@ def main():
     rt = bf.Runtime(local)
     if args.sweep:
         return run_sweep(args, rt, torch, rank, world, local, pk)
-    spec0 = wl.make_pair(WORKLOAD, seed=0)
-    reps = int(2.2 * L2_BYTES / spec0.bytes) + 1           # instances per step, together > 2 x L2
-    specs = [spec0] + [wl.make_pair(WORKLOAD, seed=s) for s in range(1, reps)]
-    pairs = [wl.DevicePair(rt, s, local) for s in specs]
     stream = torch.cuda.current_stream().cuda_stream
+    flusher = L2Flusher(torch, local)
 
-    def graph_for(pattern, mode, m=1, n=1):
+    def max_over_ranks(v):
+        if world == 1:
+            return v
+        t = torch.tensor(v if isinstance(v, list) else [v], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.tolist() if isinstance(v, list) else float(t.item())
+
+    # ---- the headline workload: this rank's shard of the one seeded batch, R instances of it ----------------
+    batch = args.batch
+    first, count = partition.shard_batch(batch, world, rank)
+    proto = wl.ConvBranchBatch(rt, torch, local, 1, seed=0)
+    shard_distinct = (proto.bytes(count) - 4 * count * proto.CI * proto.H * proto.W)      # x once + weights + both outputs
+    reps = max(2, int(2.2 * L2_BYTES / shard_distinct) + 1)
+    del proto
+    batches = [wl.ConvBranchBatch(rt, torch, local, batch, seed=i) for i in range(reps)]   # instance 0 is THE batch; every rank holds the same one
+    kernels = [b.shard(first, count) for b in batches]
+    alg_bytes_total = batches[0].bytes(batch)
+    alg_flops_total = batches[0].flops(batch)
+
+    def fusions(pat, m, n):
         try:
-            return rt.graph_create([p.fusion(pattern, m, n) for p in pairs], mode)
+            return [rt.register_fusion(k3, k1, getattr(bf, pat), m, n) for k3, k1 in kernels]
         except bf.BfuseError as e:
             if e.code not in (3, 7):
                 raise
-            return None   # the pattern cannot host this pair (clustered operators; thread split: windows or TMEM over budget)
+            return None   # the pattern cannot host this pair (thread split: the two windows do not fit one CTA)
 
-    graphs = {"fused_zigzag": graph_for(bf.ZIGZAG, bf.MODE_FUSED), "fused_range": graph_for(bf.RANGE_SPLIT, bf.MODE_FUSED, 0, 0),
-              "fused_striped": graph_for(bf.SM_STRIPED, bf.MODE_FUSED, 0, 0),
-              "fused_queue": graph_for(bf.WORK_QUEUE, bf.MODE_FUSED), "fused_thread_split": graph_for(bf.THREAD_SPLIT, bf.MODE_FUSED, 0, 0),
-              "sequential": graph_for(bf.ZIGZAG, bf.MODE_SEQUENTIAL),
-              "parallel": graph_for(bf.ZIGZAG, bf.MODE_PARALLEL)}
-    graphs = {k: g for k, g in graphs.items() if g is not None}
+    def graph_of(fus, mode, steps):
+        return rt.graph_create([fus[i % reps] for i in range(steps)], mode)
 
-    def timed(graph, steps, warmup):
-        for _ in range(warmup):
-            rt.graph_launch(graph, stream)
+    def timed(graph, steps, warm_graph=None, warm=0):
+        """Exactly `steps` steps (one graph launch of that many kernel nodes), CUDA events on the launching
+        stream, barrier + synchronize on both sides; milliseconds, the slowest rank."""
+        for _ in range(warm):
+            rt.graph_launch(warm_graph, stream)
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
             torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for _ in range(steps):
-            rt.graph_launch(graph, stream)
+        rt.graph_launch(graph, stream)
         e1.record()
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
-        ms = e0.elapsed_time(e1)
-        if world > 1:
-            t = torch.tensor([ms], device="cuda")
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms
+        return max_over_ranks(e0.elapsed_time(e1))
 
+    fus = {name: fusions(pat, m, n) for name, pat, m, n in PATTERNS}
+    fus = {k: v for k, v in fus.items() if v is not None}
     # spin ~100 ms first so the clocks have left their idle state, pick the fused pattern on a short
-    # trial, then time exactly K steps of it under the clock sampler
+    # trial (best of the patterns, the same on every rank), then time exactly K steps of it
+    one_step = {k: graph_of(v, bf.MODE_FUSED, 1) for k, v in fus.items()}
     t_spin = time.perf_counter()
     while time.perf_counter() - t_spin < 0.1:
-        rt.graph_launch(graphs["sequential"], stream)
+        rt.graph_launch(one_step["range"], stream)
         torch.cuda.synchronize()
-    trial = {k: timed(g, 3, 3) for k, g in graphs.items()}
-    best = min((k for k in trial if k.startswith("fused_")), key=lambda k: trial[k])
+    trial_steps = 2 * reps
+    trial = {k: timed(graph_of(v, bf.MODE_FUSED, trial_steps), trial_steps, one_step[k], 3) / trial_steps for k, v in fus.items()}
+    best = min(trial, key=lambda k: trial[k])
+    main_graph = graph_of(fus[best], bf.MODE_FUSED, args.steps)
     sampler = ClockSampler(local, getattr(torch.cuda.get_device_properties(local), "uuid", None))
     if rank == 0:
         sampler.start()
-    ms = timed(graphs[best], args.steps, args.warmup)
+    ms = timed(main_graph, args.steps, one_step[best], args.warmup)
     clocks = sampler.stop() if rank == 0 else None
-    side = {k: timed(g, args.steps, 3) * 1e3 / (args.steps * reps) for k, g in graphs.items() if k != best}
-    us_pair = ms * 1e3 / (args.steps * reps)
-    side[best] = us_pair
+    us_pair = ms * 1e3 / args.steps
+    side = {"fused_" + k: v * 1e3 for k, v in trial.items()}
+    side["fused_" + best] = us_pair
+    for label, mode in (("sequential", bf.MODE_SEQUENTIAL), ("parallel", bf.MODE_PARALLEL)):
+        side[label] = timed(graph_of(fus[best], mode, args.steps), args.steps, graph_of(fus[best], mode, 1), 3) * 1e3 / args.steps
     assert rt.read_status() == 0, "a bounded device-side wait gave up during the benchmark"
+    iso_fused = max_over_ranks(isolated_us(rt, torch, flusher, lambda st: rt.launch_fused(fus[best][0], st)))
+    iso_seq = max_over_ranks(isolated_us(rt, torch, flusher, lambda st: rt.launch_sequential(fus[best][0], st)))
 
     # what was just timed must equal the unfused launches of the same bodies, bit for bit
-    fused_out = pairs[0].read_outputs()
-    pairs[0].clear_outputs()
-    rt.launch_sequential(pairs[0].fusion(bf.ZIGZAG, 1, 1), stream)
-    seq_out = pairs[0].read_outputs()
-    for k in range(2):
-        assert np.array_equal(fused_out[k][0].view(np.uint8), seq_out[k][0].view(np.uint8)), "fused != unfused"
+    b0 = batches[0]
+    fused_out = (b0.y3[first:first + count].clone(), b0.y1[first:first + count].clone())
+    b0.clear_outputs()
+    rt.launch_sequential(fus[best][0], stream)
+    torch.cuda.synchronize()
+    assert torch.equal(fused_out[0], b0.y3[first:first + count]) and torch.equal(fused_out[1], b0.y1[first:first + count]), "fused != unfused"
+    assert bool(fused_out[0].any()) and bool(fused_out[1].any())
 
-    # end to end through the host-buffer entry point: pinned host inputs and outputs
-    def pinned_like(arr):
-        t = torch.from_numpy(arr.copy()).pin_memory() if arr.dtype != np.uint16 else \
-            torch.from_numpy(arr.view(np.int16).copy()).pin_memory()
-        return t
+    # ---- end to end through the host-buffer entry point: pinned host inputs and outputs ----------------------
+    # The shard goes through bfuse_run_fuse_batch in sub-shards, so that the copy in of sub-shard i + 1, the fused
+    # launch of sub-shard i and the copy out of sub-shard i - 1 overlap on three streams.
+    hx = b0.x[first:first + count].cpu().pin_memory()
+    hw3, hw1 = b0.w3.cpu().pin_memory(), b0.w1.cpu().pin_memory()
+    hy3 = torch.zeros(count, b0.CO, b0.OH, b0.OW).pin_memory()
+    hy1 = torch.zeros(count, b0.CO, b0.OH, b0.OW).pin_memory()
+    pat_name = [x for x in PATTERNS if x[0] == best][0]
 
-    e2e_pairs = pairs[: min(8, reps)]
-    host = []
-    for p in e2e_pairs:
-        h = [[None if a is None else pinned_like(a) for a in ks.host] for ks in (p.spec.a, p.spec.b)]
-        host.append([[None if t is None else t.numpy() for t in hk] for hk in h] + [h])
-    best_pat = {"fused_zigzag": bf.ZIGZAG, "fused_range": bf.RANGE_SPLIT, "fused_queue": bf.WORK_QUEUE, "fused_striped": bf.SM_STRIPED,
-                "fused_thread_split": bf.THREAD_SPLIT}[best]
-    best_mn = 1 if best_pat in (bf.ZIGZAG, bf.WORK_QUEUE) else 0
-    fus = [p.fusion(best_pat, best_mn, best_mn) for p in e2e_pairs]
-    for i in range(min(3, len(fus))):
-        rt.run_fuse(fus[i], host[i][0], host[i][1])
-    rt.run_fuse_batch(fus, [h[0] for h in host], [h[1] for h in host])
-    t0 = time.perf_counter()
-    for i, f in enumerate(fus):    # the same pairs one synchronous call each, as the reference's run_fuse does
-        rt.run_fuse(f, host[i][0], host[i][1])
-    e2e_sync_us = (time.perf_counter() - t0) * 1e6 / len(fus)
+    def e2e_plan(sub):
+        pieces = [(first + o, min(sub, count - o)) for o in range(0, count, sub)]
+        fl, h1, h2 = [], [], []
+        for f0, c0 in pieces:
+            k3, k1 = b0.shard(f0, c0)
+            fl.append(rt.register_fusion(k3, k1, getattr(bf, pat_name[1]), pat_name[2], pat_name[3]))
+            o = f0 - first
+            h1.append([hx[o:o + c0].numpy(), hw3.numpy(), hy3[o:o + c0].numpy()])
+            h2.append([hx[o:o + c0].numpy(), hw1.numpy(), hy1[o:o + c0].numpy()])   # the same host and device input: copied once
+        return pieces, fl, h1, h2
+
+    # sub-shard size: the caller's choice; fewer pieces leave more of the first copy in and the last copy out
+    # exposed, more pieces pay more per-call overhead -- the best of three sizes on a short trial
     e2e_steps = max(3, min(args.steps, 10))
+    plans = {}
+    for sub in sorted({max(1, count // d) for d in (4, 8, 16)}):
+        plan = e2e_plan(sub)
+        b0.clear_outputs()
+        hy3.zero_(), hy1.zero_()
+        rt.run_fuse_batch(plan[1], plan[2], plan[3])
+        assert torch.equal(hy3, fused_out[0].cpu()) and torch.equal(hy1, fused_out[1].cpu()), "e2e outputs differ from the device-resident run"
+        t0 = time.perf_counter()
+        for _ in range(2):
+            rt.run_fuse_batch(plan[1], plan[2], plan[3])
+        plans[sub] = (max_over_ranks(time.perf_counter() - t0), plan)
+    sub = min(plans, key=lambda k: plans[k][0])
+    pieces, e2e_fus, h1, h2 = plans[sub][1]
     if world > 1:
         dist.barrier()
     t0 = time.perf_counter()
-    for _ in range(e2e_steps):     # one call per step: the pairs' copies in, launches and copies out overlap on three streams
-        rt.run_fuse_batch(fus, [h[0] for h in host], [h[1] for h in host])
-    e2e_s = time.perf_counter() - t0
+    for _ in range(e2e_steps):
+        rt.run_fuse_batch(e2e_fus, h1, h2)
+    e2e_us = max_over_ranks((time.perf_counter() - t0) * 1e6 / e2e_steps)
+    h2d = hx.numel() * 4 + (hw3.numel() + hw1.numel()) * 4 * len(pieces)
+    d2h = (hy3.numel() + hy1.numel()) * 4
+    link = copy_bandwidth(torch, hx, b0.x[first:first + count], (b0.y3[first:first + count], b0.y1[first:first + count]), (hy3, hy1))
+    link["copies_alone_us"] = max_over_ranks(link["copies_alone_us"])
+    link["e2e_h2d_gbs"] = h2d / (e2e_us * 1e-6) / 1e9
+    link["e2e_d2h_gbs"] = d2h / (e2e_us * 1e-6) / 1e9
+    link["e2e_over_copies_alone"] = e2e_us / link["copies_alone_us"]
     if world > 1:
-        t = torch.tensor([e2e_s], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t.item())
-    e2e_us = e2e_s * 1e6 / (e2e_steps * len(fus))
-    h2d = sum(a.nbytes for ks in (spec0.a, spec0.b) for i, a in enumerate(ks.host) if a is not None and i not in ks.outputs)
-    d2h = sum(ks.host[i].nbytes for ks in (spec0.a, spec0.b) for i in ks.outputs)
+        agg = torch.tensor([link["h2d_gbs"], link["d2h_gbs"]], device="cuda", dtype=torch.float64)
+        dist.all_reduce(agg, op=dist.ReduceOp.SUM)
+        link["all_ranks_h2d_gbs"], link["all_ranks_d2h_gbs"] = agg.tolist()
+    del hx, hy3, hy1
 
-    # ---- partitioned side workloads (no collective on the data path) --------------------------------
-    side_pairs, conv256 = {}, None
+    # ---- side measurements: the other BASELINE pairs (pair i on rank i mod N) ---------------------------------
+    side_pairs = {}
     if not args.quick:
-        from bfuse_project_b200 import partition
-        names = [n for n in wl.pair_names() if n != WORKLOAD]
-        for name in partition.assign_pairs(names, world, rank):   # pair sweep: pair i on rank i mod N
-            if True:
-                try:
-                    side_pairs[name] = measure_pair(rt, torch, bf, wl, pk, name, local)
-                    side_pairs[name]["rank"] = rank
-                except Exception as e:                  # a pair that cannot run is reported, not hidden
-                    side_pairs[name] = {"error": str(e)[:300], "rank": rank}
-        # ResNet branch pair at batch 256, images split across the ranks
-        per_rank = partition.shard_batch(256, world, rank)[1]
-        try:
-            r = measure_pair(rt, torch, bf, wl, pk, "cfg5_conv_branches", local, conv_batch=per_rank, max_reps=2)
-            t = torch.tensor([r["best_fused_us"], r["sequential_us"]], device="cuda")
-            if world > 1:
-                dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            conv256 = {"images_total": 256, "images_per_rank": per_rank, "fused_us": float(t[0]), "sequential_us": float(t[1]),
-                       "speedup_vs_sequential": float(t[1] / t[0]), "alg_bytes_total": r["alg_bytes"] * world,
-                       "roofline_us": r["alg_bytes"] / (pk["hbm_gbs"] * 1e3), "images_per_s": 256 / (float(t[0]) * 1e-6)}
-            conv256["roofline_frac"] = conv256["roofline_us"] / conv256["fused_us"]
-        except Exception as e:
-            conv256 = {"error": str(e)[:300]}
+        names = wl.pair_names()
+        for name in partition.assign_pairs(names, world, rank):
+            try:
+                side_pairs[name] = measure_pair(rt, torch, bf, wl, pk, name, local, flusher=flusher)
+                side_pairs[name]["rank"] = rank
+            except Exception as e:                  # a pair that cannot run is reported, not hidden
+                side_pairs[name] = {"error": str(e)[:300], "rank": rank}
         if world > 1:
             gathered = [None] * world
             dist.all_gather_object(gathered, side_pairs)
@@ -556,44 +704,65 @@ def main():
         if world > 1:
             dist.destroy_process_group()
         return
-    cpu_us, cpu_n, cores = cpu_pair_time(spec0, 10.0)
-    t_roof_us = max(spec0.bytes / (pk["hbm_gbs"] * 1e3), spec0.flops / (pk["bf16_tflops"] * 0.5e6))
-    achieved = spec0.bytes / (us_pair * 1e-6) / 1e9
-    info = rt.fusion_info(pairs[0].fusion(best_pat, best_mn, best_mn))   # the kernel that was timed
+    cpu_s, cores = cpu_conv_pair(CPU_SAMPLE_IMAGES, runs=3)
+    cpu_us = cpu_s * 1e6 * batch / CPU_SAMPLE_IMAGES
+    hbm_us = alg_bytes_total / (pk["hbm_gbs"] * 1e3)
+    tensor_us = alg_flops_total / (pk["bf16_tflops"] * 0.5e6)
+    # roofline of the dominant kernel (the fused conv pair of one rank): algorithmic bytes of one launch over
+    # the launch's average duration inside the timed region
+    launch_bytes = batches[0].bytes(count)
+    achieved = launch_bytes / (us_pair * 1e-6) / 1e9
+    per_image = dram_bytes_per_image()
+    info = rt.fusion_info(fus[best][0])
     line = {
         "metric": "fused_pair_us", "value": us_pair, "unit": "us", "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": False, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": False, "scaling": "strong",
         "vs_baseline": None, "dtype": "tf32", "data": "synthetic",
-        "config": {"workload": WORKLOAD + ": BERT-base Q||K projection, 2x([512x768]x[768x768]+bias), fp32 in, tf32 MMA",
-                   "pattern": best, "instances_per_step": reps, "launch": "CUDA graph replay of %d fused launches" % reps,
-                   "l2": "inputs larger than L2: %d instances x %.1f MB = %.0f MB vs 126 MB L2" % (reps, spec0.bytes / 1e6, reps * spec0.bytes / 1e6),
-                   "multi_gpu": "replicas only" if world > 1 else "n/a",
-                   "fused_kernel": info},
+        "config": {"workload": WORKLOAD_DESC if batch == BATCH else WORKLOAD_DESC.replace("256", str(batch)),
+                   "pattern": best, "pattern_choice": "best of %d patterns on a %d-step trial, the same on every rank" % (len(trial), trial_steps),
+                   "images_per_rank": count, "instances": reps,
+                   "launch": "one CUDA graph of %d fused launches, rotating over %d instances of the shard" % (args.steps, reps),
+                   "l2": "inputs larger than L2: %d instances x %.0f MB = %.0f MB touched per rotation vs 126 MB L2" % (reps, shard_distinct / 1e6, reps * shard_distinct / 1e6),
+                   "multi_gpu": "images [r*256/N, (r+1)*256/N) of the one seeded batch on rank r, no collective on the data path",
+                   "fused_kernel": info, "host": numa},
         "speedup_vs_sequential": side["sequential"] / us_pair,
         "speedup_vs_parallel_streams": side["parallel"] / us_pair,
         "us": side,
-        "roofline_pair_us": t_roof_us, "roofline_pair_frac": t_roof_us / us_pair,
-        "pairs_per_s": world * 1e6 / us_pair,
+        "isolated_us": {"fused": iso_fused, "sequential": iso_seq,
+                        "note": "one launch, CUDA events around it, L2 flushed before; `value` is the per-launch average of the graph"},
+        "roofline_pair_us": max(hbm_us, tensor_us) / world, "roofline_pair_frac": max(hbm_us, tensor_us) / world / us_pair,
+        "images_per_s": batch / (us_pair * 1e-6),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                     "frac": achieved / pk["hbm_gbs"], "traffic": NCU_TRAFFIC_BYTES, "peak_source": pk["source"],
-                     "traffic_note": "dram read + write of one launch from the ncu capture summarised in "
-                                     "profiles/fused_gemm_tf32_pair_cfg2.md; the 3.15 MB of outputs are still in L2 at kernel end",
-                     "alg_bytes_per_launch": spec0.bytes, "kernel": info["KernelName"]},
+                     "frac": achieved / pk["hbm_gbs"], "traffic": None if per_image is None else per_image * count,
+                     "peak_source": pk["source"] + " (HBM copy bandwidth; the pair's tf32 time, %.1f us at half the measured bf16 burst -- "
+                                                   "no tf32 peak was measured --, is below its HBM time)" % tensor_us,
+                     "traffic_note": "dram read + write of one launch: dram_bytes_per_image of profiles/fused_conv_tf32_pair_cfg5.md "
+                                     "(ncu capture of a smaller batch; traffic grows in proportion to the images) x images per launch",
+                     "alg_bytes_per_launch": launch_bytes, "kernel": info["KernelName"],
+                     "note": "algorithmic bytes count the shared input once per operator (617 MB at batch 256; 411 MB if counted once)"},
         "cpu_baseline": {"value": cpu_us, "unit": "us", "cores": cores, "kind": "port",
-                         "sample": "one full pair (1.2 GFLOP) per run, best of %d runs" % cpu_n},
-        "e2e": {"value": e2e_us, "unit": "us", "h2d_bytes_per_step": h2d * len(fus), "d2h_bytes_per_step": d2h * len(fus),
-                "note": "bfuse_run_fuse_batch on pinned host buffers, %d pairs per call: H2D inputs, fused launch, D2H outputs of "
-                        "neighbouring pairs overlap; per pair" % len(fus),
-                "one_synchronous_call_per_pair_us": e2e_sync_us},
-        "gpu_launches": args.steps * reps,
+                         "sample": "%d of the %d images, both convs, best of 3 runs; time scaled to the batch" % (CPU_SAMPLE_IMAGES, batch)},
+        "e2e": {"value": e2e_us, "unit": "us", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "note": "bfuse_run_fuse_batch on pinned host buffers, the shard in %d sub-shards of %d images: H2D of the input, fused launch, "
+                        "D2H of both outputs of neighbouring sub-shards overlap; per 256-image pair, slowest rank" % (len(pieces), sub),
+                "link": link},
+        "gpu_launches": args.steps,
         "clocks": clocks,
     }
     if not args.quick:
         line["pairs"] = side_pairs
-        line["conv_n256_sharded"] = conv256
         line["attention_block"] = attention_block(rt, torch, bf)
         line["model_segments"] = model_segments(rt, torch, bf)
         line["reference_fuser_output"] = reference_fuser_output(rt, torch, bf, wl, pk)
+    # every configuration in one compact table, LAST in the line: [best fused us, sequential us, roofline fraction, pattern, isolated fused us]
+    table = {"cfg5_conv_branches_n%d" % batch: [round(us_pair, 2), round(side["sequential"], 2), round(max(hbm_us, tensor_us) / world / us_pair, 3), best, round(iso_fused, 2)]}
+    for name, r in side_pairs.items():
+        if "error" in r:
+            table[name] = r["error"][:60]
+        else:
+            table[name] = [round(r["best_fused_us"], 2), round(r["sequential_us"], 2), round(r["roofline_frac"], 3), r["best_pattern"],
+                           round(r.get("isolated_fused_us", 0.0), 2)]
+    line["per_config"] = table
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

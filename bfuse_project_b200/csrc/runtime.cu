@@ -1442,13 +1442,22 @@ int bfuse_set_dependent_launch(bfuse_context *ctx, int enabled) {
 
 // ---- host-buffer entry points (H2D, launch, sync, D2H) --------------------------------------------
 
-static int copy_in(bfuse_context *ctx, KernelRec &k, void *const *host, cudaStream_t s) {
+// `other` / `other_host`: the pair's first kernel, already copied in by this call -- an input of this kernel that
+// is the same device buffer fed from the same host buffer (two operators sharing their activations) is not
+// copied a second time.
+static int copy_in(bfuse_context *ctx, KernelRec &k, void *const *host, cudaStream_t s, const KernelRec *other = nullptr,
+                   void *const *other_host = nullptr) {
   // small buffers (bias, per-column tables) first: each copy pays a fixed few microseconds, which
   // then overlap the previous pair's large transfer instead of trailing this pair's
   for (int pass = 0; pass < 2; ++pass)
     for (int i = 0; i < k.nargs; ++i)
       if (!k.arg[i].is_output && k.desc.args[i] && (k.arg[i].bytes <= 65536) == (pass == 0)) {
         if (!host[i]) return fail(ctx, BFUSE_ERR_INVALID, k.name + ": missing host input buffer");
+        bool done = false;
+        for (int j = 0; other && j < other->nargs && !done; ++j)
+          done = !other->arg[j].is_output && other->desc.args[j] == k.desc.args[i] && other_host[j] == host[i] &&
+                 other->arg[j].bytes == k.arg[i].bytes;
+        if (done) continue;
         CK(cudaMemcpyAsync(k.desc.args[i], host[i], k.arg[i].bytes, cudaMemcpyHostToDevice, s));
       }
   return BFUSE_OK;
@@ -1492,7 +1501,7 @@ static int run_pair(bfuse_context *ctx, int fusion, void *const *h1, void *const
   cudaSetDevice(ctx->device);
   KernelRec &a = *ctx->kernels[f->k1], &b = *ctx->kernels[f->k2];
   int rc = copy_in(ctx, a, h1, ctx->own);
-  if (!rc) rc = copy_in(ctx, b, h2, ctx->own);
+  if (!rc) rc = copy_in(ctx, b, h2, ctx->own, &a, h1);
   if (!rc) rc = launch_mode(ctx, *f, mode, ctx->own);
   if (!rc) rc = copy_out(ctx, a, h1, ctx->own);
   if (!rc) rc = copy_out(ctx, b, h2, ctx->own);
@@ -1519,7 +1528,7 @@ int bfuse_run_fuse_batch(bfuse_context *ctx, const int *fusions, int n, void *co
     FusionRec &f = *get_fusion(ctx, fusions[i]);
     KernelRec &a = *ctx->kernels[f.k1], &b = *ctx->kernels[f.k2];
     rc = copy_in(ctx, a, h1[i], ctx->s1);
-    if (!rc) rc = copy_in(ctx, b, h2[i], ctx->s1);
+    if (!rc) rc = copy_in(ctx, b, h2[i], ctx->s1, &a, h1[i]);
     if (rc) break;
     cudaEventRecord(ev[2 * i], ctx->s1);
     cudaStreamWaitEvent(ctx->own, ev[2 * i], 0);

@@ -215,7 +215,8 @@ int bfuse_set_dependent_launch(bfuse_context *ctx, int enabled);
 
 /* Host-buffer entry points with the reference harness' semantics: H2D of every input, launch,
  * device sync, D2H of every output.  host_args follow each kernel's argument order; pointers for
- * optional arguments the kernel was registered without may be NULL. */
+ * optional arguments the kernel was registered without may be NULL.  An input that both kernels of a
+ * pair take from the same host buffer into the same device buffer (shared activations) is copied once. */
 int bfuse_run_kernel(bfuse_context *ctx, int kernel, void *const *host_args);                    /* run_kernel1/2 */
 int bfuse_run_parallel(bfuse_context *ctx, int fusion, void *const *host_args1, void *const *host_args2); /* run_parallel */
 int bfuse_run_fuse(bfuse_context *ctx, int fusion, void *const *host_args1, void *const *host_args2);     /* run_fuse     */
