@@ -216,6 +216,16 @@ struct ConvUmmaTf32 {
     return true;
   }
 
+  // Lane 0 of a converged warp waits for phase `parity` of an mbarrier, the other lanes wait for lane 0;
+  // what the barrier's completion made visible to lane 0 is visible to the whole warp after the __syncwarp.
+  // Returns the wait's outcome to every lane (false: it gave up and reported).
+  __device__ __forceinline__ static bool warp_wait(bool lane0, uint32_t bar, uint32_t parity, int *status, int code) {
+    int ok = 1;
+    if (lane0) ok = mbar_wait(bar, parity, status, code) ? 1 : 0;
+    __syncwarp();
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
+  }
+
   // The im2col operand of one tile built from the raw ring by the four epilogue warps (gt = 0..127).
   // Thread layout as in gather(): consecutive lanes take consecutive pixels, thread `sub` of a pixel its
   // share of the stage's 32 values of k, in 16-byte chunks of four.  tab[k] is the byte offset of k's
@@ -257,9 +267,9 @@ struct ConvUmmaTf32 {
     const bool lane0 = (gt & 31) == 0;
     uint32_t s = 0, ph = 1;
     for (int kb = 0; kb < num_kb; ++kb) {
-      // (a wait's outcome is made uniform over the warp: its lanes meet at __syncwarp below, and one
-      // that gave up a poll earlier than its neighbours must not leave them waiting there)
-      if (!__all_sync(0xffffffffu, mbar_wait(empty0 + 8 * s, ph, status, UMMA_WAIT_EMPTY_TIMEOUT))) return false;
+      // one lane per warp polls the barrier and the warp follows it (its lanes meet again at the __syncwarp
+      // before the arrival below, so the outcome of a wait has to be the same for all of them anyway)
+      if (!warp_wait(lane0, empty0 + 8 * s, ph, status, UMMA_WAIT_EMPTY_TIMEOUT)) return false;
       const uint32_t brow = tiles + s * kStageBytes + kUmmaABytes + (uint32_t)r * 128u;
       const int k0 = (kb0 + kb) * kBK + sub * kper;
       // phase 0: which slot holds each chunk (waiting for slots not seen yet); no shared-memory reads
@@ -274,7 +284,7 @@ struct ConvUmmaTf32 {
             if (++rs == (uint32_t)nslots) rs = 0, rph ^= 1;
           }
           if (!have) {
-            if (!__all_sync(0xffffffffu, mbar_wait(raw_full0 + 8 * rs, rph, status, UMMA_WAIT_FULL_TIMEOUT))) return false;
+            if (!warp_wait(lane0, raw_full0 + 8 * rs, rph, status, UMMA_WAIT_FULL_TIMEOUT)) return false;
             have = true;
           }
           src[i] = raw0 + rs * slot_pitch + pixoff;
