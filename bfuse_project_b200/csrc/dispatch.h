@@ -124,6 +124,9 @@ struct GroupTable {
   int bar_count[kGroupMax];
   int rot_end, rot, ratio_lo[kGroupMax + 1];
   int tail_lo[kGroupMax], tail_hi[kGroupMax], tail_base[kGroupMax];
+  // groups of two operator bodies: which of the two bodies operator i runs (0 / 1) and its index among
+  // that body's parameter blocks; all zero / i for a group of one body
+  int body[kGroupMax], slot[kGroupMax];
   int *status;
   int no_pdl;         // host side only: launch without the programmatic-dependent-launch attribute
 };

@@ -214,6 +214,39 @@ __global__ void __launch_bounds__(A::kMaxThreads, A::kMinBlocks)
   A::run(g.p[k], c);
 }
 
+// Up to four operators drawn from TWO bodies in one launch: the group's dispatch decode names the
+// operator, the table says which body it runs and which of that body's parameter blocks is its own.
+template <class A, class B>
+__global__ void __launch_bounds__(cmax(A::kMaxThreads, B::kMaxThreads), pair_min_blocks<A, B>())
+    fused_mixed_group_kernel(const __grid_constant__ GroupTable t, const __grid_constant__ GroupParams<A> ga,
+                             const __grid_constant__ GroupParams<B> gb) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char *smem = align_smem_1k(smem_raw);
+  const int tid = threadIdx.x;
+  int k = 0, vb = 0;
+  const bool mapped = decode_group_cta(t, blockIdx.x, k, vb);
+  // as in fused_block_kernel: a CTA that will not allocate tensor memory gives the permit up at once
+  if constexpr (A::kUsesTmem != B::kUsesTmem) {
+    if (tid < 32 && (!mapped || (t.body[k] == 0 ? !A::kUsesTmem : !B::kUsesTmem))) relinquish_tmem_permit();
+  }
+  if (!mapped || tid >= t.n_thr[k]) return;   // guard of the reference: KernelID_ == k && threadIdx.x < B_k
+  TileCtx c;
+  c.vblock = vb;
+  c.tid = tid;
+  c.nthreads = t.n_thr[k];
+  c.bar_id = 1 + t.body[k];
+  c.bar_count = t.bar_count[k];
+  c.gx = t.grid_x[k];
+  c.gy = t.grid_y[k];
+  c.bx = t.blk_x[k];
+  c.by = t.blk_y[k];
+  c.smem = smem;
+  c.status = t.status;
+  c.persistent = 0;
+  if (t.body[k] == 0) A::run(ga.p[t.slot[k]], c);
+  else B::run(gb.p[t.slot[k]], c);
+}
+
 template <class A>
 __global__ void __launch_bounds__(A::kMaxThreads, A::kMinBlocks)
     single_kernel(const __grid_constant__ DispatchTable t, const __grid_constant__ typename A::Params pa) {
@@ -231,6 +264,8 @@ typedef cudaError_t (*SingleLaunchFn)(const DispatchTable &, const void *pa, uns
                                       size_t smem, cudaStream_t);
 typedef cudaError_t (*GroupLaunchFn)(const GroupTable &, const void *const *params, int n, unsigned grid, unsigned block,
                                      size_t smem, cudaStream_t);
+typedef cudaError_t (*MixedGroupLaunchFn)(const GroupTable &, const void *const *params_a, int na, const void *const *params_b, int nb,
+                                          unsigned grid, unsigned block, size_t smem, cudaStream_t);
 typedef cudaError_t (*AttrFn)(cudaFuncAttributes *);
 typedef int (*ClusterCapFn)(unsigned block, size_t smem, int cluster);
 
@@ -335,6 +370,25 @@ cudaError_t launch_group(const GroupTable &t, const void *const *params, int n, 
 }
 template <class A>
 cudaError_t attr_group(cudaFuncAttributes *a) { return cudaFuncGetAttributes(a, fused_group_kernel<A>); }
+template <class A, class B>
+cudaError_t launch_mixed_group(const GroupTable &t, const void *const *pa, int na, const void *const *pb, int nb, unsigned grid,
+                               unsigned block, size_t smem, cudaStream_t s) {
+  cudaError_t e = ensure_smem(fused_mixed_group_kernel<A, B>, smem);
+  if (e != cudaSuccess) return e;
+  GroupParams<A> ga;
+  GroupParams<B> gb;
+  for (int i = 0; i < kGroupMax; ++i) {
+    ga.p[i] = *static_cast<const typename A::Params *>(pa[i < na ? i : 0]);
+    gb.p[i] = *static_cast<const typename B::Params *>(pb[i < nb ? i : 0]);
+  }
+  return launch_clustered(fused_mixed_group_kernel<A, B>, grid, block, smem, s, t.cluster, !t.no_pdl, t, ga, gb);
+}
+template <class A, class B>
+cudaError_t attr_mixed_group(cudaFuncAttributes *a) { return cudaFuncGetAttributes(a, fused_mixed_group_kernel<A, B>); }
+template <class A, class B>
+int clusters_mixed_group(unsigned block, size_t smem, int cluster) {
+  return max_resident_clusters(fused_mixed_group_kernel<A, B>, block, smem, cluster);
+}
 template <class A, class B>
 cudaError_t launch_block_pair_wide(const DispatchTable &t, const void *pa, const void *pb, unsigned grid, unsigned block,
                                    size_t smem, cudaStream_t s) {

@@ -34,6 +34,10 @@ struct PairEntry {
   AttrFn block_wide_attr;
   int wide_min_blocks;       // CTAs per SM the wide build is compiled for
   ClusterCapFn block_clusters;  // clusters of the block-level kernel that can be resident at once
+  // groups of these two bodies (built once per unordered pair: for row < column only, else nullptr)
+  MixedGroupLaunchFn mixed;
+  AttrFn mixed_attr;
+  ClusterCapFn mixed_clusters;
 };
 struct SingleEntry {
   SingleLaunchFn launch;

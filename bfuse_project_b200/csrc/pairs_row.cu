@@ -24,6 +24,23 @@ struct WideFiller<A, B, true> {
   }
 };
 
+template <class A, class B, bool HAS>
+struct MixedFiller {
+  static void fill(PairEntry &e) {
+    e.mixed = nullptr;
+    e.mixed_attr = nullptr;
+    e.mixed_clusters = nullptr;
+  }
+};
+template <class A, class B>
+struct MixedFiller<A, B, true> {
+  static void fill(PairEntry &e) {
+    e.mixed = &launch_mixed_group<A, B>;
+    e.mixed_attr = &attr_mixed_group<A, B>;
+    e.mixed_clusters = &clusters_mixed_group<A, B>;
+  }
+};
+
 template <int I, int J>
 struct RowFiller {
   static void fill(PairEntry *row) {
@@ -35,6 +52,7 @@ struct RowFiller {
     row[J].thread_attr = &attr_thread_pair<A, B>;
     row[J].block_clusters = &clusters_block_pair<A, B>;
     WideFiller<A, B, (pair_wide_blocks<A, B>() > 0)>::fill(row[J]);
+    MixedFiller<A, B, (I < J)>::fill(row[J]);
     RowFiller<I, J + 1>::fill(row);
   }
 };

@@ -70,6 +70,7 @@ struct GroupRec {
   size_t smem;
   int regs;
   int stages[kGroupMax];  // ring depths replaced so that two CTAs share an SM (0: the kernel's own)
+  int op_lo, op_hi;       // the group's operator bodies, lower id first; equal for a group of one body
 };
 
 struct GraphRec {
@@ -1041,13 +1042,22 @@ int bfuse_register_group(bfuse_context *ctx, const int *kernels, int n, int patt
   for (int i = 0; i < n; ++i) {
     ks[i] = get_kernel(ctx, kernels[i]);
     if (!ks[i] || ks[i]->alias_of >= 0) return fail(ctx, BFUSE_ERR_INVALID, "bad kernel handle");
-    if (ks[i]->desc.op != ks[0]->desc.op) return fail(ctx, BFUSE_ERR_UNSUPPORTED, "the kernels of a group must share one operator body");
     g->ks[i] = kernels[i];
     kd[i] = ks[i]->dims;
     cluster = std::max(cluster, ks[i]->cluster);
     g->name += (i ? "_" : "") + ks[i]->name;
   }
   g->name += "_fused_bfuse";
+  // one body, or two: a kernel exists per body and per unordered pair of bodies
+  g->op_lo = g->op_hi = ks[0]->desc.op;
+  for (int i = 1; i < n; ++i) {
+    const int op = ks[i]->desc.op;
+    if (op == g->op_lo || op == g->op_hi) continue;
+    if (g->op_lo != g->op_hi) return fail(ctx, BFUSE_ERR_UNSUPPORTED, "the kernels of a group may use at most two operator bodies");
+    if (op < g->op_lo) g->op_lo = op;
+    else g->op_hi = op;
+  }
+  const bool mixed = g->op_lo != g->op_hi;
   for (int i = 0; i < n; ++i)
     if (ks[i]->cluster != 1 && ks[i]->cluster != cluster)
       return fail(ctx, BFUSE_ERR_UNSUPPORTED, "the operators need different cluster widths; register them with equal splits");
@@ -1060,6 +1070,12 @@ int bfuse_register_group(bfuse_context *ctx, const int *kernels, int n, int patt
   std::string err;
   if (!plan_group(kd, n, pattern, param_m, param_n, &g->plan, &err, cluster)) return fail(ctx, BFUSE_ERR_INVALID, err);
   g->plan.table.status = ctx->d_status;
+  for (int i = 0, na = 0, nb = 0; i < n; ++i) {
+    const bool second = mixed && ks[i]->desc.op == g->op_hi;
+    g->plan.table.body[i] = second ? 1 : 0;
+    g->plan.table.slot[i] = second ? nb++ : na++;
+  }
+  const PairEntry &mixed_entry = ctx->pairs[g->op_lo][g->op_hi];
   // shared memory: the union of the windows; rings sized for a whole SM are made shallower when the
   // fused grid needs two CTAs per SM (same rule as for a pair)
   constexpr size_t kHalfSm = 111 * 1024;
@@ -1068,7 +1084,8 @@ int bfuse_register_group(bfuse_context *ctx, const int *kernels, int n, int patt
   bool second_wave = g->plan.fused_grid > ctx->sm_count;
   if (!second_wave && cluster > 1 && widest > kHalfSm) {   // clusters fit a GPC each: fewer resident CTAs than SMs
     cudaSetDevice(ctx->device);
-    const int cap = ctx->singles[ks[0]->desc.op].group_clusters((unsigned)g->plan.fused_block, widest + 1024, cluster);
+    const int cap = mixed ? mixed_entry.mixed_clusters((unsigned)g->plan.fused_block, widest + 1024, cluster)
+                          : ctx->singles[ks[0]->desc.op].group_clusters((unsigned)g->plan.fused_block, widest + 1024, cluster);
     second_wave = cap > 0 && g->plan.fused_grid / cluster > cap;
   }
   for (int i = 0; i < n; ++i) {
@@ -1088,7 +1105,7 @@ int bfuse_register_group(bfuse_context *ctx, const int *kernels, int n, int patt
   if (g->smem > kMaxSmemPerCta) return fail(ctx, BFUSE_ERR_SMEM, g->name + ": fused shared memory over the 227 KB per-CTA budget");
   cudaSetDevice(ctx->device);
   cudaFuncAttributes attr;
-  cudaError_t e = ctx->singles[ks[0]->desc.op].group_attr(&attr);
+  cudaError_t e = mixed ? mixed_entry.mixed_attr(&attr) : ctx->singles[ks[0]->desc.op].group_attr(&attr);
   if (e != cudaSuccess) return fail_cuda(ctx, e, "cudaFuncGetAttributes");
   g->regs = attr.numRegs;
   for (int i = 0; i < n; ++i) ++ks[i]->users;
@@ -1126,12 +1143,20 @@ int bfuse_launch_group(bfuse_context *ctx, int group, void *stream) {
   if (!get_group(ctx, group)) return fail(ctx, BFUSE_ERR_INVALID, "bad group handle");
   GroupRec &g = *ctx->groups[group];
   alignas(64) unsigned char scratch[kGroupMax][kParamsBytes];
-  const void *params[kGroupMax];
-  for (int i = 0; i < g.n; ++i) params[i] = params_with_stages(*ctx->kernels[g.ks[i]], g.stages[i], scratch[i]);
-  const KernelRec &k0 = *ctx->kernels[g.ks[0]];
+  const void *params[2][kGroupMax];
+  int count[2] = {0, 0};
+  for (int i = 0; i < g.n; ++i) {
+    const int b = g.plan.table.body[i];
+    params[b][count[b]++] = params_with_stages(*ctx->kernels[g.ks[i]], g.stages[i], scratch[i]);
+  }
   g.plan.table.no_pdl = ctx->no_pdl;
-  cudaError_t e = ctx->singles[k0.desc.op].group(g.plan.table, params, g.n, (unsigned)g.plan.fused_grid,
-                                                 (unsigned)g.plan.fused_block, g.smem, (cudaStream_t)stream);
+  cudaError_t e;
+  if (g.op_lo != g.op_hi)
+    e = ctx->pairs[g.op_lo][g.op_hi].mixed(g.plan.table, params[0], count[0], params[1], count[1], (unsigned)g.plan.fused_grid,
+                                           (unsigned)g.plan.fused_block, g.smem, (cudaStream_t)stream);
+  else
+    e = ctx->singles[g.op_lo].group(g.plan.table, params[0], g.n, (unsigned)g.plan.fused_grid, (unsigned)g.plan.fused_block, g.smem,
+                                    (cudaStream_t)stream);
   if (e != cudaSuccess) return fail_cuda(ctx, e, ("launch " + g.name).c_str());
   return BFUSE_OK;
 }

@@ -10,7 +10,8 @@ inputs are ready --
     * 2..4 ready operators of one body (the Q, K and V projections; the two branches of a
       down-sampling block; the same operator of independent requests) as one n-way group, the
       reference's n-kernel form of its patterns (horizontal-fuser/src/Algorithms.cc:538-587);
-    * two ready operators of different bodies as one fused pair;
+    * what that leaves over, when it is of two bodies: two operators as one fused pair, three or four
+      as one group of two bodies;
     * what is left alone.
 
 `run_sequential` is the unfused program (one launch per operator, program order, every operator
@@ -94,14 +95,30 @@ def schedule(ops, max_group=4, rule=default_rule):
                 ngroups -= 1
             left.extend(idx)
         left.sort()
+        lonely = []
         while len(left) >= 2:
             a = left.pop(0)
-            mate = next((b for b in left if ops[b].op != ops[a].op and rule([ops[a], ops[b]])), None)
-            if mate is None:
-                step.append(("single", [a]))
+            # what is left over joins operators of ONE other body: two of them are a fused pair (every pattern),
+            # three or four a group of two bodies
+            mates = {}
+            for b in left:
+                if ops[b].op != ops[a].op and rule([ops[a], ops[b]]):
+                    mates.setdefault(ops[b].op, []).append(b)
+            if not mates:
+                lonely.append(a)
                 continue
-            left.remove(mate)
-            step.append(("pair", [a, mate]))
+            other = max(mates.values(), key=len)[:max(1, max_group - 1)]
+            for b in other:
+                left.remove(b)
+            step.append(("pair", [a, other[0]]) if len(other) == 1 else ("group", [a] + other))
+        # an operator still alone joins a group of one other body that has room for it
+        left = sorted(left + lonely)
+        for a in list(left):
+            host = next((g for kind, g in step if kind == "group" and len(g) < max_group and len({ops[i].op for i in g}) == 1
+                         and ops[g[0]].op != ops[a].op and rule([ops[i] for i in g] + [ops[a]])), None)
+            if host is not None:
+                host.append(a)
+                left.remove(a)
         step.extend(("single", [i]) for i in left)
         steps.append(step)
         done.update(ready)

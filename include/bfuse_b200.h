@@ -151,10 +151,11 @@ int bfuse_fusion_map_thread(const bfuse_context *ctx, int fusion, int kernel, in
 
 /* n kernels in one fused launch -- the general form the reference's patterns are written in
  * (a `Kernels:` list of any length, horizontal-fuser/src/Algorithms.cc:323-375, 538-587, 661-685),
- * here for 2..BFUSE_GROUP_MAX registered kernels that share one operator body (the Q, K and V
- * projections of a layer; the branches of a block).  Patterns: BFUSE_PATTERN_ZIGZAG (M:N),
+ * here for 2..BFUSE_GROUP_MAX registered kernels of one operator body (the Q, K and V projections
+ * of a layer; the branches of a block) or of two bodies (the projections beside a normalisation; a
+ * tensor-core GEMM beside CUDA-core ones).  Patterns: BFUSE_PATTERN_ZIGZAG (M:N),
  * BFUSE_PATTERN_PROPORTIONAL, BFUSE_PATTERN_RANGE_SPLIT; others return BFUSE_ERR_UNSUPPORTED, as do
- * kernels of different bodies or of different cluster widths. */
+ * kernels of three or more bodies or of different cluster widths. */
 #define BFUSE_GROUP_MAX 4
 int bfuse_register_group(bfuse_context *ctx, const int *kernels, int n, int pattern, int param_m, int param_n, int *group);
 /* The fused-kernel record of a group: name "<k1>_<k2>_..._fused_bfuse", fused GridDim / BlockDim, smem, registers. */

@@ -92,14 +92,63 @@ def test_llama_projections_and_resnet_stages_full_size():
     rt.close()
 
 
+@pytest.mark.parametrize("pattern", [bf.ZIGZAG, bf.PROPORTIONAL, bf.RANGE_SPLIT])
+def test_groups_of_two_bodies(pattern):
+    """Up to four kernels of TWO operator bodies in one launch (the reference's patterns are written for n arbitrary
+    kernels, horizontal-fuser/src/Algorithms.cc:538-587): three tensor-core projections beside a residual LayerNorm,
+    two LayerNorms beside two softmaxes, a tcgen05 GEMM whose K is split over clusters beside row-wise operators
+    (padding CTAs of partly filled clusters), a conv beside a GEMM.  The decode equals the n-kernel oracle, and the
+    group writes the bits of the unfused launches."""
+    import numpy as np
+    import oracle
+    from bfuse_project_b200 import workloads as wl
+    rt = bf.Runtime(0)
+    rng = np.random.default_rng(31)
+    m, n = (1, 1) if pattern == bf.ZIGZAG else ((1, 0) if pattern == bf.PROPORTIONAL else (0, 0))
+    q, k = wl.make_pair("cfg2_q_k_proj", seed=3, scale=0.5).a, wl.make_pair("cfg2_q_k_proj", seed=4, scale=0.5).b
+    v = wl.gemm("v_proj", rng, bf.OP_GEMM_TF32, 1, 256, 768, 768, bias=True)
+    ln = wl.layernorm("ln", rng, 256, 768, 1e-5, residual=True)
+    ln2 = wl.layernorm("ln2", rng, 100, 768, 1e-5)
+    sm1, sm2 = wl.softmax("sm1", rng, 1536, 512, 0.125), wl.softmax("sm2", rng, 333, 256, 1.0)
+    gs = wl.gemm("gsplit", rng, bf.OP_GEMM_TF32, 1, 256, 256, 1024, w_std=1.0, bn=256, split=4)
+    cv = wl.conv2d("conv", rng, bf.OP_CONV2D_TF32, 2, 64, 28, 28, 128, 3, 1, 1)
+    for members in ([q, k, v, ln], [ln, sm1, ln2, sm2], [gs, ln2, ln], [cv, q], [sm2, q]):
+        pairs = [wl.DevicePair(rt, wl.PairSpec("m", ks, wl.softmax("pad", rng, 8, 128, 1.0), "f32", "hbm")) for ks in members]
+        kernels = [p.kernels[0] for p in pairs]
+        for p in pairs:
+            rt.launch_kernel(p.kernels[0])
+        want = [p.read_outputs()[0][0].copy() for p in pairs]
+        for p in pairs:
+            p.clear_outputs()
+        group = rt.register_group(kernels, pattern, m, n)
+        info = rt.group_info(group)
+        rt.launch_group(group)
+        got = [p.read_outputs()[0][0] for p in pairs]
+        assert rt.read_status() == 0
+        for ks, w, g in zip(members, want, got):
+            assert np.array_equal(w.view(np.uint8), g.view(np.uint8)) and np.any(g != 0), (ks.name, bf.PATTERN_NAMES[pattern])
+        # every CTA of the fused grid maps to one virtual block of one member, each exactly once
+        seen = {}
+        for cta in range(info["GridDim"][0]):
+            mapped = rt.group_map_block(group, cta)
+            if mapped is not None:
+                seen.setdefault(mapped[0], []).append(mapped[1])
+        assert sorted(seen) == list(range(len(members)))
+        for i, ks in enumerate(members):
+            grid = ks.launch[0]
+            assert sorted(seen[i]) == list(range(grid[0] * grid[1] * grid[2])), ks.name
+        rt.unregister_group(group)
+    rt.close()
+
+
 def test_group_registration_errors():
     import torch
     rt = bf.Runtime(0)
     b, ops = sg.bert_layer(rt, torch, seq=128, hidden=256, heads=4, ffn=512, seed=7)
     seg = sg.Segment(rt, ops)
     by_name = {o.name: k for o, k in zip(ops, seg.alone)}
-    with pytest.raises(bf.BfuseError) as e:       # different bodies
-        rt.register_group([by_name["q_proj"], by_name["softmax"]], bf.ZIGZAG, 1, 1)
+    with pytest.raises(bf.BfuseError) as e:       # three bodies: a kernel exists per body and per pair of bodies
+        rt.register_group([by_name["q_proj"], by_name["softmax"], by_name["ln1"]], bf.ZIGZAG, 1, 1)
     assert e.value.code == 7
     for pat in (bf.SM_STRIPED, bf.THREAD_SPLIT, bf.WORK_QUEUE):
         with pytest.raises(bf.BfuseError) as e:

@@ -86,7 +86,7 @@ def test_schedule_respects_dependencies_and_groups_by_body():
                 assert 1 <= len(idx) <= 4
                 assert (kind == "single") == (len(idx) == 1)
                 if kind == "group":
-                    assert len({ops[i].op for i in idx}) == 1
+                    assert len({ops[i].op for i in idx}) <= 2
                 if kind == "pair":
                     assert len(idx) == 2 and ops[idx[0]].op != ops[idx[1]].op
                 for i in idx:
@@ -138,3 +138,21 @@ def test_pairing_model_arithmetic():
     ev = pairing.evaluate(recs)
     assert (ev["pairs"], ev["advice_fuse_and_pays"], ev["advice_alone_and_slower"], ev["advice_alone_but_pays"]) == (3, 1, 1, 1)
     assert ev["median_rel_err"] == pytest.approx(1.0 / 102.0)
+
+
+def test_leftovers_of_two_bodies_share_one_group():
+    """Ready operators that no same-body group took: two of different bodies are a pair, three or four drawn from
+    two bodies one group; a third body waits for its own launch."""
+    ops = [sg.SegmentOp("g%d" % i, bf.OP_GEMM_TF32, None, ["x"], ["y%d" % i]) for i in range(5)] + \
+          [sg.SegmentOp("ln", bf.OP_LAYERNORM_F32, None, ["x"], ["z"]), sg.SegmentOp("sm", bf.OP_SOFTMAX_F32, None, ["x"], ["p"]),
+           sg.SegmentOp("sm2", bf.OP_SOFTMAX_F32, None, ["x"], ["p2"]), sg.SegmentOp("sm3", bf.OP_SOFTMAX_F32, None, ["x"], ["p3"])]
+    steps = sg.schedule(ops, rule=lambda group: True)
+    assert len(steps) == 1
+    kinds = sorted((kind, tuple(idx)) for kind, idx in steps[0])
+    # 5 GEMMs -> 3 + 2; 3 softmaxes -> one group; the LayerNorm, for which no partner is left, joins the first group with room
+    assert kinds == [("group", (0, 1, 2, 5)), ("group", (3, 4)), ("group", (6, 7, 8))]
+    ops2 = [sg.SegmentOp("g", bf.OP_GEMM_TF32, None, ["x"], ["y"]), sg.SegmentOp("ln", bf.OP_LAYERNORM_F32, None, ["x"], ["z"]),
+            sg.SegmentOp("r1", bf.OP_ROPE_BF16, None, ["x"], ["a"]), sg.SegmentOp("n1", bf.OP_RMSNORM_BF16, None, ["x"], ["b"]),
+            sg.SegmentOp("cv", bf.OP_CONV2D_TF32, None, ["x"], ["c"])]
+    steps = sg.schedule(ops2, rule=lambda group: True)
+    assert sorted((kind, tuple(idx)) for kind, idx in steps[0]) == [("pair", (0, 1)), ("pair", (2, 3)), ("single", (4,))]
