@@ -193,7 +193,7 @@ def run_sweep(args, rt, torch, rank, world, local, pk):
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     import bfuse_project_b200 as bfm
-    pattern = {"zigzag": bfm.ZIGZAG, "range": bfm.RANGE_SPLIT, "striped": bfm.SM_STRIPED, "proportional": bfm.PROPORTIONAL}[args.sweep_pattern]
+    pattern = {"zigzag": bfm.ZIGZAG, "range": bfm.RANGE_SPLIT, "striped": bfm.SM_STRIPED, "proportional": bfm.PROPORTIONAL, "all": "all"}[args.sweep_pattern]
     res = sweep.measure(rt, sets, mine, pk["hbm_gbs"], pk["bf16_tflops"] * 0.5, pattern=pattern)
     wall = time.perf_counter() - t0
     alone = sweep.alone_times(rt, sets) if rank == 0 else None      # for the pair-selection model, outside the wall time
@@ -214,11 +214,12 @@ def run_sweep(args, rt, torch, rank, world, local, pk):
                        "partition": "pair i on rank i mod %d" % world},
             "sweep": sweep.summarise(res)}
     from bfuse_project_b200 import pairing
-    line["pairing_model"] = pairing.evaluate(sweep.pairing_records(sets, res, alone, rt.sm_count))
+    records = sweep.pairing_records(sets, res, alone, rt.sm_count)
+    line["pairing_model"] = pairing.evaluate(records)
     if args.sweep_out:
         with open(args.sweep_out, "w") as f:
             json.dump({"operators": [{"name": n, "shape": list(sh), "alone_us": alone[i], "launch": [list(x) if isinstance(x, tuple) else x for x in sets[0][i].launch]}
-                                     for i, (n, sh) in enumerate(sweep.SWEEP_OPS[:n_ops])], "pairs": res}, f, indent=0)
+                                     for i, (n, sh) in enumerate(sweep.SWEEP_OPS[:n_ops])], "pairs": res, "records": records}, f, indent=0)
     print(json.dumps(line), flush=True)
 
 
@@ -294,6 +295,23 @@ def measure_pair(rt, torch, bf, wl, pk, name, device, conv_batch=1, max_reps=24,
     best = res[best_label]
     res["best_fused_us"] = best
     res["best_pattern"] = best_label[len("fused_"):-len("_us")]
+    # the pair-selection model on this pair: its advice from the two operators' times alone, against what was measured
+    try:
+        from bfuse_project_b200 import pairing
+        zz = [p.fusion(bf.ZIGZAG, 1, 1) for p in pairs]
+        alone = []
+        for mode in (bf.MODE_KERNEL1, bf.MODE_KERNEL2):
+            g = rt.graph_create(zz, mode)
+            alone.append(replay_us(rt, torch, g, reps))
+            rt.graph_destroy(g)
+        dims = lambda l: (l[0][0] * l[0][1] * l[0][2], l[1][0] * l[1][1] * l[1][2], l[2])
+        adv = pairing.advise(alone[0], alone[1], dims(spec.a.launch), dims(spec.b.launch), rt.sm_count, 1.0, spec.a.op, spec.b.op)
+        got = res.get("fused_%s_us" % adv["pattern"])
+        res["alone_us"] = alone
+        res["model"] = {"pattern": adv["pattern"], "predicted_us": adv["predicted_fused_us"], "fuse": adv["fuse"], "measured_us": got,
+                        "within_2_pct_of_best": None if got is None else bool(got <= 1.02 * best)}
+    except Exception as e:   # reported, not hidden
+        res["model"] = {"error": str(e)[:200]}
     if flusher is not None:
         lab = [x for x in MODES if "fused_" + res["best_pattern"] == x[0]][0]
         f0 = pairs[0].fusion(getattr(bf, lab[1]), lab[3], lab[4])
@@ -514,8 +532,8 @@ def main():
     ap.add_argument("--sweep", action="store_true", help="run the 42 x 42 operator cross-product sweep instead (pair i on rank i mod N)")
     ap.add_argument("--sweep-out", default="", help="with --sweep: also write the per-pair table to this JSON file")
     ap.add_argument("--sweep-limit", type=int, default=0, help="with --sweep: only the first N operators")
-    ap.add_argument("--sweep-pattern", default="zigzag", choices=["zigzag", "range", "striped", "proportional"],
-                    help="with --sweep: the block-level pattern of the fused launches")
+    ap.add_argument("--sweep-pattern", default="zigzag", choices=["zigzag", "range", "striped", "proportional", "all"],
+                    help="with --sweep: the block-level pattern of the fused launches; all: every pattern per pair (what the pair-selection model is fitted on)")
     ap.add_argument("--batch", type=int, default=BATCH, help="images of the conv batch (256: the BASELINE configuration; smaller for profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
@@ -762,6 +780,10 @@ def main():
         else:
             table[name] = [round(r["best_fused_us"], 2), round(r["sequential_us"], 2), round(r["roofline_frac"], 3), r["best_pattern"],
                            round(r.get("isolated_fused_us", 0.0), 2)]
+    judged = [r["model"]["within_2_pct_of_best"] for r in side_pairs.values() if isinstance(r.get("model"), dict) and r["model"].get("within_2_pct_of_best") is not None]
+    if judged:
+        line["pairing_model_on_baseline_pairs"] = {"pairs": len(judged), "pattern_within_2_pct_of_best": sum(judged),
+                                                   "advice": {n: r["model"].get("pattern") for n, r in side_pairs.items() if isinstance(r.get("model"), dict)}}
     line["per_config"] = table
     print(json.dumps(line), flush=True)
     if world > 1:

@@ -25,8 +25,12 @@ every operator's shape and the dependency structure of the layer, not its numeri
 """
 import math
 
-from . import (FLAG_CAUSAL, OP_CONV2D_F32_SIMT, OP_CONV2D_TF32, OP_GEMM_BF16, OP_GEMM_TF32, OP_LAYERNORM_F32,
-               OP_RMSNORM_BF16, OP_ROPE_BF16, OP_SOFTMAX_F32, ZIGZAG, BfuseError, flag_share)
+from . import (FLAG_CAUSAL, MODE_KERNEL1, OP_CONV2D_F32_SIMT, OP_CONV2D_TF32, OP_GEMM_BF16, OP_GEMM_TF32, OP_LAYERNORM_F32,
+               OP_RMSNORM_BF16, OP_ROPE_BF16, OP_SOFTMAX_F32, RANGE_SPLIT, SM_STRIPED, THREAD_SPLIT, ZIGZAG, BfuseError, flag_share, pairing)
+
+# the pair-selection model's pattern names -> (pattern, M, N) of bfuse_register_fusion
+MODEL_PATTERNS = {"zigzag": (ZIGZAG, 1, 1), "zigzag2": (ZIGZAG, 1, 2), "range": (RANGE_SPLIT, 0, 0), "striped": (SM_STRIPED, 0, 0),
+                  "thread_split": (THREAD_SPLIT, 0, 0)}
 
 
 class SegmentOp:
@@ -37,6 +41,7 @@ class SegmentOp:
     def __init__(self, name, op, kernel, reads, writes, spec=None):
         self.name, self.op, self.kernel, self.spec = name, op, kernel, spec
         self.reads, self.writes = frozenset(reads), frozenset(writes)
+        self.launch, self.alone_us = None, None      # (CTAs, threads, shared memory) alone; microseconds alone, once measured
 
     def register(self, rt, share):
         """Kernel handle of this operator tiled for `share` operators in one launch (1: alone)."""
@@ -45,7 +50,10 @@ class SegmentOp:
         shape, ptrs, kw = self.spec
         kw = dict(kw)
         kw["flags"] = kw.get("flags", 0) | flag_share(share)
-        return rt.register_kernel(rt.describe(self.name, self.op, shape, ptrs, **kw))
+        desc = rt.describe(self.name, self.op, shape, ptrs, **kw)
+        if share == 1:
+            self.launch = (desc.GridDim.size(), desc.BlockDim.size(), desc.smem_bytes)   # what the pair-selection model reads
+        return rt.register_kernel(desc)
 
 
 def dependencies(ops):
@@ -125,16 +133,38 @@ def schedule(ops, max_group=4, rule=default_rule):
     return steps
 
 
+def model_rule(ops, sm_count=148, margin=1.0):
+    """The pair-selection model as a scheduling rule: operators may share a launch when every pair of them is
+    predicted to beat its two launches back to back (pairing.advise on the operators' times alone and launch
+    records, which Segment measures at registration)."""
+    for i, a in enumerate(ops):
+        for b in ops[i + 1:]:
+            if a.alone_us is None or b.alone_us is None:
+                return default_rule([a, b])
+            if not pairing.advise(a.alone_us, b.alone_us, a.launch, b.launch, sm_count, margin, a.op, b.op)["fuse"]:
+                return False
+    return True
+
+
 class Segment:
     """A scheduled segment bound to a runtime.  Every operator is registered twice: tiled for the whole
     GPU (the program of one launch per operator, and operators the schedule leaves alone) and tiled for
-    its share of the launch it was scheduled into."""
+    its share of the launch it was scheduled into.  With rule = "model" every operator is timed alone at
+    registration and the pair-selection model decides what may share a launch, and under which pattern a pair
+    runs; the default rule is the sweep's coarse finding and the given pattern."""
 
     def __init__(self, rt, ops, pattern=ZIGZAG, max_group=4, rule=default_rule):
         self.rt, self.ops = rt, list(ops)
         self.alone = [o.register(rt, 1) for o in self.ops]
         self.shared = list(self.alone)
         self.steps = []
+        use_model = rule == "model"
+        if use_model:
+            for o, k in zip(self.ops, self.alone):
+                probe = rt.register_fusion(k, k, RANGE_SPLIT, 0, 0)      # any fusion of the kernel: mode 0 times kernel 1 alone
+                o.alone_us = rt.time(probe, MODE_KERNEL1, 3, 10)[0]
+                rt.unregister_fusion(probe)
+            rule = lambda group: model_rule(group, rt.sm_count)
         m = 1 if pattern == ZIGZAG else 0
         for step in schedule(self.ops, max_group, rule):
             out = []
@@ -146,6 +176,10 @@ class Segment:
                 try:
                     if kind == "group":
                         out.append(("group", rt.register_group(ks, pattern, m, m), idx))
+                    elif use_model:
+                        a, b = self.ops[idx[0]], self.ops[idx[1]]
+                        name = pairing.advise(a.alone_us, b.alone_us, a.launch, b.launch, rt.sm_count, 1.0, a.op, b.op)["pattern"]
+                        out.append(("pair", rt.register_fusion(ks[0], ks[1], *MODEL_PATTERNS[name]), idx))
                     else:
                         out.append(("pair", rt.register_fusion(ks[0], ks[1], pattern, m, m), idx))
                     for i, k in zip(idx, ks):

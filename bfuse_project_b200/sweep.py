@@ -16,7 +16,11 @@ stay in L2 as they do in the reference's own loop.
 import math
 
 from . import (BfuseError, MODE_FUSED, MODE_KERNEL1, MODE_SEQUENTIAL, OP_CONV2D_F32_SIMT, OP_CONV2D_TF32, OP_GEMM_TF32, PROPORTIONAL,
-               RANGE_SPLIT, ZIGZAG)
+               RANGE_SPLIT, SM_STRIPED, THREAD_SPLIT, ZIGZAG)
+
+# the fused forms a pair is timed in when every pattern is asked for: (label, pattern, M, N)
+ALL_PATTERNS = (("zigzag", ZIGZAG, 1, 1), ("zigzag2", ZIGZAG, 1, 2), ("range", RANGE_SPLIT, 0, 0), ("striped", SM_STRIPED, 0, 0),
+                ("thread_split", THREAD_SPLIT, 0, 0))
 
 # name -> shape.  dense: (M, K, N); bgemm: (batch, M, K, N); conv2d: (N, H, W, CO, CI, KH, KW, stride, pad)
 SWEEP_OPS = (
@@ -111,29 +115,43 @@ def pairing_records(sets, results, alone, sm_count):
         i, j = (by_name[n] for n in key.split("|"))
         la, lb = sets[0][i].launch, sets[1][j].launch
         dims = lambda l: (l[0][0] * l[0][1] * l[0][2], l[1][0] * l[1][1] * l[1][2], l[2])
-        recs.append({"t_a": alone[i], "t_b": alone[j], "launch_a": dims(la), "launch_b": dims(lb), "sm_count": sm_count,
-                     "fused_us": v["fused_us"], "sequential_us": v["sequential_us"]})
+        recs.append({"pair": key, "t_a": alone[i], "t_b": alone[j], "launch_a": dims(la), "launch_b": dims(lb), "sm_count": sm_count,
+                     "op_a": sets[0][i].op, "op_b": sets[1][j].op, "bytes_a": sets[0][i].bytes, "bytes_b": sets[1][j].bytes,
+                     "flops_a": sets[0][i].flops, "flops_b": sets[1][j].flops,
+                     "fused_us": v["fused_us"], "sequential_us": v["sequential_us"], "fused_us_by_pattern": v.get("fused_us_by_pattern")})
     return recs
 
 
 def measure(rt, sets, pairs, hbm_gbs, tf32_tflops, pattern=ZIGZAG, warmup=3, iters=30):
     """{"<k1>|<k2>": {...}} for the given (i, j) pairs: fused and sequential microseconds (mean of
-    `iters` launches after `warmup`), speed-up, and the pair's roofline time."""
+    `iters` launches after `warmup`), speed-up, and the pair's roofline time.  pattern = "all" times every
+    form of ALL_PATTERNS (`fused_us_by_pattern`; `fused_us` is then the zig-zag figure, as in a one-pattern sweep)."""
     out = {}
     for i, j in pairs:
         a, b = sets[0][i], sets[1][j]
         key = "%s|%s" % (a.name[:-3], b.name[:-3])   # without the set suffix
-        try:
-            mn = 1 if pattern in (ZIGZAG, PROPORTIONAL) else 0     # range split takes no parameter, SM-striped the device's SM count
-            f = rt.register_fusion(a.kernel, b.kernel, pattern, mn, mn)
-        except BfuseError as e:
-            out[key] = {"error": str(e)[:120]}
+        forms = ALL_PATTERNS if pattern == "all" else (("one", pattern, 1 if pattern in (ZIGZAG, PROPORTIONAL) else 0,
+                                                        1 if pattern in (ZIGZAG, PROPORTIONAL) else 0),)
+        by_pattern, seq, first_error = {}, None, None
+        for label, pat, m, n in forms:
+            try:
+                f = rt.register_fusion(a.kernel, b.kernel, pat, m, n)
+            except BfuseError as e:
+                first_error = first_error or str(e)[:120]
+                continue
+            by_pattern[label] = rt.time(f, MODE_FUSED, warmup, iters)[0]
+            if seq is None and not any(rt.fusion_info(f)["retiled_unsplit"]):
+                seq = rt.time(f, MODE_SEQUENTIAL, warmup, iters)[0]
+            rt.unregister_fusion(f)
+        if not by_pattern or seq is None:
+            out[key] = {"error": first_error or "no pattern could host the pair"}
             continue
-        fused = rt.time(f, MODE_FUSED, warmup, iters)[0]
-        seq = rt.time(f, MODE_SEQUENTIAL, warmup, iters)[0]
+        fused = by_pattern.get("zigzag", by_pattern.get("one", min(by_pattern.values())))
         roof = max((a.bytes + b.bytes) / (hbm_gbs * 1e3), (a.flops + b.flops) / (tf32_tflops * 1e6))
         out[key] = {"fused_us": fused, "sequential_us": seq, "speedup_vs_sequential": seq / fused, "roofline_us": roof,
                     "roofline_frac": roof / fused}
+        if pattern == "all":
+            out[key]["fused_us_by_pattern"] = by_pattern
     return out
 
 

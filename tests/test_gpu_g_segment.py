@@ -15,8 +15,8 @@ def _written(builder, ops):
     return sorted({w for o in ops for w in o.writes})
 
 
-def _run_both(rt, torch, builder, ops, pattern=bf.ZIGZAG, max_group=4):
-    seg = sg.Segment(rt, ops, pattern=pattern, max_group=max_group)
+def _run_both(rt, torch, builder, ops, pattern=bf.ZIGZAG, max_group=4, rule=sg.default_rule):
+    seg = sg.Segment(rt, ops, pattern=pattern, max_group=max_group, rule=rule)
     stream = torch.cuda.current_stream().cuda_stream
     names = _written(builder, ops)
 
@@ -138,6 +138,21 @@ def test_groups_of_two_bodies(pattern):
             grid = ks.launch[0]
             assert sorted(seen[i]) == list(range(grid[0] * grid[1] * grid[2])), ks.name
         rt.unregister_group(group)
+    rt.close()
+
+
+def test_segment_scheduled_by_the_pair_selection_model():
+    """rule = "model": every operator is timed alone at registration, the model decides what shares a launch and
+    names the pattern of every pair; the program still writes the bits of its kernels launched one by one."""
+    import torch
+    rt = bf.Runtime(0)
+    b, ops = sg.llama_layer_projections(rt, torch, seed=8)
+    seg = _run_both(rt, torch, b, ops, rule="model")
+    assert all(o.alone_us is not None and o.alone_us > 0 and o.launch is not None for o in ops)
+    assert seg.launches_fused < seg.launches_sequential
+    b2, ops2 = sg.bert_layer(rt, torch, replicas=2, seq=128, hidden=256, heads=4, ffn=512, seed=9)
+    seg2 = _run_both(rt, torch, b2, ops2, rule="model")
+    assert seg2.launches_fused < seg2.launches_sequential
     rt.close()
 
 

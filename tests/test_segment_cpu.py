@@ -127,17 +127,45 @@ def test_pairing_model_arithmetic():
     assert pairing.ctas_per_sm(256, 256, regs_per_thread=64) == 4
     assert pairing.fill(48, 192, 198656) == pytest.approx(48 / 148) and pairing.fill(1000, 192, 198656) == 1.0
     # two operators that each leave two thirds of the SMs idle overlap completely: the longer one plus the overhead
-    a = pairing.advise(8.0, 6.0, (48, 192, 198656), (48, 192, 198656))
-    assert a["predicted_fused_us"] == pytest.approx(8.0 + pairing.OVERHEAD_US) and a["fuse"]
+    a = pairing.advise(8.0, 6.0, (48, 192, 198656), (48, 192, 198656), model={})       # model = {}: the analytic core alone
+    assert a["predicted_fused_us"] == pytest.approx(8.0 + pairing.OVERHEAD_US) and a["fuse"] and a["pattern"] == "zigzag"
     # two operators that fill the GPU alone gain nothing
-    b = pairing.advise(50.0, 50.0, (300, 192, 198656), (300, 192, 198656))
+    b = pairing.advise(50.0, 50.0, (300, 192, 198656), (300, 192, 198656), model={})
     assert b["predicted_fused_us"] == pytest.approx(101.0) and not b["fuse"]
     recs = [dict(t_a=8.0, t_b=6.0, launch_a=(48, 192, 198656), launch_b=(48, 192, 198656), fused_us=9.0, sequential_us=14.0),
             dict(t_a=50.0, t_b=50.0, launch_a=(300, 192, 198656), launch_b=(300, 192, 198656), fused_us=102.0, sequential_us=100.0),
             dict(t_a=50.0, t_b=50.0, launch_a=(300, 192, 198656), launch_b=(300, 192, 198656), fused_us=95.0, sequential_us=100.0)]
-    ev = pairing.evaluate(recs)
+    ev = pairing.evaluate(recs, model={})
     assert (ev["pairs"], ev["advice_fuse_and_pays"], ev["advice_alone_and_slower"], ev["advice_alone_but_pays"]) == (3, 1, 1, 1)
     assert ev["median_rel_err"] == pytest.approx(1.0 / 102.0)
+
+
+def test_pairing_model_fit_recovers_a_planted_rule_and_names_patterns():
+    """Least-squares fit per pattern and class pair: planted linear rules come back, the advice names the pattern
+    with the smaller predicted time, and the coefficients shipped with the package load and cover every pattern."""
+    import random
+    from bfuse_project_b200 import pairing
+    rnd = random.Random(0)
+    recs = []
+    for i in range(200):
+        ta, tb = rnd.uniform(3, 40), rnd.uniform(3, 40)
+        la, lb = (rnd.choice([24, 48, 96, 300]), 192, 198656), (rnd.choice([24, 48, 96, 300]), 192, 198656)
+        fa, fb = pairing.fill(*la), pairing.fill(*lb)
+        core = max(max(ta, tb), fa * ta + fb * tb)
+        # planted: zig-zag = core + 1; range split is better by 10 % of the shorter operator when one operator is twice the other
+        zz = core + 1.0
+        rg = core + 1.0 - 0.1 * min(ta, tb) + 0.02 * (ta + tb)
+        recs.append(dict(pair="p%03d" % i, t_a=ta, t_b=tb, launch_a=la, launch_b=lb, op_a=6, op_b=6, fused_us=zz, sequential_us=ta + tb,
+                         fused_us_by_pattern={"zigzag": zz, "range": rg}))
+    w = pairing.fit(recs)
+    assert set(w) == set(pairing.PATTERNS) and w["zigzag"]["gemm|gemm"] == pytest.approx([1.0, 1.0, 0.0, 0.0], abs=1e-3)
+    assert w["range"]["*"] == pytest.approx([1.0, 1.0, -0.1, 0.02], abs=1e-3) and not w["striped"]
+    ev = pairing.evaluate(recs, model=w)
+    assert ev["median_rel_err"] < 1e-3 and ev["pattern_within_2_pct_of_best"] == 1.0
+    shipped = pairing.load_model()
+    assert shipped and set(shipped) == set(pairing.PATTERNS) and all("*" in t and len(t["*"]) == 4 for t in shipped.values())
+    adv = pairing.advise(7.3, 7.3, (48, 192, 198656), (48, 192, 198656), op_a=6, op_b=6)
+    assert adv["pattern"] in pairing.PATTERNS and adv["fuse"] and 7.0 < adv["predicted_fused_us"] < 10.0
 
 
 def test_leftovers_of_two_bodies_share_one_group():
