@@ -187,8 +187,13 @@ def run_sweep(args, rt, torch, rank, world, local, pk):
     JSON line with the summary (and writes the per-pair table when asked to)."""
     from bfuse_project_b200 import partition, sweep
     n_ops = min(args.sweep_limit or len(sweep.SWEEP_OPS), len(sweep.SWEEP_OPS))
-    sets = sweep.build_operands(rt, torch, local, seed=0, ops=sweep.SWEEP_OPS[:n_ops])
+    op_list = list(sweep.SWEEP_OPS[:n_ops])
     todo = sweep.pair_indices(n_ops)
+    if args.sweep_extra:
+        # the pair-selection model's extra operators (memory-bound bodies, bf16 projections): only the pairs that have one
+        op_list += list(sweep.MODEL_EXTRA_OPS)
+        todo = [(i, j) for i, j in sweep.pair_indices(len(op_list)) if j >= n_ops]
+    sets = sweep.build_operands(rt, torch, local, seed=0, ops=op_list)
     mine = partition.assign_pairs(todo, world, rank)
     torch.cuda.synchronize()
     t0 = time.perf_counter()
@@ -210,7 +215,7 @@ def run_sweep(args, rt, torch, rank, world, local, pk):
     line = {"metric": "sweep_wall_s", "value": wall, "unit": "s", "n_gpus": world, "higher_is_better": False, "scaling": "strong",
             "dtype": "tf32", "data": "synthetic",
             "config": {"workload": "operator cross-product sweep: %d operators, %d pairs (upper triangle), %s fusion vs "
-                                   "back-to-back launches; 3 warm-ups + 30 timed launches per mode" % (n_ops, len(todo), args.sweep_pattern),
+                                   "back-to-back launches; 3 warm-ups + 30 timed launches per mode" % (len(op_list), len(todo), args.sweep_pattern),
                        "partition": "pair i on rank i mod %d" % world},
             "sweep": sweep.summarise(res)}
     from bfuse_project_b200 import pairing
@@ -219,7 +224,7 @@ def run_sweep(args, rt, torch, rank, world, local, pk):
     if args.sweep_out:
         with open(args.sweep_out, "w") as f:
             json.dump({"operators": [{"name": n, "shape": list(sh), "alone_us": alone[i], "launch": [list(x) if isinstance(x, tuple) else x for x in sets[0][i].launch]}
-                                     for i, (n, sh) in enumerate(sweep.SWEEP_OPS[:n_ops])], "pairs": res, "records": records}, f, indent=0)
+                                     for i, (n, sh) in enumerate(op_list)], "pairs": res, "records": records}, f, indent=0)
     print(json.dumps(line), flush=True)
 
 
@@ -305,7 +310,8 @@ def measure_pair(rt, torch, bf, wl, pk, name, device, conv_batch=1, max_reps=24,
             alone.append(replay_us(rt, torch, g, reps))
             rt.graph_destroy(g)
         dims = lambda l: (l[0][0] * l[0][1] * l[0][2], l[1][0] * l[1][1] * l[1][2], l[2])
-        adv = pairing.advise(alone[0], alone[1], dims(spec.a.launch), dims(spec.b.launch), rt.sm_count, 1.0, spec.a.op, spec.b.op)
+        hosted = [k[len("fused_"):-len("_us")] for k in res if k.startswith("fused_") and k.endswith("_us")]
+        adv = pairing.advise(alone[0], alone[1], dims(spec.a.launch), dims(spec.b.launch), rt.sm_count, 1.0, spec.a.op, spec.b.op, allowed=hosted)
         got = res.get("fused_%s_us" % adv["pattern"])
         res["alone_us"] = alone
         res["model"] = {"pattern": adv["pattern"], "predicted_us": adv["predicted_fused_us"], "fuse": adv["fuse"], "measured_us": got,
@@ -532,6 +538,8 @@ def main():
     ap.add_argument("--sweep", action="store_true", help="run the 42 x 42 operator cross-product sweep instead (pair i on rank i mod N)")
     ap.add_argument("--sweep-out", default="", help="with --sweep: also write the per-pair table to this JSON file")
     ap.add_argument("--sweep-limit", type=int, default=0, help="with --sweep: only the first N operators")
+    ap.add_argument("--sweep-extra", action="store_true", help="with --sweep: the pairs of the pair-selection model's extra operators "
+                                                               "(memory-bound bodies, bf16 projections) with the suite's and with each other")
     ap.add_argument("--sweep-pattern", default="zigzag", choices=["zigzag", "range", "striped", "proportional", "all"],
                     help="with --sweep: the block-level pattern of the fused launches; all: every pattern per pair (what the pair-selection model is fitted on)")
     ap.add_argument("--batch", type=int, default=BATCH, help="images of the conv batch (256: the BASELINE configuration; smaller for profiler captures)")

@@ -13,7 +13,9 @@ time alone.  Two parts:
     least the SM-time both need (area):  core = max(max(t_a, t_b), fill_a * t_a + fill_b * t_b);
   * a per-pattern correction fitted by least squares on measured pairs: for pattern p and the class
     pair of the two bodies (row-wise / CUDA-core / tensor-core GEMM / tensor-core conv),
-        fused_p = w0 + w1 * core + w2 * min(t_a, t_b) + w3 * (t_a + t_b)
+        fused_p = w0 + w1 * core + w2 * min(t_a, t_b) + w3 * (t_a + t_b) + w4 * sum_k (slow_k - 1) * t_k
+    where slow_k is how many times more waves operator k needs once every CTA is charged the union of
+    the two shared-memory windows (`union_slowdown`)
     (`fit`, from the per-pattern times of the operator sweep, `python bench.py --sweep
     --sweep-pattern all --sweep-out F`; `python -m bfuse_project_b200.pairing F` writes the
     coefficients to pairing_model.json beside this file and prints the held-out evaluation).
@@ -57,9 +59,21 @@ def class_pair(op_a, op_b):
     return "|".join(sorted((BODY_CLASS.get(op_a, "row"), BODY_CLASS.get(op_b, "row"))))
 
 
-def features(t_a, t_b, fill_a, fill_b):
+def union_slowdown(launch, other, sm_count=148):
+    """How many times more waves an operator needs when every CTA of the fused grid is charged the larger of the
+    two shared-memory windows and the larger block (block-level fusion keeps the union of the windows): a
+    memory-bound operator of thousands of small CTAs beside a tensor-core tile with a whole-SM ring drops from
+    eight CTAs per SM to one."""
+    ctas, thr, smem = launch
+    per_alone = sm_count * ctas_per_sm(thr, smem)
+    per_union = sm_count * ctas_per_sm(max(thr, other[1]), max(smem, other[2]))
+    waves = lambda per: -(-int(ctas) // per)
+    return min(16.0, waves(per_union) / float(waves(per_alone)))
+
+
+def features(t_a, t_b, fill_a, fill_b, slow_a=1.0, slow_b=1.0):
     core = max(max(t_a, t_b), fill_a * t_a + fill_b * t_b)
-    return [1.0, core, min(t_a, t_b), t_a + t_b]
+    return [1.0, core, min(t_a, t_b), t_a + t_b, (slow_a - 1.0) * t_a + (slow_b - 1.0) * t_b]
 
 
 _model = None
@@ -80,7 +94,7 @@ def predict_by_pattern(t_a, t_b, launch_a, launch_b, op_a=None, op_b=None, sm_co
     model = load_model() if model is None else model
     if not model:
         return {"zigzag": predict_fused_us(t_a, t_b, fa, fb)}
-    x = features(t_a, t_b, fa, fb)
+    x = features(t_a, t_b, fa, fb, union_slowdown(launch_a, launch_b, sm_count), union_slowdown(launch_b, launch_a, sm_count))
     cp = class_pair(op_a, op_b)
     out = {}
     for p, table in model.items():
@@ -90,11 +104,14 @@ def predict_by_pattern(t_a, t_b, launch_a, launch_b, op_a=None, op_b=None, sm_co
     return out
 
 
-def advise(t_a, t_b, launch_a, launch_b, sm_count=148, margin=1.0, op_a=None, op_b=None, model=None):
+def advise(t_a, t_b, launch_a, launch_b, sm_count=148, margin=1.0, op_a=None, op_b=None, model=None, allowed=None):
     """The pattern with the smallest predicted fused time, the prediction, and whether to fuse (predicted
-    speed-up over back-to-back launches above `margin`)."""
+    speed-up over back-to-back launches above `margin`).  allowed: the patterns that can host the pair (a thread
+    split needs both shared-memory windows and both tensor-memory allocations in one CTA); default all."""
     fa, fb = fill(*launch_a, sm_count=sm_count), fill(*launch_b, sm_count=sm_count)
     preds = predict_by_pattern(t_a, t_b, launch_a, launch_b, op_a, op_b, sm_count, model)
+    if allowed is not None and any(p in preds for p in allowed):
+        preds = {p: v for p, v in preds.items() if p in allowed}
     pattern = min(preds, key=lambda p: preds[p])
     fused = preds[pattern]
     speedup = (t_a + t_b) / fused
@@ -105,7 +122,7 @@ def advise(t_a, t_b, launch_a, launch_b, sm_count=148, margin=1.0, op_a=None, op
 # ---------------------------------------------------------------------------------------------- fitting
 
 def _solve(rows, ys):
-    """Least squares with a small ridge term, by normal equations (4 x 4): no dependency beyond the standard library."""
+    """Least squares with a small ridge term, by normal equations: no dependency beyond the standard library."""
     n = len(rows[0])
     a = [[sum(r[i] * r[j] for r in rows) + (1e-6 if i == j else 0.0) for j in range(n)] for i in range(n)]
     b = [sum(r[i] * y for r, y in zip(rows, ys)) for i in range(n)]
@@ -134,7 +151,8 @@ def fit(records, min_bucket=12):
             if t is None:
                 continue
             fa, fb = fill(*r["launch_a"], sm_count=r.get("sm_count", 148)), fill(*r["launch_b"], sm_count=r.get("sm_count", 148))
-            x = features(r["t_a"], r["t_b"], fa, fb)
+            sm = r.get("sm_count", 148)
+            x = features(r["t_a"], r["t_b"], fa, fb, union_slowdown(r["launch_a"], r["launch_b"], sm), union_slowdown(r["launch_b"], r["launch_a"], sm))
             for bucket in (class_pair(r.get("op_a"), r.get("op_b")), "*"):
                 rows.setdefault(bucket, ([], []))
                 # relative error is what matters: weight every record by 1 / measured time
@@ -190,12 +208,14 @@ def main(argv=None):
     report on the other half, then fit on all records and write pairing_model.json."""
     import argparse
     ap = argparse.ArgumentParser(prog="pairing")
-    ap.add_argument("sweep_json", help="file written by `python bench.py --sweep --sweep-pattern all --sweep-out F`")
+    ap.add_argument("sweep_json", nargs="+", help="files written by `python bench.py --sweep --sweep-pattern all [--sweep-extra] --sweep-out F`")
     ap.add_argument("--margin", type=float, default=1.0)
     ap.add_argument("--out", default=MODEL_PATH)
     args = ap.parse_args(argv)
-    with open(args.sweep_json) as f:
-        records = [r for r in json.load(f)["records"] if r.get("fused_us_by_pattern")]
+    records = []
+    for path in args.sweep_json:
+        with open(path) as f:
+            records += [r for r in json.load(f)["records"] if r.get("fused_us_by_pattern")]
     records.sort(key=lambda r: r["pair"])
     train, held = records[0::2], records[1::2]
     report = {"records": len(records), "held_out": evaluate(held, args.margin, fit(train)),
@@ -203,7 +223,7 @@ def main(argv=None):
     weights = fit(records)
     report["all_records_refit"] = evaluate(records, args.margin, weights)
     with open(args.out, "w") as f:
-        json.dump({"fitted_on": os.path.basename(args.sweep_json), "records": len(records), "features": ["1", "core", "min(t_a,t_b)", "t_a+t_b"],
+        json.dump({"fitted_on": [os.path.basename(p) for p in args.sweep_json], "records": len(records), "features": ["1", "core", "min(t_a,t_b)", "t_a+t_b", "sum (union_slowdown-1)*t"],
                    "weights": weights, "held_out_report": report["held_out"]}, f, indent=1)
     print(json.dumps(report, indent=1))
     return 0

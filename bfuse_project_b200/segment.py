@@ -178,8 +178,19 @@ class Segment:
                         out.append(("group", rt.register_group(ks, pattern, m, m), idx))
                     elif use_model:
                         a, b = self.ops[idx[0]], self.ops[idx[1]]
-                        name = pairing.advise(a.alone_us, b.alone_us, a.launch, b.launch, rt.sm_count, 1.0, a.op, b.op)["pattern"]
-                        out.append(("pair", rt.register_fusion(ks[0], ks[1], *MODEL_PATTERNS[name]), idx))
+                        preds = pairing.advise(a.alone_us, b.alone_us, a.launch, b.launch, rt.sm_count, 1.0, a.op, b.op)["predicted_by_pattern"]
+                        handle, last = None, None
+                        for name in sorted(preds, key=lambda p: preds[p]):     # the best predicted pattern that can host the pair
+                            try:
+                                handle = rt.register_fusion(ks[0], ks[1], *MODEL_PATTERNS[name])
+                                break
+                            except BfuseError as e:
+                                if e.code not in (3, 7):
+                                    raise
+                                last = e
+                        if handle is None:
+                            raise last
+                        out.append(("pair", handle, idx))
                     else:
                         out.append(("pair", rt.register_fusion(ks[0], ks[1], pattern, m, m), idx))
                     for i, k in zip(idx, ks):

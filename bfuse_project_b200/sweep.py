@@ -15,8 +15,9 @@ stay in L2 as they do in the reference's own loop.
 """
 import math
 
-from . import (BfuseError, MODE_FUSED, MODE_KERNEL1, MODE_SEQUENTIAL, OP_CONV2D_F32_SIMT, OP_CONV2D_TF32, OP_GEMM_TF32, PROPORTIONAL,
-               RANGE_SPLIT, SM_STRIPED, THREAD_SPLIT, ZIGZAG)
+from . import (BfuseError, FLAG_CAUSAL, MODE_FUSED, MODE_KERNEL1, MODE_SEQUENTIAL, OP_CONV2D_F32_SIMT, OP_CONV2D_TF32, OP_GEMM_BF16,
+               OP_GEMM_TF32, OP_LAYERNORM_F32, OP_RMSNORM_BF16, OP_ROPE_BF16, OP_SOFTMAX_F32, PROPORTIONAL, RANGE_SPLIT, SM_STRIPED,
+               THREAD_SPLIT, ZIGZAG)
 
 # the fused forms a pair is timed in when every pattern is asked for: (label, pattern, M, N)
 ALL_PATTERNS = (("zigzag", ZIGZAG, 1, 1), ("zigzag2", ZIGZAG, 1, 2), ("range", RANGE_SPLIT, 0, 0), ("striped", SM_STRIPED, 0, 0),
@@ -45,6 +46,19 @@ SWEEP_OPS = (
 )
 
 
+# Operators beyond the reference's suite, for the pair-selection model only: the memory-bound bodies and the bf16
+# projections of the model studies, which the reference's 42 shapes (dense / batch-matmul / conv2d) do not contain.
+# softmax: (rows, cols); layernorm: (rows, cols, residual); rmsnorm: (rows, cols); rope: (seq, heads, dim);
+# dense16 (bf16 GEMM): (M, K, N); causal (QK^T with mask): (batch, M, K, N)
+MODEL_EXTRA_OPS = (
+    ("softmax_0", (6144, 512)), ("softmax_1", (16384, 512)), ("softmax_2", (1536, 1024)),
+    ("layernorm_0", (512, 768, 0)), ("layernorm_1", (512, 768, 1)), ("layernorm_2", (4096, 1024, 1)),
+    ("rmsnorm_0", (512, 4096)), ("rmsnorm_1", (2048, 4096)), ("rope_0", (512, 32, 128)), ("rope_1", (512, 8, 128)),
+    ("dense16_0", (512, 4096, 1024)), ("dense16_1", (512, 4096, 14336)), ("dense16_2", (512, 4096, 4096)),
+    ("causal_0", (12, 512, 64, 512)),
+)
+
+
 def pair_indices(n=len(SWEEP_OPS)):
     """(i, j) with j >= i, in the reference's enumeration order."""
     return [(i, j) for i in range(n) for j in range(i, n)]
@@ -69,7 +83,42 @@ class SweepOperand:
         def randn(*dims, std=1.0):
             return torch.randn(*dims, device=dev, dtype=torch.float32, generator=gen) * std
 
-        if name.startswith("conv2d"):
+        self.flops = 0.0
+        kind = name.split("_")[0]
+        if kind in ("softmax", "layernorm", "rmsnorm", "rope"):
+            bf16 = kind in ("rmsnorm", "rope")
+            dt = torch.bfloat16 if bf16 else torch.float32
+            if kind == "rope":
+                seq, heads, dim = shape
+                inv = (500000.0 ** (-2.0 * torch.arange(dim // 2, device=dev, dtype=torch.float64) / dim)).float()
+                self.bufs = [randn(seq, heads, dim).to(dt), inv, torch.zeros(seq, heads, dim, device=dev, dtype=dt)]
+                self.op, args, oshape, fparam = OP_ROPE_BF16, [0, 1, 2], (seq, heads, dim), ()
+            else:
+                rows, cols = shape[0], shape[1]
+                x, y = randn(rows, cols).to(dt), torch.zeros(rows, cols, device=dev, dtype=dt)
+                if kind == "softmax":
+                    self.bufs, self.op, args, fparam = [x, y], OP_SOFTMAX_F32, [0, 1], (0.125,)
+                elif kind == "rmsnorm":
+                    self.bufs, self.op, args, fparam = [x, (torch.rand(cols, device=dev, generator=gen) + 0.5).to(dt), y], OP_RMSNORM_BF16, [0, 1, 2], (1e-5,)
+                else:
+                    res = randn(rows, cols) if shape[2] else None
+                    g, b = torch.rand(cols, device=dev, generator=gen) + 0.5, torch.rand(cols, device=dev, generator=gen) + 0.5
+                    self.bufs, self.op, fparam = [x, g, b, y] + ([res] if res is not None else []), OP_LAYERNORM_F32, (1e-5,)
+                    args = [0, 4 if res is not None else None, 1, 2, 3]
+                oshape = (rows, cols)
+            desc = rt.describe(name, self.op, oshape, [None if i is None else self.bufs[i].data_ptr() for i in args], fparam)
+        elif kind in ("dense16", "causal"):
+            if kind == "dense16":
+                (m, k, nn), b, dt = shape, 1, torch.bfloat16
+                self.op, flags = OP_GEMM_BF16, 0
+            else:
+                (b, m, k, nn), dt = shape, torch.float32
+                self.op, flags = OP_GEMM_TF32, FLAG_CAUSAL
+            self.bufs = [randn(b, m, k).to(dt), randn(b, nn, k, std=0.02 if b == 1 else 1.0).to(dt), torch.zeros(b, m, nn, device=dev, dtype=dt)]
+            self.flops = 2.0 * b * m * nn * k
+            desc = rt.describe(name, self.op, (b, m, nn, k, 0, 0), [self.bufs[0].data_ptr(), self.bufs[1].data_ptr(), None, self.bufs[2].data_ptr()],
+                               flags=flags)
+        elif name.startswith("conv2d"):
             n, h, w, co, ci, kh, kw, stride, pad = shape
             oh, ow = (h + 2 * pad - kh) // stride + 1, (w + 2 * pad - kw) // stride + 1
             self.bufs = [randn(n, ci, h, w), randn(co, ci, kh, kw, std=math.sqrt(2.0 / (ci * kh * kw))),

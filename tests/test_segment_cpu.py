@@ -158,12 +158,12 @@ def test_pairing_model_fit_recovers_a_planted_rule_and_names_patterns():
         recs.append(dict(pair="p%03d" % i, t_a=ta, t_b=tb, launch_a=la, launch_b=lb, op_a=6, op_b=6, fused_us=zz, sequential_us=ta + tb,
                          fused_us_by_pattern={"zigzag": zz, "range": rg}))
     w = pairing.fit(recs)
-    assert set(w) == set(pairing.PATTERNS) and w["zigzag"]["gemm|gemm"] == pytest.approx([1.0, 1.0, 0.0, 0.0], abs=1e-3)
-    assert w["range"]["*"] == pytest.approx([1.0, 1.0, -0.1, 0.02], abs=1e-3) and not w["striped"]
+    assert set(w) == set(pairing.PATTERNS) and w["zigzag"]["gemm|gemm"][:4] == pytest.approx([1.0, 1.0, 0.0, 0.0], abs=1e-3)
+    assert w["range"]["*"][:4] == pytest.approx([1.0, 1.0, -0.1, 0.02], abs=1e-3) and not w["striped"]
     ev = pairing.evaluate(recs, model=w)
     assert ev["median_rel_err"] < 1e-3 and ev["pattern_within_2_pct_of_best"] == 1.0
     shipped = pairing.load_model()
-    assert shipped and set(shipped) == set(pairing.PATTERNS) and all("*" in t and len(t["*"]) == 4 for t in shipped.values())
+    assert shipped and set(shipped) == set(pairing.PATTERNS) and all("*" in t and len(t["*"]) == 5 for t in shipped.values())
     adv = pairing.advise(7.3, 7.3, (48, 192, 198656), (48, 192, 198656), op_a=6, op_b=6)
     assert adv["pattern"] in pairing.PATTERNS and adv["fuse"] and 7.0 < adv["predicted_fused_us"] < 10.0
 
