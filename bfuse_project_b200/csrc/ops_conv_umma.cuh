@@ -28,13 +28,14 @@
 // A long K (deep layers on small images leave few tiles) can be split over the CTAs of a cluster,
 // reduced through distributed shared memory like the GEMM's k-slices.
 //
-// BlockDim = (192, 1, 1); GridDim = (split * ceil(oh*ow / BN), ceil(co / 128), n).
+// BlockDim = (224, 1, 1); GridDim = (split * ceil(oh*ow / BN), ceil(co / 128), n).
 #pragma once
 
 #include "ops_umma.cuh"
 
 namespace bfuse {
 
+constexpr int kConvThreads = 224;            // warps 0-3 build the operand and run the epilogue, 4 and 6 issue loads, 5 the MMAs
 constexpr int kConvBN = 128;                 // output pixels per tile, at most
 constexpr int kConvMaxK = 8192;              // ci * kh * kw the offset table may hold (64 KB of shared memory)
 // header of the operator window: barriers etc., then the offset table -- int2 {input offset, tap
@@ -48,7 +49,9 @@ __host__ __device__ constexpr int conv_umma_smem_bytes(int stages, int bn, int K
 
 constexpr int kConvMaxRawSlots = 4;
 constexpr int kConvRawBarOffset = 256;   // byte offset of the raw ring's barriers in the header: full[4], then empty[4]
-constexpr int kConvZeroOffset = 512;     // 16 bytes of zeros in the header: what the repack reads for k >= K
+constexpr int kConvAStages = 4;          // staged convs: K blocks of the im2col operand held in tensor memory (32 columns each);
+                                         // their barriers follow the raw ring's in the header: full[4], then empty[4]
+constexpr int kConvTmemCols = 256;       // staged convs: 128 accumulator columns + 4 x 32 operand columns
 
 // Geometry of the raw-input staging of a conv (shared by the host, which sizes shared memory and
 // encodes the tensor map, and the kernel).  A slot holds `cc` channels x `rows` staged rows x
@@ -73,7 +76,7 @@ __host__ __device__ inline bool conv_staging(int ci, int h, int wd, int kh, int 
                                              ConvStaging *st) {
   (void)h;
   st->slots = 0;
-  if (wd % 4) return false;
+  if (wd % 4 || (ci * kh * kw) % 32 || bn != kConvBN) return false;   // whole K blocks, whole 128-pixel tiles (the lanes of tensor memory)
   st->ey = (kh == 1 && stride <= 8) ? stride : 1;   // a traversal stride is at most 8
   st->ex = 1;
   const int out_rows = min(oh, (bn - 1 + ow - 1) / ow + 1);   // output rows that bn consecutive pixels can touch
@@ -163,7 +166,7 @@ __device__ __forceinline__ int4 ld_shared_i4(uint32_t addr) {
 
 struct ConvUmmaTf32 {
   using Params = ConvUmmaParams;
-  static constexpr int kMaxThreads = kUmmaThreads;
+  static constexpr int kMaxThreads = kConvThreads;
   static constexpr int kMinBlocks = 2;      // two CTAs per SM: one tile's epilogue runs under the other's main loop (a build for three -- 96 registers --
                                             // gained 7 % at batch 256 and lost 30 % at batch 32, where every CTA has an SM's issue slots to itself)
   static constexpr bool kMemoryBound = false;
@@ -227,113 +230,301 @@ struct ConvUmmaTf32 {
     return __shfl_sync(0xffffffffu, ok, 0) != 0;
   }
 
-  // The im2col operand of one tile built from the raw ring by the four epilogue warps (gt = 0..127).
-  // Thread layout as in gather(): consecutive lanes take consecutive pixels, thread `sub` of a pixel its
-  // share of the stage's 32 values of k, in 16-byte chunks of four.  tab[k] is the byte offset of k's
-  // (channel within the slot, dy, dx) inside a slot, relative to the pixel's window origin.  All threads
-  // walk the same sequence of k, so the slot bookkeeping (which ring slot holds k, its phase) is
-  // uniform per warp; a warp arrives on a slot's "empty" barrier once it has moved past the slot.
+  // The staged form of a tile: 128 output pixels x 128 output channels with the operands' roles swapped
+  // relative to run() -- the im2col rows are the A operand and live in TENSOR memory, the weights are the
+  // B operand in shared memory, and the accumulator holds pixels in its lanes and output channels in its
+  // columns.  Thread r of the four repack warps owns pixel r of the tile, which is also lane r of tensor
+  // memory: it reads its window's 32 values of a K block out of the raw ring (one 16-byte table read per
+  // four values: their byte offsets from the window's origin inside a slot), and writes them with one
+  // tcgen05.st into the K block's 32 columns of a four-deep ring of A stages.  Compared with building
+  // the operand in shared memory this takes the operand's write and the MMA's read of it (2 x 16 KB per K
+  // block) off the shared-memory pipe, which the raw loads, the repack's reads, the weight loads and the
+  // MMA's weight reads already keep busy; it needs no proxy fence; it leaves the shared memory of the
+  // operand ring to four weight stages; and the epilogue's stores are coalesced as they come out of
+  // tensor memory (a warp's 32 lanes are 32 consecutive pixels of one output channel), so it needs no
+  // staging buffers either.
   //
-  // A K block is done in four straight-line phases -- slot bookkeeping and waits (the only branches),
-  // then every table read, then every raw read, then the stores -- because the compiler lets
-  // outstanding shared-memory reads complete at every branch: with a branch per chunk each chunk paid
-  // its own two round trips to shared memory (about 150 clocks per chunk, 1200 per K block; in
-  // phases the K block costs what its ~100 shared-memory wavefronts per warp cost).  A chunk past K
-  // (K padded up to a whole K block) reads a 16-byte zero area instead of branching around the reads:
-  // the weights' padding is zero too, but 0 x garbage must not be NaN.
-  template <int BN>
-  __device__ __forceinline__ static bool repack(const Params &p, const TileCtx &c, int gt, int px0, int kb0, int num_kb, int stages,
-                                                uint32_t tiles, uint32_t full0, uint32_t empty0, uint32_t raw0, uint32_t raw_full0,
-                                                uint32_t raw_empty0, uint32_t tab, uint32_t zeros, long long *tl) {
-    constexpr int kStageBytes = conv_stage_bytes(BN), kper = kBK * BN / 128, kChunks = kper / 4;
-    // Every parameter the loop needs is read into registers here: the loop is full of asm statements
-    // that clobber memory, after each of which the compiler would otherwise read the parameter block again.
-    const ConvStaging st = p.st;
-    const int K = p.K, ow = p.ow;
-    const uint32_t slot_pitch = (uint32_t)st.slot_pitch;
+  // Warps: 0-3 repack and epilogue, 4 raw loads, 5 MMA, 6 weight loads (two issuing warps: the loads a
+  // single thread issues complete one after another).  All threads walk the same k, so which ring slot
+  // holds a value of k is uniform and found by comparisons: a K block of 32 touches at most three slots
+  // (a slot holds at least 16 values of k); a loop or a branch per chunk costs this code -- one warp per
+  // scheduler, nothing to hide a branch behind -- more than the copying.  A wait costs 100-200 clocks even
+  // when its barrier has completed, so every K block looks at the next one's barriers without blocking
+  // while its own reads are in flight, and the next K block waits only for what was not there yet.
+  __device__ __forceinline__ static void run_staged(const Params &p, const TileCtx &c) {
+    const int warp = c.tid >> 5, lane = c.tid & 31;
+    const int quad = (threadIdx.x >> 5) & 3;
+    const int px0 = c.block_x() * kConvBN, co0 = c.block_y() * kUmmaBM, img = c.block_z();
+    const int ohw = p.oh * p.ow, K = p.K, num_kb = K / kBK;   // staged: K is a whole number of K blocks
+    const int wstages = min(2 * p.stages, kUmmaMaxStages);    // the operand ring's stages hold two 16 KB weight stages each
     int *const status = c.status;
-    const int r = gt & (BN - 1), sub = gt / BN, pix = px0 + r, ohw = p.oh * ow;
-    // a row past the image reads the window of pixel 0 of the tile: finite values, and its output
-    // columns are clipped by the store
-    const int oy0 = px0 / ow;
-    int oy = pix / ow, ox = pix - oy * ow;
-    if (pix >= ohw) oy = oy0, ox = px0 - oy0 * ow;
-    const uint32_t pixoff = (uint32_t)(((oy - oy0) * st.step_y * st.pitch + ox * st.step_x + st.x_off) * 4);
-    const int kslot = st.cc * p.kh * p.kw, nslots = st.slots;
-    // ring slot (index, phase) that holds the next k, k's position inside it, first slot not yet released
-    int kin = kb0 * kBK + sub * kper - (kb0 * kBK / kslot) * kslot;
-    uint32_t rs = 0, rph = 0, rel_s = 0;
-    bool have = false;
-    const uint32_t swz = (uint32_t)(r & 7);
-    const bool lane0 = (gt & 31) == 0;
-    uint32_t s = 0, ph = 1;
-    for (int kb = 0; kb < num_kb; ++kb) {
-      // one lane per warp polls the barrier and the warp follows it (its lanes meet again at the __syncwarp
-      // before the arrival below, so the outcome of a wait has to be the same for all of them anyway)
-      if (!warp_wait(lane0, empty0 + 8 * s, ph, status, UMMA_WAIT_EMPTY_TIMEOUT)) return false;
-      const uint32_t brow = tiles + s * kStageBytes + kUmmaABytes + (uint32_t)r * 128u;
-      const int k0 = (kb0 + kb) * kBK + sub * kper;
-      // phase 0: which slot holds each chunk (waiting for slots not seen yet); no shared-memory reads
-      uint32_t src[kChunks], tix[kChunks];
-      int rel = 0;
-#pragma unroll
-      for (int i = 0; i < kChunks; ++i) {
-        const int k = k0 + 4 * i;
-        if (k < K) {
-          while (kin >= kslot) {   // k lies in a later slot: pass the current one
-            kin -= kslot, ++rel, have = false;
-            if (++rs == (uint32_t)nslots) rs = 0, rph ^= 1;
-          }
-          if (!have) {
-            if (!warp_wait(lane0, raw_full0 + 8 * rs, rph, status, UMMA_WAIT_FULL_TIMEOUT)) return false;
-            have = true;
-          }
-          src[i] = raw0 + rs * slot_pitch + pixoff;
-          tix[i] = tab + (uint32_t)(k - kb0 * kBK) * 4u;
-        } else {
-          src[i] = zeros;   // with the table entry of k = kb0 * 32 replaced by offsets 0 below
-          tix[i] = 0;
-        }
-        kin += 4;
-      }
-      // phase 1: the table entries (four byte offsets per chunk)
-      int4 off[kChunks];
-#pragma unroll
-      for (int i = 0; i < kChunks; ++i) off[i] = ld_shared_i4(tix[i] ? tix[i] : tab);
-      // phase 2: the raw values
-      float v[kChunks][4];
-#pragma unroll
-      for (int i = 0; i < kChunks; ++i) {
-        const bool pad = tix[i] == 0;
-        v[i][0] = ld_shared_f32(src[i] + (pad ? 0u : (uint32_t)off[i].x));
-        v[i][1] = ld_shared_f32(src[i] + (pad ? 4u : (uint32_t)off[i].y));
-        v[i][2] = ld_shared_f32(src[i] + (pad ? 8u : (uint32_t)off[i].z));
-        v[i][3] = ld_shared_f32(src[i] + (pad ? 12u : (uint32_t)off[i].w));
-      }
-      // phase 3: the operand row's 16-byte chunks
-#pragma unroll
-      for (int i = 0; i < kChunks; ++i)
-        st_shared_u4(brow + ((((uint32_t)(sub * kChunks + i)) ^ swz) << 4), __float_as_uint(v[i][0]), __float_as_uint(v[i][1]),
-                     __float_as_uint(v[i][2]), __float_as_uint(v[i][3]));
-      kin += kBK - kper;   // the other threads of this pixel take the rest of the K block
-      fence_async_smem();  // the operand was written through the generic proxy; the MMA reads it through the async proxy
-      __syncwarp();
-      // One arrival per warp (its lanes walk the same k): 128 arrivals on one barrier word serialise.
-      // The raw reads above have completed (their values were stored), so the slots passed on the way are free.
-      if (lane0) {
-        mbar_arrive(full0 + 8 * s);
-        for (int i = 0; i < rel; ++i) mbar_arrive(raw_empty0 + 8 * (rel_s + i < (uint32_t)nslots ? rel_s + i : rel_s + i - nslots));
-      }
-      rel_s += rel;
-      if (rel_s >= (uint32_t)nslots) rel_s -= nslots;
-      if (tl && gt == 0 && kb == 0) tl[MARK_FIRST_LOAD_ISSUED] = (long long)global_ns();
-      if (tl && gt == 0 && kb == num_kb - 1) tl[MARK_LAST_LOAD_ISSUED] = (long long)global_ns();
-      if (++s == (uint32_t)stages) s = 0, ph ^= 1;
+    const uint32_t idesc = umma_idesc(0, kUmmaBM);            // M = 128 pixels, N = 128 output channels
+
+    uint64_t *bars = reinterpret_cast<uint64_t *>(c.smem);
+    const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * kUmmaMaxStages, acc_bar = empty0 + 8 * kUmmaMaxStages;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(c.smem + 8 * (2 * kUmmaMaxStages + 2));
+    const uint32_t raw_full0 = full0 + kConvRawBarOffset, raw_empty0 = raw_full0 + 8 * kConvMaxRawSlots;
+    const uint32_t a_full0 = raw_empty0 + 8 * kConvMaxRawSlots, a_empty0 = a_full0 + 8 * kConvAStages;
+    const uint32_t raw0 = smem_u32(c.smem) + conv_header_bytes(K);
+    const uint32_t wring = raw0 + (uint32_t)conv_raw_bytes(p.st.slots, p.st.slot_pitch);
+    if (warp == 5) {
+      tmem_alloc(smem_u32(tmem_slot), kConvTmemCols);
+      if (!c.persistent) tmem_relinquish();
     }
-    return true;
+    long long *const tl = (p.timeline && c.vblock == 0) ? p.timeline : nullptr;
+    auto mark = [&](int what, bool who) {
+      if (tl && who) tl[what] = (long long)global_ns();
+    };
+    mark(MARK_START, c.tid == 0);
+    if (warp == 4) {
+      if (lane < wstages) {
+        mbar_init(full0 + 8 * lane, 1);    // the weight load's arrive.expect_tx
+        mbar_init(empty0 + 8 * lane, 1);   // the MMA's commit
+      }
+      if (lane < kConvAStages) {
+        mbar_init(a_full0 + 8 * lane, 4);  // one arrival per repack warp
+        mbar_init(a_empty0 + 8 * lane, 1); // the MMA's commit
+      }
+      if (lane < p.st.slots) {
+        mbar_init(raw_full0 + 8 * lane, 1);   // the slot's TMA load (arrive.expect_tx)
+        mbar_init(raw_empty0 + 8 * lane, 4);  // every repack warp, once it has moved past the slot
+      }
+      if (lane == 0) mbar_init(acc_bar, 1);
+      asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&p.map_w) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&p.map_x) : "memory");
+      }
+    }
+    int *tab4 = reinterpret_cast<int *>(c.smem + kUmmaHeaderBytes);
+    if (warp < 4) {
+      // entry k: the byte offset of (channel within its slot, dy, dx) inside a raw slot.  Thread t fills
+      // entries t, t + 128, ...: (channel, tap) advance by the decomposition of 128, and tap -> (dy, dx)
+      // is a multiply-shift (exact for taps < 32), so the loop has no division.
+      const int khw = p.kh * p.kw, step_ch = 128 / khw, step_r = 128 % khw;
+      const int inv_kw = (65536 + p.kw - 1) / p.kw;
+      const int plane = p.st.rows * p.st.pitch;
+      int ch = c.tid / khw, r = c.tid - ch * khw;
+      for (int k = c.tid; k < K; k += 128) {
+        const int dy = (r * inv_kw) >> 16, dx = r - dy * p.kw;
+        tab4[k] = (((ch & (p.st.cc - 1)) * plane) + dy * p.st.pitch + dx) * 4;
+        ch += step_ch, r += step_r;
+        if (r >= khw) r -= khw, ++ch;
+      }
+    }
+    c.dependency_wait();   // nothing above touches global memory: barriers, tensor memory and the table overlap the previous kernel
+    tc_fence_before();
+    c.sync();
+    tc_fence_after();
+    const uint32_t tmem_acc = *reinterpret_cast<volatile uint32_t *>(tmem_slot);
+    const uint32_t tmem_row = tmem_acc + ((uint32_t)(quad * 32) << 16);   // this warp's lanes; columns 0-127: accumulator, then the A stages
+    mark(MARK_SETUP_DONE, c.tid == 0);
+
+    if (warp == 4) {
+      if (elect_one()) {
+        const int cc = p.st.cc, kslot = cc * p.kh * p.kw, x_start = p.st.x_start, nslots = p.st.slots;
+        const uint32_t slot_bytes = (uint32_t)p.st.slot_bytes, slot_pitch = (uint32_t)p.st.slot_pitch;
+        const int g_end = (K - 1) / kslot + 1;
+        const int y_start = (px0 / p.ow) * p.stride - p.pad;
+        uint32_t rs = 0, rph = 1;
+        for (int g = 0; g < g_end; ++g) {
+          if (!mbar_wait(raw_empty0 + 8 * rs, rph, status, UMMA_WAIT_EMPTY_TIMEOUT)) break;
+          mbar_expect_tx(raw_full0 + 8 * rs, slot_bytes);
+          tma_load_4d(raw0 + rs * slot_pitch, &p.map_x, raw_full0 + 8 * rs, x_start, y_start, g * cc, img);
+          if (++rs == (uint32_t)nslots) rs = 0, rph ^= 1;
+        }
+      }
+      __syncwarp();
+    } else if (warp == 6) {
+      if (elect_one()) {
+        uint32_t s = 0, ph = 1, dst = wring, bar = full0;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(empty0 + 8 * s, ph, status, UMMA_WAIT_EMPTY_TIMEOUT)) break;
+          mbar_expect_tx(bar, kUmmaABytes);
+          tma_load_3d(dst, &p.map_w, bar, kb * kBK, co0, 0);
+          if (++s == (uint32_t)wstages) s = 0, ph ^= 1, dst = wring, bar = full0;
+          else dst += kUmmaABytes, bar += 8;
+        }
+      }
+      __syncwarp();
+    } else if (warp == 5) {
+      if (elect_one()) {
+        const uint32_t lo0 = ((wring >> 4) & 0x3fffu) | (1u << 16);
+        uint32_t s = 0, ph = 0, lo = lo0, as = 0, aph = 0, accumulate = 0;
+        bool ok = true;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = mbar_wait(a_full0 + 8 * as, aph, status, UMMA_WAIT_FULL_TIMEOUT) && mbar_wait(full0 + 8 * s, ph, status, UMMA_WAIT_FULL_TIMEOUT);
+          if (!ok) break;
+          tc_fence_after();
+          if (kb == 0) mark(MARK_FIRST_FULL, true);
+          const uint32_t a_tmem = tmem_acc + (uint32_t)(kUmmaBM + as * kBK);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            umma_ts_tf32(tmem_acc, a_tmem + 8 * j, lo + 2 * j, idesc, accumulate);
+            accumulate = 1;
+          }
+          umma_commit(empty0 + 8 * s);
+          umma_commit(a_empty0 + 8 * as);
+          if (++s == (uint32_t)wstages) s = 0, ph ^= 1, lo = lo0;
+          else lo += (uint32_t)kUmmaABytes >> 4;
+          if (++as == (uint32_t)kConvAStages) as = 0, aph ^= 1;
+        }
+        umma_commit(acc_bar);
+        mark(MARK_LAST_MMA_ISSUED, true);
+        // every commit has arrived before the barriers are invalidated and the ring is given up
+        for (int kb = max(0, num_kb - wstages); kb < num_kb && ok; ++kb)
+          ok = mbar_wait(empty0 + 8 * (kb % wstages), (kb / wstages) & 1, status, UMMA_WAIT_EMPTY_TIMEOUT);
+        for (int kb = max(0, num_kb - kConvAStages); kb < num_kb && ok; ++kb)
+          ok = mbar_wait(a_empty0 + 8 * (kb % kConvAStages), (kb / kConvAStages) & 1, status, UMMA_WAIT_EMPTY_TIMEOUT);
+      }
+      __syncwarp();
+    } else {
+      const int r = quad * 32 + lane, pix = px0 + r;
+      const bool lane0 = lane == 0;
+      bool ok = true;
+      {
+        // Every parameter the loop needs is read into registers here: the loop is full of asm statements
+        // that clobber memory, after each of which the compiler would otherwise read the parameter block again.
+        const ConvStaging st = p.st;
+        const int ow = p.ow;
+        const uint32_t slot_pitch = (uint32_t)st.slot_pitch;
+        // a row past the image reads the window of pixel 0 of the tile: finite values, and it is not stored
+        const int oy0 = px0 / ow;
+        int oy = pix / ow, ox = pix - oy * ow;
+        if (pix >= ohw) oy = oy0, ox = px0 - oy0 * ow;
+        const uint32_t pixoff = (uint32_t)(((oy - oy0) * st.step_y * st.pitch + ox * st.step_x + st.x_off) * 4);
+        const int kslot = st.cc * p.kh * p.kw, nslots = st.slots;
+        const uint32_t tab = smem_u32(tab4), rawpix = raw0 + pixoff, ring_bytes = (uint32_t)nslots * slot_pitch;
+        const uint32_t a_row = tmem_row + (uint32_t)kUmmaBM;
+        // The K block's first slot: ring index, phase, and where the K block starts inside it; how many slots
+        // from there on have been seen full.
+        int kin = 0, ahead = 0;
+        uint32_t rs = 0, rph = 0, as = 0, aph = 1;
+        bool seen_empty = false, seen_raw = false;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          // one lane per warp polls a barrier and the warp follows it (its lanes meet again at the __syncwarp
+          // before the arrival below, so the outcome of a wait has to be the same for all of them anyway)
+          if (!seen_empty && !(ok = warp_wait(lane0, a_empty0 + 8 * as, aph, status, UMMA_WAIT_EMPTY_TIMEOUT))) break;
+          tc_fence_after();   // the MMAs that read this A stage have completed (their commit): it may be written again
+          // slots the K block reads: the first one and `last` more
+          const int reach = kin + kBK - 1;
+          const int last = (reach >= kslot) + (reach >= 2 * kslot);
+          if (seen_raw) ++ahead;
+          while (ahead <= last) {
+            uint32_t w = rs + (uint32_t)ahead, wph = rph;
+            if (w >= (uint32_t)nslots) w -= nslots, wph ^= 1;
+            if (!(ok = warp_wait(lane0, raw_full0 + 8 * w, wph, status, UMMA_WAIT_FULL_TIMEOUT))) break;
+            ++ahead;
+          }
+          if (!ok) break;
+          // the table entries (four byte offsets per chunk of four k) and which slot each chunk reads: chunk i
+          // starts kin + 4 i values of k into slot rs, so the chunks from j1 on read the next slot and those
+          // from j2 on the one after (all multiples of 4: exact shifts)
+          const uint32_t tabk = tab + (uint32_t)(kb * kBK) * 4u;
+          uint32_t b0 = rawpix + rs * slot_pitch, b1 = b0 + slot_pitch, b2 = b1 + slot_pitch;
+          if (rs + 1 >= (uint32_t)nslots) b1 -= ring_bytes;
+          if (rs + 2 >= (uint32_t)nslots) b2 -= ring_bytes;
+          const int j1 = (kslot - kin) >> 2, j2 = j1 + (kslot >> 2);
+          int4 off[8];
+          uint32_t src[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            off[i] = ld_shared_i4(tabk + 16u * i);
+            src[i] = i >= j2 ? b2 : i >= j1 ? b1 : b0;
+          }
+          // on to the next K block's position in the ring (the slots that end inside this one are released below)
+          const int passed = (kin + kBK >= kslot) + (kin + kBK >= 2 * kslot);
+          const uint32_t rs_old = rs, as_old = as;
+          kin += kBK - passed * kslot, ahead -= passed, rs += passed;
+          if (rs >= (uint32_t)nslots) rs -= nslots, rph ^= 1;
+          if (++as == (uint32_t)kConvAStages) as = 0, aph ^= 1;
+          seen_empty = false, seen_raw = false;
+          if (kb + 1 < num_kb) {
+            const int reach_n = kin + kBK - 1;
+            const bool more = ahead <= (reach_n >= kslot) + (reach_n >= 2 * kslot);
+            uint32_t w = rs + (uint32_t)ahead, wph = rph;
+            if (w >= (uint32_t)nslots) w -= nslots, wph ^= 1;
+            const bool e = mbar_test(a_empty0 + 8 * as, aph);
+            const bool f = more && mbar_test(raw_full0 + 8 * w, wph);
+            seen_empty = __all_sync(0xffffffffu, e);
+            seen_raw = __all_sync(0xffffffffu, f);
+          }
+          // the raw values, then all 32 into this lane's columns of the A stage
+          uint32_t v[32];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            v[4 * i] = __float_as_uint(ld_shared_f32(src[i] + (uint32_t)off[i].x));
+            v[4 * i + 1] = __float_as_uint(ld_shared_f32(src[i] + (uint32_t)off[i].y));
+            v[4 * i + 2] = __float_as_uint(ld_shared_f32(src[i] + (uint32_t)off[i].z));
+            v[4 * i + 3] = __float_as_uint(ld_shared_f32(src[i] + (uint32_t)off[i].w));
+          }
+          tmem_st_32x32(a_row + as_old * (uint32_t)kBK, v);
+          tmem_st_wait();
+          tc_fence_before();
+          __syncwarp();
+          // One arrival per warp.  The raw reads above have completed (their values were stored), so the
+          // slots that end inside this K block are free.
+          if (lane0) {
+            mbar_arrive(a_full0 + 8 * as_old);
+            if (passed > 0) mbar_arrive(raw_empty0 + 8 * rs_old);
+            if (passed > 1) mbar_arrive(raw_empty0 + 8 * (rs_old + 1 < (uint32_t)nslots ? rs_old + 1 : 0u));
+          }
+          if (kb == 0) mark(MARK_FIRST_LOAD_ISSUED, r == 0);
+          if (kb == num_kb - 1) mark(MARK_LAST_LOAD_ISSUED, r == 0);
+        }
+      }
+      // epilogue: lane = pixel, column = output channel; a warp's store covers 32 consecutive pixels of one channel
+      const bool acc_ok = ok && mbar_wait(acc_bar, 0, status, UMMA_WAIT_ACC_TIMEOUT);
+      tc_fence_after();
+      mark(MARK_ACC_READY, c.tid == 0);
+      if (acc_ok) {
+        float *const yp = p.y + ((size_t)img * p.co + co0) * ohw + pix;
+        const bool live = pix < ohw;
+        const int co_left = p.co - co0;
+#pragma unroll 1
+        for (int cc = 0; cc < kUmmaBM; cc += 32) {
+          uint32_t r0[16], r1[16];
+          tmem_ld_32x16(tmem_row + cc, r0);
+          tmem_ld_32x16(tmem_row + cc + 16, r1);
+          tmem_ld_wait();
+          if (live) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (cc + j < co_left) yp[(size_t)(cc + j) * ohw] = __uint_as_float(r0[j]);
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (cc + 16 + j < co_left) yp[(size_t)(cc + 16 + j) * ohw] = __uint_as_float(r1[j]);
+          }
+        }
+      }
+    }
+    tc_fence_before();
+    c.sync();
+    if (warp == 5) tmem_dealloc(tmem_acc, kConvTmemCols);
+    if (c.persistent) {  // the next tile of a persistent CTA initialises them again
+      if (c.tid < wstages) {
+        mbar_inval(full0 + 8 * c.tid);
+        mbar_inval(empty0 + 8 * c.tid);
+      }
+      if (c.tid < kConvAStages) {
+        mbar_inval(a_full0 + 8 * c.tid);
+        mbar_inval(a_empty0 + 8 * c.tid);
+      }
+      if (c.tid < p.st.slots) {
+        mbar_inval(raw_full0 + 8 * c.tid);
+        mbar_inval(raw_empty0 + 8 * c.tid);
+      }
+      if (c.tid == 0) mbar_inval(acc_bar);
+    }
+    mark(MARK_END, c.tid == 0);
   }
 
   __device__ __forceinline__ static void run(const Params &p, const TileCtx &c) {
+    if (p.st.slots > 0) {
+      run_staged(p, c);
+      return;
+    }
     const int warp = c.tid >> 5, lane = c.tid & 31;
     const int quad = (threadIdx.x >> 5) & 3;
     const int BN = p.bn, kStageBytes = conv_stage_bytes(BN);
@@ -357,10 +548,7 @@ struct ConvUmmaTf32 {
       if (!c.persistent) tmem_relinquish();
     }
     int2 *tab = reinterpret_cast<int2 *>(c.smem + kUmmaHeaderBytes);
-    const bool staged = p.st.slots > 0;
-    const uint32_t raw_full0 = full0 + kConvRawBarOffset, raw_empty0 = raw_full0 + 8 * kConvMaxRawSlots;
-    const uint32_t raw0 = smem_u32(c.smem) + conv_header_bytes(K);                     // the raw ring of a staged conv
-    const uint32_t tiles = raw0 + (uint32_t)conv_raw_bytes(p.st.slots, p.st.slot_pitch);  // the operand ring
+    const uint32_t tiles = smem_u32(c.smem) + conv_header_bytes(K);   // the operand ring
     // once the MMAs are done the ring holds the k-slices' partial sums (split > 1) and the store buffers
     const int chunks = BN / 32, max_owned = (chunks + split - 1) / split;
     const uint32_t staging = tiles + (uint32_t)umma_recv_bytes(BN, split, 4);
@@ -376,24 +564,18 @@ struct ConvUmmaTf32 {
     mark(MARK_START, c.tid == 0);
     if (warp == 4) {
       if (lane < stages) {
-        mbar_init(full0 + 8 * lane, staged ? 1 + 4 : 1 + 128);  // the weight copy's arrive.expect_tx + one arrive per gather thread / repack warp
+        mbar_init(full0 + 8 * lane, 1 + 128);  // the weight copy's arrive.expect_tx + one arrive per gather thread
         mbar_init(empty0 + 8 * lane, 1);
       }
       if (lane == 0) {
         mbar_init(acc_bar, 1);
         mbar_init(recv_bar, 1);
       }
-      if (lane == 0) st_shared_u4(full0 + kConvZeroOffset, 0u, 0u, 0u, 0u);
-      if (lane < p.st.slots) {
-        mbar_init(raw_full0 + 8 * lane, 1);      // the slot's TMA load (arrive.expect_tx)
-        mbar_init(raw_empty0 + 8 * lane, 4);     // every repack warp, once it has moved past the slot
-      }
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
       __syncwarp();
       if (lane == 0) {
         asm volatile("prefetch.tensormap [%0];" ::"l"(&p.map_w) : "memory");
         if ((ohw & 3) == 0) asm volatile("prefetch.tensormap [%0];" ::"l"(&p.map_out) : "memory");
-        if (staged) asm volatile("prefetch.tensormap [%0];" ::"l"(&p.map_x) : "memory");
       }
       if (lane == 0 && split > 1) {
         // bytes this CTA will receive: one partial per owned 32-pixel chunk from every k-slice (itself included)
@@ -409,26 +591,12 @@ struct ConvUmmaTf32 {
       // per entry made this set-up take 11 us for K = 4608.
       const int khw = p.kh * p.kw, step_ch = 128 / khw, step_r = 128 % khw;
       const int inv_kw = (65536 + p.kw - 1) / p.kw;
-      if (!staged) {
-        int ch = c.tid / khw, r = c.tid % khw;
-        for (int k = c.tid; k < total_kb * kBK; k += 128) {
-          const int dy = (r * inv_kw) >> 16, dx = r - dy * p.kw;
-          tab[k] = k < K ? make_int2((ch * p.h + dy) * p.wd + dx, r) : make_int2(0, 31);
-          ch += step_ch, r += step_r;
-          if (r >= khw) r -= khw, ++ch;
-        }
-      } else {
-        // staged: this k-slice's range only, entry j <-> k = kb0 * 32 + j, as the byte offset of
-        // (channel within its slot, dy, dx) inside a raw slot
-        int *tab4 = reinterpret_cast<int *>(tab);
-        const int plane = p.st.rows * p.st.pitch, k_lo = kb0 * kBK + c.tid;
-        int ch = k_lo / khw, r = k_lo - ch * khw;
-        for (int j = c.tid; j < num_kb * kBK; j += 128) {
-          const int dy = (r * inv_kw) >> 16, dx = r - dy * p.kw;
-          tab4[j] = (((ch & (p.st.cc - 1)) * plane) + dy * p.st.pitch + dx) * 4;
-          ch += step_ch, r += step_r;
-          if (r >= khw) r -= khw, ++ch;
-        }
+      int ch = c.tid / khw, r = c.tid % khw;
+      for (int k = c.tid; k < total_kb * kBK; k += 128) {
+        const int dy = (r * inv_kw) >> 16, dx = r - dy * p.kw;
+        tab[k] = k < K ? make_int2((ch * p.h + dy) * p.wd + dx, r) : make_int2(0, 31);
+        ch += step_ch, r += step_r;
+        if (r >= khw) r -= khw, ++ch;
       }
     }
     c.dependency_wait();   // nothing above touches global memory: barriers, tensor memory and the table overlap the previous kernel
@@ -442,9 +610,10 @@ struct ConvUmmaTf32 {
     // weight producer and MMA issuer: one elected thread each, ring slot / phase / descriptor word
     // carried incrementally (the issue loop is a dependent chain on one thread; see GemmUmma)
     bool acc_ok = true;
-    if (warp == 4) {
-      const bool leader = elect_one();
-      if (leader && !staged) {
+    if (warp == 6) {
+      // idle: the staged form's second loading warp
+    } else if (warp == 4) {
+      if (elect_one()) {
         uint32_t s = 0, ph = 1, dst = tiles, bar = full0;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(empty0 + 8 * s, ph, c.status, UMMA_WAIT_EMPTY_TIMEOUT)) break;
@@ -452,47 +621,6 @@ struct ConvUmmaTf32 {
           tma_load_3d(dst, &p.map_w, bar, (kb0 + kb) * kBK, co0, 0);
           if (++s == (uint32_t)stages) s = 0, ph ^= 1, dst = tiles, bar = full0;
           else dst += kStageBytes, bar += 8;
-        }
-      } else if (leader) {
-        // Staged: one thread feeds two rings -- the raw slots (input rows of `cc` channels, one tiled TMA
-        // load each) and the weight half of the operand stages -- by polling both "empty" barriers, so
-        // neither ring's back-pressure holds the other up.  Raw slots first: the repack needs them a
-        // stage earlier.
-        const int cc = p.st.cc, kslot = cc * p.kh * p.kw, x_start = p.st.x_start, nslots = p.st.slots;
-        const uint32_t slot_bytes = (uint32_t)p.st.slot_bytes, slot_pitch = (uint32_t)p.st.slot_pitch;
-        const int k_end = min(K, (kb0 + num_kb) * kBK);
-        int g = kb0 * kBK / kslot;
-        const int g_end = (k_end - 1) / kslot + 1;
-        const int y_start = (px0 / p.ow) * p.stride - p.pad;
-        uint32_t ws = 0, wph = 1, wdst = tiles, wbar = full0, rs = 0, rph = 1, idle = 0;
-        int kb = 0;
-        uint64_t t0 = 0;
-        while (kb < num_kb || g < g_end) {
-          bool progress = false;
-          if (g < g_end && mbar_test(raw_empty0 + 8 * rs, rph)) {
-            mbar_expect_tx(raw_full0 + 8 * rs, slot_bytes);
-            tma_load_4d(raw0 + rs * slot_pitch, &p.map_x, raw_full0 + 8 * rs, x_start, y_start, g * cc, img);
-            ++g, progress = true;
-            if (++rs == (uint32_t)nslots) rs = 0, rph ^= 1;
-          }
-          if (kb < num_kb && mbar_test(empty0 + 8 * ws, wph)) {
-            mbar_expect_tx(wbar, kUmmaABytes);
-            tma_load_3d(wdst, &p.map_w, wbar, (kb0 + kb) * kBK, co0, 0);
-            ++kb, progress = true;
-            if (++ws == (uint32_t)stages) ws = 0, wph ^= 1, wdst = tiles, wbar = full0;
-            else wdst += kStageBytes, wbar += 8;
-          }
-          if (progress) {
-            idle = 0, t0 = 0;
-          } else if ((++idle & 1023u) == 0) {   // bounded like every other wait: ~1 s without progress
-            if (status && *reinterpret_cast<volatile int *>(status) != 0) break;
-            const uint64_t now = global_ns();
-            if (t0 == 0) t0 = now;
-            if (now - t0 > 1000000000ull) {
-              if (status) atomicExch(status, (int)UMMA_WAIT_EMPTY_TIMEOUT);
-              break;
-            }
-          }
         }
       }
       __syncwarp();
@@ -525,17 +653,10 @@ struct ConvUmmaTf32 {
     } else {
       bool ok;
       const int gt = quad * 32 + lane;
-      if (staged) {
-        const uint32_t tab_s = smem_u32(tab), zeros = full0 + kConvZeroOffset;
-        if (BN == 128) ok = repack<128>(p, c, gt, px0, kb0, num_kb, stages, tiles, full0, empty0, raw0, raw_full0, raw_empty0, tab_s, zeros, tl);
-        else if (BN == 64) ok = repack<64>(p, c, gt, px0, kb0, num_kb, stages, tiles, full0, empty0, raw0, raw_full0, raw_empty0, tab_s, zeros, tl);
-        else ok = repack<32>(p, c, gt, px0, kb0, num_kb, stages, tiles, full0, empty0, raw0, raw_full0, raw_empty0, tab_s, zeros, tl);
-      } else {
-        const int2 *tab_slice = tab + kb0 * kBK;
-        if (BN == 128) ok = gather<128>(p, c, gt, px0, img, num_kb, stages, tiles, full0, empty0, tab_slice, tl);
-        else if (BN == 64) ok = gather<64>(p, c, gt, px0, img, num_kb, stages, tiles, full0, empty0, tab_slice, tl);
-        else ok = gather<32>(p, c, gt, px0, img, num_kb, stages, tiles, full0, empty0, tab_slice, tl);
-      }
+      const int2 *tab_slice = tab + kb0 * kBK;
+      if (BN == 128) ok = gather<128>(p, c, gt, px0, img, num_kb, stages, tiles, full0, empty0, tab_slice, tl);
+      else if (BN == 64) ok = gather<64>(p, c, gt, px0, img, num_kb, stages, tiles, full0, empty0, tab_slice, tl);
+      else ok = gather<32>(p, c, gt, px0, img, num_kb, stages, tiles, full0, empty0, tab_slice, tl);
       (void)ok;
       // epilogue: accumulator rows are output channels, columns are this tile's pixels
       acc_ok = mbar_wait(acc_bar, 0, c.status, UMMA_WAIT_ACC_TIMEOUT);
@@ -572,10 +693,6 @@ struct ConvUmmaTf32 {
         mbar_inval(acc_bar);
         mbar_inval(recv_bar);
       }
-    }
-    if (c.persistent && c.tid < p.st.slots) {
-      mbar_inval(raw_full0 + 8 * c.tid);
-      mbar_inval(raw_empty0 + 8 * c.tid);
     }
     mark(MARK_END, c.tid == 0);
   }

@@ -221,6 +221,7 @@ int default_launch(const bfuse_context *ctx, bfuse_kernel_desc *d, std::string *
       // pixels per tile: the widest of 128 / 64 / 32 that still gives the operator about half the
       // SMs (its pair partner takes the other half); a single small image gets 32-pixel tiles
       int bn = s[9];
+      if (bn <= 0 && s[11] == 1) bn = kConvBN;   // the staged form has one tile: the 128 lanes of tensor memory
       if (bn <= 0) {
         bn = 32;
         for (int cand = kConvBN; cand > 32; cand /= 2)
@@ -235,7 +236,7 @@ int default_launch(const bfuse_context *ctx, bfuse_kernel_desc *d, std::string *
       // share a launch (a fused launch has one cluster width): 4 when the k-slices still fit three
       // quarters of the SMs and keep at least 4 K blocks each (8-wide clusters measured slower in pairs)
       int split = s[10];
-      if (split <= 0) split = (tiles * 4 * share <= 3 * sm / 2 && num_kb >= 16) ? 4 : 1;
+      if (split <= 0) split = (s[11] != 1 && tiles * 4 * share <= 3 * sm / 2 && num_kb >= 16) ? 4 : 1;   // the staged form does not split K
       if (split > 8 || split > num_kb) { *err = "conv2d: k-slices must be 1..8 and at most the number of K blocks"; return BFUSE_ERR_SHAPE; }
       const int q = ceil_div(num_kb, split);
       split = ceil_div(num_kb, q);
@@ -251,8 +252,8 @@ int default_launch(const bfuse_context *ctx, bfuse_kernel_desc *d, std::string *
       // 3 x 3 branch alone 191 us gathered at three CTAs per SM, 216 us staged at two).
       ConvStaging st;
       st.slots = 0;
-      if (s[11] == 1 && !conv_staging(s[1], s[2], s[3], s[5], s[6], s[7], s[8], oh, ow, bn, &st)) {
-        *err = "conv2d: shape[11] = 1 (staged operand) needs image rows of 16-byte multiples and a window whose rows fit a 24 KB slot";
+      if (s[11] == 1 && (split != 1 || !conv_staging(s[1], s[2], s[3], s[5], s[6], s[7], s[8], oh, ow, bn, &st))) {
+        *err = "conv2d: shape[11] = 1 (staged operand) needs 128-pixel tiles, an unsplit K of whole K blocks, image rows of 16-byte multiples and a window whose rows fit a 24 KB slot";
         return BFUSE_ERR_SHAPE;
       }
       if (s[11] < 0 || s[11] > 2) { *err = "conv2d: shape[11] (operand mode) must be 0, 1 or 2"; return BFUSE_ERR_SHAPE; }
@@ -265,7 +266,7 @@ int default_launch(const bfuse_context *ctx, bfuse_kernel_desc *d, std::string *
       int stages = std::max(1, std::min({q, kUmmaMaxStages, (budget - conv_header_bytes(K) - raw) / conv_stage_bytes(bn)}));
       stages = std::max(stages, ceil_div(umma_epilogue_bytes(bn, split, 4), conv_stage_bytes(bn)));
       if (st.slots) stages = std::max(stages, 2);   // the repack of stage s + 1 runs while the MMAs read stage s
-      set(split * ceil_div(oh * ow, bn), ceil_div(s[4], kUmmaBM), s[0], kUmmaThreads, 1, conv_umma_smem_bytes(stages, bn, K, raw), 3);
+      set(split * ceil_div(oh * ow, bn), ceil_div(s[4], kUmmaBM), s[0], kConvThreads, 1, conv_umma_smem_bytes(stages, bn, K, raw), 3);
       return BFUSE_OK;
     }
     case BFUSE_OP_GEMM_TF32:
@@ -460,7 +461,7 @@ int build_params(bfuse_context *ctx, KernelRec &k) {
       const int K = s[1] * s[5] * s[6];
       if (K > kConvMaxK || K % 4) return shape_err("ci*kh*kw must be a multiple of 4 and at most 8192 (offset table, TMA stride rule)");
       if (s[5] * s[6] > 31) return shape_err("kernel window larger than 31 taps");
-      if (kd.bx != kUmmaThreads || kd.by != 1 || kd.bz != 1) return shape_err("BlockDim must be (192, 1, 1)");
+      if (kd.bx != kConvThreads || kd.by != 1 || kd.bz != 1) return shape_err("BlockDim must be (224, 1, 1)");
       const int bn = s[9] > 0 ? s[9] : kConvBN;
       if (bn != 32 && bn != 64 && bn != 128) return shape_err("shape[9] (pixels per tile) must be 32, 64 or 128");
       const int split = s[10] > 0 ? s[10] : 1, num_kb = ceil_div(K, ConvUmmaTf32::kBK), q = ceil_div(num_kb, split);
@@ -476,8 +477,8 @@ int build_params(bfuse_context *ctx, KernelRec &k) {
       // whole-SM operand ring as well.
       const int min_stages = ceil_div(umma_epilogue_bytes(bn, split, 4), conv_stage_bytes(bn));
       if (s[11] < 0 || s[11] > 2) return shape_err("shape[11] (operand mode) must be 0 (the runtime's choice), 1 (staged) or 2 (gathered)");
-      if (s[11] == 1 && !conv_staging(s[1], s[2], s[3], s[5], s[6], s[7], s[8], oh, ow, bn, &p.st))
-        return shape_err("shape[11] = 1 (staged operand) needs image rows of 16-byte multiples and a window whose rows fit a 24 KB slot");
+      if (s[11] == 1 && (split != 1 || !conv_staging(s[1], s[2], s[3], s[5], s[6], s[7], s[8], oh, ow, bn, &p.st)))
+        return shape_err("shape[11] = 1 (staged operand) needs 128-pixel tiles, an unsplit K of whole K blocks, image rows of 16-byte multiples and a window whose rows fit a 24 KB slot");
       if (s[11] == 1) {
         if (k.smem >= (size_t)conv_umma_smem_bytes(std::max(min_stages, 4), bn, K, conv_raw_bytes(kConvMaxRawSlots, p.st.slot_pitch)) &&
             k.smem > 150 * 1024)
@@ -1411,8 +1412,9 @@ int bfuse_debug_gemm_timeline(bfuse_context *ctx, int kernel, long long *marks, 
     return fail(ctx, BFUSE_ERR_UNSUPPORTED, "only the tcgen05 GEMM / conv bodies record a timeline");
   cudaSetDevice(ctx->device);
   long long *d = nullptr;
-  CK(cudaMalloc(&d, sizeof(long long) * MARK_COUNT));
-  cudaMemset(d, 0, sizeof(long long) * MARK_COUNT);
+  const int held = std::max(n, (int)MARK_COUNT);
+  CK(cudaMalloc(&d, sizeof(long long) * held));
+  cudaMemset(d, 0, sizeof(long long) * held);
   long long **slot = is_conv ? &reinterpret_cast<ConvUmmaParams *>(k->params)->timeline
                              : &reinterpret_cast<GemmUmmaParams *>(k->params)->timeline;
   int rc = launch_one(ctx, *k, ctx->own);  // warm run
@@ -1420,7 +1422,7 @@ int bfuse_debug_gemm_timeline(bfuse_context *ctx, int kernel, long long *marks, 
   if (!rc) rc = launch_one(ctx, *k, ctx->own);
   *slot = nullptr;
   cudaError_t e = cudaStreamSynchronize(ctx->own);
-  if (!rc && e == cudaSuccess) e = cudaMemcpy(marks, d, sizeof(long long) * MARK_COUNT, cudaMemcpyDeviceToHost);
+  if (!rc && e == cudaSuccess) e = cudaMemcpy(marks, d, sizeof(long long) * held, cudaMemcpyDeviceToHost);
   cudaFree(d);
   if (rc) return rc;
   if (e != cudaSuccess) return fail_cuda(ctx, e, "timeline");

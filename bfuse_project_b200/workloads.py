@@ -158,7 +158,7 @@ def make_pair(name, seed=0, scale=1.0, tensor_cores=True, conv_batch=1, split=0,
     if name == "cfg5_conv_branches":
         x = rng.standard_normal((conv_batch, 64, 56, 56), dtype=np.float32)
         op = OP_CONV2D_TF32 if tensor_cores else OP_CONV2D_F32_SIMT
-        return PairSpec(name, conv2d("conv3x3_s2", rng, op, conv_batch, 64, 56, 56, 128, 3, 2, 1, x=x, mode=conv_mode),
+        return PairSpec(name, conv2d("conv3x3_s2", rng, op, conv_batch, 64, 56, 56, 128, 3, 2, 1, x=x, mode=conv_mode, bn=128 if conv_mode == 1 else 0),
                         conv2d("conv1x1_s2", rng, op, conv_batch, 64, 56, 56, 128, 1, 2, 0, x=x),
                         "tf32" if tensor_cores else "f32", "hbm", "ResNet-18 3x3 s2 conv || 1x1 s2 downsample (same input)")
     raise KeyError(name)

@@ -155,27 +155,31 @@ def test_conv_tensor_core_pairs(rt):
 
 
 def test_conv_staged_operand_mode(rt):
-    """shape[11] = 1: the im2col operand built from input rows staged in shared memory by TMA (zero padding =
-    the load's out-of-bounds fill, one-row windows with a stride load only the rows they use) and repacked there.
-    Padded strided 3x3, a 1x1 with stride, a 5x5 with stride 3, odd channel counts (a last slot partly past ci),
-    every pixel-tile width, a K split over a cluster, and the ResNet branch pair; each against the oracle and
-    fused == unfused under every pattern.  Rows that are no 16-byte multiples cannot be staged: rejected."""
+    """shape[11] = 1: input rows staged in shared memory by TMA (zero padding = the load's out-of-bounds fill,
+    one-row windows with a stride load only the rows they use), the im2col rows written from there into TENSOR
+    memory as the MMA's A operand, pixels in the accumulator's lanes.  Padded strided 3x3 whose K blocks straddle
+    the raw slots, a 1x1 with stride, a 5x5 with stride 3 on an image smaller than a tile, a ragged second
+    channel tile, a long K, and the ResNet branch pair; each against the oracle and fused == unfused under every
+    pattern.  What the form cannot do is rejected: rows that are no 16-byte multiples, tiles other than 128
+    pixels, a split K, a K that is no whole number of K blocks."""
     rng = np.random.default_rng(61)
     run_and_check(rt, wl.make_pair("cfg5_conv_branches", seed=13, conv_batch=3, conv_mode=1), BLOCK_PATTERNS)
-    for bn in (32, 64, 128):
-        a = wl.conv2d("s3x3", rng, bf.OP_CONV2D_TF32, 2, 20, 20, 24, 136, 3, 2, 1, bn=bn, mode=1)     # K = 180 (20 channels: a slot of 16 ends past ci)
-        b = wl.conv2d("s1x1", rng, bf.OP_CONV2D_TF32, 1, 36, 31, 16, 40, 1, 2, 0, bn=bn, mode=1)      # one-row window: rows loaded with element stride 2
-        pair = run_and_check(rt, wl.PairSpec("staged_bn%d" % bn, a, b, "tf32", "hbm"), [(bf.ZIGZAG, 1, 1), (bf.WORK_QUEUE, 1, 1), (bf.THREAD_SPLIT, 0, 0)])
-        assert pair.spec.a.shape[11] == 1
-    c = wl.conv2d("s5x5", rng, bf.OP_CONV2D_TF32, 1, 8, 20, 20, 130, 5, 3, 2, mode=1)                  # 5x5 stride 3 pad 2, K = 200
-    d = wl.conv2d("s3x3s1", rng, bf.OP_CONV2D_TF32, 2, 128, 28, 28, 128, 3, 1, 1, mode=1)              # K = 1152, stride 1
+    a = wl.conv2d("s3x3", rng, bf.OP_CONV2D_TF32, 2, 32, 20, 24, 136, 3, 2, 1, bn=128, mode=1)     # K = 288 in slots of 36: K blocks straddle slots
+    b = wl.conv2d("s1x1", rng, bf.OP_CONV2D_TF32, 1, 96, 31, 16, 40, 1, 2, 0, bn=128, mode=1)      # one-row window: rows loaded with element stride 2
+    pair = run_and_check(rt, wl.PairSpec("staged_a", a, b, "tf32", "hbm"), [(bf.ZIGZAG, 1, 1), (bf.WORK_QUEUE, 1, 1), (bf.THREAD_SPLIT, 0, 0)])
+    assert pair.spec.a.shape[11] == 1 and pair.spec.b.shape[11] == 1
+    c = wl.conv2d("s5x5", rng, bf.OP_CONV2D_TF32, 1, 32, 20, 20, 130, 5, 3, 2, bn=128, mode=1)     # 5x5 stride 3 pad 2, K = 800, 49 pixels
+    d = wl.conv2d("s3x3s1", rng, bf.OP_CONV2D_TF32, 2, 128, 28, 28, 128, 3, 1, 1, bn=128, mode=1)  # K = 1152, stride 1
     run_and_check(rt, wl.PairSpec("staged_5x5", c, d, "tf32", "hbm"), [(bf.ZIGZAG, 1, 1), (bf.RANGE_SPLIT, 0, 0)])
-    e = wl.conv2d("ssplit", rng, bf.OP_CONV2D_TF32, 1, 260, 16, 16, 256, 3, 1, 1, bn=64, split=4, mode=1)   # K = 2340 in 4 k-slices
-    f = wl.conv2d("ssplit1", rng, bf.OP_CONV2D_TF32, 2, 768, 16, 16, 160, 1, 1, 0, bn=64, split=4, mode=1)  # 1x1, K = 768 in 4 k-slices
-    run_and_check(rt, wl.PairSpec("staged_split", e, f, "tf32", "hbm"), [(bf.ZIGZAG, 1, 1), (bf.RANGE_SPLIT, 0, 0)])
-    with pytest.raises(bf.BfuseError) as err:       # 17 floats per row
-        wl.DevicePair(rt, wl.PairSpec("odd", wl.conv2d("o", rng, bf.OP_CONV2D_TF32, 1, 96, 17, 17, 96, 3, 2, 0, mode=1), f, "tf32", "hbm"))
-    assert err.value.code == 2
+    g = wl.gemm("g", rng, bf.OP_GEMM_TF32, 1, 100, 64, 64, w_std=1.0, bn=64, split=1)
+    run_and_check(rt, wl.PairSpec("staged_gemm", a, g, "tf32", "hbm"), BLOCK_PATTERNS)
+    for bad in (wl.conv2d("o", rng, bf.OP_CONV2D_TF32, 1, 96, 17, 17, 96, 3, 2, 0, bn=128, mode=1),        # 17 floats per row
+                wl.conv2d("o", rng, bf.OP_CONV2D_TF32, 1, 32, 20, 24, 136, 3, 2, 1, bn=64, mode=1),        # 64-pixel tiles
+                wl.conv2d("o", rng, bf.OP_CONV2D_TF32, 1, 256, 16, 16, 256, 3, 1, 1, bn=128, split=4, mode=1),   # K split over a cluster
+                wl.conv2d("o", rng, bf.OP_CONV2D_TF32, 1, 20, 20, 24, 136, 3, 2, 1, bn=128, mode=1)):      # K = 180
+        with pytest.raises(bf.BfuseError) as err:
+            wl.DevicePair(rt, wl.PairSpec("bad", bad, g, "tf32", "hbm"))
+        assert err.value.code == 2
 
 
 def test_conv_tensor_core_ragged_shapes(rt):
