@@ -47,8 +47,8 @@ __host__ __device__ constexpr int conv_umma_smem_bytes(int stages, int bn, int K
   return conv_header_bytes(K) + raw_bytes + stages * conv_stage_bytes(bn);
 }
 
-constexpr int kConvMaxRawSlots = 4;
-constexpr int kConvRawBarOffset = 256;   // byte offset of the raw ring's barriers in the header: full[4], then empty[4]
+constexpr int kConvMaxRawSlots = 6;
+constexpr int kConvRawBarOffset = 256;   // byte offset of the raw ring's barriers in the header: full[6], then empty[6]
 constexpr int kConvAStages = 4;          // staged convs: K blocks of the im2col operand held in tensor memory (32 columns each);
                                          // their barriers follow the raw ring's in the header: full[4], then empty[4]
 constexpr int kConvTmemCols = 256;       // staged convs: 128 accumulator columns + 4 x 32 operand columns
@@ -110,7 +110,7 @@ struct ConvUmmaParams {
   const float *x;
   int n, ci, h, wd, co, kh, kw, stride, pad, oh, ow;
   int K;
-  int stages;
+  int stages;           // ring depth: operand stages (gathered) or 16 KB weight stages (staged)
   int bn;               // output pixels per tile: 32, 64 or 128
   int split;            // CTAs (k-slices) per tile = cluster width; 1: no split
   int kb_per_slice;     // K blocks per k-slice
@@ -120,6 +120,29 @@ struct ConvUmmaParams {
 
 // bytes of the raw ring, rounded so that the operand ring behind it stays 1 KB aligned (128B swizzle)
 __host__ __device__ constexpr int conv_raw_bytes(int slots, int slot_pitch) { return (slots * slot_pitch + 1023) / 1024 * 1024; }
+
+// How a staged conv divides a shared-memory window of `smem` bytes: header, raw slots, 16 KB weight stages.
+// Weights come out of L2 and three stages ahead cover that; the input comes out of DRAM, whose latency under
+// load is several K blocks long, so what is left goes to raw slots first (up to 6, never more than the tile
+// loads), then to more weight stages.  A K block touches up to three slots, so fewer than three only when
+// the tile has fewer.  Returns false when the window is too small.
+__host__ __device__ inline bool conv_staged_ring(int smem, int K, int kslot, int slot_pitch, int *slots, int *wstages) {
+  const int num_kb = K / 32, loads = (K - 1) / kslot + 1;
+  const int room = smem - conv_header_bytes(K);
+  const int w_min = num_kb < 3 ? num_kb : 3, s_min = loads < 3 ? loads : 3;
+  int s = (room - w_min * kUmmaABytes) / slot_pitch;
+  if (s > kConvMaxRawSlots) s = kConvMaxRawSlots;
+  if (s > loads) s = loads;
+  if (s < s_min) s = s_min;
+  int w = (room - conv_raw_bytes(s, slot_pitch)) / kUmmaABytes;
+  if (w > kUmmaMaxStages) w = kUmmaMaxStages;
+  if (w > num_kb) w = num_kb;
+  *slots = s, *wstages = w;
+  return w >= (num_kb < 2 ? num_kb : 2);
+}
+__host__ __device__ inline int conv_staged_smem_bytes(int K, int slots, int slot_pitch, int wstages) {
+  return conv_header_bytes(K) + conv_raw_bytes(slots, slot_pitch) + wstages * kUmmaABytes;
+}
 
 // 4-byte asynchronous copy global -> shared; src_bytes = 0 writes zeros instead
 __device__ __forceinline__ void cp_async_4(uint32_t dst, const float *src, uint32_t src_bytes) {
@@ -256,7 +279,7 @@ struct ConvUmmaTf32 {
     const int quad = (threadIdx.x >> 5) & 3;
     const int px0 = c.block_x() * kConvBN, co0 = c.block_y() * kUmmaBM, img = c.block_z();
     const int ohw = p.oh * p.ow, K = p.K, num_kb = K / kBK;   // staged: K is a whole number of K blocks
-    const int wstages = min(2 * p.stages, kUmmaMaxStages);    // the operand ring's stages hold two 16 KB weight stages each
+    const int wstages = p.stages;                             // 16 KB weight stages behind the raw ring
     int *const status = c.status;
     const uint32_t idesc = umma_idesc(0, kUmmaBM);            // M = 128 pixels, N = 128 output channels
 

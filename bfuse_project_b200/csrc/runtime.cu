@@ -245,28 +245,35 @@ int default_launch(const bfuse_context *ctx, bfuse_kernel_desc *d, std::string *
       // an SM of its own (a long-K conv on few CTAs is bound by the ring's round trip, not by issue
       // rate); deep enough to hold the k-slices' partial sums after the MMAs
       const long long ctas = tiles * split;
-      // How the im2col operand is built, shape[11]: 1 = staged (input rows by TMA into a raw ring, repacked in
-      // shared memory), 2 = gathered from global memory, 0 = the runtime's choice -- gathered: it needs no raw
-      // ring, so a third CTA fits an SM, and with the whole grid streaming weights and input out of L2 that
-      // occupancy was worth more than the cheaper operand path at every batch size measured (batch 256:
-      // 3 x 3 branch alone 191 us gathered at three CTAs per SM, 216 us staged at two).
+      // How the im2col operand is built, shape[11]: 1 = staged (input rows by TMA into a raw ring, the im2col rows
+      // written from there into tensor memory), 2 = gathered from global memory with 4-byte copies, 0 = the
+      // runtime's choice: staged wherever its one tiling (128-pixel tiles, unsplit K) is what the runtime would
+      // pick anyway and the geometry allows it -- 3 x 3 stride-2 branch of ResNet-18 at batch 256: 113 us staged,
+      // 193 us gathered; at batch 32: 17 us and 31 us.
       ConvStaging st;
       st.slots = 0;
       if (s[11] == 1 && (split != 1 || !conv_staging(s[1], s[2], s[3], s[5], s[6], s[7], s[8], oh, ow, bn, &st))) {
         *err = "conv2d: shape[11] = 1 (staged operand) needs 128-pixel tiles, an unsplit K of whole K blocks, image rows of 16-byte multiples and a window whose rows fit a 24 KB slot";
         return BFUSE_ERR_SHAPE;
       }
+      if (s[11] == 0 && split == 1 && !conv_staging(s[1], s[2], s[3], s[5], s[6], s[7], s[8], oh, ow, bn, &st)) st.slots = 0;
       if (s[11] < 0 || s[11] > 2) { *err = "conv2d: shape[11] (operand mode) must be 0, 1 or 2"; return BFUSE_ERR_SHAPE; }
       d->shape[11] = st.slots ? 1 : 2;
       // ring budget: the whole SM when the operator and an equal partner leave every CTA an SM of its own, else
-      // two CTAs per SM (staged) or three (gathered)
+      // two CTAs per SM (staged: tensor memory holds two) or three (gathered)
       const int budget = (share * ctas <= sm ? 200 : (st.slots ? 110 : 74)) * 1024;
-      if (st.slots && budget > 150 * 1024) st.slots = kConvMaxRawSlots;   // a CTA with an SM to itself: deeper raw ring
-      const int raw = conv_raw_bytes(st.slots, st.slot_pitch);
-      int stages = std::max(1, std::min({q, kUmmaMaxStages, (budget - conv_header_bytes(K) - raw) / conv_stage_bytes(bn)}));
+      if (st.slots) {
+        int wst;
+        if (!conv_staged_ring(budget, K, st.cc * s[5] * s[6], st.slot_pitch, &st.slots, &wst)) {
+          *err = "conv2d: shape[11] = 1 (staged operand): the raw ring and two weight stages do not fit the shared-memory budget";
+          return BFUSE_ERR_SHAPE;
+        }
+        set(ceil_div(oh * ow, bn), ceil_div(s[4], kUmmaBM), s[0], kConvThreads, 1, conv_staged_smem_bytes(K, st.slots, st.slot_pitch, wst), 3);
+        return BFUSE_OK;
+      }
+      int stages = std::max(1, std::min({q, kUmmaMaxStages, (budget - conv_header_bytes(K)) / conv_stage_bytes(bn)}));
       stages = std::max(stages, ceil_div(umma_epilogue_bytes(bn, split, 4), conv_stage_bytes(bn)));
-      if (st.slots) stages = std::max(stages, 2);   // the repack of stage s + 1 runs while the MMAs read stage s
-      set(split * ceil_div(oh * ow, bn), ceil_div(s[4], kUmmaBM), s[0], kConvThreads, 1, conv_umma_smem_bytes(stages, bn, K, raw), 3);
+      set(split * ceil_div(oh * ow, bn), ceil_div(s[4], kUmmaBM), s[0], kConvThreads, 1, conv_umma_smem_bytes(stages, bn, K, 0), 3);
       return BFUSE_OK;
     }
     case BFUSE_OP_GEMM_TF32:
@@ -479,16 +486,13 @@ int build_params(bfuse_context *ctx, KernelRec &k) {
       if (s[11] < 0 || s[11] > 2) return shape_err("shape[11] (operand mode) must be 0 (the runtime's choice), 1 (staged) or 2 (gathered)");
       if (s[11] == 1 && (split != 1 || !conv_staging(s[1], s[2], s[3], s[5], s[6], s[7], s[8], oh, ow, bn, &p.st)))
         return shape_err("shape[11] = 1 (staged operand) needs 128-pixel tiles, an unsplit K of whole K blocks, image rows of 16-byte multiples and a window whose rows fit a 24 KB slot");
+      int wstages = 0;
       if (s[11] == 1) {
-        if (k.smem >= (size_t)conv_umma_smem_bytes(std::max(min_stages, 4), bn, K, conv_raw_bytes(kConvMaxRawSlots, p.st.slot_pitch)) &&
-            k.smem > 150 * 1024)
-          p.st.slots = kConvMaxRawSlots;
-        if (k.smem < (size_t)conv_umma_smem_bytes(std::max(min_stages, 2), bn, K, conv_raw_bytes(p.st.slots, p.st.slot_pitch)))
-          return shape_err("shape[11] = 1 (staged operand): shared memory below the raw ring plus two operand stages");
-      }
-      const int raw = conv_raw_bytes(p.st.slots, p.st.slot_pitch);
-      if (k.smem < (size_t)conv_umma_smem_bytes(min_stages, bn, K, raw))
+        if (!conv_staged_ring((int)std::min<size_t>(k.smem, kMaxSmemPerCta), K, p.st.cc * s[5] * s[6], p.st.slot_pitch, &p.st.slots, &wstages))
+          return shape_err("shape[11] = 1 (staged operand): shared memory below the raw ring plus two weight stages");
+      } else if (k.smem < (size_t)conv_umma_smem_bytes(min_stages, bn, K, 0)) {
         return shape_err("shared memory below the store buffers (and, for a split conv, the receive area of the k-slices)");
+      }
       int rc = encode_map(ctx, &p.map_w, 4, a[1], K, s[4], 1, kUmmaBM);
       if (rc) return rc;
       if (p.st.slots) {
@@ -509,7 +513,7 @@ int build_params(bfuse_context *ctx, KernelRec &k) {
       p.x = (const float *)a[0];
       p.n = s[0], p.ci = s[1], p.h = s[2], p.wd = s[3], p.co = s[4], p.kh = s[5], p.kw = s[6], p.stride = s[7], p.pad = s[8];
       p.oh = oh, p.ow = ow, p.K = K;
-      p.stages = std::min<int>(kUmmaMaxStages, (int)((k.smem - conv_header_bytes(K) - raw) / conv_stage_bytes(bn)));
+      p.stages = wstages ? wstages : std::min<int>(kUmmaMaxStages, (int)((k.smem - conv_header_bytes(K)) / conv_stage_bytes(bn)));
       p.bn = bn;
       p.split = split;
       p.kb_per_slice = q;
@@ -661,8 +665,14 @@ bool ring_info(const KernelRec &k, int *header, int *stage_bytes, int *min_stage
   if (k.desc.op == BFUSE_OP_CONV2D_TF32) {
     const int bn = s[9] > 0 ? s[9] : kConvBN;
     const ConvUmmaParams *cp = reinterpret_cast<const ConvUmmaParams *>(k.params);
-    *header = conv_header_bytes(s[1] * s[5] * s[6]) + conv_raw_bytes(cp->st.slots, cp->st.slot_pitch), *stage_bytes = conv_stage_bytes(bn);
-    *min_stages = std::max(cp->st.slots ? 2 : 1, ceil_div(umma_epilogue_bytes(bn, std::max(1, s[10]), 4), conv_stage_bytes(bn)));
+    const int K = s[1] * s[5] * s[6];
+    if (cp->st.slots) {   // staged: the raw ring stays as registered, the 16 KB weight stages are what can be given up
+      *header = conv_header_bytes(K) + conv_raw_bytes(cp->st.slots, cp->st.slot_pitch), *stage_bytes = kUmmaABytes;
+      *min_stages = std::min(2, K / ConvUmmaTf32::kBK);
+    } else {
+      *header = conv_header_bytes(K), *stage_bytes = conv_stage_bytes(bn);
+      *min_stages = std::max(1, ceil_div(umma_epilogue_bytes(bn, std::max(1, s[10]), 4), conv_stage_bytes(bn)));
+    }
     *stages = cp->stages;
     return true;
   }
@@ -950,6 +960,7 @@ int bfuse_register_fusion(bfuse_context *ctx, int kernel1, int kernel2, int patt
     // would block for ever, so the sum has to fit the SM's 512 columns
     auto tmem_cols = [](const KernelRec &k) {
       if (k.desc.op == BFUSE_OP_GEMM_TF32 || k.desc.op == BFUSE_OP_GEMM_BF16) return k.desc.shape[4] * std::max(1, k.desc.shape[6] / kUmmaBM);
+      if (k.desc.op == BFUSE_OP_CONV2D_TF32 && k.desc.shape[11] == 1) return kConvTmemCols;   // staged: accumulator and operand stages
       return k.desc.op == BFUSE_OP_CONV2D_TF32 ? (k.desc.shape[9] > 0 ? k.desc.shape[9] : kConvBN) : 0;
     };
     if (tmem_cols(*a) + tmem_cols(*b) > 512)
