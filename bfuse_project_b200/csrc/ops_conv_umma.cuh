@@ -4,29 +4,28 @@
 //   y[n, co, pixel] = sum_k  w[co, k] * im2col(x)[n, pixel, k],   k = (ci, kh, kw) as in w[co][ci][kh][kw]
 //
 // A tile is 128 output channels x BN output pixels of one image (BN = 128, or 64 / 32 for small
-// images, so that a single image still spreads over many SMs).  The weight operand is K-major in
-// global memory and arrives by TMA (128B swizzle).  The im2col operand does not exist in memory; the
-// four epilogue warps, idle during the main loop, build it in the swizzled K-major layout the MMA
-// expects (128 / BN threads per output pixel, 32 values of k per pixel and stage), in one of two ways:
+// images, so that a single image still spreads over many SMs).  The weights are K-major in global
+// memory and arrive by TMA (128B swizzle).  The im2col matrix does not exist in memory; the four
+// epilogue warps, idle during the main loop, build it, 32 values of k per pixel and K block, in one of
+// two ways:
 //
-//   staged (image rows of 16-byte multiples): the input rows a tile needs -- every row its output
-//     pixels' windows touch, full width, a few channels at a time -- arrive by tiled TMA loads over
-//     the NCHW tensor into a ring of raw slots (padding is the TMA's out-of-bounds zero fill; a
-//     one-row window with a stride loads only the rows it uses through the map's element stride),
-//     and the warps repack shared memory -> shared memory: per 16-byte chunk of a pixel's row one
-//     16-byte table read (four byte offsets), four 4-byte reads of the raw slot and one 16-byte
-//     store.  A direct TMA load of the taps is not possible: a tap's first column is  dx - pad, and a
-//     tiled TMA copy must start at a multiple of 16 bytes;
-//   gathered (any other row length): 4-byte cp.async copies from global memory straight into the
-//     operand (out-of-image taps zero-filled by the copy), bound by the issue rate of those copies --
-//     about four times slower per K block than the staged form.
-//
-// Either way the stage's "full" barrier fires when the weights have landed and every repack thread has
-// arrived, so the operand is built several stages ahead of the tensor core.  Per-k offsets are
-// tabulated once per CTA in shared memory, so neither loop divides.
-//
-// A long K (deep layers on small images leave few tiles) can be split over the CTAs of a cluster,
-// reduced through distributed shared memory like the GEMM's k-slices.
+//   staged (run_staged: 128-pixel tiles, K a whole number of K blocks and unsplit, image rows of
+//     16-byte multiples): the input rows a tile needs -- every row its output pixels' windows touch,
+//     full width, a few channels at a time -- arrive by tiled TMA loads over the NCHW tensor into a ring
+//     of raw slots (padding is the TMA's out-of-bounds zero fill; a one-row window with a stride loads
+//     only the rows it uses through the map's element stride).  The operands' roles are swapped: thread
+//     r owns pixel r, reads its window out of the raw slots (per four values of k one 16-byte table read
+//     -- their byte offsets inside a slot -- and four 4-byte reads) and writes the 32 values with one
+//     tcgen05.st into TENSOR memory, where they are the MMA's A operand; the weights are the B operand;
+//     the accumulator holds pixels in its lanes, so the epilogue's stores are coalesced as they are.  A
+//     direct TMA load of the taps is not possible: a tap's first column is  dx - pad, and a tiled TMA copy
+//     must start at a multiple of 16 bytes, nor has it a traversal stride in the innermost dimension;
+//   gathered (run: everything else): 4-byte cp.async copies from global memory straight into a
+//     swizzled K-major operand stage in shared memory (out-of-image taps zero-filled by the copy),
+//     weights as the A operand, bound by the issue rate of those copies.  Per-k offsets are tabulated
+//     once per CTA in shared memory, so the loop does not divide.  A long K (deep layers on small images
+//     leave few tiles) can be split over the CTAs of a cluster, reduced through distributed shared
+//     memory like the GEMM's k-slices.
 //
 // BlockDim = (224, 1, 1); GridDim = (split * ceil(oh*ow / BN), ceil(co / 128), n).
 #pragma once
