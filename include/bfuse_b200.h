@@ -50,8 +50,10 @@ enum {
   BFUSE_OP_CONV2D_TF32 = 8,   /* as CONV2D_F32_SIMT on tcgen05 kind::tf32 (implicit GEMM); shape[9] = output */
                               /* pixels per tile (32, 64, 128), shape[10] = k-slices per tile (a cluster    */
                               /* reduces them), shape[11] = how the im2col operand is built: 1 staged (input */
-                              /* rows by TMA into shared memory, repacked there; needs rows of 16-byte       */
-                              /* multiples), 2 gathered from global memory; 0 = chosen by the runtime        */
+                              /* rows by TMA into shared memory, im2col rows written from there into tensor  */
+                              /* memory; needs 128-pixel tiles, one k-slice, ci*kh*kw a multiple of 32 and   */
+                              /* image rows of 16-byte multiples), 2 gathered from global memory; 0 = chosen */
+                              /* by the runtime (staged wherever it can be)                                  */
   BFUSE_OP_COUNT = 9
 };
 
@@ -200,7 +202,7 @@ int bfuse_debug_gemm_timeline(bfuse_context *ctx, int kernel, long long *marks, 
 int bfuse_debug_fused_timeline(bfuse_context *ctx, const int *fusions, int n, long long *times, const int *slots);
 /* Diagnostic, no reference counterpart, no GPU needed: how the tensor-core conv body would stage the input
  * of a conv of shape {n, ci, h, w, co, kh, kw, stride, pad} with bn output pixels per tile.  out (12 ints):
- * ring slots (0: the conv is gathered from global memory instead), channels per slot, staged rows,
+ * ring slots before the window is sized (0: the conv cannot be staged and is gathered from global memory), channels per slot, staged rows,
  * floats per staged row, element strides x / y of the load, staged columns / rows between neighbouring
  * output pixels / rows, tensor column of staged column 0, staged column of tap 0 of output column 0,
  * bytes per slot, slot pitch in bytes. */
