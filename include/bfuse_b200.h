@@ -52,8 +52,9 @@ enum {
                               /* reduces them), shape[11] = how the im2col operand is built: 1 staged (input */
                               /* rows by TMA into shared memory, im2col rows written from there into tensor  */
                               /* memory; needs 128-pixel tiles, one k-slice, ci*kh*kw a multiple of 32 and   */
-                              /* image rows of 16-byte multiples), 2 gathered from global memory; 0 = chosen */
-                              /* by the runtime (staged wherever it can be)                                  */
+                              /* image rows of 16-byte multiples), 2 gathered from global memory; 0: chosen  */
+                              /* by bfuse_default_launch (staged wherever it can be), which writes 1 or 2    */
+                              /* back; a kernel registered with 0 is gathered                                */
   BFUSE_OP_COUNT = 9
 };
 
