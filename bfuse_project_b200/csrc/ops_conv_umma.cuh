@@ -129,7 +129,7 @@ __host__ __device__ constexpr int conv_raw_bytes(int slots, int slot_pitch) { re
 __host__ __device__ inline bool conv_staged_ring(int smem, int K, int kslot, int slot_pitch, int *slots, int *wstages) {
   const int num_kb = K / 32, loads = (K - 1) / kslot + 1;
   const int room = smem - conv_header_bytes(K);
-  const int w_min = num_kb < 3 ? num_kb : 3, s_min = loads < 3 ? loads : 3;
+  const int w_min = num_kb < 2 ? num_kb : 2, s_min = loads < 3 ? loads : 3;
   int s = (room - w_min * kUmmaABytes) / slot_pitch;
   if (s > kConvMaxRawSlots) s = kConvMaxRawSlots;
   if (s > loads) s = loads;
