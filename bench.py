@@ -677,7 +677,7 @@ def main():
         return pieces, fl, h1, h2
 
     # sub-shard size: the caller's choice; fewer pieces leave more of the first copy in and the last copy out
-    # exposed, more pieces pay more per-call overhead -- the best of three sizes on a short trial
+    # exposed, more pieces pay more per-copy overhead -- the best of three sizes on a short trial (best of 4 calls each)
     e2e_steps = max(3, min(args.steps, 10))
     plans = {}
     for sub in sorted({max(1, count // d) for d in (4, 8, 16)}):
@@ -686,10 +686,12 @@ def main():
         hy3.zero_(), hy1.zero_()
         rt.run_fuse_batch(plan[1], plan[2], plan[3])
         assert torch.equal(hy3, fused_out[0].cpu()) and torch.equal(hy1, fused_out[1].cpu()), "e2e outputs differ from the device-resident run"
-        t0 = time.perf_counter()
-        for _ in range(2):
+        best_of = float("inf")
+        for _ in range(4):
+            t0 = time.perf_counter()
             rt.run_fuse_batch(plan[1], plan[2], plan[3])
-        plans[sub] = (max_over_ranks(time.perf_counter() - t0), plan)
+            best_of = min(best_of, time.perf_counter() - t0)
+        plans[sub] = (max_over_ranks(best_of), plan)
     sub = min(plans, key=lambda k: plans[k][0])
     pieces, e2e_fus, h1, h2 = plans[sub][1]
     if world > 1:
@@ -698,7 +700,7 @@ def main():
     for _ in range(e2e_steps):
         rt.run_fuse_batch(e2e_fus, h1, h2)
     e2e_us = max_over_ranks((time.perf_counter() - t0) * 1e6 / e2e_steps)
-    h2d = hx.numel() * 4 + (hw3.numel() + hw1.numel()) * 4 * len(pieces)
+    h2d = hx.numel() * 4 + (hw3.numel() + hw1.numel()) * 4   # the weights every sub-shard shares go in once per call
     d2h = (hy3.numel() + hy1.numel()) * 4
     link = copy_bandwidth(torch, hx, b0.x[first:first + count], (b0.y3[first:first + count], b0.y1[first:first + count]), (hy3, hy1))
     link["copies_alone_us"] = max_over_ranks(link["copies_alone_us"])

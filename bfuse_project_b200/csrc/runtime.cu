@@ -1483,8 +1483,13 @@ int bfuse_set_dependent_launch(bfuse_context *ctx, int enabled) {
 // `other` / `other_host`: the pair's first kernel, already copied in by this call -- an input of this kernel that
 // is the same device buffer fed from the same host buffer (two operators sharing their activations) is not
 // copied a second time.
+// One host -> device copy already issued in the current call: same destination, source and size
+struct CopyDone {
+  const void *dev, *host;
+  size_t bytes;
+};
 static int copy_in(bfuse_context *ctx, KernelRec &k, void *const *host, cudaStream_t s, const KernelRec *other = nullptr,
-                   void *const *other_host = nullptr) {
+                   void *const *other_host = nullptr, std::vector<CopyDone> *seen = nullptr) {
   // small buffers (bias, per-column tables) first: each copy pays a fixed few microseconds, which
   // then overlap the previous pair's large transfer instead of trailing this pair's
   for (int pass = 0; pass < 2; ++pass)
@@ -1495,7 +1500,12 @@ static int copy_in(bfuse_context *ctx, KernelRec &k, void *const *host, cudaStre
         for (int j = 0; other && j < other->nargs && !done; ++j)
           done = !other->arg[j].is_output && other->desc.args[j] == k.desc.args[i] && other_host[j] == host[i] &&
                  other->arg[j].bytes == k.arg[i].bytes;
+        // (a batch call: the weights that every sub-shard's pair shares go in once, not once per pair -- each
+        // copy costs the copy engine a fixed ten-odd microseconds that nothing overlaps)
+        for (size_t j = 0; seen && j < seen->size() && !done; ++j)
+          done = (*seen)[j].dev == k.desc.args[i] && (*seen)[j].host == host[i] && (*seen)[j].bytes == k.arg[i].bytes;
         if (done) continue;
+        if (seen) seen->push_back({k.desc.args[i], host[i], k.arg[i].bytes});
         CK(cudaMemcpyAsync(k.desc.args[i], host[i], k.arg[i].bytes, cudaMemcpyHostToDevice, s));
       }
   return BFUSE_OK;
@@ -1562,11 +1572,12 @@ int bfuse_run_fuse_batch(bfuse_context *ctx, const int *fusions, int n, void *co
     if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) rc = fail(ctx, BFUSE_ERR_CUDA, "cudaEventCreate");
     else ev.push_back(e);
   }
+  std::vector<CopyDone> seen;   // inputs already on their way in this call
   for (int i = 0; i < n && !rc; ++i) {
     FusionRec &f = *get_fusion(ctx, fusions[i]);
     KernelRec &a = *ctx->kernels[f.k1], &b = *ctx->kernels[f.k2];
-    rc = copy_in(ctx, a, h1[i], ctx->s1);
-    if (!rc) rc = copy_in(ctx, b, h2[i], ctx->s1, &a, h1[i]);
+    rc = copy_in(ctx, a, h1[i], ctx->s1, nullptr, nullptr, &seen);
+    if (!rc) rc = copy_in(ctx, b, h2[i], ctx->s1, &a, h1[i], &seen);
     if (rc) break;
     cudaEventRecord(ev[2 * i], ctx->s1);
     cudaStreamWaitEvent(ctx->own, ev[2 * i], 0);

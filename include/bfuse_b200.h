@@ -228,7 +228,9 @@ int bfuse_run_fuse(bfuse_context *ctx, int fusion, void *const *host_args1, void
  * run_fuse, tests/benchmark/main.cc:183-200, for independent pairs instead of one repeated): the copies in of fusion i + 1, the fused launch of fusion i and the copies out
  * of fusion i - 1 run on three streams, so host <-> device transfers in both directions overlap the kernels.
  * host_args1[i] / host_args2[i] are the argument lists bfuse_run_fuse takes; pinned host memory is needed for the
- * overlap.  Returns after everything has completed; a fusion listed twice is rejected (its buffers would race). */
+ * overlap.  An input that an earlier fusion of the same call already takes from the same host buffer into the same
+ * device buffer (weights shared by the sub-shards of a batch) is copied once.  Returns after everything has
+ * completed; a fusion listed twice is rejected (its buffers would race). */
 int bfuse_run_fuse_batch(bfuse_context *ctx, const int *fusions, int n, void *const *const *host_args1,
                          void *const *const *host_args2);
 
