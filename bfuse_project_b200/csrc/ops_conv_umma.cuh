@@ -68,6 +68,8 @@ struct ConvStaging {
   int x_off;        // staged column of tap dx = 0 of output column 0
   int slot_bytes;   // cc * rows * pitch * 4: what one TMA load delivers
   int slot_pitch;   // slot_bytes rounded up to 128
+  int tile_px;      // output pixels per tile: 128, or whole output rows (the most that fit 128) when that leaves at
+                    // most a quarter of the 128 lanes idle -- tiles that start at a row need fewer staged rows
 };
 
 // Fills `st` for an image of h x wd and a kh x kw window; returns false when the conv cannot be staged
@@ -79,7 +81,10 @@ __host__ __device__ inline bool conv_staging(int ci, int h, int wd, int kh, int 
   if (wd % 4 || (ci * kh * kw) % 32 || bn != kConvBN) return false;   // whole K blocks, whole 128-pixel tiles (the lanes of tensor memory)
   st->ey = (kh == 1 && stride <= 8) ? stride : 1;   // a traversal stride is at most 8
   st->ex = 1;
-  const int out_rows = min(oh, (bn - 1 + ow - 1) / ow + 1);   // output rows that bn consecutive pixels can touch
+  st->tile_px = bn;
+  if (ow <= bn && (bn / ow) * ow >= bn - bn / 4) st->tile_px = (bn / ow) * ow;
+  // output rows that tile_px consecutive pixels can touch (tiles of whole rows: exactly their rows)
+  const int out_rows = st->tile_px % ow == 0 ? min(oh, st->tile_px / ow) : min(oh, (st->tile_px - 1 + ow - 1) / ow + 1);
   st->step_y = st->ey == 1 ? stride : 1;
   st->step_x = st->ex == 1 ? stride : 1;
   st->rows = (out_rows - 1) * st->step_y + (st->ey == 1 ? kh : 1);
@@ -278,7 +283,7 @@ struct ConvUmmaTf32 {
   __device__ __forceinline__ static void run_staged(const Params &p, const TileCtx &c) {
     const int warp = c.tid >> 5, lane = c.tid & 31;
     const int quad = (threadIdx.x >> 5) & 3;
-    const int px0 = c.block_x() * kConvBN, co0 = c.block_y() * kUmmaBM, img = c.block_z();
+    const int tile_px = p.st.tile_px, px0 = c.block_x() * tile_px, co0 = c.block_y() * kUmmaBM, img = c.block_z();
     const int ohw = p.oh * p.ow, K = p.K, num_kb = K / kBK;   // staged: K is a whole number of K blocks
     const int wstages = p.stages;                             // 16 KB weight stages behind the raw ring
     int *const status = c.status;
@@ -413,10 +418,11 @@ struct ConvUmmaTf32 {
         const ConvStaging st = p.st;
         const int ow = p.ow;
         const uint32_t slot_pitch = (uint32_t)st.slot_pitch;
-        // a row past the image reads the window of pixel 0 of the tile: finite values, and it is not stored
+        // a lane past the tile's pixels or past the image reads the window of pixel 0 of the tile: finite
+        // values, and it is not stored
         const int oy0 = px0 / ow;
         int oy = pix / ow, ox = pix - oy * ow;
-        if (pix >= ohw) oy = oy0, ox = px0 - oy0 * ow;
+        if (r >= tile_px || pix >= ohw) oy = oy0, ox = px0 - oy0 * ow;
         const uint32_t pixoff = (uint32_t)(((oy - oy0) * st.step_y * st.pitch + ox * st.step_x + st.x_off) * 4);
         const int kslot = st.cc * p.kh * p.kw, nslots = st.slots;
         const uint32_t tab = smem_u32(tab4), rawpix = raw0 + pixoff, ring_bytes = (uint32_t)nslots * slot_pitch;
@@ -504,7 +510,7 @@ struct ConvUmmaTf32 {
       mark(MARK_ACC_READY, c.tid == 0);
       if (acc_ok) {
         float *const yp = p.y + ((size_t)img * p.co + co0) * ohw + pix;
-        const bool live = pix < ohw;
+        const bool live = r < tile_px && pix < ohw;
         const int co_left = p.co - co0;
 #pragma unroll 1
         for (int cc = 0; cc < kUmmaBM; cc += 32) {

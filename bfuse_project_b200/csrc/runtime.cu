@@ -268,7 +268,7 @@ int default_launch(const bfuse_context *ctx, bfuse_kernel_desc *d, std::string *
           *err = "conv2d: shape[11] = 1 (staged operand): the raw ring and two weight stages do not fit the shared-memory budget";
           return BFUSE_ERR_SHAPE;
         }
-        set(ceil_div(oh * ow, bn), ceil_div(s[4], kUmmaBM), s[0], kConvThreads, 1, conv_staged_smem_bytes(K, st.slots, st.slot_pitch, wst), 3);
+        set(ceil_div(oh * ow, st.tile_px), ceil_div(s[4], kUmmaBM), s[0], kConvThreads, 1, conv_staged_smem_bytes(K, st.slots, st.slot_pitch, wst), 3);
         return BFUSE_OK;
       }
       int stages = std::max(1, std::min({q, kUmmaMaxStages, (budget - conv_header_bytes(K)) / conv_stage_bytes(bn)}));
@@ -473,8 +473,10 @@ int build_params(bfuse_context *ctx, KernelRec &k) {
       if (bn != 32 && bn != 64 && bn != 128) return shape_err("shape[9] (pixels per tile) must be 32, 64 or 128");
       const int split = s[10] > 0 ? s[10] : 1, num_kb = ceil_div(K, ConvUmmaTf32::kBK), q = ceil_div(num_kb, split);
       if (split > 8 || (split - 1) * q >= num_kb) return shape_err("shape[10] (k-slices) must be 1..8 with every k-slice non-empty");
-      if (kd.gx != split * ceil_div(oh * ow, bn) || kd.gy != ceil_div(s[4], kUmmaBM) || kd.gz != s[0])
-        return shape_err("GridDim must be (k-slices * ceil(oh*ow/BN), ceil(co/128), n)");
+      ConvStaging geometry;   // a staged conv's tiles may be whole output rows: fewer than BN pixels
+      const int tile_px = s[11] == 1 && conv_staging(s[1], s[2], s[3], s[5], s[6], s[7], s[8], oh, ow, bn, &geometry) ? geometry.tile_px : bn;
+      if (kd.gx != split * ceil_div(oh * ow, tile_px) || kd.gy != ceil_div(s[4], kUmmaBM) || kd.gz != s[0])
+        return shape_err("GridDim must be (k-slices * ceil(oh*ow / pixels per tile), ceil(co/128), n)");
       k.cluster = split;
       ConvUmmaParams p;
       std::memset(&p, 0, sizeof(p));
@@ -1455,8 +1457,9 @@ int bfuse_debug_conv_staging(const int *shape, int bn, int *out, int n) {
   ConvStaging st;
   std::memset(&st, 0, sizeof(st));
   const bool ok = oh > 0 && ow > 0 && conv_staging(s[1], s[2], s[3], s[5], s[6], s[7], s[8], oh, ow, bn, &st);
-  const int v[12] = {ok ? st.slots : 0, st.cc, st.rows, st.pitch, st.ex, st.ey, st.step_x, st.step_y, st.x_start, st.x_off, st.slot_bytes, st.slot_pitch};
-  std::memcpy(out, v, sizeof(v));
+  const int v[13] = {ok ? st.slots : 0, st.cc, st.rows, st.pitch, st.ex, st.ey, st.step_x, st.step_y, st.x_start, st.x_off, st.slot_bytes, st.slot_pitch,
+                     st.tile_px};
+  std::memcpy(out, v, sizeof(int) * (n >= 13 ? 13 : 12));
   return BFUSE_OK;
 }
 

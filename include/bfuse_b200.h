@@ -206,7 +206,7 @@ int bfuse_debug_fused_timeline(bfuse_context *ctx, const int *fusions, int n, lo
  * ring slots before the window is sized (0: the conv cannot be staged and is gathered from global memory), channels per slot, staged rows,
  * floats per staged row, element strides x / y of the load, staged columns / rows between neighbouring
  * output pixels / rows, tensor column of staged column 0, staged column of tap 0 of output column 0,
- * bytes per slot, slot pitch in bytes. */
+ * bytes per slot, slot pitch in bytes; with n >= 13 also the output pixels per tile (bn, or whole output rows). */
 int bfuse_debug_conv_staging(const int *shape, int bn, int *out, int n);
 /* Read and clear the device status word (0 = no bounded wait gave up). Synchronises.  A non-zero
  * status also restarts the ticket counters of every work-queue fusion from zero. */

@@ -11,15 +11,15 @@ import pytest
 
 import bfuse_project_b200 as bf
 
-NAMES = ("slots", "cc", "rows", "pitch", "ex", "ey", "step_x", "step_y", "x_start", "x_off", "slot_bytes", "slot_pitch")
+NAMES = ("slots", "cc", "rows", "pitch", "ex", "ey", "step_x", "step_y", "x_start", "x_off", "slot_bytes", "slot_pitch", "tile_px")
 
 
 def staging(shape, bn):
     fn = bf.lib().bfuse_debug_conv_staging
     fn.argtypes = [C.POINTER(C.c_int), C.c_int, C.POINTER(C.c_int), C.c_int]
     fn.restype = C.c_int
-    out = (C.c_int * 12)()
-    assert fn((C.c_int * 9)(*shape), bn, out, 12) == 0
+    out = (C.c_int * 13)()
+    assert fn((C.c_int * 9)(*shape), bn, out, 13) == 0
     return dict(zip(NAMES, out))
 
 
@@ -45,7 +45,10 @@ def test_staged_operand_equals_im2col(shape, bn):
     k = np.arange(K)
     ch, t = k // khw, k % khw
     tab = (ch % st["cc"]) * plane + (t // kw) * st["pitch"] + t % kw
-    for px0 in range(0, oh * ow, bn):
+    # tiles of whole output rows wherever they fill at least three quarters of the 128 lanes
+    tile = st["tile_px"]
+    assert tile == ((bn // ow) * ow if ow <= bn and (bn // ow) * ow >= bn - bn // 4 else bn)
+    for px0 in range(0, oh * ow, tile):
         oy0 = px0 // ow
         y0 = oy0 * stride - pad
         # every slot of the tile as the TMA delivers it
@@ -75,7 +78,7 @@ def test_staged_operand_equals_im2col(shape, bn):
             first += passed
             assert 0 <= kin < kslot
         assert np.array_equal(slot_of, np.arange(K) // kslot)
-        for pix in range(px0, min(px0 + bn, oh * ow)):
+        for pix in range(px0, min(px0 + tile, oh * ow)):
             oy, ox = divmod(pix, ow)
             pixoff = (oy - oy0) * st["step_y"] * st["pitch"] + ox * st["step_x"] + st["x_off"]
             assert 0 <= pixoff and pixoff + tab.max() < st["cc"] * plane
