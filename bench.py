@@ -790,9 +790,9 @@ def main():
         else:
             table[name] = [round(r["best_fused_us"], 2), round(r["sequential_us"], 2), round(r["roofline_frac"], 3), r["best_pattern"],
                            round(r.get("isolated_fused_us", 0.0), 2)]
-    judged = [r["model"]["within_2_pct_of_best"] for r in side_pairs.values() if isinstance(r.get("model"), dict) and r["model"].get("within_2_pct_of_best") is not None]
-    if judged:
-        line["pairing_model_on_baseline_pairs"] = {"pairs": len(judged), "pattern_within_2_pct_of_best": sum(judged),
+    scored = [r["model"]["within_2_pct_of_best"] for r in side_pairs.values() if isinstance(r.get("model"), dict) and r["model"].get("within_2_pct_of_best") is not None]
+    if scored:
+        line["pairing_model_on_baseline_pairs"] = {"pairs": len(scored), "pattern_within_2_pct_of_best": sum(scored),
                                                    "advice": {n: r["model"].get("pattern") for n, r in side_pairs.items() if isinstance(r.get("model"), dict)}}
     line["per_config"] = table
     print(json.dumps(line), flush=True)

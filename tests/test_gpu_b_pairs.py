@@ -306,3 +306,29 @@ def test_run_fuse_batch_matches_one_call_per_pair(rt):
     with pytest.raises(bf.BfuseError) as e:
         rt.run_fuse_batch([fus[0], fus[0]], [got[0][0], got[0][0]], [got[0][1], got[0][1]])
     assert e.value.code == 1
+
+
+def test_run_fuse_batch_over_sub_shards_that_share_their_weights(rt):
+    """Sub-shards of one batch (the conv pair's images in pieces, as the end-to-end bench sends them): every piece
+    names the same host and device weight buffers, which the call copies once; the pieces' outputs, written into
+    slices of one host array, equal the outputs of the whole batch computed in one launch."""
+    import torch
+    n, sub = 6, 2
+    b = wl.ConvBranchBatch(rt, torch, 0, n, seed=5)
+    k3, k1 = b.shard(0, n)
+    rt.launch_fused(rt.register_fusion(k3, k1, bf.RANGE_SPLIT, 0, 0))
+    assert rt.read_status() == 0
+    want3, want1 = b.y3.cpu().numpy(), b.y1.cpu().numpy()
+    assert np.any(want3 != 0) and np.any(want1 != 0)
+    b.clear_outputs()
+    hx, hw3, hw1 = b.x.cpu().numpy(), b.w3.cpu().numpy(), b.w1.cpu().numpy()
+    b.w3.zero_(), b.w1.zero_(), b.x.zero_()          # everything the kernels read has to come from the host buffers
+    hy3, hy1 = np.zeros_like(want3), np.zeros_like(want1)
+    fus, h1, h2 = [], [], []
+    for o in range(0, n, sub):
+        s3, s1 = b.shard(o, sub)
+        fus.append(rt.register_fusion(s3, s1, bf.RANGE_SPLIT, 0, 0))
+        h1.append([hx[o:o + sub], hw3, hy3[o:o + sub]])
+        h2.append([hx[o:o + sub], hw1, hy1[o:o + sub]])
+    rt.run_fuse_batch(fus, h1, h2)
+    assert np.array_equal(hy3.view(np.uint8), want3.view(np.uint8)) and np.array_equal(hy1.view(np.uint8), want1.view(np.uint8))
