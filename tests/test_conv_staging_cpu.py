@@ -26,7 +26,7 @@ def staging(shape, bn):
 CASES = [((1, 64, 56, 56, 128, 3, 3, 2, 1), 128), ((1, 64, 56, 56, 128, 1, 1, 2, 0), 128), ((1, 32, 56, 56, 128, 3, 3, 2, 1), 128),
          ((1, 32, 20, 20, 200, 3, 3, 1, 1), 128), ((1, 96, 31, 16, 40, 1, 1, 2, 0), 128), ((1, 32, 12, 12, 130, 5, 5, 3, 2), 128),
          ((1, 32, 28, 28, 128, 3, 3, 1, 1), 128), ((1, 32, 9, 24, 16, 1, 3, 2, 1), 128), ((1, 32, 16, 8, 16, 3, 1, 1, 1), 128),
-         ((1, 8, 14, 12, 16, 2, 2, 2, 0), 128)]
+         ((1, 8, 14, 12, 16, 2, 2, 2, 0), 128), ((1, 32, 5, 160, 16, 3, 3, 1, 1), 128), ((1, 32, 6, 200, 16, 3, 3, 2, 1), 128)]
 
 
 @pytest.mark.parametrize("shape,bn", CASES)

@@ -173,6 +173,8 @@ def test_conv_staged_operand_mode(rt):
     run_and_check(rt, wl.PairSpec("staged_5x5", c, d, "tf32", "hbm"), [(bf.ZIGZAG, 1, 1), (bf.RANGE_SPLIT, 0, 0)])
     g = wl.gemm("g", rng, bf.OP_GEMM_TF32, 1, 100, 64, 64, w_std=1.0, bn=64, split=1)
     run_and_check(rt, wl.PairSpec("staged_gemm", a, g, "tf32", "hbm"), BLOCK_PATTERNS)
+    wide = wl.conv2d("swide", rng, bf.OP_CONV2D_TF32, 1, 32, 5, 160, 136, 3, 1, 1, bn=128, mode=1)       # rows of 160 pixels: tiles start inside a row
+    run_and_check(rt, wl.PairSpec("staged_wide", wide, g, "tf32", "hbm"), [(bf.ZIGZAG, 1, 1), (bf.RANGE_SPLIT, 0, 0)])
     for bad in (wl.conv2d("o", rng, bf.OP_CONV2D_TF32, 1, 96, 17, 17, 96, 3, 2, 0, bn=128, mode=1),        # 17 floats per row
                 wl.conv2d("o", rng, bf.OP_CONV2D_TF32, 1, 32, 20, 24, 136, 3, 2, 1, bn=64, mode=1),        # 64-pixel tiles
                 wl.conv2d("o", rng, bf.OP_CONV2D_TF32, 1, 256, 16, 16, 256, 3, 1, 1, bn=128, split=4, mode=1),   # K split over a cluster
