@@ -48,6 +48,8 @@ struct DispatchTable {
   int *status;             // device status word; non-zero = a bounded wait gave up
   unsigned long long *cta_times;  // diagnostic: when non-null, every block-level dispatch slot records 3 globaltimer marks
   int no_pdl;              // host side only: launch without the programmatic-dependent-launch attribute
+  int tmem_cols;           // queue launches: tensor-memory columns a persistent CTA allocates ONCE for all its tickets
+                           // (the larger need of the two operators, a power of two; 0: neither uses tensor memory)
 };
 
 // Dispatch unit (or ticket) b -> operator k and its virtual unit.  Returns false if b is unmapped.

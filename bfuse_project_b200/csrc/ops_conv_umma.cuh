@@ -297,8 +297,10 @@ struct ConvUmmaTf32 {
     const uint32_t raw0 = smem_u32(c.smem) + conv_header_bytes(K);
     const uint32_t wring = raw0 + (uint32_t)conv_raw_bytes(p.st.slots, p.st.slot_pitch);
     if (warp == 5) {
-      tmem_alloc(smem_u32(tmem_slot), kConvTmemCols);
-      if (!c.persistent) tmem_relinquish();
+      if (!c.tmem_given) {   // (a persistent CTA of the work queue holds its columns already)
+        tmem_alloc(smem_u32(tmem_slot), kConvTmemCols);
+        if (!c.persistent) tmem_relinquish();
+      }
     }
     long long *const tl = (p.timeline && c.vblock == 0) ? p.timeline : nullptr;
     auto mark = [&](int what, bool who) {
@@ -346,7 +348,7 @@ struct ConvUmmaTf32 {
     tc_fence_before();
     c.sync();
     tc_fence_after();
-    const uint32_t tmem_acc = *reinterpret_cast<volatile uint32_t *>(tmem_slot);
+    const uint32_t tmem_acc = c.tmem_given ? c.tmem_base : *reinterpret_cast<volatile uint32_t *>(tmem_slot);
     const uint32_t tmem_row = tmem_acc + ((uint32_t)(quad * 32) << 16);   // this warp's lanes; columns 0-127: accumulator, then the A stages
     mark(MARK_SETUP_DONE, c.tid == 0);
 
@@ -531,7 +533,7 @@ struct ConvUmmaTf32 {
     }
     tc_fence_before();
     c.sync();
-    if (warp == 5) tmem_dealloc(tmem_acc, kConvTmemCols);
+    if (warp == 5 && !c.tmem_given) tmem_dealloc(tmem_acc, kConvTmemCols);
     if (c.persistent) {  // the next tile of a persistent CTA initialises them again
       if (c.tid < wstages) {
         mbar_inval(full0 + 8 * c.tid);
@@ -574,8 +576,10 @@ struct ConvUmmaTf32 {
     // tensor memory first: the SM starts its next CTA of this kernel only once this one has given up
     // its permit to allocate
     if (warp == 5) {
-      tmem_alloc(smem_u32(tmem_slot), BN);
-      if (!c.persistent) tmem_relinquish();
+      if (!c.tmem_given) {   // (a persistent CTA of the work queue holds its columns already)
+        tmem_alloc(smem_u32(tmem_slot), BN);
+        if (!c.persistent) tmem_relinquish();
+      }
     }
     int2 *tab = reinterpret_cast<int2 *>(c.smem + kUmmaHeaderBytes);
     const uint32_t tiles = smem_u32(c.smem) + conv_header_bytes(K);   // the operand ring
@@ -633,7 +637,7 @@ struct ConvUmmaTf32 {
     tc_fence_before();
     c.sync();
     tc_fence_after();
-    const uint32_t tmem_acc = *reinterpret_cast<volatile uint32_t *>(tmem_slot);
+    const uint32_t tmem_acc = c.tmem_given ? c.tmem_base : *reinterpret_cast<volatile uint32_t *>(tmem_slot);
     const uint32_t tmem_row = tmem_acc + ((uint32_t)(quad * 32) << 16);
     mark(MARK_SETUP_DONE, c.tid == 0);
 
@@ -715,7 +719,7 @@ struct ConvUmmaTf32 {
     if (split > 1) umma_split_reduce<0>(c, BN, split, kslice, tiles, recv_bar, tmem_row, acc_ok, w, px0, nullptr, tl);
     tc_fence_before();
     c.sync();
-    if (warp == 5) tmem_dealloc(tmem_acc, BN);
+    if (warp == 5 && !c.tmem_given) tmem_dealloc(tmem_acc, BN);
     if (c.persistent && c.tid < stages) {  // the next tile of a persistent CTA initialises them again
       mbar_inval(full0 + 8 * c.tid);
       mbar_inval(empty0 + 8 * c.tid);

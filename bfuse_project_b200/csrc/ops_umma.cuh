@@ -514,8 +514,10 @@ struct GemmUmma {
     // entirely above the diagonal of a causal product needs no accumulator.
     const bool masked_tile = p.causal && n0 > m0 + BM - 1;
     if (warp == 5) {
-      if (!masked_tile) tmem_alloc(smem_u32(tmem_slot), BN * halves);
-      if (!c.persistent) tmem_relinquish();
+      if (!c.tmem_given) {   // (a persistent CTA of the work queue holds its columns already)
+        if (!masked_tile) tmem_alloc(smem_u32(tmem_slot), BN * halves);
+        if (!c.persistent) tmem_relinquish();
+      }
     }
     const uint32_t tiles = smem_u32(c.smem) + kUmmaHeaderBytes;
     const uint32_t recv_bar = acc_bar + 8;                                  // counts partial sums delivered by peers
@@ -606,7 +608,7 @@ struct GemmUmma {
     tc_fence_before();
     c.sync();
     tc_fence_after();
-    const uint32_t tmem_acc = *reinterpret_cast<volatile uint32_t *>(tmem_slot);
+    const uint32_t tmem_acc = c.tmem_given ? c.tmem_base : *reinterpret_cast<volatile uint32_t *>(tmem_slot);
     const uint32_t tmem_row = tmem_acc + ((uint32_t)(quad * 32) << 16);
     mark(MARK_SETUP_DONE, c.tid == 0);
 
@@ -688,7 +690,7 @@ struct GemmUmma {
     if (split > 1) umma_split_reduce<KIND>(c, BN, split, kslice, tiles, recv_bar, tmem_row, acc_ok, w, n0, bias_tile, tl);
     tc_fence_before();
     c.sync();
-    if (warp == 5) tmem_dealloc(tmem_acc, BN * halves);
+    if (warp == 5 && !c.tmem_given) tmem_dealloc(tmem_acc, BN * halves);
     if (c.persistent && c.tid < stages) {  // the next tile of a persistent CTA initialises them again
       mbar_inval(full0 + 8 * c.tid);
       mbar_inval(empty0 + 8 * c.tid);

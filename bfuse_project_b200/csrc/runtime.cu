@@ -957,14 +957,22 @@ int bfuse_register_fusion(bfuse_context *ctx, int kernel1, int kernel2, int patt
   f->name = a->name + "_" + b->name + (thread_split ? "_fused_hfuse" : "_fused_bfuse");
   // shared memory: union for block-level fusion, sum for thread-level fusion (Matchers.cc:512-519)
   f->stages[0] = f->stages[1] = 0;
+  // tensor-memory columns an operator's CTA allocates
+  auto tmem_cols = [](const KernelRec &k) {
+    if (k.desc.op == BFUSE_OP_GEMM_TF32 || k.desc.op == BFUSE_OP_GEMM_BF16) return k.desc.shape[4] * std::max(1, k.desc.shape[6] / kUmmaBM);
+    if (k.desc.op == BFUSE_OP_CONV2D_TF32 && k.desc.shape[11] == 1) return kConvTmemCols;   // staged: accumulator and operand stages
+    return k.desc.op == BFUSE_OP_CONV2D_TF32 ? (k.desc.shape[9] > 0 ? k.desc.shape[9] : kConvBN) : 0;
+  };
+  // a persistent CTA of the work queue allocates once what either operator's tile may need (a power of two >= 32)
+  t.tmem_cols = 0;
+  if (t.queue) {
+    const int need = std::max(tmem_cols(*a), tmem_cols(*b));
+    for (int c = 32; need > 0 && t.tmem_cols == 0; c *= 2)
+      if (c >= need) t.tmem_cols = c;
+  }
   if (thread_split) {
     // both operators allocate tensor memory in the same CTA; an allocation that cannot be granted
     // would block for ever, so the sum has to fit the SM's 512 columns
-    auto tmem_cols = [](const KernelRec &k) {
-      if (k.desc.op == BFUSE_OP_GEMM_TF32 || k.desc.op == BFUSE_OP_GEMM_BF16) return k.desc.shape[4] * std::max(1, k.desc.shape[6] / kUmmaBM);
-      if (k.desc.op == BFUSE_OP_CONV2D_TF32 && k.desc.shape[11] == 1) return kConvTmemCols;   // staged: accumulator and operand stages
-      return k.desc.op == BFUSE_OP_CONV2D_TF32 ? (k.desc.shape[9] > 0 ? k.desc.shape[9] : kConvBN) : 0;
-    };
     if (tmem_cols(*a) + tmem_cols(*b) > 512)
       return fail(ctx, BFUSE_ERR_UNSUPPORTED, "thread split: the two operators need more than 512 tensor-memory columns together");
     // both windows live side by side; rings registered for a whole SM each are made shallower until

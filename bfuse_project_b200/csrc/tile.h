@@ -26,6 +26,8 @@ struct TileCtx {
   int *status;          // device status word (bounded waits report here)
   int persistent;       // 1: more tensor-memory allocations may follow in this CTA (work queue: the next
                         // tile; thread split: the other operator), so the allocation permit must be kept
+  unsigned tmem_base;   // tmem_given: the tensor-memory columns the CTA already holds for this operator (a persistent
+  int tmem_given;       // CTA of the work queue allocates once for all its tickets); the body neither allocates nor frees
 
   // Programmatic dependent launch: the CTA may have started while the previous kernel on the stream
   // was still running.  Every thread calls this before its first access to global memory; what comes
