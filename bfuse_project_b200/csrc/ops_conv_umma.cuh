@@ -471,16 +471,16 @@ struct ConvUmmaTf32 {
           kin += kBK - passed * kslot, ahead -= passed, rs += passed;
           if (rs >= (uint32_t)nslots) rs -= nslots, rph ^= 1;
           if (++as == (uint32_t)kConvAStages) as = 0, aph ^= 1;
-          seen_empty = false, seen_raw = false;
+          // the look at the next K block's barriers: asked here, answered (the votes below) once this K block's
+          // reads have been issued, so that the answers' round trip hides behind them
+          bool e = false, f = false;
           if (kb + 1 < num_kb) {
             const int reach_n = kin + kBK - 1;
             const bool more = ahead <= (reach_n >= kslot) + (reach_n >= 2 * kslot);
             uint32_t w = rs + (uint32_t)ahead, wph = rph;
             if (w >= (uint32_t)nslots) w -= nslots, wph ^= 1;
-            const bool e = mbar_test(a_empty0 + 8 * as, aph);
-            const bool f = more && mbar_test(raw_full0 + 8 * w, wph);
-            seen_empty = __all_sync(0xffffffffu, e);
-            seen_raw = __all_sync(0xffffffffu, f);
+            e = mbar_test(a_empty0 + 8 * as, aph);
+            f = more && mbar_test(raw_full0 + 8 * w, wph);
           }
           // the raw values, then all 32 into this lane's columns of the A stage
           uint32_t v[32];
@@ -492,6 +492,8 @@ struct ConvUmmaTf32 {
             v[4 * i + 3] = __float_as_uint(ld_shared_f32(src[i] + (uint32_t)off[i].w));
           }
           tmem_st_32x32(a_row + as_old * (uint32_t)kBK, v);
+          seen_empty = __all_sync(0xffffffffu, e);
+          seen_raw = __all_sync(0xffffffffu, f);
           tmem_st_wait();
           tc_fence_before();
           __syncwarp();
