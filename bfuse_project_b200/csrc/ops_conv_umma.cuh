@@ -50,7 +50,6 @@ constexpr int kConvMaxRawSlots = 6;
 constexpr int kConvRawBarOffset = 256;   // byte offset of the raw ring's barriers in the header: full[6], then empty[6]
 constexpr int kConvAStages = 4;          // staged convs: K blocks of the im2col operand held in tensor memory (32 columns each);
                                          // their barriers follow the raw ring's in the header: full[4], then empty[4]
-constexpr int kConvPollNs = 200;         // staged convs: pause between polls of the loading and MMA threads
 constexpr int kConvTmemCols = 256;       // staged convs: 128 accumulator columns + 4 x 32 operand columns
 
 // Geometry of the raw-input staging of a conv (shared by the host, which sizes shared memory and
@@ -360,7 +359,7 @@ struct ConvUmmaTf32 {
         const int y_start = (px0 / p.ow) * p.stride - p.pad;
         uint32_t rs = 0, rph = 1;
         for (int g = 0; g < g_end; ++g) {
-          if (!mbar_wait<kConvPollNs>(raw_empty0 + 8 * rs, rph, status, UMMA_WAIT_EMPTY_TIMEOUT)) break;
+          if (!mbar_wait(raw_empty0 + 8 * rs, rph, status, UMMA_WAIT_EMPTY_TIMEOUT)) break;
           mbar_expect_tx(raw_full0 + 8 * rs, slot_bytes);
           tma_load_4d(raw0 + rs * slot_pitch, &p.map_x, raw_full0 + 8 * rs, x_start, y_start, g * cc, img);
           if (++rs == (uint32_t)nslots) rs = 0, rph ^= 1;
@@ -371,7 +370,7 @@ struct ConvUmmaTf32 {
       if (elect_one()) {
         uint32_t s = 0, ph = 1, dst = wring, bar = full0;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait<kConvPollNs>(empty0 + 8 * s, ph, status, UMMA_WAIT_EMPTY_TIMEOUT)) break;
+          if (!mbar_wait(empty0 + 8 * s, ph, status, UMMA_WAIT_EMPTY_TIMEOUT)) break;
           mbar_expect_tx(bar, kUmmaABytes);
           tma_load_3d(dst, &p.map_w, bar, kb * kBK, co0, 0);
           if (++s == (uint32_t)wstages) s = 0, ph ^= 1, dst = wring, bar = full0;
@@ -385,7 +384,7 @@ struct ConvUmmaTf32 {
         uint32_t s = 0, ph = 0, lo = lo0, as = 0, aph = 0, accumulate = 0;
         bool ok = true;
         for (int kb = 0; kb < num_kb; ++kb) {
-          ok = mbar_wait<kConvPollNs>(a_full0 + 8 * as, aph, status, UMMA_WAIT_FULL_TIMEOUT) && mbar_wait<kConvPollNs>(full0 + 8 * s, ph, status, UMMA_WAIT_FULL_TIMEOUT);
+          ok = mbar_wait(a_full0 + 8 * as, aph, status, UMMA_WAIT_FULL_TIMEOUT) && mbar_wait(full0 + 8 * s, ph, status, UMMA_WAIT_FULL_TIMEOUT);
           if (!ok) break;
           tc_fence_after();
           if (kb == 0) mark(MARK_FIRST_FULL, true);

@@ -65,7 +65,6 @@ __device__ __forceinline__ uint64_t global_ns() {
   return t;
 }
 // Wait for phase `parity` of an mbarrier, for at most ~1 s.  Returns false after reporting.
-template <int SLEEP_NS = 0>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int *status, int code) {
   uint64_t t0 = 0;
   for (uint32_t it = 0;; ++it) {
@@ -78,7 +77,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int *st
         : "r"(bar), "r"(parity)
         : "memory");
     if (ok) return true;
-    if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);   // a waiter that can afford to react late leaves the issue slots to the others meanwhile
     if ((it & 1023u) == 1023u) {
       // once any wait of the launch has given up, the others follow at once: a failed launch then ends
       // after about one second in all, not one second per CTA
