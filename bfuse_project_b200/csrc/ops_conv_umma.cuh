@@ -258,6 +258,90 @@ struct ConvUmmaTf32 {
     return __shfl_sync(0xffffffffu, ok, 0) != 0;
   }
 
+  // The repack of a 3 x 3 window: it walks the K range four channels at a time (a whole raw slot, or a quarter,
+  // an eighth ... of one) -- 36 values of k, every one's channel, row and tap known when this is compiled -- instead of one K block
+  // at a time.  A slot costs 12 row addresses and 24 reads (the taps dx = 1, 2 of a row as one 8-byte read
+  // where PAIR says they start at an even float), no table and no address add per value, and it is waited
+  // for and released exactly once.  The 36 values go into the ring of A stages as into 128 consecutive
+  // columns (nine tcgen05.st of 4 columns, each wrapped on its own), so the MMA side keeps its K blocks
+  // of 32: a stage is handed over as soon as its 32nd column is written.  `rawpix_p` points at the pixel's
+  // window origin in slot 0 of the ring.
+  template <bool PAIR>
+  __device__ __forceinline__ static bool repack_3x3(const TileCtx &c, int K, bool lane0, const unsigned char *rawpix_p, uint32_t slot_pitch,
+                                                    int nslots, int quads, uint32_t plane4, uint32_t pitch4, uint32_t a_row, uint32_t raw_full0,
+                                                    uint32_t raw_empty0, uint32_t a_full0, uint32_t a_empty0) {
+    int *const status = c.status;
+    const int steps = K / 36;
+    uint32_t rs = 0, rph = 0;   // raw slot of this step, its phase
+    int quad_in_slot = 0;       // a slot of more than 4 channels is walked in `quads` steps of 4
+    int kdone = 0;              // values of k written so far
+    int acquired = 0;           // A stages (counted over the tile) whose "empty" has been seen
+    bool seen_raw = false, seen_empty = false;
+    for (int s = 0; s < steps; ++s) {
+      if (quad_in_slot == 0 && !seen_raw && !warp_wait(lane0, raw_full0 + 8 * rs, rph, status, UMMA_WAIT_FULL_TIMEOUT)) return false;
+      // the stages this slot's 36 columns fall into: kdone / 32 and, mostly, the one after
+      const int g_last = (kdone + 35) >> 5;
+      if (seen_empty) ++acquired;
+      while (acquired <= g_last) {
+        if (!warp_wait(lane0, a_empty0 + 8 * (acquired & (kConvAStages - 1)), (uint32_t)((acquired / kConvAStages) & 1) ^ 1u, status,
+                       UMMA_WAIT_EMPTY_TIMEOUT))
+          return false;
+        ++acquired;
+      }
+      tc_fence_after();   // the MMAs that read these stages have completed (their commit): they may be written again
+      const unsigned char *base = rawpix_p + rs * slot_pitch + (uint32_t)(4 * quad_in_slot) * plane4;
+      uint32_t v[36];
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) {
+#pragma unroll
+        for (int dy = 0; dy < 3; ++dy) {
+          const unsigned char *row = base + ch * plane4 + dy * pitch4;
+          const int i = 9 * ch + 3 * dy;
+          v[i] = __float_as_uint(*reinterpret_cast<const float *>(row));
+          if (PAIR) {
+            const float2 t = *reinterpret_cast<const float2 *>(row + 4);
+            v[i + 1] = __float_as_uint(t.x), v[i + 2] = __float_as_uint(t.y);
+          } else {
+            v[i + 1] = __float_as_uint(*reinterpret_cast<const float *>(row + 4));
+            v[i + 2] = __float_as_uint(*reinterpret_cast<const float *>(row + 8));
+          }
+        }
+      }
+      // a look at the next step's barriers while the reads are in flight: a wait costs 100-200 clocks even
+      // when its barrier has completed
+      const uint32_t rs_old = rs;
+      const bool slot_done = ++quad_in_slot == quads;
+      if (slot_done) {
+        quad_in_slot = 0;
+        if (++rs == (uint32_t)nslots) rs = 0, rph ^= 1;
+      }
+      bool e = false, f = false;
+      if (s + 1 < steps) {
+        f = slot_done && mbar_test(raw_full0 + 8 * rs, rph);
+        if (acquired <= (kdone + 36 + 35) >> 5)
+          e = mbar_test(a_empty0 + 8 * (acquired & (kConvAStages - 1)), (uint32_t)((acquired / kConvAStages) & 1) ^ 1u);
+      }
+      const uint32_t col = (uint32_t)kdone & 127u;
+#pragma unroll
+      for (int q = 0; q < 9; ++q) tmem_st_32x4(a_row + ((col + 4u * q) & 127u), v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+      seen_raw = __all_sync(0xffffffffu, f);
+      seen_empty = __all_sync(0xffffffffu, e);
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      // one arrival per warp: the slot is free (its values were written), and so is every stage whose 32nd
+      // column this step wrote
+      const int done_before = kdone >> 5;
+      kdone += 36;
+      const int done_after = kdone >> 5;
+      if (lane0) {
+        if (slot_done) mbar_arrive(raw_empty0 + 8 * rs_old);
+        for (int g = done_before; g < done_after; ++g) mbar_arrive(a_full0 + 8 * (g & (kConvAStages - 1)));
+      }
+    }
+    return true;
+  }
+
   // The staged form of a tile: 128 output pixels x 128 output channels with the operands' roles swapped
   // relative to run() -- the im2col rows are the A operand and live in TENSOR memory, the weights are the
   // B operand in shared memory, and the accumulator holds pixels in its lanes and output channels in its
@@ -433,7 +517,18 @@ struct ConvUmmaTf32 {
         int kin = 0, ahead = 0;
         uint32_t rs = 0, rph = 0, as = 0, aph = 1;
         bool seen_empty = false, seen_raw = false;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        // 3 x 3 windows go four channels at a time, without the table
+        extern __shared__ __align__(16) unsigned char conv_window[];
+        const bool by_slot = p.kh == 3 && p.kw == 3;   // (slots hold 4, 8, 16 ... channels; K is a multiple of 32 and of 9)
+        if (by_slot) {
+          const unsigned char *const rawpix_p = conv_window + (rawpix - smem_u32(conv_window));
+          const uint32_t plane4 = (uint32_t)(st.rows * st.pitch * 4), pitch4 = (uint32_t)(st.pitch * 4);
+          // taps dx = 1, 2 of every pixel start at an even float (rows, planes and slots are 16-byte multiples)
+          const bool pair = (st.step_x & 1) == 0 && (st.x_off & 1) == 1;
+          ok = pair ? repack_3x3<true>(c, K, lane0, rawpix_p, slot_pitch, nslots, st.cc / 4, plane4, pitch4, a_row, raw_full0, raw_empty0, a_full0, a_empty0)
+                    : repack_3x3<false>(c, K, lane0, rawpix_p, slot_pitch, nslots, st.cc / 4, plane4, pitch4, a_row, raw_full0, raw_empty0, a_full0, a_empty0);
+        }
+        for (int kb = 0; kb < num_kb && !by_slot; ++kb) {
           // one lane per warp polls a barrier and the warp follows it (its lanes meet again at the __syncwarp
           // before the arrival below, so the outcome of a wait has to be the same for all of them anyway)
           if (!seen_empty && !(ok = warp_wait(lane0, a_empty0 + 8 * as, aph, status, UMMA_WAIT_EMPTY_TIMEOUT))) break;
