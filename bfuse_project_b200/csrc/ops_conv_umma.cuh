@@ -118,6 +118,7 @@ struct ConvUmmaParams {
   int bn;               // output pixels per tile: 32, 64 or 128
   int split;            // CTAs (k-slices) per tile = cluster width; 1: no split
   int kb_per_slice;     // K blocks per k-slice
+  int ctas;             // staged: CTAs of the grid (a CTA takes every ctas-th tile)
   ConvStaging st;       // st.slots == 0: gathered from global memory
   long long *timeline;  // diagnostic: when non-null, CTA 0 records globaltimer marks (UmmaMark indices)
 };
@@ -266,16 +267,21 @@ struct ConvUmmaTf32 {
   // columns (nine tcgen05.st of 4 columns, each wrapped on its own), so the MMA side keeps its K blocks
   // of 32: a stage is handed over as soon as its 32nd column is written.  `rawpix_p` points at the pixel's
   // window origin in slot 0 of the ring.
+  // where the four-channel walk stands, across the tiles of a CTA
+  struct SlotWalk {
+    uint32_t rs = 0, rph = 0;   // raw slot of the next step, its phase
+    int quad_in_slot = 0;       // a slot of more than 4 channels is walked in `quads` steps of 4
+    int kdone = 0;              // values of k written so far (over all tiles: the A ring's column is kdone mod 128)
+    int acquired = 0;           // A stages (counted over all tiles) whose "empty" has been seen
+  };
   template <bool PAIR>
   __device__ __forceinline__ static bool repack_3x3(const TileCtx &c, int K, bool lane0, const unsigned char *rawpix_p, uint32_t slot_pitch,
                                                     int nslots, int quads, uint32_t plane4, uint32_t pitch4, uint32_t a_row, uint32_t raw_full0,
-                                                    uint32_t raw_empty0, uint32_t a_full0, uint32_t a_empty0) {
+                                                    uint32_t raw_empty0, uint32_t a_full0, uint32_t a_empty0, SlotWalk &walk) {
     int *const status = c.status;
     const int steps = K / 36;
-    uint32_t rs = 0, rph = 0;   // raw slot of this step, its phase
-    int quad_in_slot = 0;       // a slot of more than 4 channels is walked in `quads` steps of 4
-    int kdone = 0;              // values of k written so far
-    int acquired = 0;           // A stages (counted over the tile) whose "empty" has been seen
+    uint32_t rs = walk.rs, rph = walk.rph;
+    int quad_in_slot = walk.quad_in_slot, kdone = walk.kdone, acquired = walk.acquired;
     bool seen_raw = false, seen_empty = false;
     for (int s = 0; s < steps; ++s) {
       if (quad_in_slot == 0 && !seen_raw && !warp_wait(lane0, raw_full0 + 8 * rs, rph, status, UMMA_WAIT_FULL_TIMEOUT)) return false;
@@ -339,6 +345,12 @@ struct ConvUmmaTf32 {
         for (int g = done_before; g < done_after; ++g) mbar_arrive(a_full0 + 8 * (g & (kConvAStages - 1)));
       }
     }
+    if (quad_in_slot) {   // the tile's channels end inside a slot: it is free too, and the next tile starts in a fresh one
+      if (lane0) mbar_arrive(raw_empty0 + 8 * rs);
+      quad_in_slot = 0;
+      if (++rs == (uint32_t)nslots) rs = 0, rph ^= 1;
+    }
+    walk.rs = rs, walk.rph = rph, walk.quad_in_slot = quad_in_slot, walk.kdone = kdone, walk.acquired = acquired;
     return true;
   }
 
@@ -366,8 +378,14 @@ struct ConvUmmaTf32 {
   __device__ __forceinline__ static void run_staged(const Params &p, const TileCtx &c) {
     const int warp = c.tid >> 5, lane = c.tid & 31;
     const int quad = (threadIdx.x >> 5) & 3;
-    const int tile_px = p.st.tile_px, px0 = c.block_x() * tile_px, co0 = c.block_y() * kUmmaBM, img = c.block_z();
+    const int tile_px = p.st.tile_px;
     const int ohw = p.oh * p.ow, K = p.K, num_kb = K / kBK;   // staged: K is a whole number of K blocks
+    // The CTA's tiles: its block index, then every p.ctas-th one (tiles numbered pixel tile fastest, then
+    // channel tile, then image; a grid of one CTA per tile makes a single pass).  The rings, their barriers'
+    // phases and tensor memory live across tiles, so the loads of the next tile run under this tile's
+    // epilogue, and only the first tile pays for the set-up and the first loads' latency.
+    const int px_tiles = (ohw + tile_px - 1) / tile_px, co_tiles = (p.co + kUmmaBM - 1) / kUmmaBM;
+    const int total_tiles = px_tiles * co_tiles * p.n, tile_step = p.ctas;
     const int wstages = p.stages;                             // 16 KB weight stages behind the raw ring
     int *const status = c.status;
     const uint32_t idesc = umma_idesc(0, kUmmaBM);            // M = 128 pixels, N = 128 output channels
@@ -377,6 +395,7 @@ struct ConvUmmaTf32 {
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(c.smem + 8 * (2 * kUmmaMaxStages + 2));
     const uint32_t raw_full0 = full0 + kConvRawBarOffset, raw_empty0 = raw_full0 + 8 * kConvMaxRawSlots;
     const uint32_t a_full0 = raw_empty0 + 8 * kConvMaxRawSlots, a_empty0 = a_full0 + 8 * kConvAStages;
+    const uint32_t acc_empty = a_empty0 + 8 * kConvAStages;   // the epilogue has read the accumulator: the next tile's MMAs may start
     const uint32_t raw0 = smem_u32(c.smem) + conv_header_bytes(K);
     const uint32_t wring = raw0 + (uint32_t)conv_raw_bytes(p.st.slots, p.st.slot_pitch);
     if (warp == 5) {
@@ -403,7 +422,10 @@ struct ConvUmmaTf32 {
         mbar_init(raw_full0 + 8 * lane, 1);   // the slot's TMA load (arrive.expect_tx)
         mbar_init(raw_empty0 + 8 * lane, 4);  // every repack warp, once it has moved past the slot
       }
-      if (lane == 0) mbar_init(acc_bar, 1);
+      if (lane == 0) {
+        mbar_init(acc_bar, 1);
+        mbar_init(acc_empty, 4);   // one arrival per epilogue warp
+      }
       asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
       __syncwarp();
       if (lane == 0) {
@@ -440,94 +462,115 @@ struct ConvUmmaTf32 {
         const int cc = p.st.cc, kslot = cc * p.kh * p.kw, x_start = p.st.x_start, nslots = p.st.slots;
         const uint32_t slot_bytes = (uint32_t)p.st.slot_bytes, slot_pitch = (uint32_t)p.st.slot_pitch;
         const int g_end = (K - 1) / kslot + 1;
-        const int y_start = (px0 / p.ow) * p.stride - p.pad;
         uint32_t rs = 0, rph = 1;
-        for (int g = 0; g < g_end; ++g) {
-          if (!mbar_wait(raw_empty0 + 8 * rs, rph, status, UMMA_WAIT_EMPTY_TIMEOUT)) break;
-          mbar_expect_tx(raw_full0 + 8 * rs, slot_bytes);
-          tma_load_4d(raw0 + rs * slot_pitch, &p.map_x, raw_full0 + 8 * rs, x_start, y_start, g * cc, img);
-          if (++rs == (uint32_t)nslots) rs = 0, rph ^= 1;
+        bool ok = true;
+        for (int t = c.vblock; t < total_tiles && ok; t += tile_step) {
+          const int px0 = (t % px_tiles) * tile_px, img = t / (px_tiles * co_tiles);
+          const int y_start = (px0 / p.ow) * p.stride - p.pad;
+          for (int g = 0; g < g_end; ++g) {
+            if (!(ok = mbar_wait(raw_empty0 + 8 * rs, rph, status, UMMA_WAIT_EMPTY_TIMEOUT))) break;
+            mbar_expect_tx(raw_full0 + 8 * rs, slot_bytes);
+            tma_load_4d(raw0 + rs * slot_pitch, &p.map_x, raw_full0 + 8 * rs, x_start, y_start, g * cc, img);
+            if (++rs == (uint32_t)nslots) rs = 0, rph ^= 1;
+          }
         }
       }
       __syncwarp();
     } else if (warp == 6) {
       if (elect_one()) {
         uint32_t s = 0, ph = 1, dst = wring, bar = full0;
-        for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(empty0 + 8 * s, ph, status, UMMA_WAIT_EMPTY_TIMEOUT)) break;
-          mbar_expect_tx(bar, kUmmaABytes);
-          tma_load_3d(dst, &p.map_w, bar, kb * kBK, co0, 0);
-          if (++s == (uint32_t)wstages) s = 0, ph ^= 1, dst = wring, bar = full0;
-          else dst += kUmmaABytes, bar += 8;
+        bool ok = true;
+        for (int t = c.vblock; t < total_tiles && ok; t += tile_step) {
+          const int co0 = (t / px_tiles % co_tiles) * kUmmaBM;
+          for (int kb = 0; kb < num_kb; ++kb) {
+            if (!(ok = mbar_wait(empty0 + 8 * s, ph, status, UMMA_WAIT_EMPTY_TIMEOUT))) break;
+            mbar_expect_tx(bar, kUmmaABytes);
+            tma_load_3d(dst, &p.map_w, bar, kb * kBK, co0, 0);
+            if (++s == (uint32_t)wstages) s = 0, ph ^= 1, dst = wring, bar = full0;
+            else dst += kUmmaABytes, bar += 8;
+          }
         }
       }
       __syncwarp();
     } else if (warp == 5) {
       if (elect_one()) {
         const uint32_t lo0 = ((wring >> 4) & 0x3fffu) | (1u << 16);
-        uint32_t s = 0, ph = 0, lo = lo0, as = 0, aph = 0, accumulate = 0;
+        uint32_t s = 0, ph = 0, lo = lo0, as = 0, aph = 0;
         bool ok = true;
-        for (int kb = 0; kb < num_kb; ++kb) {
-          ok = mbar_wait(a_full0 + 8 * as, aph, status, UMMA_WAIT_FULL_TIMEOUT) && mbar_wait(full0 + 8 * s, ph, status, UMMA_WAIT_FULL_TIMEOUT);
-          if (!ok) break;
+        int done = 0;   // K blocks issued so far, over all tiles
+        for (int t = c.vblock, it = 0; t < total_tiles && ok; t += tile_step, ++it) {
+          // the accumulator is free again once the epilogue of the tile before has read it
+          if (it > 0 && !(ok = mbar_wait(acc_empty, (uint32_t)(it - 1) & 1u, status, UMMA_WAIT_ACC_TIMEOUT))) break;
           tc_fence_after();
-          if (kb == 0) mark(MARK_FIRST_FULL, true);
-          const uint32_t a_tmem = tmem_acc + (uint32_t)(kUmmaBM + as * kBK);
+          uint32_t accumulate = 0;
+          for (int kb = 0; kb < num_kb; ++kb) {
+            ok = mbar_wait(a_full0 + 8 * as, aph, status, UMMA_WAIT_FULL_TIMEOUT) && mbar_wait(full0 + 8 * s, ph, status, UMMA_WAIT_FULL_TIMEOUT);
+            if (!ok) break;
+            tc_fence_after();
+            if (kb == 0 && it == 0) mark(MARK_FIRST_FULL, true);
+            const uint32_t a_tmem = tmem_acc + (uint32_t)(kUmmaBM + as * kBK);
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            umma_ts_tf32(tmem_acc, a_tmem + 8 * j, lo + 2 * j, idesc, accumulate);
-            accumulate = 1;
+            for (int j = 0; j < 4; ++j) {
+              umma_ts_tf32(tmem_acc, a_tmem + 8 * j, lo + 2 * j, idesc, accumulate);
+              accumulate = 1;
+            }
+            umma_commit(empty0 + 8 * s);
+            umma_commit(a_empty0 + 8 * as);
+            if (++s == (uint32_t)wstages) s = 0, ph ^= 1, lo = lo0;
+            else lo += (uint32_t)kUmmaABytes >> 4;
+            if (++as == (uint32_t)kConvAStages) as = 0, aph ^= 1;
+            ++done;
           }
-          umma_commit(empty0 + 8 * s);
-          umma_commit(a_empty0 + 8 * as);
-          if (++s == (uint32_t)wstages) s = 0, ph ^= 1, lo = lo0;
-          else lo += (uint32_t)kUmmaABytes >> 4;
-          if (++as == (uint32_t)kConvAStages) as = 0, aph ^= 1;
+          umma_commit(acc_bar);   // this tile's accumulator is complete (also arrives if the loop bailed out)
+          if (it == 0) mark(MARK_LAST_MMA_ISSUED, true);
         }
-        umma_commit(acc_bar);
-        mark(MARK_LAST_MMA_ISSUED, true);
         // every commit has arrived before the barriers are invalidated and the ring is given up
-        for (int kb = max(0, num_kb - wstages); kb < num_kb && ok; ++kb)
-          ok = mbar_wait(empty0 + 8 * (kb % wstages), (kb / wstages) & 1, status, UMMA_WAIT_EMPTY_TIMEOUT);
-        for (int kb = max(0, num_kb - kConvAStages); kb < num_kb && ok; ++kb)
-          ok = mbar_wait(a_empty0 + 8 * (kb % kConvAStages), (kb / kConvAStages) & 1, status, UMMA_WAIT_EMPTY_TIMEOUT);
+        for (int j = max(0, done - wstages); j < done && ok; ++j)
+          ok = mbar_wait(empty0 + 8 * (j % wstages), (uint32_t)(j / wstages) & 1u, status, UMMA_WAIT_EMPTY_TIMEOUT);
+        for (int j = max(0, done - kConvAStages); j < done && ok; ++j)
+          ok = mbar_wait(a_empty0 + 8 * (j % kConvAStages), (uint32_t)(j / kConvAStages) & 1u, status, UMMA_WAIT_EMPTY_TIMEOUT);
       }
       __syncwarp();
     } else {
-      const int r = quad * 32 + lane, pix = px0 + r;
+      const int r = quad * 32 + lane;
       const bool lane0 = lane == 0;
       bool ok = true;
-      {
-        // Every parameter the loop needs is read into registers here: the loop is full of asm statements
-        // that clobber memory, after each of which the compiler would otherwise read the parameter block again.
-        const ConvStaging st = p.st;
-        const int ow = p.ow;
-        const uint32_t slot_pitch = (uint32_t)st.slot_pitch;
+      // Every parameter the loops need is read into registers here: they are full of asm statements that
+      // clobber memory, after each of which the compiler would otherwise read the parameter block again.
+      const ConvStaging st = p.st;
+      const int ow = p.ow, co_total = p.co;
+      float *const y = p.y;
+      const uint32_t slot_pitch = (uint32_t)st.slot_pitch;
+      const int kslot = st.cc * p.kh * p.kw, nslots = st.slots;
+      const uint32_t tab = smem_u32(tab4), ring_bytes = (uint32_t)nslots * slot_pitch;
+      const uint32_t a_row = tmem_row + (uint32_t)kUmmaBM;
+      // 3 x 3 windows go four channels at a time, without the table
+      extern __shared__ __align__(16) unsigned char conv_window[];
+      const bool by_slot = p.kh == 3 && p.kw == 3;   // (slots hold 4, 8, 16 ... channels; K is a multiple of 32 and of 9)
+      const uint32_t plane4 = (uint32_t)(st.rows * st.pitch * 4), pitch4 = (uint32_t)(st.pitch * 4);
+      // taps dx = 1, 2 of every pixel start at an even float (rows, planes and slots are 16-byte multiples)
+      const bool pair = (st.step_x & 1) == 0 && (st.x_off & 1) == 1;
+      SlotWalk walk;
+      // The rings' positions live across tiles (every tile starts in a fresh raw slot): the slot and phase of the
+      // next k, how many slots from there on have been seen full, the A stage and its phase.
+      int ahead = 0;
+      uint32_t rs = 0, rph = 0, as = 0, aph = 1;
+      for (int t = c.vblock, it = 0; t < total_tiles && ok; t += tile_step, ++it) {
+        const int px0 = (t % px_tiles) * tile_px, co0 = (t / px_tiles % co_tiles) * kUmmaBM, img = t / (px_tiles * co_tiles);
+        const int pix = px0 + r;
         // a lane past the tile's pixels or past the image reads the window of pixel 0 of the tile: finite
         // values, and it is not stored
         const int oy0 = px0 / ow;
         int oy = pix / ow, ox = pix - oy * ow;
         if (r >= tile_px || pix >= ohw) oy = oy0, ox = px0 - oy0 * ow;
-        const uint32_t pixoff = (uint32_t)(((oy - oy0) * st.step_y * st.pitch + ox * st.step_x + st.x_off) * 4);
-        const int kslot = st.cc * p.kh * p.kw, nslots = st.slots;
-        const uint32_t tab = smem_u32(tab4), rawpix = raw0 + pixoff, ring_bytes = (uint32_t)nslots * slot_pitch;
-        const uint32_t a_row = tmem_row + (uint32_t)kUmmaBM;
-        // The K block's first slot: ring index, phase, and where the K block starts inside it; how many slots
-        // from there on have been seen full.
-        int kin = 0, ahead = 0;
-        uint32_t rs = 0, rph = 0, as = 0, aph = 1;
-        bool seen_empty = false, seen_raw = false;
-        // 3 x 3 windows go four channels at a time, without the table
-        extern __shared__ __align__(16) unsigned char conv_window[];
-        const bool by_slot = p.kh == 3 && p.kw == 3;   // (slots hold 4, 8, 16 ... channels; K is a multiple of 32 and of 9)
+        const uint32_t rawpix = raw0 + (uint32_t)(((oy - oy0) * st.step_y * st.pitch + ox * st.step_x + st.x_off) * 4);
         if (by_slot) {
           const unsigned char *const rawpix_p = conv_window + (rawpix - smem_u32(conv_window));
-          const uint32_t plane4 = (uint32_t)(st.rows * st.pitch * 4), pitch4 = (uint32_t)(st.pitch * 4);
-          // taps dx = 1, 2 of every pixel start at an even float (rows, planes and slots are 16-byte multiples)
-          const bool pair = (st.step_x & 1) == 0 && (st.x_off & 1) == 1;
-          ok = pair ? repack_3x3<true>(c, K, lane0, rawpix_p, slot_pitch, nslots, st.cc / 4, plane4, pitch4, a_row, raw_full0, raw_empty0, a_full0, a_empty0)
-                    : repack_3x3<false>(c, K, lane0, rawpix_p, slot_pitch, nslots, st.cc / 4, plane4, pitch4, a_row, raw_full0, raw_empty0, a_full0, a_empty0);
+          ok = pair ? repack_3x3<true>(c, K, lane0, rawpix_p, slot_pitch, nslots, st.cc / 4, plane4, pitch4, a_row, raw_full0, raw_empty0, a_full0, a_empty0, walk)
+                    : repack_3x3<false>(c, K, lane0, rawpix_p, slot_pitch, nslots, st.cc / 4, plane4, pitch4, a_row, raw_full0, raw_empty0, a_full0, a_empty0, walk);
         }
+        int kin = 0;   // where the K block starts inside slot rs
+        bool seen_empty = false, seen_raw = false;
         for (int kb = 0; kb < num_kb && !by_slot; ++kb) {
           // one lane per warp polls a barrier and the warp follows it (its lanes meet again at the __syncwarp
           // before the arrival below, so the outcome of a wait has to be the same for all of them anyway)
@@ -560,9 +603,11 @@ struct ConvUmmaTf32 {
             src[i] = i >= j2 ? b2 : i >= j1 ? b1 : b0;
           }
           // on to the next K block's position in the ring (the slots that end inside this one are released below)
-          const int passed = (kin + kBK >= kslot) + (kin + kBK >= 2 * kslot);
+          int passed = (kin + kBK >= kslot) + (kin + kBK >= 2 * kslot);
+          kin += kBK - passed * kslot;
+          if (kb + 1 == num_kb && kin > 0) ++passed, kin = 0;   // the tile's K ends inside a slot: it is free too
           const uint32_t rs_old = rs, as_old = as;
-          kin += kBK - passed * kslot, ahead -= passed, rs += passed;
+          ahead -= passed, rs += passed;
           if (rs >= (uint32_t)nslots) rs -= nslots, rph ^= 1;
           if (++as == (uint32_t)kConvAStages) as = 0, aph ^= 1;
           // the look at the next K block's barriers: asked here, answered (the votes below) once this K block's
@@ -597,25 +642,35 @@ struct ConvUmmaTf32 {
             mbar_arrive(a_full0 + 8 * as_old);
             if (passed > 0) mbar_arrive(raw_empty0 + 8 * rs_old);
             if (passed > 1) mbar_arrive(raw_empty0 + 8 * (rs_old + 1 < (uint32_t)nslots ? rs_old + 1 : 0u));
+            if (passed > 2) mbar_arrive(raw_empty0 + 8 * ((rs_old + 2) % (uint32_t)nslots));
           }
-          if (kb == 0) mark(MARK_FIRST_LOAD_ISSUED, r == 0);
-          if (kb == num_kb - 1) mark(MARK_LAST_LOAD_ISSUED, r == 0);
+          if (it == 0 && kb == 0) mark(MARK_FIRST_LOAD_ISSUED, r == 0);
+          if (it == 0 && kb == num_kb - 1) mark(MARK_LAST_LOAD_ISSUED, r == 0);
         }
-      }
-      // epilogue: lane = pixel, column = output channel; a warp's store covers 32 consecutive pixels of one channel
-      const bool acc_ok = ok && mbar_wait(acc_bar, 0, status, UMMA_WAIT_ACC_TIMEOUT);
-      tc_fence_after();
-      mark(MARK_ACC_READY, c.tid == 0);
-      if (acc_ok) {
-        float *const yp = p.y + ((size_t)img * p.co + co0) * ohw + pix;
+        if (ahead < 0) ahead = 0;
+        // epilogue: lane = pixel, column = output channel; a warp's store covers 32 consecutive pixels of one channel
+        const bool acc_ok = ok && mbar_wait(acc_bar, (uint32_t)it & 1u, status, UMMA_WAIT_ACC_TIMEOUT);
+        tc_fence_after();
+        if (it == 0) mark(MARK_ACC_READY, c.tid == 0);
+        if (!acc_ok) {
+          ok = false;
+          break;
+        }
+        float *const yp = y + ((size_t)img * co_total + co0) * ohw + pix;
         const bool live = r < tile_px && pix < ohw;
-        const int co_left = p.co - co0;
+        const int co_left = co_total - co0;
 #pragma unroll 1
         for (int cc = 0; cc < kUmmaBM; cc += 32) {
           uint32_t r0[16], r1[16];
           tmem_ld_32x16(tmem_row + cc, r0);
           tmem_ld_32x16(tmem_row + cc + 16, r1);
           tmem_ld_wait();
+          if (cc + 32 == kUmmaBM && t + tile_step < total_tiles) {
+            // the accumulator has been read: hand it back to the MMA thread before the last stores go out
+            tc_fence_before();
+            __syncwarp();
+            if (lane0) mbar_arrive(acc_empty);
+          }
           if (live) {
 #pragma unroll
             for (int j = 0; j < 16; ++j)
@@ -643,7 +698,10 @@ struct ConvUmmaTf32 {
         mbar_inval(raw_full0 + 8 * c.tid);
         mbar_inval(raw_empty0 + 8 * c.tid);
       }
-      if (c.tid == 0) mbar_inval(acc_bar);
+      if (c.tid == 0) {
+        mbar_inval(acc_bar);
+        mbar_inval(acc_empty);
+      }
     }
     mark(MARK_END, c.tid == 0);
   }

@@ -268,7 +268,16 @@ int default_launch(const bfuse_context *ctx, bfuse_kernel_desc *d, std::string *
           *err = "conv2d: shape[11] = 1 (staged operand): the raw ring and two weight stages do not fit the shared-memory budget";
           return BFUSE_ERR_SHAPE;
         }
-        set(ceil_div(oh * ow, st.tile_px), ceil_div(s[4], kUmmaBM), s[0], kConvThreads, 1, conv_staged_smem_bytes(K, st.slots, st.slot_pitch, wst), 3);
+        // A CTA takes several tiles (every grid-size-th one) once there are more tiles than the two CTAs per SM
+        // that fit at a time: its rings and tensor memory live across them, so only the first tile pays for the
+        // set-up and the first loads' latency (a third of a tile's time), and the next tile's loads run under
+        // the epilogue.  Never more CTAs than fit at once: a few left over for a second round would each still
+        // walk their whole share of the tiles, alone.
+        const long long staged_tiles = (long long)ceil_div(oh * ow, st.tile_px) * ceil_div(s[4], kUmmaBM) * s[0];
+        if (staged_tiles > 2 * sm)
+          set(2 * sm, 1, 1, kConvThreads, 1, conv_staged_smem_bytes(K, st.slots, st.slot_pitch, wst), 3);
+        else
+          set(ceil_div(oh * ow, st.tile_px), ceil_div(s[4], kUmmaBM), s[0], kConvThreads, 1, conv_staged_smem_bytes(K, st.slots, st.slot_pitch, wst), 3);
         return BFUSE_OK;
       }
       int stages = std::max(1, std::min({q, kUmmaMaxStages, (budget - conv_header_bytes(K)) / conv_stage_bytes(bn)}));
@@ -475,8 +484,12 @@ int build_params(bfuse_context *ctx, KernelRec &k) {
       if (split > 8 || (split - 1) * q >= num_kb) return shape_err("shape[10] (k-slices) must be 1..8 with every k-slice non-empty");
       ConvStaging geometry;   // a staged conv's tiles may be whole output rows: fewer than BN pixels
       const int tile_px = s[11] == 1 && conv_staging(s[1], s[2], s[3], s[5], s[6], s[7], s[8], oh, ow, bn, &geometry) ? geometry.tile_px : bn;
-      if (kd.gx != split * ceil_div(oh * ow, tile_px) || kd.gy != ceil_div(s[4], kUmmaBM) || kd.gz != s[0])
+      if (s[11] == 1) {
+        if ((long long)kd.gx * kd.gy * kd.gz > (long long)ceil_div(oh * ow, tile_px) * ceil_div(s[4], kUmmaBM) * s[0])
+          return shape_err("GridDim of a staged conv must not hold more CTAs than the conv has tiles (a CTA takes every grid-size-th tile)");
+      } else if (kd.gx != split * ceil_div(oh * ow, tile_px) || kd.gy != ceil_div(s[4], kUmmaBM) || kd.gz != s[0]) {
         return shape_err("GridDim must be (k-slices * ceil(oh*ow / pixels per tile), ceil(co/128), n)");
+      }
       k.cluster = split;
       ConvUmmaParams p;
       std::memset(&p, 0, sizeof(p));
@@ -519,6 +532,7 @@ int build_params(bfuse_context *ctx, KernelRec &k) {
       p.bn = bn;
       p.split = split;
       p.kb_per_slice = q;
+      p.ctas = kd.gx * kd.gy * kd.gz;
       static_assert(sizeof(p) <= kParamsBytes, "parameter block too small");
       std::memcpy(k.params, &p, sizeof(p));
       return BFUSE_OK;

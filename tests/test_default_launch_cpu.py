@@ -58,7 +58,10 @@ def test_conv_pixel_tile_width_and_k_slices_follow_the_image_count():
     short = default(bf.OP_CONV2D_TF32, (1, 64, 56, 56, 128, 1, 1, 2, 0))      # K = 64: nothing to split
     assert (short.shape[9], short.shape[10]) == (32, 1) and short.GridDim.tuple() == (25, 1, 1)
     many = default(bf.OP_CONV2D_TF32, (256, 64, 56, 56, 128, 3, 3, 2, 1))
-    assert (many.shape[9], many.shape[10]) == (128, 1) and many.GridDim.tuple() == (7, 1, 256)
+    # 1792 tiles, staged: more than the two CTAs per SM that fit at a time, so a CTA takes 6 or 7 tiles (every 296th)
+    assert (many.shape[9], many.shape[10], many.shape[11]) == (128, 1, 1) and many.GridDim.tuple() == (296, 1, 1)
+    some = default(bf.OP_CONV2D_TF32, (32, 64, 56, 56, 128, 3, 3, 2, 1))      # 224 tiles: one each
+    assert (some.shape[9], some.shape[11]) == (128, 1) and some.GridDim.tuple() == (7, 1, 32)
     deep = default(bf.OP_CONV2D_TF32, (1, 512, 7, 7, 512, 3, 3, 1, 1))        # K = 4608 on 8 tiles: the table takes 36 KB
     assert (deep.shape[9], deep.shape[10]) == (32, 4) and deep.GridDim.tuple() == (8, 4, 1)
     assert deep.smem_bytes >= 2048 + 36 * 1024 + 4 * 16 * 1024 + 16 * 1024   # header, table, 4 partial sums, store buffers
