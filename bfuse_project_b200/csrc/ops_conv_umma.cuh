@@ -839,13 +839,12 @@ struct ConvUmmaTf32 {
       }
       __syncwarp();
     } else {
-      bool ok;
       const int gt = quad * 32 + lane;
       const int2 *tab_slice = tab + kb0 * kBK;
-      if (BN == 128) ok = gather<128>(p, c, gt, px0, img, num_kb, stages, tiles, full0, empty0, tab_slice, tl);
-      else if (BN == 64) ok = gather<64>(p, c, gt, px0, img, num_kb, stages, tiles, full0, empty0, tab_slice, tl);
-      else ok = gather<32>(p, c, gt, px0, img, num_kb, stages, tiles, full0, empty0, tab_slice, tl);
-      (void)ok;
+      // (a gather that gave up has reported to the status word; the wait below then returns at once)
+      if (BN == 128) (void)gather<128>(p, c, gt, px0, img, num_kb, stages, tiles, full0, empty0, tab_slice, tl);
+      else if (BN == 64) (void)gather<64>(p, c, gt, px0, img, num_kb, stages, tiles, full0, empty0, tab_slice, tl);
+      else (void)gather<32>(p, c, gt, px0, img, num_kb, stages, tiles, full0, empty0, tab_slice, tl);
       // epilogue: accumulator rows are output channels, columns are this tile's pixels
       acc_ok = mbar_wait(acc_bar, 0, c.status, UMMA_WAIT_ACC_TIMEOUT);
       tc_fence_after();
