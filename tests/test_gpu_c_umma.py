@@ -184,6 +184,42 @@ def test_conv_staged_operand_mode(rt):
         assert err.value.code == 2
 
 
+def test_conv_staged_ctas_that_walk_several_tiles(rt):
+    """A staged conv registered on fewer CTAs than it has tiles: every CTA takes every grid-size-th tile with its
+    rings, barrier phases and tensor memory kept across tiles.  3 x 3 (the four-channel walk), 1 x 1 with stride and
+    5 x 5 (the table-driven repack), on grids of 5 and of 1 CTA, alone and fused: the same bits as one CTA per tile."""
+    import torch
+    g = torch.Generator(device="cuda")
+    g.manual_seed(3)
+    for (ci, h, w, co, k, stride, pad) in ((32, 56, 56, 136, 3, 2, 1), (64, 31, 16, 40, 1, 2, 0), (32, 20, 20, 130, 5, 3, 2)):
+        n = 6
+        oh, ow = (h + 2 * pad - k) // stride + 1, (w + 2 * pad - k) // stride + 1
+        x = torch.randn(n, ci, h, w, device="cuda", generator=g)
+        wt = torch.randn(co, ci, k, k, device="cuda", generator=g) * 0.05
+        outs, kernels = [], []
+        for grid in (None, (5, 1, 1), (1, 1, 1)):
+            y = torch.zeros(n, co, oh, ow, device="cuda")
+            d = rt.describe("c", bf.OP_CONV2D_TF32, (n, ci, h, w, co, k, k, stride, pad, 128, 1, 1), [x.data_ptr(), wt.data_ptr(), y.data_ptr()], grid=grid)
+            kern = rt.register_kernel(d)
+            rt.launch_kernel(kern)
+            assert rt.read_status() == 0
+            outs.append(y)
+            kernels.append(kern)
+        assert bool(outs[0].any())
+        assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2]), (ci, k)
+        # fused with itself on another grid, under a block-level pattern and the work queue
+        for pattern in ((bf.ZIGZAG, 1, 1), (bf.WORK_QUEUE, 1, 1)):
+            want = outs[0].clone()
+            outs[1].zero_(), outs[2].zero_()
+            rt.launch_fused(rt.register_fusion(kernels[1], kernels[2], *pattern))
+            assert rt.read_status() == 0
+            assert torch.equal(want, outs[1]) and torch.equal(want, outs[2]), (ci, k, pattern)
+    with pytest.raises(bf.BfuseError) as err:   # more CTAs than tiles
+        rt.register_kernel(rt.describe("c", bf.OP_CONV2D_TF32, (1, 32, 56, 56, 128, 3, 3, 2, 1, 128, 1, 1), [x.data_ptr(), wt.data_ptr(), outs[0].data_ptr()],
+                                       grid=(8, 1, 1)))
+    assert err.value.code == 2
+
+
 def test_conv_tensor_core_ragged_shapes(rt):
     rng = np.random.default_rng(11)
     # co not a multiple of 128, pixels not a multiple of 128, K = ci*kh*kw not a multiple of the K block
