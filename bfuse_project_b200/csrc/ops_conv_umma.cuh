@@ -672,12 +672,20 @@ struct ConvUmmaTf32 {
             if (lane0) mbar_arrive(acc_empty);
           }
           if (live) {
+            float *q = yp + (size_t)cc * ohw;
+            if (cc + 32 <= co_left) {   // a whole group of 32 channels: no test per store
 #pragma unroll
-            for (int j = 0; j < 16; ++j)
-              if (cc + j < co_left) yp[(size_t)(cc + j) * ohw] = __uint_as_float(r0[j]);
+              for (int j = 0; j < 16; ++j) q[(size_t)j * ohw] = __uint_as_float(r0[j]);
 #pragma unroll
-            for (int j = 0; j < 16; ++j)
-              if (cc + 16 + j < co_left) yp[(size_t)(cc + 16 + j) * ohw] = __uint_as_float(r1[j]);
+              for (int j = 0; j < 16; ++j) q[(size_t)(16 + j) * ohw] = __uint_as_float(r1[j]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (cc + j < co_left) q[(size_t)j * ohw] = __uint_as_float(r0[j]);
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (cc + 16 + j < co_left) q[(size_t)(16 + j) * ohw] = __uint_as_float(r1[j]);
+            }
           }
         }
       }
